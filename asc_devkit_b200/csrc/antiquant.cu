@@ -1,0 +1,220 @@
+// ascq_antiquant: AscendAntiQuant on global-memory tensors.
+#include "elementwise.cuh"
+
+namespace ascq {
+namespace {
+
+template <typename Dst, typename Sc, typename CT>
+ascq_status run_fast(const EwArgs& a, int smode, bool hasOff, cudaStream_t st)
+{
+    return launch_ew_rows<kOpAntiQuant, int8_t, Dst, Sc, CT>(a, smode, hasOff, false, st);
+}
+
+ascq_status dispatch_fast(const EwArgs& a, ascq_dtype dstT, ascq_dtype scT, ascq_dtype ct, int smode, bool hasOff,
+                          cudaStream_t st, bool* handled)
+{
+    *handled = true;
+    if (ct == ASCQ_DT_F16 && dstT == ASCQ_DT_F16 && (scT == ASCQ_DT_F16 || smode == kSScalar))
+        return run_fast<__half, __half, __half>(a, smode, hasOff, st);
+    if (ct == ASCQ_DT_BF16 && dstT == ASCQ_DT_BF16 && scT == ASCQ_DT_BF16)
+        return run_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(a, smode, hasOff, st);
+    if (ct == ASCQ_DT_F32) {
+        if (dstT == ASCQ_DT_BF16 && (scT == ASCQ_DT_BF16 || smode == kSScalar))
+            return run_fast<__nv_bfloat16, __nv_bfloat16, float>(a, smode, hasOff, st);
+        if (scT == ASCQ_DT_F32) {
+            if (dstT == ASCQ_DT_F32) return run_fast<float, float, float>(a, smode, hasOff, st);
+            if (dstT == ASCQ_DT_F16) return run_fast<__half, float, float>(a, smode, hasOff, st);
+            if (dstT == ASCQ_DT_BF16) return run_fast<__nv_bfloat16, float, float>(a, smode, hasOff, st);
+        }
+    }
+    *handled = false;
+    return ASCQ_OK;
+}
+
+// ---- MX decode: fp4x2 (E2M1) + E8M0 scale -> bf16 / half ------------------------------------------
+// One thread converts 32 elements (16 source bytes -> 64 destination bytes).  With the groups along the
+// columns (transposed layout) the 32 elements share one scale byte; with the groups along the rows the
+// thread reads the 32 scale bytes of its columns.
+template <typename Dst, bool TRANSPOSED>
+__global__ void __launch_bounds__(256) mx_decode_kernel(Dst* __restrict__ dst, const uint8_t* __restrict__ src,
+                                                        const uint8_t* __restrict__ scale, uint32_t rows, uint32_t cols)
+{
+    const uint32_t c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 32u;
+    if (c0 >= cols) return;
+    for (uint32_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(src + (static_cast<size_t>(r) * cols + c0) / 2));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t sb[8];  // 32 scale bytes (row-grouped) or one broadcast byte
+        if (TRANSPOSED) {
+            sb[0] = scale[static_cast<size_t>(r) * (cols / 32) + c0 / 32];
+        } else {
+            const uint4* sp = reinterpret_cast<const uint4*>(scale + static_cast<size_t>(r / 32) * cols + c0);
+            const uint4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+            sb[0] = s0.x; sb[1] = s0.y; sb[2] = s0.z; sb[3] = s0.w; sb[4] = s1.x; sb[5] = s1.y; sb[6] = s1.z; sb[7] = s1.w;
+        }
+        Pack<Dst, 32> out;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const uint32_t code = (w[i >> 3] >> ((i & 7) * 4)) & 0xFu;
+            const uint32_t e = TRANSPOSED ? sb[0] : ((sb[i >> 2] >> ((i & 3) * 8)) & 0xFFu);
+            const __nv_bfloat16 s = __ushort_as_bfloat16(e8m0_to_bf16_bits(e));
+            const __nv_bfloat16 v = __float2bfloat16_rn(e2m1_to_f32(code));
+            if constexpr (std::is_same<Dst, __nv_bfloat16>::value) out.v[i] = Ct<__nv_bfloat16>::mul(s, v);
+            else out.v[i] = __hmul_rn(f32_to_f16_sat(__bfloat162float(s)), f32_to_f16_sat(__bfloat162float(v)));
+        }
+        store_pack<Dst, 32>(dst + static_cast<size_t>(r) * cols + c0, out);
+    }
+}
+}  // namespace
+}  // namespace ascq
+
+using namespace ascq;
+
+extern "C" ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* offset,
+                                      const void* scale, ascq_dtype scaleT, float offsetScalar, float scaleScalar,
+                                      ascq_policy policy, const ascq_antiquant_param* p, void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!dst || !src || !p) return fail(ASCQ_ERR_INVALID_ARG, "dst, src and param must not be NULL");
+    if (policy == ASCQ_PER_CHANNEL_PER_GROUP || policy == ASCQ_PER_TOKEN_PER_GROUP)
+        return fail(ASCQ_ERR_UNSUPPORTED, "unsupported policy for AscendAntiQuant in current device!");
+    if (policy < ASCQ_PER_TENSOR || policy > ASCQ_PER_GROUP) return fail(ASCQ_ERR_INVALID_ARG, "unknown policy %d", (int)policy);
+    if (dst == src) return fail(ASCQ_ERR_INVALID_ARG, "src and dst must not overlap");
+    if (p->n == 0) return fail(ASCQ_ERR_INVALID_ARG, "n must be greater than 0");
+    const uint64_t total64 = p->calCount ? p->calCount : static_cast<uint64_t>(p->m) * p->n;
+    if (total64 > 0xFFFFFFFFull) return fail(ASCQ_ERR_INVALID_ARG, "element count exceeds 2^32-1");
+    const uint32_t total = static_cast<uint32_t>(total64);
+    if (total % p->n != 0) return fail(ASCQ_ERR_INVALID_ARG, "calCount is %u, which should be an integer multiple of n %u", total, p->n);
+    const uint32_t rows = total / p->n, n = p->n;
+    if (rows == 0) return ASCQ_OK;
+
+    if (srcT == ASCQ_DT_FP4X2_E2M1) {
+        // include/adv_api/quantization/ascend_antiquant.h:211-231
+        if (scaleT != ASCQ_DT_E8M0 || !scale) return fail(ASCQ_ERR_INVALID_ARG, "fp4 input takes an fp8_e8m0 scale tensor");
+        if (offset || p->hasOffset) return fail(ASCQ_ERR_UNSUPPORTED, "AscendAntiQuant from fp4 does not take an offset");
+        if (dstT != ASCQ_DT_BF16 && dstT != ASCQ_DT_F16) return fail(ASCQ_ERR_UNSUPPORTED, "fp4 input decodes to half or bfloat16_t");
+        const uint32_t kext = p->isTranspose ? n : rows;
+        if (kext % 32 != 0) return fail(ASCQ_ERR_INVALID_ARG, "the K extent %u must be a multiple of the group size 32", kext);
+        if (n % 2) return fail(ASCQ_ERR_INVALID_ARG, "n must be even for packed fp4");
+        if (n % 32 == 0 && aligned16(src) && aligned16(dst) && (p->isTranspose || aligned16(scale))) {
+            dim3 grid, block;
+            ew_grid(rows, n, 32, &grid, &block);
+            uint8_t const* s8 = static_cast<const uint8_t*>(src);
+            uint8_t const* sc = static_cast<const uint8_t*>(scale);
+            if (dstT == ASCQ_DT_BF16) {
+                if (p->isTranspose) mx_decode_kernel<__nv_bfloat16, true><<<grid, block, 0, st>>>(static_cast<__nv_bfloat16*>(dst), s8, sc, rows, n);
+                else mx_decode_kernel<__nv_bfloat16, false><<<grid, block, 0, st>>>(static_cast<__nv_bfloat16*>(dst), s8, sc, rows, n);
+            } else {
+                if (p->isTranspose) mx_decode_kernel<__half, true><<<grid, block, 0, st>>>(static_cast<__half*>(dst), s8, sc, rows, n);
+                else mx_decode_kernel<__half, false><<<grid, block, 0, st>>>(static_cast<__half*>(dst), s8, sc, rows, n);
+            }
+            ASCQ_CUDA_CHECK(cudaGetLastError());
+            return ASCQ_OK;
+        }
+        GenericArgs g{};
+        g.op = kOpAntiQuant; g.srcT = srcT; g.dstT = dstT; g.scT = scaleT; g.ct = dstT;
+        g.src = src; g.dst = dst; g.rows = rows; g.cols = n; g.srcStride = g.dstStride = n;
+        g.scale.p = scale; g.fp4Transposed = p->isTranspose;
+        return launch_ew_generic(g, st);
+    }
+    if (srcT != ASCQ_DT_I8)
+        return fail(ASCQ_ERR_UNSUPPORTED, "AscendAntiQuant source dtype %d is not built (int8 and fp4x2_e2m1 are)", (int)srcT);
+
+    EwArgs a{};
+    a.src = src;
+    a.dst = dst;
+    a.rows = rows;
+    a.cols = n;
+    a.srcStride = a.dstStride = n;
+    a.roundMode = kRoundRint;
+    int smode = kSScalar;
+    bool hasOff = true;
+    ascq_dtype ct;
+
+    if (policy == ASCQ_PER_TENSOR || policy == ASCQ_PER_CHANNEL) {
+        // impl/adv_api/detail/quantization/antiquant/ascend_antiquant_c220_impl.h:33-43
+        if (dstT != ASCQ_DT_F16 && dstT != ASCQ_DT_BF16)
+            return fail(ASCQ_ERR_UNSUPPORTED, "current api support dtype combination is src: int8_t / int4b_t, dst: half / bfloat16_t.");
+        ct = (dstT == ASCQ_DT_F16) ? ASCQ_DT_F16 : ASCQ_DT_F32;
+        if (policy == ASCQ_PER_TENSOR) {
+            if (scale || offset) return fail(ASCQ_ERR_INVALID_ARG, "per-tensor AscendAntiQuant takes scalar scale/offset; tensors must be NULL");
+            hasOff = p->hasOffset != 0;
+            // the scalars are dstT values in the reference signature: round them to dstT first
+            a.scale.scalar = scaleScalar;
+            a.offset.scalar = offsetScalar;
+        } else {
+            if (!scale) return fail(ASCQ_ERR_INVALID_ARG, "scale tensor must not be NULL");
+            if (scaleT != dstT) return fail(ASCQ_ERR_UNSUPPORTED, "scale/offset dtype must equal the output dtype");
+            hasOff = offset != nullptr;
+            const uint32_t K = p->isTranspose ? n : rows;
+            const uint32_t gs = p->groupSize ? p->groupSize : K;
+            if (K % gs != 0) return fail(ASCQ_ERR_INVALID_ARG, "K %u must be a multiple of groupSize %u", K, gs);
+            if (p->isTranspose && (static_cast<size_t>(K) * dtype_size(srcT)) % 32 != 0)
+                return fail(ASCQ_ERR_INVALID_ARG, "When isTranspose is true, srcShape is [N, K] where the dimension K must be 32B aligned!");
+            a.scale.p = scale;
+            if (!p->isTranspose) {
+                a.scale.rdiv = gs; a.scale.cdiv = 1; a.scale.stride = n;
+                smode = (gs == K) ? kSColVec : kSRowVec;
+                if (gs == K) a.scale.rdiv = 0;
+            } else {
+                a.scale.rdiv = 1; a.scale.cdiv = gs; a.scale.stride = K / gs;
+                smode = kSRowBcast;
+            }
+            a.offset = a.scale;
+            a.offset.p = offset;
+        }
+    } else {
+        if (!scale) return fail(ASCQ_ERR_INVALID_ARG, "scale tensor must not be NULL");
+        if (scaleT != ASCQ_DT_F16 && scaleT != ASCQ_DT_BF16 && scaleT != ASCQ_DT_F32)
+            return fail(ASCQ_ERR_UNSUPPORTED, "scale dtype must be half, bfloat16_t or float");
+        if (dstT != ASCQ_DT_F16 && dstT != ASCQ_DT_BF16 && dstT != ASCQ_DT_F32)
+            return fail(ASCQ_ERR_UNSUPPORTED, "dst dtype must be half, bfloat16_t or float");
+        if (scaleT != ASCQ_DT_F32 && dstT != scaleT)
+            return fail(ASCQ_ERR_UNSUPPORTED, "unsupported (dst, scale) dtype pair for AscendAntiQuant PER_TOKEN/PER_GROUP");
+        ct = scaleT;
+        hasOff = p->hasOffset != 0;
+        if (hasOff && !offset) return fail(ASCQ_ERR_INVALID_ARG, "hasOffset is set but the offset tensor is NULL");
+        a.scale.p = scale;
+        if (policy == ASCQ_PER_TOKEN) {
+            if (p->isTranspose) { a.scale.rdiv = 0; a.scale.cdiv = 1; a.scale.stride = 0; smode = kSColVec; }
+            else { a.scale.rdiv = 1; a.scale.cdiv = 0; a.scale.stride = 1; smode = kSRowBcast; }
+        } else {
+            if (p->groupSize == 0 || p->groupSize % 32 != 0)
+                return fail(ASCQ_ERR_INVALID_ARG, "groupSize is %u, which must be a positive multiple of 32", p->groupSize);
+            // impl/adv_api/detail/quantization/antiquant/ascend_antiquant_3510_impl.h:2214-2220
+            const bool alongCols = (p->kDim == 1 && !p->isTranspose) || (p->kDim == 0 && p->isTranspose);
+            if (alongCols) {
+                a.scale.rdiv = 1; a.scale.cdiv = p->groupSize; a.scale.stride = (n + p->groupSize - 1) / p->groupSize;
+                smode = kSRowBcast;
+            } else {
+                a.scale.rdiv = p->groupSize; a.scale.cdiv = 1; a.scale.stride = n;
+                smode = kSRowVec;
+            }
+        }
+        a.offset = a.scale;
+        a.offset.p = hasOff ? offset : nullptr;
+    }
+    if (policy == ASCQ_PER_TENSOR) {
+        // round the scalars to the type the reference signature carries them in
+        // (include/adv_api/quantization/ascend_antiquant.h:136-205)
+        if (dstT == ASCQ_DT_F16) {
+            a.scale.scalar = __half2float(__float2half_rn(a.scale.scalar));
+            a.offset.scalar = __half2float(__float2half_rn(a.offset.scalar));
+        } else {
+            a.scale.scalar = __bfloat162float(__float2bfloat16_rn(a.scale.scalar));
+            a.offset.scalar = __bfloat162float(__float2bfloat16_rn(a.offset.scalar));
+        }
+    }
+
+    if (ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {
+        bool handled = false;
+        ascq_status rc = dispatch_fast(a, dstT, scaleT, ct, smode, hasOff, st, &handled);
+        if (rc != ASCQ_OK || handled) return rc;
+    }
+    GenericArgs g{};
+    g.op = kOpAntiQuant; g.srcT = srcT; g.dstT = dstT; g.scT = scaleT; g.ct = ct;
+    g.src = src; g.dst = dst; g.rows = a.rows; g.cols = a.cols; g.srcStride = a.srcStride; g.dstStride = a.dstStride;
+    g.scale = a.scale; g.offset = a.offset; g.scaleIsScalar = (smode == kSScalar); g.hasOff = hasOff;
+    g.offIsScalar = (smode == kSScalar); g.roundMode = kRoundRint;
+    return launch_ew_generic(g, st);
+}

@@ -1,0 +1,39 @@
+// Shared host-side helpers of the C ABI: error reporting, CUDA call checking, dtype sizes.
+#ifndef ASCQ_INTERNAL_H_
+#define ASCQ_INTERNAL_H_
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/ascq.h"
+
+namespace ascq {
+
+// Records a printf-style message in the thread-local slot behind ascq_last_error() and returns `s`.
+ascq_status fail(ascq_status s, const char* fmt, ...);
+void clear_error();
+
+inline int dtype_size(ascq_dtype t)
+{
+    switch (t) {
+        case ASCQ_DT_F16: case ASCQ_DT_BF16: return 2;
+        case ASCQ_DT_F32: case ASCQ_DT_I32: return 4;
+        case ASCQ_DT_I8: case ASCQ_DT_E8M0: case ASCQ_DT_FP4X2_E2M1: case ASCQ_DT_FP4X2_E1M2:
+        case ASCQ_DT_FP8_E4M3: case ASCQ_DT_FP8_E5M2: case ASCQ_DT_HIF8: case ASCQ_DT_I4X2: return 1;
+        case ASCQ_DT_U64: return 8;
+    }
+    return 0;
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace ascq
+
+#define ASCQ_CUDA_CHECK(expr)                                                                      \
+    do {                                                                                           \
+        cudaError_t err__ = (expr);                                                                \
+        if (err__ != cudaSuccess)                                                                  \
+            return ::ascq::fail(ASCQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+    } while (0)
+
+#endif  // ASCQ_INTERNAL_H_

@@ -1,0 +1,250 @@
+// Row-streaming elementwise kernel shared by AscendQuant / AscendDequant / AscendAntiQuant.
+//
+// Data layout in HBM: src is a row-major [rows, cols] matrix (row stride srcStride elements), dst
+// likewise with dstStride.  One thread owns VEC consecutive columns (16 bytes of the narrower of the
+// two element types) and walks down the rows blockIdx.y, blockIdx.y + gridDim.y, ...; a warp therefore
+// reads and writes fully coalesced 128-bit segments.  Per-column scale/offset vectors are loaded once
+// per thread and stay in registers; per-row (per-token / per-group) scales are one broadcast load per
+// row.  src is read with ld.global.cs and dst written with st.global.cs (both are touched exactly
+// once); scales go through the read-only path and stay cached.
+//
+// The roofline is HBM: algorithmic bytes = rows*cols*(sizeof(Src)+sizeof(Dst)) + the scale vectors.
+#ifndef ASCQ_ELEMENTWISE_CUH_
+#define ASCQ_ELEMENTWISE_CUH_
+
+#include <cuda_runtime.h>
+
+#include <type_traits>
+
+#include "ascq_internal.h"
+#include "numerics.cuh"
+
+namespace ascq {
+
+enum : int { kOpQuant = 0, kOpDequant = 1, kOpAntiQuant = 2 };
+// How a scale / offset operand is addressed for element (r, c):
+enum : int {
+    kSScalar = 0,   // one value for the whole tensor (passed by value)
+    kSColVec = 1,   // p[c]                           -- per channel, row invariant
+    kSRowBcast = 2, // p[(r/rdiv)*stride + c/cdiv]    -- one value per VEC columns (per token; groups along columns)
+    kSRowVec = 3    // p[(r/rdiv)*stride + c]         -- groups along rows
+};
+
+struct SRef {
+    const void* p;
+    uint32_t rdiv, cdiv, stride;  // rdiv / cdiv == 0: the index does not depend on r / c
+    float scalar;
+};
+
+struct EwArgs {
+    const void* src;
+    void* dst;
+    uint32_t rows, cols, srcStride, dstStride;
+    SRef scale, offset;
+    const float* tok;  // dequant only: optional fp32 per-row multiplier applied after the scale
+    int roundMode;
+};
+
+template <int BYTES> struct Chunk;
+template <> struct Chunk<16> { using type = uint4; };
+template <> struct Chunk<8> { using type = uint2; };
+template <> struct Chunk<4> { using type = uint32_t; };
+
+template <typename T, int N> struct alignas((sizeof(T) * N >= 16) ? 16 : sizeof(T) * N) Pack { T v[N]; };
+
+template <typename T, int N, bool STREAM> __device__ __forceinline__ Pack<T, N> load_pack(const T* p)
+{
+    constexpr int BYTES = sizeof(T) * N;
+    constexpr int CB = BYTES >= 16 ? 16 : BYTES;
+    using C = typename Chunk<CB>::type;
+    Pack<T, N> r;
+    const C* q = reinterpret_cast<const C*>(p);
+    C* o = reinterpret_cast<C*>(&r);
+#pragma unroll
+    for (int i = 0; i < BYTES / CB; ++i) o[i] = STREAM ? __ldcs(q + i) : __ldg(q + i);
+    return r;
+}
+template <typename T, int N> __device__ __forceinline__ void store_pack(T* p, const Pack<T, N>& r)
+{
+    constexpr int BYTES = sizeof(T) * N;
+    constexpr int CB = BYTES >= 16 ? 16 : BYTES;
+    using C = typename Chunk<CB>::type;
+    C* q = reinterpret_cast<C*>(p);
+    const C* o = reinterpret_cast<const C*>(&r);
+#pragma unroll
+    for (int i = 0; i < BYTES / CB; ++i) __stcs(q + i, o[i]);
+}
+
+template <typename Src, typename Dst> struct VecOf {
+    static constexpr int kMin = sizeof(Src) < sizeof(Dst) ? sizeof(Src) : sizeof(Dst);
+    static constexpr int value = 16 / kMin;
+};
+
+// CT result -> destination element.
+template <typename Dst, typename CT> __device__ __forceinline__ Dst finish(CT x, int roundMode)
+{
+    if constexpr (std::is_same<Dst, int8_t>::value) {
+        return static_cast<int8_t>(f32_to_i8_sat(Ct<CT>::to_f32(x), roundMode));
+    } else if constexpr (std::is_same<Dst, CT>::value) {
+        return x;
+    } else if constexpr (std::is_same<Dst, __half>::value) {
+        return f32_to_f16_sat(Ct<CT>::to_f32(x));
+    } else if constexpr (std::is_same<Dst, __nv_bfloat16>::value) {
+        return f32_to_bf16_sat(Ct<CT>::to_f32(x));
+    } else {
+        return Ct<CT>::to_f32(x);
+    }
+}
+
+template <int OP, typename Src, typename Dst, typename Sc, typename CT, int SMODE, bool HAS_OFF, bool HAS_TOK>
+__global__ void __launch_bounds__(256) ew_rows_kernel(const EwArgs a)
+{
+    constexpr int VEC = VecOf<Src, Dst>::value;
+    constexpr bool kVecScale = (SMODE == kSColVec || SMODE == kSRowVec);
+    constexpr int SV = kVecScale ? VEC : 1;
+    const uint32_t c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (c0 >= a.cols) return;
+
+    CT s[SV], o[SV];
+    if constexpr (SMODE == kSScalar) {
+        s[0] = Ct<CT>::from_f32(a.scale.scalar);
+        o[0] = Ct<CT>::from_f32(a.offset.scalar);
+    } else if constexpr (SMODE == kSColVec) {
+        const Pack<Sc, VEC> sp = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.scale.p) + c0);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) s[i] = Ct<CT>::from_f32(to_f32<Sc>(sp.v[i]));
+        if constexpr (HAS_OFF) {
+            if (a.offset.p != nullptr) {
+                const Pack<Sc, VEC> op = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.offset.p) + c0);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(to_f32<Sc>(op.v[i]));
+            } else {  // per-channel scale with a scalar offset
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(a.offset.scalar);
+            }
+        }
+    }
+    const uint32_t sc_col = a.scale.cdiv ? c0 / a.scale.cdiv : 0u;
+
+#pragma unroll 2
+    for (uint32_t r = blockIdx.y; r < a.rows; r += gridDim.y) {
+        if constexpr (SMODE == kSRowBcast) {
+            const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + sc_col;
+            s[0] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.scale.p) + idx)));
+            if constexpr (HAS_OFF) o[0] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.offset.p) + idx)));
+        } else if constexpr (SMODE == kSRowVec) {
+            const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + c0;
+            const Pack<Sc, VEC> sp = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.scale.p) + idx);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) s[i] = Ct<CT>::from_f32(to_f32<Sc>(sp.v[i]));
+            if constexpr (HAS_OFF) {
+                const Pack<Sc, VEC> op = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.offset.p) + idx);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(to_f32<Sc>(op.v[i]));
+            }
+        }
+        float tok = 1.0f;
+        if constexpr (HAS_TOK) tok = __ldg(a.tok + r);
+
+        const Pack<Src, VEC> in =
+            load_pack<Src, VEC, true>(static_cast<const Src*>(a.src) + static_cast<size_t>(r) * a.srcStride + c0);
+        Pack<Dst, VEC> out;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const int si = kVecScale ? i : 0;
+            CT x = Ct<CT>::from_f32(to_f32<Src>(in.v[i]));
+            if constexpr (OP == kOpQuant) {
+                x = Ct<CT>::mul(x, s[si]);
+                if constexpr (HAS_OFF) x = Ct<CT>::add(x, o[si]);
+            } else if constexpr (OP == kOpDequant) {
+                x = Ct<CT>::mul(x, s[si]);
+                if constexpr (HAS_TOK) x = Ct<CT>::mul(x, Ct<CT>::from_f32(tok));
+            } else {
+                if constexpr (HAS_OFF) x = Ct<CT>::add(x, o[si]);
+                x = Ct<CT>::mul(x, s[si]);
+            }
+            out.v[i] = finish<Dst, CT>(x, a.roundMode);
+        }
+        store_pack<Dst, VEC>(static_cast<Dst*>(a.dst) + static_cast<size_t>(r) * a.dstStride + c0, out);
+    }
+}
+
+// Grid shape: x covers the column vectors, y strides the rows; about eight 256-thread CTAs per SM.
+inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* block)
+{
+    const uint32_t nvec = (cols + vec - 1) / vec;
+    auto waste = [nvec](uint32_t b) { return (nvec + b - 1) / b * b - nvec; };
+    uint32_t bx = 256;  // narrower CTAs only when they idle clearly fewer threads on the last column block
+    for (uint32_t cand : {128u, 64u})
+        if (waste(cand) + nvec / 32 < waste(bx)) bx = cand;
+    if (nvec < bx) bx = (nvec + 31) / 32 * 32;
+    const uint32_t gx = (nvec + bx - 1) / bx;
+    const uint32_t target = 148u * 8u * 256u / bx;  // CTAs
+    uint32_t gy = (target + gx - 1) / gx;
+    if (gy > rows) gy = rows;
+    if (gy < 1) gy = 1;
+    if (gy > 65535u) gy = 65535u;
+    *grid = dim3(gx, gy, 1);
+    *block = dim3(bx, 1, 1);
+}
+
+// Launches the instantiation selected by (smode, hasOff, hasTok).  Offsets exist for quant and
+// antiquant, the per-row multiplier for dequant.
+template <int OP, typename Src, typename Dst, typename Sc, typename CT>
+ascq_status launch_ew_rows(const EwArgs& a, int smode, bool hasOff, bool hasTok, cudaStream_t stream)
+{
+    if (a.rows == 0 || a.cols == 0) return ASCQ_OK;
+    dim3 grid, block;
+    ew_grid(a.rows, a.cols, VecOf<Src, Dst>::value, &grid, &block);
+#define ASCQ_EW_LAUNCH(SM, OFF, TOK) \
+    ew_rows_kernel<OP, Src, Dst, Sc, CT, SM, OFF, TOK><<<grid, block, 0, stream>>>(a)
+#define ASCQ_EW_SMODE(OFF, TOK)                            \
+    switch (smode) {                                       \
+        case kSScalar: ASCQ_EW_LAUNCH(kSScalar, OFF, TOK); break;     \
+        case kSColVec: ASCQ_EW_LAUNCH(kSColVec, OFF, TOK); break;     \
+        case kSRowBcast: ASCQ_EW_LAUNCH(kSRowBcast, OFF, TOK); break; \
+        default: ASCQ_EW_LAUNCH(kSRowVec, OFF, TOK); break;           \
+    }
+    if constexpr (OP == kOpDequant) {
+        if (hasTok) { ASCQ_EW_SMODE(false, true) } else { ASCQ_EW_SMODE(false, false) }
+    } else {
+        if (hasOff) { ASCQ_EW_SMODE(true, false) } else { ASCQ_EW_SMODE(false, false) }
+    }
+#undef ASCQ_EW_SMODE
+#undef ASCQ_EW_LAUNCH
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}
+
+// ---- runtime-typed scalar kernel for everything the vector kernel cannot take --------------------
+// (ragged extents, unaligned pointers, odd group sizes, fp4 sources and destinations).
+struct GenericArgs {
+    int op;
+    int srcT, dstT, scT, ct;  // ascq_dtype codes; ct in {F16, BF16, F32}
+    const void* src;
+    void* dst;
+    uint32_t rows, cols, srcStride, dstStride;
+    SRef scale, offset;
+    int scaleIsScalar, hasOff, offIsScalar;
+    const float* tok;
+    int roundMode;
+    int fp4Transposed;  // fp4 source: scale index (r, c/32) instead of (r/32, c)
+    size_t srcBase, dstBase;  // element offsets added to the flat index (tail launches)
+};
+ascq_status launch_ew_generic(const GenericArgs& g, cudaStream_t stream);
+
+// True when the vector kernel can be used for this shape and these pointers.
+inline bool ew_fast_ok(const EwArgs& a, int vec, int smode, int scSize)
+{
+    if (a.cols % vec || a.srcStride % vec || a.dstStride % vec) return false;
+    if (!aligned16(a.src) || !aligned16(a.dst)) return false;
+    if (smode != kSScalar) {
+        if (!aligned16(a.scale.p) || (a.offset.p && !aligned16(a.offset.p))) return false;
+        if (smode == kSRowBcast && a.scale.cdiv && a.scale.cdiv % vec) return false;
+        if (smode == kSRowVec && (a.scale.stride * scSize) % 16) return false;
+    }
+    return true;
+}
+
+}  // namespace ascq
+#endif  // ASCQ_ELEMENTWISE_CUH_

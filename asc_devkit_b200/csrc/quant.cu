@@ -1,0 +1,266 @@
+// ascq_quant / ascq_dynamic_quant_per_token: AscendQuant on global-memory tensors.
+#include "elementwise.cuh"
+
+namespace ascq {
+namespace {
+
+bool is_float_type(ascq_dtype t) { return t == ASCQ_DT_F16 || t == ASCQ_DT_BF16 || t == ASCQ_DT_F32; }
+
+// Scale / offset addressing of the PER_TOKEN / PER_GROUP overloads
+// (impl/adv_api/detail/quantization/quant/ascend_quant_per_group_3510_impl.h:142-178, 498-538, 1000-1044).
+ascq_status policy_sref(SRef* s, const void* p, ascq_policy policy, uint32_t n, uint32_t groupSize, int kDim,
+                        int* smode)
+{
+    s->p = p;
+    s->scalar = 0.f;
+    if (policy == ASCQ_PER_TOKEN) {
+        s->rdiv = 1; s->cdiv = 0; s->stride = 1;
+        *smode = kSRowBcast;
+        return ASCQ_OK;
+    }
+    if (groupSize == 0 || groupSize % 32 != 0)
+        return fail(ASCQ_ERR_INVALID_ARG, "groupSize is %u, which must be a positive multiple of 32", groupSize);
+    if (kDim == 1) {
+        s->rdiv = 1; s->cdiv = groupSize; s->stride = (n + groupSize - 1) / groupSize;
+        *smode = kSRowBcast;
+    } else if (kDim == 0) {
+        s->rdiv = groupSize; s->cdiv = 1; s->stride = n;
+        *smode = kSRowVec;
+    } else {
+        return fail(ASCQ_ERR_INVALID_ARG, "kDim is %d, which must be 0 or 1", kDim);
+    }
+    return ASCQ_OK;
+}
+
+template <typename Src, typename Sc, typename CT>
+ascq_status run_fast(const EwArgs& a, int smode, bool hasOff, cudaStream_t st)
+{
+    return launch_ew_rows<kOpQuant, Src, int8_t, Sc, CT>(a, smode, hasOff, false, st);
+}
+
+ascq_status dispatch_fast(const EwArgs& a, ascq_dtype srcT, ascq_dtype scT, ascq_dtype ct, int smode, bool hasOff,
+                          cudaStream_t st, bool* handled)
+{
+    *handled = true;
+    if (ct == ASCQ_DT_F16) {
+        // scalar operands carry no storage type: reuse the half instantiation
+        const ascq_dtype sc = (smode == kSScalar) ? ASCQ_DT_F16 : scT;
+        if (srcT == ASCQ_DT_F16 && sc == ASCQ_DT_F16) return run_fast<__half, __half, __half>(a, smode, hasOff, st);
+        if (srcT == ASCQ_DT_F16 && sc == ASCQ_DT_F32) return run_fast<__half, float, __half>(a, smode, hasOff, st);
+        if (srcT == ASCQ_DT_F32 && sc == ASCQ_DT_F16) return run_fast<float, __half, __half>(a, smode, hasOff, st);
+        if (srcT == ASCQ_DT_F32 && sc == ASCQ_DT_F32) return run_fast<float, float, __half>(a, smode, hasOff, st);
+        if (srcT == ASCQ_DT_BF16 && sc == ASCQ_DT_F16) return run_fast<__nv_bfloat16, __half, __half>(a, smode, hasOff, st);
+    } else if (ct == ASCQ_DT_BF16) {
+        if (srcT == ASCQ_DT_BF16 && scT == ASCQ_DT_BF16)
+            return run_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(a, smode, hasOff, st);
+    } else {
+        if (scT == ASCQ_DT_F32) {
+            if (srcT == ASCQ_DT_F16) return run_fast<__half, float, float>(a, smode, hasOff, st);
+            if (srcT == ASCQ_DT_BF16) return run_fast<__nv_bfloat16, float, float>(a, smode, hasOff, st);
+            if (srcT == ASCQ_DT_F32) return run_fast<float, float, float>(a, smode, hasOff, st);
+        }
+    }
+    *handled = false;
+    return ASCQ_OK;
+}
+
+}  // namespace
+}  // namespace ascq
+
+using namespace ascq;
+
+extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
+                                  const void* offset, ascq_dtype scaleT, float scaleScalar, float offsetScalar,
+                                  ascq_policy policy, const ascq_quant_param* p, void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!dst || !src || !p) return fail(ASCQ_ERR_INVALID_ARG, "dst, src and param must not be NULL");
+    if (policy == ASCQ_PER_CHANNEL_PER_GROUP || policy == ASCQ_PER_TOKEN_PER_GROUP)
+        return fail(ASCQ_ERR_UNSUPPORTED, "unsupported policy for AscendQuant in current device!");
+    if (policy < ASCQ_PER_TENSOR || policy > ASCQ_PER_GROUP) return fail(ASCQ_ERR_INVALID_ARG, "unknown policy %d", (int)policy);
+    if (!is_float_type(srcT)) return fail(ASCQ_ERR_UNSUPPORTED, "AscendQuant only supports half/float/bfloat16_t input dtype");
+    if (dstT != ASCQ_DT_I8 && dstT != ASCQ_DT_FP4X2_E2M1)
+        return fail(ASCQ_ERR_UNSUPPORTED, "AscendQuant destination dtype %d is not built (int8 and fp4x2_e2m1 are)", (int)dstT);
+    if (dst == src) return fail(ASCQ_ERR_INVALID_ARG, "src and dst must not overlap");
+
+    EwArgs a{};
+    a.src = src;
+    a.dst = dst;
+    a.roundMode = kRoundRint;
+    int smode = kSScalar;
+    bool hasOff = true;
+    ascq_dtype ct = ASCQ_DT_F16;
+
+    if (policy == ASCQ_PER_TENSOR) {
+        if (dstT != ASCQ_DT_I8) return fail(ASCQ_ERR_UNSUPPORTED, "per-tensor AscendQuant writes int8 only");
+        if (scale || offset) return fail(ASCQ_ERR_INVALID_ARG, "per-tensor AscendQuant takes scalar scale/offset; tensors must be NULL");
+        a.scale.scalar = scaleScalar;
+        a.offset.scalar = offsetScalar;
+        a.rows = 1;
+        a.cols = p->calCount;
+        a.srcStride = a.dstStride = p->calCount;
+    } else {
+        if (p->n == 0) return fail(ASCQ_ERR_INVALID_ARG, "n (scaleCount) must be greater than 0");
+        if (p->calCount % p->n != 0)
+            return fail(ASCQ_ERR_INVALID_ARG, "calCount is %u, which should be an integer multiple of n/scaleCount %u", p->calCount, p->n);
+        if (!scale) return fail(ASCQ_ERR_INVALID_ARG, "scale tensor must not be NULL");
+        a.rows = p->calCount / p->n;
+        a.cols = p->n;
+        a.srcStride = a.dstStride = p->n;
+        if (policy == ASCQ_PER_CHANNEL) {
+            if (dstT != ASCQ_DT_I8) return fail(ASCQ_ERR_UNSUPPORTED, "per-channel AscendQuant writes int8 only");
+            if (scaleT != ASCQ_DT_F16 && scaleT != ASCQ_DT_F32)
+                return fail(ASCQ_ERR_UNSUPPORTED, "per-channel scale dtype must be half or float");
+            if ((static_cast<size_t>(p->n) * dtype_size(scaleT)) % 32 != 0)
+                return fail(ASCQ_ERR_INVALID_ARG, "scaleCount is %u, which should be 32B aligned", p->n);
+            smode = kSColVec;
+            a.scale.p = scale; a.scale.rdiv = 0; a.scale.cdiv = 1; a.scale.stride = 0;
+            a.offset = a.scale;
+            a.offset.p = offset;  // NULL: scalar offset
+            a.offset.scalar = offsetScalar;
+        } else {
+            if (!is_float_type(scaleT)) return fail(ASCQ_ERR_UNSUPPORTED, "scale dtype must be half, bfloat16_t or float");
+            if (scaleT != ASCQ_DT_F32 && scaleT != srcT)
+                return fail(ASCQ_ERR_UNSUPPORTED, "unsupported (src, scale) dtype pair for AscendQuant PER_TOKEN/PER_GROUP");
+            ct = scaleT;
+            hasOff = p->hasOffset != 0;
+            if (hasOff && !offset) return fail(ASCQ_ERR_INVALID_ARG, "hasOffset is set but the offset tensor is NULL");
+            if (p->roundMode < ASCQ_CAST_NONE || p->roundMode > ASCQ_CAST_TRUNC)
+                return fail(ASCQ_ERR_INVALID_ARG, "unknown roundMode %d", (int)p->roundMode);
+            a.roundMode = static_cast<int>(p->roundMode);
+            ascq_status rc = policy_sref(&a.scale, scale, policy, p->n, p->groupSize, p->kDim, &smode);
+            if (rc != ASCQ_OK) return rc;
+            a.offset = a.scale;
+            a.offset.p = offset;
+            if (dstT == ASCQ_DT_FP4X2_E2M1) {
+                if (policy != ASCQ_PER_GROUP) return fail(ASCQ_ERR_UNSUPPORTED, "fp4 destination needs PER_GROUP");
+                if (hasOff) return fail(ASCQ_ERR_UNSUPPORTED, "AscendQuant to fp4 does not take an offset");
+                if (p->n % 2) return fail(ASCQ_ERR_INVALID_ARG, "n must be even for a packed fp4 destination");
+            }
+        }
+    }
+    if (a.rows == 0 || a.cols == 0) return ASCQ_OK;
+
+    constexpr int kVec = 16;
+    if (dstT == ASCQ_DT_I8) {
+        if (policy == ASCQ_PER_TENSOR) {
+            // flat tensor: full rows of kVec*256 elements through the vector kernel, the tail through the scalar one
+            const uint32_t width = kVec * 256;
+            const uint32_t fullRows = (aligned16(src) && aligned16(dst)) ? p->calCount / width : 0;
+            if (fullRows) {
+                EwArgs b = a;
+                b.rows = fullRows; b.cols = width; b.srcStride = b.dstStride = width;
+                bool handled = false;
+                ascq_status rc = dispatch_fast(b, srcT, scaleT, ct, smode, hasOff, st, &handled);
+                if (rc != ASCQ_OK) return rc;
+                if (!handled) return fail(ASCQ_ERR_UNSUPPORTED, "unsupported dtype combination");
+            }
+            const uint32_t done = fullRows * width;
+            if (done == p->calCount) return ASCQ_OK;
+            a.cols = p->calCount - done;
+            GenericArgs g{};
+            g.op = kOpQuant; g.srcT = srcT; g.dstT = dstT; g.scT = scaleT; g.ct = ct;
+            g.src = src; g.dst = dst; g.rows = 1; g.cols = a.cols; g.srcStride = g.dstStride = a.cols;
+            g.scale = a.scale; g.offset = a.offset; g.scaleIsScalar = 1; g.hasOff = 1; g.offIsScalar = 1;
+            g.roundMode = a.roundMode; g.srcBase = g.dstBase = done;
+            return launch_ew_generic(g, st);
+        }
+        if (ew_fast_ok(a, kVec, smode, dtype_size(scaleT))) {
+            bool handled = false;
+            ascq_status rc = dispatch_fast(a, srcT, scaleT, ct, smode, hasOff, st, &handled);
+            if (rc != ASCQ_OK || handled) return rc;
+        }
+    }
+    GenericArgs g{};
+    g.op = kOpQuant; g.srcT = srcT; g.dstT = dstT; g.scT = scaleT; g.ct = ct;
+    g.src = src; g.dst = dst; g.rows = a.rows; g.cols = a.cols; g.srcStride = a.srcStride; g.dstStride = a.dstStride;
+    g.scale = a.scale; g.offset = a.offset;
+    g.scaleIsScalar = (smode == kSScalar);
+    g.hasOff = hasOff;
+    g.offIsScalar = (smode == kSScalar) || (policy == ASCQ_PER_CHANNEL && !offset);
+    g.roundMode = a.roundMode;
+    return launch_ew_generic(g, st);
+}
+
+// ---- dynamic per-token quantisation -------------------------------------------------------------
+namespace ascq {
+namespace {
+
+template <typename Src> __device__ __forceinline__ float absmax8(const Pack<Src, 8>& v)
+{
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(to_f32<Src>(v.v[i])));
+    return m;
+}
+
+// One CTA per row.  Pass 1 streams the row (8 elements per thread per step) and reduces |x| with
+// warp shuffles, then across the CTA's warps through shared memory; pass 2 re-reads the row
+// (it is L2 resident: a row is at most a few hundred KB) and writes int8.
+template <typename Src> __global__ void __launch_bounds__(256) dyn_quant_kernel(int8_t* __restrict__ dst,
+                                                                                float* __restrict__ scaleOut,
+                                                                                float* __restrict__ deqOut,
+                                                                                const Src* __restrict__ src,
+                                                                                uint32_t n, int vecOk)
+{
+    __shared__ float warpMax[8];
+    __shared__ float rowScale;
+    const uint32_t r = blockIdx.x;
+    const Src* row = src + static_cast<size_t>(r) * n;
+    int8_t* out = dst + static_cast<size_t>(r) * n;
+    float m = 0.f;
+    if (vecOk) {
+        for (uint32_t c = threadIdx.x * 8; c < n; c += blockDim.x * 8) m = fmaxf(m, absmax8<Src>(load_pack<Src, 8, false>(row + c)));
+    } else {
+        for (uint32_t c = threadIdx.x; c < n; c += blockDim.x) m = fmaxf(m, fabsf(to_f32<Src>(row[c])));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    if ((threadIdx.x & 31) == 0) warpMax[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float w = (threadIdx.x < (blockDim.x >> 5)) ? warpMax[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) w = fmaxf(w, __shfl_xor_sync(0xFFFFFFFFu, w, off));
+        if (threadIdx.x == 0) {
+            const float s = (w > 0.f) ? __fdiv_rn(127.0f, w) : 1.0f;
+            rowScale = s;
+            scaleOut[r] = s;
+            if (deqOut) deqOut[r] = (w > 0.f) ? __fdiv_rn(w, 127.0f) : 1.0f;
+        }
+    }
+    __syncthreads();
+    const float s = rowScale;
+    if (vecOk) {
+        for (uint32_t c = threadIdx.x * 8; c < n; c += blockDim.x * 8) {
+            const Pack<Src, 8> v = load_pack<Src, 8, true>(row + c);
+            Pack<int8_t, 8> q;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q.v[i] = static_cast<int8_t>(f32_to_i8_sat(__fmul_rn(to_f32<Src>(v.v[i]), s), kRoundRint));
+            store_pack<int8_t, 8>(out + c, q);
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < n; c += blockDim.x)
+            out[c] = static_cast<int8_t>(f32_to_i8_sat(__fmul_rn(to_f32<Src>(row[c]), s), kRoundRint));
+    }
+}
+}  // namespace
+}  // namespace ascq
+
+extern "C" ascq_status ascq_dynamic_quant_per_token(int8_t* dst, float* scaleOut, float* deqScaleOut, const void* src,
+                                                    ascq_dtype srcT, uint32_t m, uint32_t n, void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!dst || !scaleOut || !src) return fail(ASCQ_ERR_INVALID_ARG, "dst, scaleOut and src must not be NULL");
+    if (!is_float_type(srcT)) return fail(ASCQ_ERR_UNSUPPORTED, "src dtype must be half, bfloat16_t or float");
+    if (m == 0 || n == 0) return ASCQ_OK;
+    const int vecOk = (n % 8 == 0) && aligned16(src) && ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0);
+    if (srcT == ASCQ_DT_F16)
+        dyn_quant_kernel<__half><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, static_cast<const __half*>(src), n, vecOk);
+    else if (srcT == ASCQ_DT_BF16)
+        dyn_quant_kernel<__nv_bfloat16><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, static_cast<const __nv_bfloat16*>(src), n, vecOk);
+    else
+        dyn_quant_kernel<float><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, static_cast<const float*>(src), n, vecOk);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}

@@ -1,0 +1,213 @@
+"""Python mirror of the Ascend C quantization operator interface, on CUDA tensors.
+
+The names, argument order and argument meaning follow ``include/adv_api/quantization/ascend_quant.h``,
+``ascend_dequant.h`` and ``ascend_antiquant.h`` of asc-devkit; compile-time config structs become keyword
+arguments.  Each function forwards device pointers to the C ABI (``include/ascq.h``) and raises
+:class:`AscqError` where the reference would assert.  torch is used only to own device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+from ._lib import (AscqError, CAST_CEIL, CAST_FLOOR, CAST_NONE, CAST_RINT, CAST_ROUND, CAST_TRUNC,  # noqa: F401
+                   PER_CHANNEL, PER_CHANNEL_PER_GROUP, PER_GROUP, PER_TENSOR, PER_TOKEN, PER_TOKEN_PER_GROUP)
+
+_TORCH_DT = {torch.float16: L.DT_F16, torch.bfloat16: L.DT_BF16, torch.float32: L.DT_F32, torch.int8: L.DT_I8,
+             torch.int32: L.DT_I32}
+
+
+def dtype_code(t: torch.Tensor, override: Optional[int] = None) -> int:
+    """ascq_dtype of a tensor; uint8/int64 carriers of fp4x2 / e8m0 / uint64 scales need ``override``."""
+    if override is not None:
+        return override
+    if t.dtype not in _TORCH_DT:
+        raise TypeError(f"no ascq dtype for {t.dtype}; pass the dtype code explicitly")
+    return _TORCH_DT[t.dtype]
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("ascq operators take CUDA tensors (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError("ascq operators take contiguous tensors")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream(stream: Optional[torch.cuda.Stream]):
+    s = torch.cuda.current_stream() if stream is None else stream
+    return C.c_void_p(s.cuda_stream)
+
+
+@dataclass
+class AscendQuantParam:
+    """include/adv_api/quantization/ascend_quant_utils.h:82-87"""
+    m: int
+    n: int
+    calCount: int
+    groupSize: int = 0
+
+
+def AscendQuant(dstTensor: torch.Tensor, srcTensor: torch.Tensor, scale, offset, calCount: Optional[int] = None, *,
+                policy: int = PER_TENSOR, para: Optional[AscendQuantParam] = None, scaleCount: Optional[int] = None,
+                hasOffset: Optional[bool] = None, kDim: int = 1, roundMode: int = CAST_RINT, dst_dtype: int = L.DT_I8,
+                stream=None) -> torch.Tensor:
+    """AscendQuant (include/adv_api/quantization/ascend_quant.h).
+
+    * per tensor  : ``scale`` and ``offset`` are Python floats (ascend_quant.h:63-97).
+    * per channel : ``scale`` is a tensor of ``scaleCount`` elements, ``offset`` a float or a tensor
+      (ascend_quant.h:159-347); ``calCount`` must be a multiple of ``scaleCount``.
+    * PER_TOKEN / PER_GROUP : ``scale``/``offset`` tensors and ``para`` (ascend_quant.h:667-762).
+    """
+    scale_is_t = isinstance(scale, torch.Tensor)
+    offset_is_t = isinstance(offset, torch.Tensor)
+    if policy == PER_TENSOR and scale_is_t:
+        policy = PER_CHANNEL
+    cal = srcTensor.numel() if calCount is None else int(calCount)
+    if para is not None:
+        m, n, cal, gs = para.m, para.n, para.calCount, para.groupSize
+    elif policy == PER_CHANNEL:
+        n = int(scaleCount if scaleCount is not None else scale.numel())
+        m, gs = (cal // n if n else 0), 0
+    else:
+        m, n, gs = 1, cal, 0
+    if hasOffset is None:
+        hasOffset = offset is not None
+    p = L.QuantParam(m, n, cal, gs, int(bool(hasOffset)), kDim, roundMode)
+    scaleT = dtype_code(scale) if scale_is_t else L.DT_F32
+    L.check(L.lib().ascq_quant(_ptr(dstTensor), dst_dtype, _ptr(srcTensor), dtype_code(srcTensor),
+                               _ptr(scale) if scale_is_t else None, _ptr(offset) if offset_is_t else None, scaleT,
+                               float(scale) if not scale_is_t else 0.0,
+                               float(offset) if (offset is not None and not offset_is_t) else 0.0,
+                               policy, C.byref(p), _stream(stream)))
+    return dstTensor
+
+
+def DynamicQuantPerToken(dstTensor, scaleOut, srcTensor, deqScaleOut=None, stream=None):
+    """Per-token absmax -> scale -> int8 in one launch (``ascq_dynamic_quant_per_token``)."""
+    m, n = srcTensor.shape
+    L.check(L.lib().ascq_dynamic_quant_per_token(_ptr(dstTensor), _ptr(scaleOut), _ptr(deqScaleOut), _ptr(srcTensor),
+                                                 dtype_code(srcTensor), m, n, _stream(stream)))
+    return dstTensor, scaleOut
+
+
+@dataclass
+class DequantParams:
+    """include/adv_api/quantization/ascend_dequant_utils.h:26-30"""
+    m: int
+    n: int
+    calCount: int
+    groupSize: int = 0
+
+
+def dequant_dst_stride(n: int, dst: torch.dtype) -> int:
+    """Row stride of AscendDequant's destination: n rounded up to 32 bytes."""
+    per_blk = 32 // torch.empty((), dtype=dst).element_size()
+    return (n + per_blk - 1) // per_blk * per_blk
+
+
+def AscendDequant(dstTensor: torch.Tensor, srcTensor: torch.Tensor, deqScale, params: DequantParams, *,
+                  policy: Optional[int] = None, tokScale: Optional[torch.Tensor] = None, kDim: int = 1,
+                  scale_dtype: Optional[int] = None, stream=None) -> torch.Tensor:
+    """AscendDequant (include/adv_api/quantization/ascend_dequant.h).
+
+    ``deqScale`` float -> scalar overload; tensor -> per channel (default) or PER_TOKEN / PER_GROUP when
+    ``policy`` says so.  ``tokScale`` (fp32 [m]) fuses the per-token multiply of the grouped-matmul epilogue.
+    A uint64 scale tensor is passed as int64 storage with ``scale_dtype=DT_U64``."""
+    is_t = isinstance(deqScale, torch.Tensor)
+    if policy is None:
+        policy = PER_CHANNEL if is_t else PER_TENSOR
+    p = L.DequantParam(params.m, params.n, params.calCount, params.groupSize, kDim)
+    scaleT = dtype_code(deqScale, scale_dtype) if is_t else L.DT_F32
+    L.check(L.lib().ascq_dequant(_ptr(dstTensor), dtype_code(dstTensor), _ptr(srcTensor), dtype_code(srcTensor),
+                                 _ptr(deqScale) if is_t else None, _ptr(tokScale), scaleT,
+                                 0.0 if is_t else float(deqScale), policy, C.byref(p), _stream(stream)))
+    return dstTensor
+
+
+@dataclass
+class AscendAntiQuantParam:
+    m: int
+    n: int
+    calCount: int = 0
+    groupSize: int = 0
+
+
+def AscendAntiQuant(dstTensor: torch.Tensor, srcTensor: torch.Tensor, offset, scale, para: AscendAntiQuantParam, *,
+                    isTranspose: bool = False, policy: Optional[int] = None, hasOffset: Optional[bool] = None,
+                    kDim: int = 1, src_dtype: Optional[int] = None, scale_dtype: Optional[int] = None,
+                    stream=None) -> torch.Tensor:
+    """AscendAntiQuant (include/adv_api/quantization/ascend_antiquant.h): dst = scale * (src + offset).
+
+    ``para.m, para.n`` is the shape of ``srcTensor`` as stored ([K,N], or [N,K] with ``isTranspose``).
+    fp4 sources are uint8 tensors with ``src_dtype=DT_FP4X2_E2M1`` and an e8m0 scale (``scale_dtype=DT_E8M0``)."""
+    is_t = isinstance(scale, torch.Tensor)
+    off_t = isinstance(offset, torch.Tensor)
+    if policy is None:
+        policy = PER_CHANNEL if is_t else PER_TENSOR
+    if hasOffset is None:
+        hasOffset = offset is not None
+    p = L.AntiQuantParam(para.m, para.n, para.calCount, para.groupSize, int(bool(hasOffset)), int(isTranspose), kDim)
+    scaleT = dtype_code(scale, scale_dtype) if is_t else dtype_code(dstTensor)
+    L.check(L.lib().ascq_antiquant(_ptr(dstTensor), dtype_code(dstTensor), _ptr(srcTensor),
+                                   dtype_code(srcTensor, src_dtype), _ptr(offset) if off_t else None,
+                                   _ptr(scale) if is_t else None, scaleT,
+                                   float(offset) if (offset is not None and not off_t) else 0.0,
+                                   0.0 if is_t else float(scale), policy, C.byref(p), _stream(stream)))
+    return dstTensor
+
+
+# ---- host tiling helpers (include/adv_api/quantization/ascend_*_tiling.h) ------------------------
+def _dims(d):
+    return (C.c_int64 * len(d))(*d), len(d)
+
+
+def GetAscendQuantMaxMinTmpSize(srcShape, typeSize):
+    a, r = _dims(srcShape)
+    mx, mn = C.c_uint32(), C.c_uint32()
+    L.check(L.lib().ascq_get_ascend_quant_max_min_tmp_size(a, r, typeSize, C.byref(mx), C.byref(mn)))
+    return mx.value, mn.value
+
+
+def GetAscendQuantTmpBufferFactorSize():
+    a, b = C.c_uint32(), C.c_uint32(1)
+    L.lib().ascq_get_ascend_quant_tmp_buffer_factor_size(C.byref(a), C.byref(b))
+    return a.value, b.value
+
+
+def GetAscendDequantMaxMinTmpSize(srcShape, typeSize):
+    a, r = _dims(srcShape)
+    mx, mn = C.c_uint32(), C.c_uint32()
+    L.check(L.lib().ascq_get_ascend_dequant_max_min_tmp_size(a, r, typeSize, C.byref(mx), C.byref(mn)))
+    return mx.value, mn.value
+
+
+def GetAscendDequantTmpBufferFactorSize(srcShape):
+    a, r = _dims(srcShape)
+    x, y = C.c_uint32(), C.c_uint32()
+    L.lib().ascq_get_ascend_dequant_tmp_buffer_factor_size(a, r, C.byref(x), C.byref(y))
+    return x.value, y.value
+
+
+def GetAscendAntiQuantMaxMinTmpSize(srcShape, scaleShape, isTranspose, inputDataType, outputDataType):
+    a, r = _dims(srcShape)
+    b, s = _dims(scaleShape)
+    mx, mn = C.c_uint32(), C.c_uint32()
+    L.check(L.lib().ascq_get_ascend_antiquant_max_min_tmp_size(a, r, b, s, int(isTranspose), inputDataType,
+                                                               outputDataType, C.byref(mx), C.byref(mn)))
+    return mx.value, mn.value
+
+
+def GetAscendAntiQuantTmpBufferFactorSize(srcShape, scaleShape, isTranspose, inputDataType, outputDataType):
+    a, r = _dims(srcShape)
+    b, s = _dims(scaleShape)
+    x, y = C.c_uint32(), C.c_uint32()
+    L.lib().ascq_get_ascend_antiquant_tmp_buffer_factor_size(a, r, b, s, int(isTranspose), inputDataType,
+                                                             outputDataType, C.byref(x), C.byref(y))
+    return x.value, y.value

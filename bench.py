@@ -1,0 +1,458 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  A "step" is one pass of the headline workload over its synthetic input:
+the operator call(s) through the C ABI with inputs resident in HBM (``value``), and the same call with
+pinned-host inputs and a device->host read of the result inside the timed region (``e2e``).  The other
+BASELINE configurations are measured in the same run and reported under ``workloads``.  Timing is by CUDA
+events on the launching stream; buffers rotate over a set larger than L2 so every step reads DRAM.
+``--impl reference`` times the CPU restatement of the reference operators (oracle/, all host threads) on a
+bounded sample of the same workload; the reference's own CPU-debug build needs the closed tikicpulib and
+cannot be produced here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+SEED = 20251125
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+# Synthetic inputs (numpy, seeded): the five BASELINE configurations.
+# ------------------------------------------------------------------------------------------------
+def f32_to_bf16_bits(x):
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def gen_quant_cfg1(rows=256, cols=4096):
+    rng = np.random.default_rng(SEED + 1)
+    return {"x": rng.standard_normal((rows, cols), dtype=np.float32).astype(np.float16)}
+
+
+def gen_antiquant_cfg2(K=4096, N=11008):
+    rng = np.random.default_rng(SEED + 2)
+    return {"w": rng.integers(-127, 128, (K, N), dtype=np.int8),
+            "scale": f32_to_bf16_bits(rng.uniform(0.001, 0.02, N).astype(np.float32)),
+            "offset": f32_to_bf16_bits(rng.uniform(-4, 4, N).astype(np.float32))}
+
+
+def gen_dequant_cfg3(M=2048, N=4096):
+    rng = np.random.default_rng(SEED + 3)
+    return {"acc": rng.integers(-2 ** 20, 2 ** 20 + 1, (M, N)).astype(np.int32),
+            "sch": rng.uniform(1e-5, 1e-3, N).astype(np.float32), "stok": rng.uniform(0.5, 2.0, M).astype(np.float32)}
+
+
+# ------------------------------------------------------------------------------------------------
+# Workloads.  Each owns `nsets` rotating device buffer sets and knows its algorithmic bytes.
+# ------------------------------------------------------------------------------------------------
+class Workload:
+    name = ""
+    unit = "GB/s"
+    bound = "hbm"
+    dtype = ""
+    launches_per_step = 1
+
+    def work_per_step(self):  # algorithmic bytes (hbm) or ops (tensor)
+        raise NotImplementedError
+
+    def nsets_for(self, bytes_per_set):
+        return max(2, int(np.ceil(2.0 * L2_BYTES / bytes_per_set)) + 1)
+
+
+class AntiQuantCfg2(Workload):
+    name = "AscendAntiQuant per-channel int8[4096,11008] -> bf16 (config 2)"
+    dtype = "f32"
+    key = "antiquant_cfg2"
+
+    def __init__(self, torch, ops, dev):
+        self.torch, self.ops = torch, ops
+        self.K, self.N = 4096, 11008
+        h = gen_antiquant_cfg2(self.K, self.N)
+        self.host = h
+        per_set = self.K * self.N * 3
+        self.nsets = self.nsets_for(per_set)
+        self.w = [torch.from_numpy(h["w"]).to(dev) for _ in range(self.nsets)]
+        self.out = [torch.empty((self.K, self.N), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
+        self.scale = torch.from_numpy(h["scale"].view(np.int16)).to(dev).view(torch.bfloat16)
+        self.offset = torch.from_numpy(h["offset"].view(np.int16)).to(dev).view(torch.bfloat16)
+        self.para = ops.AscendAntiQuantParam(self.K, self.N)
+        # e2e: pinned host input and output
+        self.h_in = torch.from_numpy(h["w"]).pin_memory()
+        self.h_out = torch.empty((self.K, self.N), dtype=torch.bfloat16).pin_memory()
+
+    def work_per_step(self):
+        return self.K * self.N * 3 + 2 * self.N * 2
+
+    def step(self, i):
+        s = i % self.nsets
+        self.ops.AscendAntiQuant(self.out[s], self.w[s], self.offset, self.scale, self.para)
+
+    def e2e_step(self, i):
+        s = i % self.nsets
+        self.w[s].copy_(self.h_in, non_blocking=True)
+        self.ops.AscendAntiQuant(self.out[s], self.w[s], self.offset, self.scale, self.para)
+        self.h_out.copy_(self.out[s], non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.K * self.N, self.K * self.N * 2
+
+    def cpu_sample(self, O):
+        rows = 512
+        w = np.ascontiguousarray(self.host["w"][:rows])
+        t0 = time.perf_counter()
+        O.ascend_antiquant(w, O.I8, O.BF16, policy=O.PER_CHANNEL, m=rows, n=self.N, scale=self.host["scale"],
+                           offset=self.host["offset"], scaleT=O.BF16)
+        dt = time.perf_counter() - t0
+        return rows * self.N * 3 / dt / 1e9, f"{rows} of {self.K} rows"
+
+    def check(self, O):
+        rows = 64
+        want = O.ascend_antiquant(np.ascontiguousarray(self.host["w"][:rows]), O.I8, O.BF16, policy=O.PER_CHANNEL, m=rows,
+                                  n=self.N, scale=self.host["scale"], offset=self.host["offset"], scaleT=O.BF16)
+        got = self.out[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
+        return bool(np.array_equal(got, want))
+
+
+class DequantCfg3(Workload):
+    name = "AscendDequant per-channel x per-token int32[2048,4096] -> bf16 (config 3)"
+    dtype = "f32"
+    key = "dequant_cfg3"
+
+    def __init__(self, torch, ops, dev):
+        self.torch, self.ops = torch, ops
+        self.M, self.N = 2048, 4096
+        h = gen_dequant_cfg3(self.M, self.N)
+        self.host = h
+        self.nsets = self.nsets_for(self.M * self.N * 6)
+        self.acc = [torch.from_numpy(h["acc"]).to(dev) for _ in range(self.nsets)]
+        self.out = [torch.empty((self.M, self.N), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
+        self.sch = torch.from_numpy(h["sch"]).to(dev)
+        self.stok = torch.from_numpy(h["stok"]).to(dev)
+        self.params = ops.DequantParams(self.M, self.N, self.N)
+        self.h_in = torch.from_numpy(h["acc"]).pin_memory()
+        self.h_out = torch.empty((self.M, self.N), dtype=torch.bfloat16).pin_memory()
+
+    def work_per_step(self):
+        return self.M * self.N * 6 + self.N * 4 + self.M * 4
+
+    def step(self, i):
+        s = i % self.nsets
+        self.ops.AscendDequant(self.out[s], self.acc[s], self.sch, self.params, tokScale=self.stok)
+
+    def e2e_step(self, i):
+        s = i % self.nsets
+        self.acc[s].copy_(self.h_in, non_blocking=True)
+        self.ops.AscendDequant(self.out[s], self.acc[s], self.sch, self.params, tokScale=self.stok)
+        self.h_out.copy_(self.out[s], non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.M * self.N * 4, self.M * self.N * 2
+
+    def cpu_sample(self, O):
+        rows = 512
+        acc = np.ascontiguousarray(self.host["acc"][:rows])
+        t0 = time.perf_counter()
+        O.ascend_dequant(acc, O.I32, O.BF16, policy=O.PER_CHANNEL, m=rows, n=self.N, calCount=self.N,
+                         scale=self.host["sch"], tokScale=self.host["stok"][:rows].copy(), scaleT=O.F32)
+        dt = time.perf_counter() - t0
+        return rows * self.N * 6 / dt / 1e9, f"{rows} of {self.M} rows"
+
+    def check(self, O):
+        rows = 64
+        want = O.ascend_dequant(np.ascontiguousarray(self.host["acc"][:rows]), O.I32, O.BF16, policy=O.PER_CHANNEL, m=rows,
+                                n=self.N, calCount=self.N, scale=self.host["sch"],
+                                tokScale=self.host["stok"][:rows].copy(), scaleT=O.F32)
+        got = self.out[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
+        return bool(np.array_equal(got, want))
+
+
+class QuantScaled(Workload):
+    """Config 1's operator (per-tensor fp16 -> int8, scale 64) on fp16 [16384, 8192]: config 1 itself is 3 MiB,
+    which no kernel can stream from DRAM at a meaningful rate; its latency is reported separately."""
+    name = "AscendQuant per-tensor fp16[16384,8192] -> int8 (config 1 operator, DRAM-sized)"
+    dtype = "f16"
+    key = "quant_scaled"
+
+    def __init__(self, torch, ops, dev, rows=16384, cols=8192):
+        self.torch, self.ops = torch, ops
+        self.rows, self.cols = rows, cols
+        h = gen_quant_cfg1(rows, cols)
+        self.host = h
+        self.nsets = self.nsets_for(rows * cols * 3)
+        self.x = [torch.from_numpy(h["x"]).to(dev) for _ in range(self.nsets)]
+        self.out = [torch.empty((rows, cols), dtype=torch.int8, device=dev) for _ in range(self.nsets)]
+        self.h_in = torch.from_numpy(h["x"]).pin_memory()
+        self.h_out = torch.empty((rows, cols), dtype=torch.int8).pin_memory()
+
+    def work_per_step(self):
+        return self.rows * self.cols * 3
+
+    def step(self, i):
+        s = i % self.nsets
+        self.ops.AscendQuant(self.out[s], self.x[s], 64.0, 0.0, self.rows * self.cols)
+
+    def e2e_step(self, i):
+        s = i % self.nsets
+        self.x[s].copy_(self.h_in, non_blocking=True)
+        self.ops.AscendQuant(self.out[s], self.x[s], 64.0, 0.0, self.rows * self.cols)
+        self.h_out.copy_(self.out[s], non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.rows * self.cols * 2, self.rows * self.cols
+
+    def cpu_sample(self, O):
+        rows = 1024
+        x = np.ascontiguousarray(self.host["x"][:rows])
+        t0 = time.perf_counter()
+        O.ascend_quant(x, O.F16, policy=O.PER_TENSOR, scaleScalar=64.0, offsetScalar=0.0)
+        dt = time.perf_counter() - t0
+        return rows * self.cols * 3 / dt / 1e9, f"{rows} of {self.rows} rows"
+
+    def check(self, O):
+        rows = 64
+        want = O.ascend_quant(np.ascontiguousarray(self.host["x"][:rows]), O.F16, policy=O.PER_TENSOR, scaleScalar=64.0,
+                              offsetScalar=0.0)
+        return bool(np.array_equal(self.out[0][:rows].cpu().numpy(), want))
+
+
+WORKLOADS = {"antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3, "quant_scaled": QuantScaled}
+HEADLINE = "antiquant_cfg2"
+
+
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi in the background for the length of the timed region (read-only queries)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(gpu_index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.tmp.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        self.tmp.close()
+        os.unlink(self.tmp.name)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def time_steps(torch, fn, steps, warmup, dist=None):
+    """W untimed + K timed calls of fn(i); CUDA events on the current stream; returns seconds (max over ranks)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3
+    if dist is not None:
+        t = torch.tensor([sec], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    return sec
+
+
+def run_ours(args):
+    import torch
+    from asc_devkit_b200 import _lib, ops
+    _lib.lib()  # fail loudly if the CUDA library is missing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(local)
+        dist_mod.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        dist = dist_mod
+    else:
+        torch.cuda.set_device(0)
+    dev = torch.device(f"cuda:{local}")
+    peaks = measured_peaks()
+    names = [args.workload] if args.workload != "all" else list(WORKLOADS)
+    if HEADLINE not in names:
+        names = [HEADLINE] + names if args.workload == "all" else names
+    results = {}
+    head = None
+    clocks = None
+    for nm in names:
+        wl = WORKLOADS[nm](torch, ops, dev)
+        is_head = nm == (args.workload if args.workload != "all" else HEADLINE)
+        sampler = ClockSampler(local) if (is_head and rank == 0) else None
+        sec = time_steps(torch, wl.step, args.steps, args.warmup, dist)
+        if sampler:
+            clocks = sampler.stop()
+        per = sec / args.steps
+        work = wl.work_per_step()
+        achieved = work / per / 1e9  # GB/s (each rank does the full workload: replicas)
+        e2e_sec = time_steps(torch, wl.e2e_step, max(2, args.steps // 4), 2, dist)
+        e2e_per = e2e_sec / max(2, args.steps // 4)
+        h2d, d2h = wl.e2e_bytes()
+        rec = {"name": wl.name, "value": achieved * world, "unit": wl.unit, "ms_per_step": per * 1e3,
+               "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]},
+               "e2e": {"value": work / e2e_per / 1e9 * world, "unit": wl.unit, "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": d2h},
+               "nsets": wl.nsets, "launches_per_step": wl.launches_per_step}
+        if rank == 0:
+            from oracle import oracle as O
+            rec["parity_vs_oracle"] = wl.check(O)
+            if world == 1:
+                v, sample = wl.cpu_sample(O)
+                rec["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": O.num_threads(), "kind": "port",
+                                       "sample": sample}
+        results[nm] = rec
+        if is_head:
+            head = (wl, rec)
+        del wl
+        torch.cuda.empty_cache()
+    if rank == 0:
+        wl, rec = head
+        line = {"metric": "W8A8/MXFP4 GEMM TOPS at 1/2/4/8 B200; quant/dequant GB/s vs HBM peak",
+                "value": rec["value"], "unit": rec["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": wl.dtype, "data": "synthetic",
+                "config": {"workload": rec["name"], "timing": "buffers rotate over a set larger than L2 (126 MB)",
+                           "sharding": "replicas only (elementwise operators do not shard)"},
+                "roofline": rec["roofline"], "e2e": rec["e2e"], "gpu_launches": args.steps * rec["launches_per_step"],
+                "clocks": clocks, "workloads": results}
+        if "cpu_baseline" in rec:
+            line["cpu_baseline"] = rec["cpu_baseline"]
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement of the reference operators on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    nm = args.workload if args.workload != "all" else HEADLINE
+    if nm == "antiquant_cfg2":
+        h = gen_antiquant_cfg2()
+        rows, N = 1024, 11008
+        w = np.ascontiguousarray(h["w"][:rows])
+
+        def step():
+            O.ascend_antiquant(w, O.I8, O.BF16, policy=O.PER_CHANNEL, m=rows, n=N, scale=h["scale"], offset=h["offset"],
+                               scaleT=O.BF16)
+        work, sample, name = rows * N * 3, f"{rows} of 4096 rows per step", AntiQuantCfg2.name
+    elif nm == "dequant_cfg3":
+        h = gen_dequant_cfg3()
+        rows, N = 1024, 4096
+        acc = np.ascontiguousarray(h["acc"][:rows])
+        tok = h["stok"][:rows].copy()
+
+        def step():
+            O.ascend_dequant(acc, O.I32, O.BF16, policy=O.PER_CHANNEL, m=rows, n=N, calCount=N, scale=h["sch"], tokScale=tok,
+                             scaleT=O.F32)
+        work, sample, name = rows * N * 6, f"{rows} of 2048 rows per step", DequantCfg3.name
+    else:
+        h = gen_quant_cfg1(1024, 8192)
+
+        def step():
+            O.ascend_quant(h["x"], O.F16, policy=O.PER_TENSOR, scaleScalar=64.0, offsetScalar=0.0)
+        work, sample, name = 1024 * 8192 * 3, "1024 of 16384 rows per step", QuantScaled.name
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    per = (time.perf_counter() - t0) / args.steps
+    v = work / per / 1e9
+    print(json.dumps({"impl": "reference", "metric": "W8A8/MXFP4 GEMM TOPS at 1/2/4/8 B200; quant/dequant GB/s vs HBM peak",
+                      "value": v, "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": name},
+                      "cpu_baseline": {"value": v, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                                       "sample": sample},
+                      "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "note": "CPU restatement of the reference operators (oracle/); the reference's own CPU-debug "
+                              "build needs the closed tikicpulib"}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="all", choices=["all"] + list(WORKLOADS))
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

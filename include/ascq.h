@@ -1,0 +1,220 @@
+/*
+ * ascq.h -- C ABI of the B200 (sm_100a) quantized-inference operators.
+ *
+ * Every entry point replaces one operator (or one host helper) of the Ascend C
+ * high-level API; the reference file:line each one follows is cited beside it
+ * (paths are relative to the asc-devkit source tree).
+ *
+ * Conventions (all entry points):
+ *   - every tensor pointer is a DEVICE pointer owned by the caller;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) and the call returns without synchronising;
+ *   - no entry point allocates or frees device memory unless its comment says so;
+ *   - argument errors are reported by return code (the reference aborts through
+ *     ASCENDC_ASSERT in CPU-debug builds, impl/basic_api/kernel_log.h:41-71);
+ *     ascq_last_error() returns a thread-local description of the last failure;
+ *   - there is no CPU fallback: without a CUDA device the compute calls fail
+ *     with ASCQ_ERR_CUDA.
+ */
+#ifndef ASCQ_H_
+#define ASCQ_H_
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ASCQ_VERSION_MAJOR 0
+#define ASCQ_VERSION_MINOR 1
+
+typedef enum {
+    ASCQ_OK = 0,
+    ASCQ_ERR_INVALID_ARG = 1,  /* a rule the reference checks with ASCENDC_ASSERT is violated          */
+    ASCQ_ERR_UNSUPPORTED = 2,  /* dtype / policy combination the reference static_asserts away         */
+    ASCQ_ERR_ALIGNMENT = 3,    /* pointer or extent not aligned for the vectorised path                */
+    ASCQ_ERR_CUDA = 4,         /* a CUDA runtime / driver call failed                                  */
+    ASCQ_ERR_NCCL = 5,
+    ASCQ_ERR_TIMEOUT = 6       /* a bounded device-side wait expired (kernel left cleanly)             */
+} ascq_status;
+
+/* Element types.  fp4x2 = two E2M1 values per byte, element 2i in the low nibble
+ * (include of impl/utils/common_types.h:33-47; packing as in
+ * examples/.../matmul_mxfp4_high_performance/scripts/gen_data.py:25-35). */
+typedef enum {
+    ASCQ_DT_F16 = 0,
+    ASCQ_DT_BF16 = 1,
+    ASCQ_DT_F32 = 2,
+    ASCQ_DT_I8 = 3,
+    ASCQ_DT_I32 = 4,
+    ASCQ_DT_U64 = 5,        /* AscendDequant scale: low 32 bits hold fp32 bits */
+    ASCQ_DT_FP4X2_E2M1 = 6,
+    ASCQ_DT_E8M0 = 7,
+    ASCQ_DT_FP8_E4M3 = 8,   /* declared by the reference, not built here: ASCQ_ERR_UNSUPPORTED */
+    ASCQ_DT_FP8_E5M2 = 9,
+    ASCQ_DT_HIF8 = 10,
+    ASCQ_DT_FP4X2_E1M2 = 11,
+    ASCQ_DT_I4X2 = 12
+} ascq_dtype;
+
+/* include/adv_api/quantization/ascend_quant_utils.h:73-80 (same order in the
+ * antiquant enum, impl/adv_api/detail/quantization/antiquant/ascend_antiquant_common.h:51-58). */
+typedef enum {
+    ASCQ_PER_TENSOR = 0,
+    ASCQ_PER_CHANNEL = 1,
+    ASCQ_PER_TOKEN = 2,
+    ASCQ_PER_GROUP = 3,
+    ASCQ_PER_CHANNEL_PER_GROUP = 4, /* declared, static_assert'ed away by every implementation */
+    ASCQ_PER_TOKEN_PER_GROUP = 5
+} ascq_policy;
+
+/* impl/basic_api/utils/kernel_utils_mode.h:94-108.  CAST_NONE behaves as CAST_RINT
+ * whenever the conversion is lossy (docs .../precision_conversion.md:19-20). */
+typedef enum {
+    ASCQ_CAST_NONE = 0,
+    ASCQ_CAST_RINT = 1,  /* round half to even            */
+    ASCQ_CAST_FLOOR = 2,
+    ASCQ_CAST_CEIL = 3,
+    ASCQ_CAST_ROUND = 4, /* round half away from zero     */
+    ASCQ_CAST_TRUNC = 5
+} ascq_round;
+
+/* AscendQuantParam + the run-time relevant fields of AscendQuantConfig
+ * (include/adv_api/quantization/ascend_quant_utils.h:31-87). */
+typedef struct {
+    uint32_t m;          /* rows (tokens)                                                     */
+    uint32_t n;          /* columns (channels); PER_CHANNEL: scaleCount                       */
+    uint32_t calCount;   /* elements to process; multiple of n for every policy but PER_TENSOR */
+    uint32_t groupSize;  /* PER_GROUP only; multiple of 32                                    */
+    int32_t hasOffset;   /* PER_TOKEN / PER_GROUP: add the offset tensor                      */
+    int32_t kDim;        /* PER_GROUP: 1 = groups along n, 0 = groups along m                 */
+    ascq_round roundMode;
+} ascq_quant_param;
+
+/* DequantParams / AscendDeQuantParam (include/adv_api/quantization/ascend_dequant_utils.h:26-44). */
+typedef struct {
+    uint32_t m;
+    uint32_t n;
+    uint32_t calCount;   /* PER_TENSOR / PER_CHANNEL: columns of each row that are scaled (<= n);
+                            PER_TOKEN / PER_GROUP: total element count (multiple of n)           */
+    uint32_t groupSize;
+    int32_t kDim;
+} ascq_dequant_param;
+
+/* AscendAntiQuantParam + AscendAntiQuantConfig + the K / AntiQuantShapeInfo arguments of the
+ * legacy overloads (ascend_antiquant_common.h:45-66, include/adv_api/quantization/ascend_antiquant_utils.h:27-32). */
+typedef struct {
+    uint32_t m;          /* src rows    : K when !isTranspose, N when isTranspose (legacy);
+                            tokens for the policy overloads                                     */
+    uint32_t n;          /* src columns : N when !isTranspose, K when isTranspose               */
+    uint32_t calCount;   /* elements to process (multiple of n); 0 = m*n                        */
+    uint32_t groupSize;  /* PER_CHANNEL: 0 = one scale row/column for the whole K extent
+                            (scale shape [1,N] or [N,1]); else K/groupSize scale rows/columns.
+                            PER_GROUP: group length; fp4 source: fixed to 32                    */
+    int32_t hasOffset;
+    int32_t isTranspose;
+    int32_t kDim;
+} ascq_antiquant_param;
+
+const char* ascq_status_string(ascq_status s);
+/* Thread-local text of the most recent non-OK status returned on this thread ("" if none). */
+const char* ascq_last_error(void);
+/* major*100 + minor */
+int ascq_version(void);
+
+/*
+ * AscendQuant.  dst = sat(round(x * scale + offset)) evaluated with the reference's operation
+ * sequence (two separately rounded operations, never a fused multiply-add):
+ *   PER_TENSOR  include/adv_api/quantization/ascend_quant.h:63-97, arithmetic
+ *               impl/adv_api/detail/quantization/quant/ascend_quant_pre_impl.h:320-397: src -> half,
+ *               half mul, half add, half -> int8 (RINT, saturate).  scale/offset come from
+ *               scaleScalar/offsetScalar; `scale`/`offset` must be NULL.
+ *   PER_CHANNEL ascend_quant.h:159-347, ascend_quant_pre_impl.h:101-209,399-483: same half
+ *               arithmetic with scale[n] (dtype scaleT = half or float; float is rounded to half
+ *               first) and either offset[n] (offset != NULL) or offsetScalar.
+ *   PER_TOKEN / PER_GROUP  ascend_quant.h:667-762, impl .../ascend_quant_per_group_3510_impl.h:
+ *               arithmetic in scaleT, scale (and offset when hasOffset) shaped [m] /
+ *               [m, ceil(n/groupSize)] (kDim 1) / [ceil(m/groupSize), n] (kDim 0);
+ *               to-int8 chain .../ascend_quant_3510_impl.h:934-992.
+ * dstT: ASCQ_DT_I8 (all policies) or ASCQ_DT_FP4X2_E2M1 (PER_GROUP, no offset).
+ */
+ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT,
+                       const void* scale, const void* offset, ascq_dtype scaleT,
+                       float scaleScalar, float offsetScalar, ascq_policy policy,
+                       const ascq_quant_param* param, void* stream);
+
+/*
+ * Dynamic per-token quantisation front end (no counterpart in the reference, which always takes
+ * the scale as an input): scaleOut[row] = 127 / max|x[row,:]| in fp32 (1.0 for an all-zero row),
+ * then AscendQuant PER_TOKEN with scaleT = float, no offset, CAST_RINT.  One pass over src.
+ * deqScaleOut[row] (optional) receives max|x|/127, the per-token scale the W8A8 matmul wants.
+ */
+ascq_status ascq_dynamic_quant_per_token(int8_t* dst, float* scaleOut, float* deqScaleOut, const void* src,
+                                         ascq_dtype srcT, uint32_t m, uint32_t n, void* stream);
+
+/*
+ * AscendDequant.  dst = cast(float(src) * scale), fp32 arithmetic, final cast RINT + saturate.
+ *   PER_TENSOR  scalar deqScale overloads, include/adv_api/quantization/ascend_dequant.h:186-281
+ *               (scaleScalar; `scale` NULL).
+ *   PER_CHANNEL ascend_dequant.h:59-181, impl .../dequant/ascend_dequant_common_impl.h:365-429:
+ *               scale[>=calCount] of scaleT in {U64, F32, BF16}; the first calCount columns of
+ *               each of the m rows are scaled; dst rows start every dstStride elements, where
+ *               dstStride = n rounded up to 32 bytes of dstT (ascend_dequant_common_impl.h:100-105).
+ *               tokScale (optional, fp32 [m]) multiplies each row AFTER the per-channel scale,
+ *               still in fp32 -- the order of the grouped-matmul epilogue,
+ *               examples/.../quant_group_matmul_high_performance/quant_group_matmul_custom.asc:433-441.
+ *   PER_TOKEN / PER_GROUP  ascend_dequant.h:286-307, impl .../ascend_dequant_3510_impl.h:226-296,
+ *               337-446: srcT in {I32, F32}; scale [m] or grouped as for AscendQuant.
+ * dstT in {F16, BF16, F32}.
+ */
+ascq_status ascq_dequant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT,
+                         const void* scale, const float* tokScale, ascq_dtype scaleT, float scaleScalar,
+                         ascq_policy policy, const ascq_dequant_param* param, void* stream);
+
+/*
+ * AscendAntiQuant.  dst = scale * (src + offset)  (include/adv_api/quantization/ascend_antiquant.h:37).
+ *   PER_TENSOR  scalar overloads ascend_antiquant.h:136-205 (offsetScalar / scaleScalar).
+ *   PER_CHANNEL legacy tensor overloads ascend_antiquant.h:50-134; layouts
+ *               impl/.../antiquant/ascend_antiquant_impl.h:283-408: !isTranspose: src [K,N],
+ *               scale/offset [K/groupSize, N]; isTranspose: src [N,K], scale/offset [N, K/groupSize].
+ *               dst bf16: int8 -> fp32, fp32 add, fp32 mul, RINT to bf16
+ *               (ascend_antiquant_c220_impl.h:45-102); dst half: half add, half mul
+ *               (ascend_antiquant_impl.h:62-76).  scaleT must equal dstT.
+ *   PER_TOKEN / PER_GROUP  ascend_antiquant.h:233-262, impl .../ascend_antiquant_3510_impl.h:
+ *               1458-1495, 2167-2222: arithmetic in scaleT, result cast to dstT.
+ *   srcT = FP4X2_E2M1 with scaleT = E8M0 (ascend_antiquant.h:211-231, impl :49-138): one scale per
+ *               32 K-elements, no offset; scale byte e -> 2^(e-127), 0x00 -> 2^-127, 0xFF -> NaN.
+ */
+ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT,
+                           const void* offset, const void* scale, ascq_dtype scaleT,
+                           float offsetScalar, float scaleScalar, ascq_policy policy,
+                           const ascq_antiquant_param* param, void* stream);
+
+/*
+ * Host-side temporary-buffer size queries, kept for API parity (the CUDA kernels need no
+ * temporary buffer).  Formulas: impl/adv_api/tiling/quantization/ascend_quant_tiling_impl.cpp:31-69,
+ * ascend_dequant_tiling_impl.cpp:31-106, ascend_antiquant_tiling_impl.cpp:71-181.
+ * Shapes are passed as (dims pointer, rank).  Return ASCQ_ERR_INVALID_ARG where the reference's
+ * ASCENDC_HOST_ASSERT fires.
+ */
+ascq_status ascq_get_ascend_quant_max_min_tmp_size(const int64_t* srcDims, int rank, uint32_t typeSize,
+                                                   uint32_t* maxValue, uint32_t* minValue);
+void ascq_get_ascend_quant_tmp_buffer_factor_size(uint32_t* maxLiveNodeCount, uint32_t* extraBuf);
+ascq_status ascq_get_ascend_dequant_max_min_tmp_size(const int64_t* srcDims, int rank, uint32_t typeSize,
+                                                     uint32_t* maxValue, uint32_t* minValue);
+void ascq_get_ascend_dequant_tmp_buffer_factor_size(const int64_t* srcDims, int rank,
+                                                    uint32_t* maxLiveNodeCount, uint32_t* extraBuf);
+ascq_status ascq_get_ascend_antiquant_max_min_tmp_size(const int64_t* srcDims, int srcRank,
+                                                       const int64_t* scaleDims, int scaleRank,
+                                                       int isTranspose, ascq_dtype inputT, ascq_dtype outputT,
+                                                       uint32_t* maxValue, uint32_t* minValue);
+void ascq_get_ascend_antiquant_tmp_buffer_factor_size(const int64_t* srcDims, int srcRank,
+                                                      const int64_t* scaleDims, int scaleRank,
+                                                      int isTranspose, ascq_dtype inputT, ascq_dtype outputT,
+                                                      uint32_t* maxLiveNodeCount, uint32_t* extraBuf);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASCQ_H_ */

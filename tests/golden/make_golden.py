@@ -1,0 +1,67 @@
+"""Regenerates the golden fixtures in this directory from the reference's own example generators.
+
+Run in a checkout that has the asc-devkit tree available (default /root/reference):
+
+    python tests/golden/make_golden.py [--reference /path/to/asc-devkit]
+
+Each reference ``scripts/gen_data.py`` is executed unmodified (runpy, in a scratch directory, numpy's global
+seed fixed first) and the ``input/*.bin`` / ``output/golden.bin`` files it writes are collected into one
+``.npz`` per example.  The fixtures are what the oracle is pinned against; the tests never need the reference
+tree itself.
+"""
+import argparse
+import os
+import runpy
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+EX = "examples/01_simd_cpp_api/04_advanced_api/03_quantization"
+
+# (fixture name, script, argv, seed, {bin file: (dtype, shape)})
+CASES = [
+    ("quant_dav2201", f"{EX}/quant/scripts/gen_data.py", ["dav-2201"], 101,
+     {"input/input.bin": (np.float32, (1024,)), "output/golden.bin": (np.int8, (1024,))}),
+    ("quant_dav3510", f"{EX}/quant/scripts/gen_data.py", ["dav-3510"], 102,
+     {"input/input.bin": (np.float32, (1024,)), "output/golden.bin": (np.int8, (1024,))}),
+    ("dequant", f"{EX}/dequant/scripts/gen_data.py", [], 103,
+     {"input/input.bin": (np.int32, (128, 32)), "input/scale.bin": (np.float32, (32,)),
+      "output/golden.bin": (np.float32, (128, 32))}),
+    ("antiquant_dav2201", f"{EX}/antiquant/scripts/gen_data.py", ["dav-2201"], None,
+     {"input/input_src.bin": (np.int8, (8, 128)), "input/input_offset.bin": (np.float16, (1, 128)),
+      "input/input_scale.bin": (np.float16, (1, 128)), "output/golden.bin": (np.float16, (8, 128))}),
+    ("antiquant_dav3510", f"{EX}/antiquant/scripts/gen_data.py", ["dav-3510"], None,
+     {"input/input_src.bin": (np.int8, (8, 128)), "input/input_offset.bin": (np.float16, (1, 128)),
+      "input/input_scale.bin": (np.float16, (1, 128)), "output/golden.bin": (np.float16, (8, 128))}),
+]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    for name, script, argv, seed, files in CASES:
+        path = os.path.join(args.reference, script)
+        with tempfile.TemporaryDirectory() as tmp:
+            cwd, old_argv = os.getcwd(), sys.argv
+            os.chdir(tmp)
+            try:
+                if seed is not None:
+                    np.random.seed(seed)
+                sys.argv = [path] + argv
+                runpy.run_path(path, run_name="__main__")
+                out = {}
+                for rel, (dt, shape) in files.items():
+                    key = os.path.splitext(os.path.basename(rel))[0]
+                    out[key] = np.fromfile(os.path.join(tmp, rel), dtype=dt).reshape(shape)
+            finally:
+                os.chdir(cwd)
+                sys.argv = old_argv
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+        print(name, {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main()

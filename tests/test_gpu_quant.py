@@ -1,0 +1,182 @@
+"""GPU parity of AscendQuant (C ABI -> CUDA) against the CPU oracle.  Bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from asc_devkit_b200 import _lib as L
+from asc_devkit_b200 import ops
+from oracle import oracle as O
+from tests.gpu_util import DEV, assert_bits_equal, empty_dev, rand_float, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+def run_quant(src, srcT, **kw):
+    """Same keyword interface as oracle.ascend_quant, executed by the CUDA library."""
+    policy = kw["policy"]
+    dstT = kw.get("dstT", O.I8)
+    d_src = to_dev(src, srcT)
+    if dstT == O.I8:
+        d_dst = torch.full(src.shape, 77, dtype=torch.int8, device=DEV)
+    else:
+        d_dst = torch.zeros(src.size // 2, dtype=torch.uint8, device=DEV)
+    scaleT = kw.get("scaleT", O.F16)
+    scale = kw.get("scale")
+    offset = kw.get("offset")
+    cal = kw.get("calCount", src.size)
+    p = L.QuantParam(kw.get("m", 0), kw.get("n", 0), cal, kw.get("groupSize", 0), int(kw.get("hasOffset", False)),
+                     kw.get("kDim", 1), kw.get("roundMode", O.CAST_RINT))
+    import ctypes as C
+    d_scale = to_dev(scale, scaleT) if scale is not None else None
+    d_off = to_dev(offset, scaleT) if offset is not None else None
+    rc = L.lib().ascq_quant(ops._ptr(d_dst), dstT, ops._ptr(d_src), srcT, ops._ptr(d_scale), ops._ptr(d_off), scaleT,
+                            kw.get("scaleScalar", 0.0), kw.get("offsetScalar", 0.0), policy, C.byref(p),
+                            ops._stream(None))
+    L.check(rc)
+    torch.cuda.synchronize()
+    return d_dst.cpu().numpy()
+
+
+def test_cfg1_per_tensor_full_size():
+    # BASELINE config 1: fp16 [256, 4096] ~ N(0,1), scale 64, offset 0
+    x = np.random.default_rng(20251125 + 1).standard_normal((256, 4096)).astype(np.float16)
+    want = O.ascend_quant(x, O.F16, policy=O.PER_TENSOR, scaleScalar=64.0, offsetScalar=0.0)
+    got = run_quant(x, O.F16, policy=O.PER_TENSOR, scaleScalar=64.0, offsetScalar=0.0)
+    assert_bits_equal(got, want, "cfg1")
+    assert 0.02 < np.mean((got == 127) | (got == -128)) < 0.08
+
+
+def test_sample_golden_through_gpu(golden_dir):
+    import os
+    g = np.load(os.path.join(golden_dir, "quant_dav2201.npz"))
+    got = run_quant(g["input"], O.F32, policy=O.PER_TENSOR, scaleScalar=2.0, offsetScalar=0.9)
+    assert_bits_equal(got, g["golden"], "quant sample golden")
+
+
+@pytest.mark.parametrize("srcT", [O.F16, O.F32, O.BF16])
+@pytest.mark.parametrize("count", [1, 31, 32, 4096, 4097, 8192 + 17, 100003])
+def test_per_tensor_ragged_counts(srcT, count):
+    rng = np.random.default_rng(count * 7 + srcT)
+    x = rand_float(rng, (count,), srcT, -80, 80)
+    kw = dict(policy=O.PER_TENSOR, scaleScalar=1.7, offsetScalar=-0.35)
+    assert_bits_equal(run_quant(x, srcT, **kw), O.ascend_quant(x, srcT, **kw), f"per-tensor {count}")
+
+
+def test_per_tensor_calcount_prefix_only():
+    rng = np.random.default_rng(5)
+    x = rand_float(rng, (10000,), O.F16, -50, 50)
+    kw = dict(policy=O.PER_TENSOR, scaleScalar=3.0, offsetScalar=0.5, calCount=4100)
+    got = run_quant(x, O.F16, **kw)
+    want = O.ascend_quant(x, O.F16, **kw)
+    assert_bits_equal(got[:4100], want[:4100], "prefix")
+    assert (got[4100:] == 77).all(), "elements beyond calCount must stay untouched"
+
+
+def test_unaligned_base_pointers():
+    rng = np.random.default_rng(6)
+    x = rand_float(rng, (5000,), O.F16, -50, 50)
+    d_src = to_dev(x, O.F16)[1:]            # 2-byte offset: not 16-byte aligned
+    d_dst = torch.zeros(4999 + 3, dtype=torch.int8, device=DEV)[3:]
+    ops.AscendQuant(d_dst, d_src, 2.0, 0.25, 4999)
+    torch.cuda.synchronize()
+    want = O.ascend_quant(np.ascontiguousarray(x[1:]), O.F16, policy=O.PER_TENSOR, scaleScalar=2.0, offsetScalar=0.25)
+    assert_bits_equal(d_dst.cpu().numpy(), want, "unaligned")
+
+
+@pytest.mark.parametrize("srcT", [O.F16, O.F32])
+@pytest.mark.parametrize("tensor_offset", [False, True])
+@pytest.mark.parametrize("m,n", [(7, 256), (33, 1024), (5, 48), (3, 16)])
+def test_per_channel(srcT, tensor_offset, m, n):
+    if (n * O.DT_SIZE[srcT]) % 32:
+        pytest.skip("scaleCount must be 32-byte aligned")
+    rng = np.random.default_rng(m * n + srcT)
+    x = rand_float(rng, (m, n), srcT, -30, 30)
+    scale = rand_float(rng, (n,), srcT, 0.5, 4.0)
+    offset = rand_float(rng, (n,), srcT, -2, 2) if tensor_offset else None
+    kw = dict(policy=O.PER_CHANNEL, n=n, calCount=m * n, scale=scale, offset=offset, scaleT=srcT, offsetScalar=0.37)
+    assert_bits_equal(run_quant(x, srcT, **kw), O.ascend_quant(x, srcT, **kw), "per-channel")
+
+
+PAIRS = [(O.F16, O.F16), (O.BF16, O.BF16), (O.F32, O.F32), (O.F16, O.F32), (O.BF16, O.F32)]
+
+
+@pytest.mark.parametrize("srcT,scaleT", PAIRS)
+@pytest.mark.parametrize("hasOffset", [False, True])
+@pytest.mark.parametrize("m,n", [(10, 256), (10, 288), (8, 512), (3, 40)])
+def test_per_token(srcT, scaleT, hasOffset, m, n):
+    # shapes of tests/api/adv_api/quantization/quant/test_ascend_quant_per_token.cpp:146-173 (+ a ragged one)
+    rng = np.random.default_rng(m * n + srcT * 10 + scaleT)
+    x = rand_float(rng, (m, n), srcT, -20, 20)
+    scale = rand_float(rng, (m,), scaleT, 0.5, 8.0)
+    offset = rand_float(rng, (m,), scaleT, -3, 3)
+    kw = dict(policy=O.PER_TOKEN, m=m, n=n, calCount=m * n, scale=scale, offset=offset if hasOffset else None,
+              scaleT=scaleT, hasOffset=hasOffset)
+    assert_bits_equal(run_quant(x, srcT, **kw), O.ascend_quant(x, srcT, **kw), "per-token")
+
+
+@pytest.mark.parametrize("srcT,scaleT", PAIRS)
+@pytest.mark.parametrize("kDim", [0, 1])
+@pytest.mark.parametrize("groupSize", [32, 64, 128])
+def test_per_group(srcT, scaleT, kDim, groupSize):
+    m, n = 128, 256
+    rng = np.random.default_rng(groupSize + kDim + srcT * 10 + scaleT)
+    x = rand_float(rng, (m, n), srcT, -20, 20)
+    sshape = (m, n // groupSize) if kDim == 1 else (m // groupSize, n)
+    scale = rand_float(rng, sshape, scaleT, 0.5, 8.0)
+    offset = rand_float(rng, sshape, scaleT, -3, 3)
+    kw = dict(policy=O.PER_GROUP, m=m, n=n, calCount=m * n, scale=scale, offset=offset, scaleT=scaleT, hasOffset=True,
+              groupSize=groupSize, kDim=kDim)
+    assert_bits_equal(run_quant(x, srcT, **kw), O.ascend_quant(x, srcT, **kw), "per-group")
+
+
+@pytest.mark.parametrize("roundMode", [O.CAST_NONE, O.CAST_RINT, O.CAST_FLOOR, O.CAST_CEIL, O.CAST_ROUND, O.CAST_TRUNC])
+@pytest.mark.parametrize("srcT,scaleT", [(O.F16, O.F16), (O.F32, O.F32), (O.BF16, O.BF16)])
+def test_round_modes_on_exact_halves(roundMode, srcT, scaleT):
+    # values k + 0.5 hit every tie; scale 1 keeps them exact
+    vals = (np.arange(-300, 300, dtype=np.float32) * 0.5).reshape(4, 150)
+    vals = np.tile(vals, (1, 2))[:, :288]
+    x = vals.astype(np.float16) if srcT == O.F16 else (O.f32_to_bf16_bits(vals) if srcT == O.BF16 else vals)
+    one = rand_float(np.random.default_rng(0), (4,), scaleT, 1.0, 1.0)
+    kw = dict(policy=O.PER_TOKEN, m=4, n=288, calCount=4 * 288, scale=one, scaleT=scaleT, roundMode=roundMode)
+    assert_bits_equal(run_quant(np.ascontiguousarray(x), srcT, **kw), O.ascend_quant(np.ascontiguousarray(x), srcT, **kw),
+                      f"round mode {roundMode}")
+
+
+@pytest.mark.parametrize("srcT,scaleT", [(O.F16, O.F16), (O.BF16, O.BF16), (O.F16, O.F32)])
+def test_per_group_to_fp4(srcT, scaleT):
+    m, n, gs = 16, 128, 32
+    rng = np.random.default_rng(99 + srcT + scaleT)
+    x = rand_float(rng, (m, n), srcT, -7, 7)
+    scale = rand_float(rng, (m, n // gs), scaleT, 0.5, 2.0)
+    kw = dict(policy=O.PER_GROUP, m=m, n=n, calCount=m * n, scale=scale, scaleT=scaleT, groupSize=gs, kDim=1,
+              dstT=O.FP4X2_E2M1)
+    assert_bits_equal(run_quant(x, srcT, **kw), O.ascend_quant(x, srcT, **kw), "fp4 quant")
+
+
+def test_dynamic_per_token_quant():
+    rng = np.random.default_rng(1234)
+    for m, n, dt in [(64, 4096, O.F16), (5, 1000, O.F32), (17, 8192, O.BF16), (3, 7, O.F16)]:
+        x = rand_float(rng, (m, n), dt, -9, 9)
+        if m > 4:
+            x[2] = 0  # an all-zero token
+        want_q, want_s, want_d = O.dynamic_quant_per_token(x, dt, m, n)
+        d_x = to_dev(x, dt)
+        d_q = torch.empty((m, n), dtype=torch.int8, device=DEV)
+        d_s = torch.empty(m, dtype=torch.float32, device=DEV)
+        d_d = torch.empty(m, dtype=torch.float32, device=DEV)
+        ops.DynamicQuantPerToken(d_q, d_s, d_x, d_d)
+        torch.cuda.synchronize()
+        assert_bits_equal(d_s.cpu().numpy(), want_s, "scale")
+        assert_bits_equal(d_d.cpu().numpy(), want_d, "dequant scale")
+        assert_bits_equal(d_q.cpu().numpy(), want_q, "int8")
+
+
+def test_quant_is_monotone_at_scale():
+    # size-independent property at a size the oracle is not run on: quantisation preserves order
+    n = 1 << 24
+    x = torch.linspace(-3.0, 3.0, n, device=DEV, dtype=torch.float32).to(torch.float16)
+    q = torch.empty(n, dtype=torch.int8, device=DEV)
+    ops.AscendQuant(q, x, 64.0, 0.0, n)
+    torch.cuda.synchronize()
+    d = q[1:].to(torch.int16) - q[:-1].to(torch.int16)
+    assert int(d.min()) >= 0 and int(q.min()) == -128 and int(q.max()) == 127
