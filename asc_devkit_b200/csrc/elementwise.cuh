@@ -80,19 +80,101 @@ template <typename Src, typename Dst> struct VecOf {
     static constexpr int value = 16 / kMin;
 };
 
-// CT result -> destination element.
-template <typename Dst, typename CT> __device__ __forceinline__ Dst finish(CT x, int roundMode)
+// Source vector -> compute type.
+template <typename Src, typename CT, int VEC>
+__device__ __forceinline__ void unpack_src(const Pack<Src, VEC>& in, CT (&x)[VEC])
+{
+    if constexpr (std::is_same<Src, int8_t>::value && std::is_same<CT, float>::value) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&in);
+#pragma unroll
+        for (int q = 0; q < VEC / 4; ++q) {
+            float f[4];
+            unpack_i8x4_f32(w[q], f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[q * 4 + j] = f[j];
+        }
+    } else if constexpr (std::is_same<Src, CT>::value) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) x[i] = in.v[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) x[i] = Ct<CT>::from_f32(to_f32<Src>(in.v[i]));
+    }
+}
+
+// Compute-type results -> destination vector (final cast: RINT + saturation, or the round mode for int8).
+template <typename Dst, typename CT, int VEC>
+__device__ __forceinline__ void pack_dst(const CT (&x)[VEC], Pack<Dst, VEC>& out, int roundMode)
 {
     if constexpr (std::is_same<Dst, int8_t>::value) {
-        return static_cast<int8_t>(f32_to_i8_sat(Ct<CT>::to_f32(x), roundMode));
+        uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+        if (roundMode <= kRoundRint) {
+#pragma unroll
+            for (int q = 0; q < VEC / 4; ++q)
+                w[q] = pack_i8x4_rni(Ct<CT>::to_f32(x[q * 4]), Ct<CT>::to_f32(x[q * 4 + 1]), Ct<CT>::to_f32(x[q * 4 + 2]),
+                                     Ct<CT>::to_f32(x[q * 4 + 3]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) out.v[i] = static_cast<int8_t>(f32_to_i8_sat(Ct<CT>::to_f32(x[i]), roundMode));
+        }
     } else if constexpr (std::is_same<Dst, CT>::value) {
-        return x;
-    } else if constexpr (std::is_same<Dst, __half>::value) {
-        return f32_to_f16_sat(Ct<CT>::to_f32(x));
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) out.v[i] = x[i];
     } else if constexpr (std::is_same<Dst, __nv_bfloat16>::value) {
-        return f32_to_bf16_sat(Ct<CT>::to_f32(x));
+        uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+        for (int q = 0; q < VEC / 2; ++q) w[q] = pack_bf16x2_sat(Ct<CT>::to_f32(x[2 * q]), Ct<CT>::to_f32(x[2 * q + 1]));
+    } else if constexpr (std::is_same<Dst, __half>::value) {
+        uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+        for (int q = 0; q < VEC / 2; ++q) w[q] = pack_f16x2_sat(Ct<CT>::to_f32(x[2 * q]), Ct<CT>::to_f32(x[2 * q + 1]));
     } else {
-        return Ct<CT>::to_f32(x);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) out.v[i] = Ct<CT>::to_f32(x[i]);
+    }
+}
+
+// The arithmetic of one vector: quant x*s(+o), dequant x*s(*tok), antiquant (x+o)*s.  Half math runs two
+// lanes per instruction (HMUL2 / HADD2, each lane individually rounded).
+template <int OP, typename CT, int VEC, int SV, bool HAS_OFF, bool HAS_TOK>
+__device__ __forceinline__ void apply_op(CT (&x)[VEC], const CT (&s)[SV], const CT (&o)[SV], float tok)
+{
+    constexpr bool kVecScale = SV != 1;
+    if constexpr (std::is_same<CT, __half>::value && (VEC % 2 == 0)) {
+        __half2* x2 = reinterpret_cast<__half2*>(x);
+#pragma unroll
+        for (int q = 0; q < VEC / 2; ++q) {
+            const __half2 s2 = kVecScale ? __halves2half2(s[2 * q], s[2 * q + 1]) : __half2half2(s[0]);
+            const __half2 o2 = kVecScale ? __halves2half2(o[2 * q], o[2 * q + 1]) : __half2half2(o[0]);
+            __half2 v = x2[q];
+            if constexpr (OP == kOpQuant) {
+                v = __hmul2_rn(v, s2);
+                if constexpr (HAS_OFF) v = __hadd2_rn(v, o2);
+            } else if constexpr (OP == kOpDequant) {
+                v = __hmul2_rn(v, s2);
+            } else {
+                if constexpr (HAS_OFF) v = __hadd2_rn(v, o2);
+                v = __hmul2_rn(v, s2);
+            }
+            x2[q] = v;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const int si = kVecScale ? i : 0;
+            CT v = x[i];
+            if constexpr (OP == kOpQuant) {
+                v = Ct<CT>::mul(v, s[si]);
+                if constexpr (HAS_OFF) v = Ct<CT>::add(v, o[si]);
+            } else if constexpr (OP == kOpDequant) {
+                v = Ct<CT>::mul(v, s[si]);
+                if constexpr (HAS_TOK) v = Ct<CT>::mul(v, Ct<CT>::from_f32(tok));
+            } else {
+                if constexpr (HAS_OFF) v = Ct<CT>::add(v, o[si]);
+                v = Ct<CT>::mul(v, s[si]);
+            }
+            x[i] = v;
+        }
     }
 }
 
@@ -126,46 +208,53 @@ __global__ void __launch_bounds__(256) ew_rows_kernel(const EwArgs a)
     }
     const uint32_t sc_col = a.scale.cdiv ? c0 / a.scale.cdiv : 0u;
 
-#pragma unroll 2
-    for (uint32_t r = blockIdx.y; r < a.rows; r += gridDim.y) {
-        if constexpr (SMODE == kSRowBcast) {
-            const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + sc_col;
-            s[0] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.scale.p) + idx)));
-            if constexpr (HAS_OFF) o[0] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.offset.p) + idx)));
-        } else if constexpr (SMODE == kSRowVec) {
-            const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + c0;
-            const Pack<Sc, VEC> sp = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.scale.p) + idx);
+    // Rows are taken U at a time: all U source vectors (and the per-row scalars) are requested before
+    // the first result is stored, so every thread keeps U 128-bit loads in flight.
+    constexpr int U = (SMODE == kSRowVec) ? 1 : 4;
+    const uint32_t gy = gridDim.y;
+    for (uint32_t r0 = blockIdx.y; r0 < a.rows; r0 += gy * U) {
+        Pack<Src, VEC> in[U];
+        CT srow[U], orow[U];
+        float tok[U];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) s[i] = Ct<CT>::from_f32(to_f32<Sc>(sp.v[i]));
-            if constexpr (HAS_OFF) {
-                const Pack<Sc, VEC> op = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.offset.p) + idx);
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(to_f32<Sc>(op.v[i]));
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gy;
+            if (r < a.rows) {
+                in[u] = load_pack<Src, VEC, true>(static_cast<const Src*>(a.src) + static_cast<size_t>(r) * a.srcStride + c0);
+                if constexpr (SMODE == kSRowBcast) {
+                    const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + sc_col;
+                    srow[u] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.scale.p) + idx)));
+                    if constexpr (HAS_OFF)
+                        orow[u] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.offset.p) + idx)));
+                }
+                if constexpr (HAS_TOK) tok[u] = __ldg(a.tok + r);
             }
         }
-        float tok = 1.0f;
-        if constexpr (HAS_TOK) tok = __ldg(a.tok + r);
-
-        const Pack<Src, VEC> in =
-            load_pack<Src, VEC, true>(static_cast<const Src*>(a.src) + static_cast<size_t>(r) * a.srcStride + c0);
-        Pack<Dst, VEC> out;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            const int si = kVecScale ? i : 0;
-            CT x = Ct<CT>::from_f32(to_f32<Src>(in.v[i]));
-            if constexpr (OP == kOpQuant) {
-                x = Ct<CT>::mul(x, s[si]);
-                if constexpr (HAS_OFF) x = Ct<CT>::add(x, o[si]);
-            } else if constexpr (OP == kOpDequant) {
-                x = Ct<CT>::mul(x, s[si]);
-                if constexpr (HAS_TOK) x = Ct<CT>::mul(x, Ct<CT>::from_f32(tok));
-            } else {
-                if constexpr (HAS_OFF) x = Ct<CT>::add(x, o[si]);
-                x = Ct<CT>::mul(x, s[si]);
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gy;
+            if (r >= a.rows) break;
+            if constexpr (SMODE == kSRowBcast) {
+                s[0] = srow[u];
+                if constexpr (HAS_OFF) o[0] = orow[u];
+            } else if constexpr (SMODE == kSRowVec) {
+                const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + c0;
+                const Pack<Sc, VEC> sp = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.scale.p) + idx);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) s[i] = Ct<CT>::from_f32(to_f32<Sc>(sp.v[i]));
+                if constexpr (HAS_OFF) {
+                    const Pack<Sc, VEC> op = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.offset.p) + idx);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(to_f32<Sc>(op.v[i]));
+                }
             }
-            out.v[i] = finish<Dst, CT>(x, a.roundMode);
+            alignas(4) CT x[VEC];
+            unpack_src<Src, CT, VEC>(in[u], x);
+            apply_op<OP, CT, VEC, SV, HAS_OFF, HAS_TOK>(x, s, o, HAS_TOK ? tok[u] : 1.0f);
+            Pack<Dst, VEC> out;
+            pack_dst<Dst, CT, VEC>(x, out, a.roundMode);
+            store_pack<Dst, VEC>(static_cast<Dst*>(a.dst) + static_cast<size_t>(r) * a.dstStride + c0, out);
         }
-        store_pack<Dst, VEC>(static_cast<Dst*>(a.dst) + static_cast<size_t>(r) * a.dstStride + c0, out);
     }
 }
 

@@ -88,6 +88,56 @@ __device__ __forceinline__ uint32_t f32_to_e2m1(float f, int mode)
     return sign | static_cast<uint32_t>(pick);
 }
 
+// ---- packed conversions used by the vector kernels -------------------------------------------------
+// Two floats -> packed bf16x2 / f16x2 (RINT) in one instruction; the saturation rule (finite overflow ->
+// largest finite value, Inf and NaN kept) is applied only when a lane came out as Inf/NaN, which is rare.
+__device__ __forceinline__ uint32_t pack_bf16x2_sat(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    const uint32_t t = r & 0x7F807F80u;
+    if (__builtin_expect(t >= 0x7F800000u || (t & 0xFFFFu) == 0x7F80u, 0)) {
+        r = static_cast<uint32_t>(__bfloat16_as_ushort(f32_to_bf16_sat(lo))) |
+            (static_cast<uint32_t>(__bfloat16_as_ushort(f32_to_bf16_sat(hi))) << 16);
+    }
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    const uint32_t t = r & 0x7C007C00u;
+    if (__builtin_expect(t >= 0x7C000000u || (t & 0xFFFFu) == 0x7C00u, 0)) {
+        r = static_cast<uint32_t>(__half_as_ushort(f32_to_f16_sat(lo))) |
+            (static_cast<uint32_t>(__half_as_ushort(f32_to_f16_sat(hi))) << 16);
+    }
+    return r;
+}
+// Four floats -> four saturated int8 in one word, round-half-even: cvt.rni.s32.f32 clamps to int32 and
+// turns NaN into 0; cvt.pack.sat.s8.s32 clamps to [-128, 127] while packing.
+__device__ __forceinline__ uint32_t pack_i8x4_rni(float x0, float x1, float x2, float x3)
+{
+    int a, b, c, d;
+    asm("cvt.rni.s32.f32 %0, %1;" : "=r"(a) : "f"(x0));
+    asm("cvt.rni.s32.f32 %0, %1;" : "=r"(b) : "f"(x1));
+    asm("cvt.rni.s32.f32 %0, %1;" : "=r"(c) : "f"(x2));
+    asm("cvt.rni.s32.f32 %0, %1;" : "=r"(d) : "f"(x3));
+    uint32_t hi, r;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+    return r;
+}
+// Four int8 of one word -> four floats without the conversion pipe: byte ^ 0x80 placed in the mantissa
+// of 2^23 gives 2^23 + (v + 128); subtracting 2^23 + 128 is exact.
+__device__ __forceinline__ void unpack_i8x4_f32(uint32_t w, float (&f)[4])
+{
+    const uint32_t b = w ^ 0x80808080u;
+    f[0] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7650)), -8388736.0f);
+    f[1] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7651)), -8388736.0f);
+    f[2] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7652)), -8388736.0f);
+    f[3] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7653)), -8388736.0f);
+}
+
 // ---- compute-type algebra: CT in {__half, __nv_bfloat16, float} ------------------------------
 template <typename CT> struct Ct;
 template <> struct Ct<float> {

@@ -256,9 +256,13 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(gpu_index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+                                          "-lms", "50", "-i", str(gpu_index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+        # nvidia-smi needs a moment to start: wait for its first line so the timed region is covered
+        t0 = time.time()
+        while self.proc is not None and time.time() - t0 < 3.0 and os.path.getsize(self.tmp.name) == 0:
+            time.sleep(0.02)
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
@@ -346,14 +350,14 @@ def run_ours(args):
         is_head = nm == (args.workload if args.workload != "all" else HEADLINE)
         sampler = ClockSampler(local) if (is_head and rank == 0) else None
         sec = time_steps(torch, wl.step, args.steps, args.warmup, dist)
-        if sampler:
-            clocks = sampler.stop()
         per = sec / args.steps
         work = wl.work_per_step()
         achieved = work / per / 1e9  # GB/s (each rank does the full workload: replicas)
         e2e_sec = time_steps(torch, wl.e2e_step, max(2, args.steps // 4), 2, dist)
         e2e_per = e2e_sec / max(2, args.steps // 4)
         h2d, d2h = wl.e2e_bytes()
+        if sampler:
+            clocks = sampler.stop()
         rec = {"name": wl.name, "value": achieved * world, "unit": wl.unit, "ms_per_step": per * 1e3,
                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]},
@@ -442,7 +446,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="all", choices=["all"] + list(WORKLOADS))

@@ -151,7 +151,8 @@ def ascend_dequant(src, srcT, dstT, *, policy, m, n, calCount, scale=None, tokSc
         rows, stride = m, dequant_dst_stride(n, dstT)
     else:
         rows, stride = calCount // n, n
-    dst = np.full((rows, stride), fill, NP_DTYPE[dstT])
+    dst = np.empty((rows, stride), NP_DTYPE[dstT])
+    dst.view(np.uint16 if DT_SIZE[dstT] == 2 else np.uint32).fill(fill)  # `fill` is a bit pattern
     p = _DequantParam(m, n, calCount, groupSize, kDim)
     _check(lib().ascq_oracle_dequant(_p(dst), dstT, _p(src), srcT, _p(scale), _p(tokScale), scaleT,
                                      C.c_float(scaleScalar), policy, C.byref(p)))
