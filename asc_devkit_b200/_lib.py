@@ -54,6 +54,8 @@ SIGNATURES = {
     "ascq_dynamic_quant_per_token": (_i, [_vp, _vp, _vp, _vp, _i, _u32, _u32, _vp]),
     "ascq_dequant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _i, C.POINTER(DequantParam), _vp]),
     "ascq_antiquant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(AntiQuantParam), _vp]),
+    "ascq_matmul_w8a8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "ascq_matmul_status": (_i, [_vp]),
     "ascq_get_ascend_quant_max_min_tmp_size": (_i, [_P64, _i, _u32, _PU32, _PU32]),
     "ascq_get_ascend_quant_tmp_buffer_factor_size": (None, [_PU32, _PU32]),
     "ascq_get_ascend_dequant_max_min_tmp_size": (_i, [_P64, _i, _u32, _PU32, _PU32]),

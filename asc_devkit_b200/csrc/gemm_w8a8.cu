@@ -1,0 +1,345 @@
+// ascq_matmul_w8a8: int8 x int8 -> int32 matmul on the 5th-generation tensor cores (tcgen05.mma kind::i8)
+// with the per-channel x per-token dequantisation, bias and bf16 cast fused into the epilogue.
+//
+// Data layout in HBM: A [M,K] int8 row-major, B [N,K] int8 row-major (both K-major), C [M,ldc] bf16.
+// One persistent CTA per SM walks output tiles of 128 x BN.  Per k-block of 128 bytes a TMA producer warp
+// loads a 128x128 A tile and a BNx128 B tile into a 128B-swizzled shared-memory stage; one thread of the
+// MMA warp issues four tcgen05.mma (K = 32 each) accumulating int32 in tensor memory; tcgen05.commit frees
+// the stage.  The accumulator is double buffered (2 x BN TMEM columns) so the four epilogue warps drain
+// tile i (tcgen05.ld -> fp32 scale, scale, bias -> bf16 -> 64-byte row segments to global) while the
+// tensor cores work on tile i+1.
+//
+// Roofline: dense int8 tensor throughput; 2*M*N*K operations per call.  Algorithmic HBM bytes are
+// M*K + N*K + 2*M*N (operands are re-read from L2 across tiles).
+//
+// Every mbarrier wait is bounded; on expiry the CTA raises an abort flag, all roles leave their loops, the
+// TMEM allocation is released and a device status word reports the timeout.
+#include <cuda_bf16.h>
+
+#include "ascq_internal.h"
+#include "numerics.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ascq {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;        // bytes == int8 elements per k-block: one 128B swizzle atom
+constexpr int kUmmaK = 32;      // K per tcgen05.mma for 8-bit operands
+constexpr int kThreads = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+
+__device__ int g_w8a8_status = 0;  // 0 ok, 1 = a bounded wait expired
+
+template <int BN> struct Cfg {
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kABytes = kBM * kBK;
+    static constexpr int kBBytes = BN * kBK;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators
+    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct Params {
+    __nv_bfloat16* C;
+    const float* sA;
+    const float* sB;
+    const __nv_bfloat16* bias;
+    int32_t* accDump;
+    int M, N, K, ldc;
+    int tilesM, tilesN;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
+{
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // stage buffers need 1024-byte alignment for the 128B swizzle pattern
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+    uint64_t* fullBar = bars;                      // [kStages] TMA -> MMA
+    uint64_t* emptyBar = bars + C::kStages;        // [kStages] MMA -> TMA
+    uint64_t* tmemFull = bars + 2 * C::kStages;    // [2] MMA -> epilogue
+    uint64_t* tmemEmpty = tmemFull + 2;            // [2] epilogue -> MMA
+    uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
+    volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int numTiles = p.tilesM * p.tilesN;
+    const int kBlocks = (p.K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&fullBar[s], 1);
+            mbar_init(&emptyBar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmemFull[a], 1);
+            mbar_init(&tmemEmpty[a], 4);  // one arrival per epilogue warp
+        }
+        *abortFlag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tmapA);
+        prefetch_tensormap(&tmapB);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmemBaseSlot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmemBase = *tmemBaseSlot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.tilesM) * kBM;
+                const int n0 = (tile / p.tilesM) * BN;
+                for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!(ok = mbar_wait_bounded(&emptyBar[s], ph ^ 1, abortFlag))) break;
+                    uint8_t* sa = smem + s * C::kStageBytes;
+                    mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
+                    tma_load_2d(sa, &tmapA, &fullBar[s], kb * kBK, m0);
+                    tma_load_2d(sa + C::kABytes, &tmapB, &fullBar[s], kb * kBK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_i8(kBM, BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t accPh = (local >> 1) & 1;
+                if (!(ok = mbar_wait_bounded(&tmemEmpty[acc], accPh ^ 1, abortFlag))) break;
+                tc_fence_after();
+                const uint32_t tmemD = tmemBase + acc * BN;
+                for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!(ok = mbar_wait_bounded(&fullBar[s], ph, abortFlag))) break;
+                    tc_fence_after();
+                    const uint32_t aAddr = smem_u32(smem + s * C::kStageBytes);
+                    const uint64_t descA = smem_desc_sw128(aAddr);
+                    const uint64_t descB = smem_desc_sw128(aAddr + C::kABytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // advancing K inside the swizzle atom: +32 bytes on the start address (>> 4 = 2)
+                        mma_i8(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    tc_commit(&emptyBar[s]);  // the stage is free once these MMAs have read it
+                }
+                if (ok) tc_commit(&tmemFull[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----------------
+        const int q = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const uint32_t accPh = (local >> 1) & 1;
+            const int m0 = (tile % p.tilesM) * kBM;
+            const int n0 = (tile / p.tilesM) * BN;
+            if (!(ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag))) break;
+            tc_fence_after();
+            const int m = m0 + q * 32 + lane;
+            const float sa = (p.sA != nullptr && m < p.M) ? __ldg(p.sA + m) : 1.0f;
+            const uint32_t taddr = tmemBase + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+            const bool vecStore = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const int n = n0 + c * 32;
+                if (m < p.M && n < p.N) {
+                    if (p.accDump != nullptr) {
+                        int32_t* d = p.accDump + static_cast<size_t>(m) * p.N + n;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n + j < p.N) d[j] = static_cast<int32_t>(r[j]);
+                    }
+                    if (p.C != nullptr) {
+                        __nv_bfloat16* crow = p.C + static_cast<size_t>(m) * p.ldc + n;
+                        const bool full = (n + 32 <= p.N);
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            float f0 = __int2float_rn(static_cast<int32_t>(r[j]));
+                            float f1 = __int2float_rn(static_cast<int32_t>(r[j + 1]));
+                            const int n0j = full ? n + j : min(n + j, p.N - 1);
+                            const int n1j = full ? n + j + 1 : min(n + j + 1, p.N - 1);
+                            if (p.sB != nullptr) {
+                                f0 = __fmul_rn(f0, __ldg(p.sB + n0j));
+                                f1 = __fmul_rn(f1, __ldg(p.sB + n1j));
+                            }
+                            f0 = __fmul_rn(f0, sa);
+                            f1 = __fmul_rn(f1, sa);
+                            if (p.bias != nullptr) {
+                                f0 = __fadd_rn(f0, __bfloat162float(p.bias[n0j]));
+                                f1 = __fadd_rn(f1, __bfloat162float(p.bias[n1j]));
+                            }
+                            packed[j >> 1] = pack_bf16x2_sat(f0, f1);
+                        }
+                        if (full && vecStore) {
+                            uint4* dst = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v)
+                                dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (n + j < p.N)
+                                    crow[j] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[j >> 1] >> ((j & 1) * 16)));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmemEmpty[acc]);
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncthreads();
+    if (*abortFlag) {
+        if (threadIdx.x == 0) atomicExch(&g_w8a8_status, 1);
+        // give bulk copies that may still be in flight time to land before the shared memory is handed back
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmemBase, C::kTmemCols);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// uint8 [rows, colsBytes] row-major tensor map with a [boxRows, 128-byte] box and 128B swizzle.
+ascq_status make_tmap_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t colsBytes, uint32_t boxRows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    const cuuint64_t dims[2] = {colsBytes, rows};
+    const cuuint64_t strides[1] = {colsBytes};
+    const cuuint32_t box[2] = {128, boxRows};
+    const cuuint32_t elemStrides[2] = {1, 1};
+    const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elemStrides,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(rc));
+    return ASCQ_OK;
+}
+
+int sm_count()
+{
+    static int n = [] {
+        int dev = 0, v = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v;
+    }();
+    return n;
+}
+
+template <int BN> ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
+{
+    using C = Cfg<BN>;
+    static bool attrSet = false;
+    if (!attrSet) {
+        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(C::kSmemBytes)));
+        attrSet = true;
+    }
+    p.tilesM = (p.M + kBM - 1) / kBM;
+    p.tilesN = (p.N + BN - 1) / BN;
+    const int tiles = p.tilesM * p.tilesN;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    w8a8_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}
+
+}  // namespace
+}  // namespace ascq
+
+using namespace ascq;
+
+extern "C" ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int8_t* B_nk, const float* sA_m,
+                                        const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc,
+                                        int32_t* accDump, void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!A || !B_nk) return fail(ASCQ_ERR_INVALID_ARG, "A and B must not be NULL");
+    if (!C_bf16 && !accDump) return fail(ASCQ_ERR_INVALID_ARG, "one of C and accDump must be given");
+    if (M < 0 || N < 0 || K < 0) return fail(ASCQ_ERR_INVALID_ARG, "M, N, K must be non-negative");
+    if (C_bf16 && ldc < N) return fail(ASCQ_ERR_INVALID_ARG, "ldc %d is smaller than N %d", ldc, N);
+    if (M == 0 || N == 0) return ASCQ_OK;
+    if (K == 0) return fail(ASCQ_ERR_INVALID_ARG, "K must be positive");
+    if (K % 16 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of 16 (TMA row pitch)", K);
+    if (!aligned16(A) || !aligned16(B_nk)) return fail(ASCQ_ERR_ALIGNMENT, "A and B must be 16-byte aligned");
+
+    Params p{};
+    p.C = static_cast<__nv_bfloat16*>(C_bf16);
+    p.sA = sA_m;
+    p.sB = sB_n;
+    p.bias = static_cast<const __nv_bfloat16*>(bias_bf16);
+    p.accDump = accDump;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+
+    // wide tiles when they fill the machine, narrower ones for small problems (e.g. a column shard)
+    const int tiles256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
+    const bool wide = tiles256 >= sm_count();
+    CUtensorMap ta, tb;
+    ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K), kBM);
+    if (rc != ASCQ_OK) return rc;
+    rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), wide ? 256 : 128);
+    if (rc != ASCQ_OK) return rc;
+    return wide ? launch<256>(ta, tb, p, st) : launch<128>(ta, tb, p, st);
+}
+
+// Reads and clears the device status word of the GEMM kernels on the current device (synchronises `stream`).
+extern "C" ascq_status ascq_matmul_status(void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int v = 0, zero = 0;
+    ASCQ_CUDA_CHECK(cudaMemcpyFromSymbolAsync(&v, g_w8a8_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+    ASCQ_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (v != 0) {
+        ASCQ_CUDA_CHECK(cudaMemcpyToSymbolAsync(g_w8a8_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+        return fail(ASCQ_ERR_TIMEOUT, "a bounded wait inside the matmul kernel expired (status %d)", v);
+    }
+    return ASCQ_OK;
+}

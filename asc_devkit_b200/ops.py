@@ -163,6 +163,28 @@ def AscendAntiQuant(dstTensor: torch.Tensor, srcTensor: torch.Tensor, offset, sc
     return dstTensor
 
 
+def MatmulW8A8(C: Optional[torch.Tensor], A: torch.Tensor, B_nk: torch.Tensor, scaleA: Optional[torch.Tensor] = None,
+               scaleB: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+               accDump: Optional[torch.Tensor] = None, stream=None):
+    """int8 x int8 -> int32 matmul with the per-channel x per-token dequant, bias and bf16 cast fused
+    (``ascq_matmul_w8a8``).  A [M,K], B_nk [N,K] (K-major, the reference's SetTensorB(..., isTransposeB=true)),
+    C bf16 [M, ldc>=N] (row stride taken from C.stride(0))."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    if C is not None and C.stride(1) != 1:
+        raise ValueError("C must have unit column stride")
+    ldc = C.stride(0) if C is not None else N
+    cptr = C.data_ptr() if C is not None else None
+    L.check(L.lib().ascq_matmul_w8a8(cptr, _ptr(A), _ptr(B_nk), _ptr(scaleA), _ptr(scaleB), _ptr(bias), M, N, K, ldc,
+                                     _ptr(accDump), _stream(stream)))
+    return C
+
+
+def MatmulStatus(stream=None):
+    """Synchronise and raise AscqError(ERR_TIMEOUT) if a matmul kernel gave up a bounded wait."""
+    L.check(L.lib().ascq_matmul_status(_stream(stream)))
+
+
 # ---- host tiling helpers (include/adv_api/quantization/ascend_*_tiling.h) ------------------------
 def _dims(d):
     return (C.c_int64 * len(d))(*d), len(d)

@@ -67,6 +67,14 @@ def gen_dequant_cfg3(M=2048, N=4096):
             "sch": rng.uniform(1e-5, 1e-3, N).astype(np.float32), "stok": rng.uniform(0.5, 2.0, M).astype(np.float32)}
 
 
+def gen_w8a8_cfg4(M=4096, N=4096, K=4096):
+    rng = np.random.default_rng(SEED + 4)
+    return {"A": np.clip(np.rint(rng.normal(0, 30, (M, K))), -127, 127).astype(np.int8),
+            "B": rng.integers(-127, 128, (N, K), dtype=np.int8),
+            "sA": rng.uniform(0.005, 0.02, M).astype(np.float32), "sB": rng.uniform(0.001, 0.01, N).astype(np.float32),
+            "bias": f32_to_bf16_bits(rng.normal(0, 0.1, N).astype(np.float32))}
+
+
 # ------------------------------------------------------------------------------------------------
 # Workloads.  Each owns `nsets` rotating device buffer sets and knows its algorithmic bytes.
 # ------------------------------------------------------------------------------------------------
@@ -240,8 +248,84 @@ class QuantScaled(Workload):
         return bool(np.array_equal(self.out[0][:rows].cpu().numpy(), want))
 
 
-WORKLOADS = {"antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3, "quant_scaled": QuantScaled}
-HEADLINE = "antiquant_cfg2"
+class W8A8Cfg4(Workload):
+    """Config 4.  With `world` > 1 the weight matrix B (and sB, bias) is column-sharded over the ranks: each rank
+    computes C[:, shard] and an NCCL all-gather reassembles the output on every rank (strong scaling)."""
+    name = "W8A8 int8 matmul M=N=K=4096 + per-token x per-channel dequant + bias -> bf16 (config 4)"
+    dtype = "int8"
+    unit = "TOPS"
+    bound = "tensor"
+    key = "w8a8_cfg4"
+
+    def __init__(self, torch, ops, dev, dist=None, world=1, rank=0):
+        self.torch, self.ops, self.dist, self.world, self.rank = torch, ops, dist, world, rank
+        self.M = self.N = self.K = 4096
+        h = gen_w8a8_cfg4(self.M, self.N, self.K)
+        self.host = h
+        self.nl = self.N // world
+        n0 = rank * self.nl
+        per_set = self.M * self.K + self.nl * self.K + self.M * self.nl * 2
+        self.nsets = self.nsets_for(per_set)
+        bf = lambda a: torch.from_numpy(a.view(np.int16).copy()).to(dev).view(torch.bfloat16)  # noqa: E731
+        self.A = [torch.from_numpy(h["A"]).to(dev) for _ in range(self.nsets)]
+        self.B = [torch.from_numpy(np.ascontiguousarray(h["B"][n0:n0 + self.nl])).to(dev) for _ in range(self.nsets)]
+        self.C = [torch.empty((self.M, self.nl), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
+        self.sA = torch.from_numpy(h["sA"]).to(dev)
+        self.sB = torch.from_numpy(h["sB"][n0:n0 + self.nl].copy()).to(dev)
+        self.bias = bf(h["bias"][n0:n0 + self.nl])
+        self.gathered = torch.empty((world, self.M, self.nl), dtype=torch.bfloat16, device=dev) if world > 1 else None
+        self.h_A = torch.from_numpy(h["A"]).pin_memory()
+        self.h_sA = torch.from_numpy(h["sA"]).pin_memory()
+        self.h_C = torch.empty((world, self.M, self.nl), dtype=torch.bfloat16).pin_memory()
+        self.launches_per_step = 1
+
+    def work_per_step(self):
+        return 2 * self.M * self.N * self.K  # whole job (all ranks together)
+
+    def step(self, i):
+        s = i % self.nsets
+        self.ops.MatmulW8A8(self.C[s], self.A[s], self.B[s], self.sA, self.sB, self.bias)
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.gathered, self.C[s])
+
+    def gemm_only_step(self, i):
+        s = i % self.nsets
+        self.ops.MatmulW8A8(self.C[s], self.A[s], self.B[s], self.sA, self.sB, self.bias)
+
+    def e2e_step(self, i):
+        s = i % self.nsets
+        self.A[s].copy_(self.h_A, non_blocking=True)     # this step's activations and their scales
+        self.sA.copy_(self.h_sA, non_blocking=True)
+        self.step(i)
+        if self.world > 1:
+            self.h_C.copy_(self.gathered, non_blocking=True)
+        else:
+            self.h_C[0].copy_(self.C[s], non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.M * self.K + self.M * 4, self.M * self.N * 2
+
+    def cpu_sample(self, O):
+        rows = 64
+        A = np.ascontiguousarray(self.host["A"][:rows])
+        t0 = time.perf_counter()
+        O.matmul_w8a8(A, self.host["B"], self.host["sA"][:rows].copy(), self.host["sB"], self.host["bias"])
+        dt = time.perf_counter() - t0
+        return 2 * rows * self.N * self.K / dt / 1e12, f"{rows} of {self.M} rows of A"
+
+    def check(self, O):
+        rows = 16
+        n0 = self.rank * self.nl
+        want = O.matmul_w8a8(np.ascontiguousarray(self.host["A"][:rows]), np.ascontiguousarray(self.host["B"][n0:n0 + self.nl]),
+                             self.host["sA"][:rows].copy(), self.host["sB"][n0:n0 + self.nl].copy(),
+                             self.host["bias"][n0:n0 + self.nl].copy())
+        got = self.C[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
+        self.ops.MatmulStatus()
+        return bool(np.array_equal(got, want))
+
+
+WORKLOADS = {"w8a8_cfg4": W8A8Cfg4, "antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3, "quant_scaled": QuantScaled}
+HEADLINE = "w8a8_cfg4"
 
 
 # ------------------------------------------------------------------------------------------------
@@ -346,23 +430,37 @@ def run_ours(args):
     head = None
     clocks = None
     for nm in names:
-        wl = WORKLOADS[nm](torch, ops, dev)
+        sharded = nm == "w8a8_cfg4"
+        wl = WORKLOADS[nm](torch, ops, dev, dist, world, rank) if sharded else WORKLOADS[nm](torch, ops, dev)
         is_head = nm == (args.workload if args.workload != "all" else HEADLINE)
         sampler = ClockSampler(local) if (is_head and rank == 0) else None
         sec = time_steps(torch, wl.step, args.steps, args.warmup, dist)
         per = sec / args.steps
         work = wl.work_per_step()
-        achieved = work / per / 1e9  # GB/s (each rank does the full workload: replicas)
+        if sharded:
+            achieved = work / per / 1e12          # TOPS of the whole job (strong scaling: work is split over ranks)
+            total_value = achieved
+            gsec = time_steps(torch, wl.gemm_only_step, args.steps, args.warmup, dist)
+            kern = work / world / (gsec / args.steps) / 1e12   # this rank's matmul kernel alone
+            peak = 2.0 * peaks["bf16_tflops"]
+            roof = {"bound": "tensor", "achieved": kern, "peak": peak, "unit": "TOPS", "frac": kern / peak, "traffic": None,
+                    "peak_source": "2 x %s dense bf16 cuBLAS burst (int8 runs at twice the bf16 rate; nominal 4500)"
+                                   % peaks["source"], "kernel_ms": gsec / args.steps * 1e3}
+        else:
+            achieved = work / per / 1e9           # GB/s (each rank does the full workload: replicas)
+            total_value = achieved * world
+            roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
         e2e_sec = time_steps(torch, wl.e2e_step, max(2, args.steps // 4), 2, dist)
         e2e_per = e2e_sec / max(2, args.steps // 4)
         h2d, d2h = wl.e2e_bytes()
         if sampler:
             clocks = sampler.stop()
-        rec = {"name": wl.name, "value": achieved * world, "unit": wl.unit, "ms_per_step": per * 1e3,
-               "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                            "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]},
-               "e2e": {"value": work / e2e_per / 1e9 * world, "unit": wl.unit, "h2d_bytes_per_step": h2d,
-                       "d2h_bytes_per_step": d2h},
+        e2e_value = work / e2e_per / 1e12 if sharded else work / e2e_per / 1e9 * world
+        rec = {"name": wl.name, "value": total_value, "unit": wl.unit, "ms_per_step": per * 1e3,
+               "roofline": roof,
+               "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+               "scaling": "strong" if sharded else "weak",
                "nsets": wl.nsets, "launches_per_step": wl.launches_per_step}
         if rank == 0:
             from oracle import oracle as O
@@ -380,10 +478,11 @@ def run_ours(args):
         wl, rec = head
         line = {"metric": "W8A8/MXFP4 GEMM TOPS at 1/2/4/8 B200; quant/dequant GB/s vs HBM peak",
                 "value": rec["value"], "unit": rec["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": rec["scaling"], "vs_baseline": None,
                 "dtype": wl.dtype, "data": "synthetic",
                 "config": {"workload": rec["name"], "timing": "buffers rotate over a set larger than L2 (126 MB)",
-                           "sharding": "replicas only (elementwise operators do not shard)"},
+                           "sharding": ("B column-sharded over N, NCCL all-gather of C inside the step" if rec["scaling"] == "strong"
+                                        else "replicas only (elementwise operators do not shard)")},
                 "roofline": rec["roofline"], "e2e": rec["e2e"], "gpu_launches": args.steps * rec["launches_per_step"],
                 "clocks": clocks, "workloads": results}
         if "cpu_baseline" in rec:
@@ -400,7 +499,17 @@ def run_reference(args):
         return
     from oracle import oracle as O
     nm = args.workload if args.workload != "all" else HEADLINE
-    if nm == "antiquant_cfg2":
+    unit = "GB/s"
+    if nm == "w8a8_cfg4":
+        h = gen_w8a8_cfg4()
+        rows = 128
+        A = np.ascontiguousarray(h["A"][:rows])
+        sA = h["sA"][:rows].copy()
+
+        def step():
+            O.matmul_w8a8(A, h["B"], sA, h["sB"], h["bias"])
+        work, sample, name, unit = 2 * rows * 4096 * 4096 / 1e3, f"{rows} of 4096 rows of A per step", W8A8Cfg4.name, "TOPS"
+    elif nm == "antiquant_cfg2":
         h = gen_antiquant_cfg2()
         rows, N = 1024, 11008
         w = np.ascontiguousarray(h["w"][:rows])
@@ -433,12 +542,12 @@ def run_reference(args):
     per = (time.perf_counter() - t0) / args.steps
     v = work / per / 1e9
     print(json.dumps({"impl": "reference", "metric": "W8A8/MXFP4 GEMM TOPS at 1/2/4/8 B200; quant/dequant GB/s vs HBM peak",
-                      "value": v, "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
-                      "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak",
-                      "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": name},
-                      "cpu_baseline": {"value": v, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
-                                       "sample": sample},
-                      "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "value": v, "unit": unit, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "strong" if unit == "TOPS" else "weak",
+                      "vs_baseline": None, "dtype": "int8" if unit == "TOPS" else "f32", "data": "synthetic",
+                      "config": {"workload": name},
+                      "cpu_baseline": {"value": v, "unit": unit, "cores": O.num_threads(), "kind": "port", "sample": sample},
+                      "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                       "note": "CPU restatement of the reference operators (oracle/); the reference's own CPU-debug "
                               "build needs the closed tikicpulib"}))
 

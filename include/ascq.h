@@ -192,6 +192,31 @@ ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* src, ascq_dty
                            const ascq_antiquant_param* param, void* stream);
 
 /*
+ * W8A8 matmul with fused dequant epilogue (AscendC::Matmul<int8,int8,int32> +
+ * AscendDequant per-channel x per-token; include/adv_api/matmul/matmul.h:79-398,
+ * impl/adv_api/detail/matmul/stage/compute/mmad_compute.h:83, epilogue order
+ * examples/.../quant_group_matmul_custom.asc:425-454):
+ *   acc[m,n] = sum_k A[m,k] * B[n,k]                       (int32, exact)
+ *   C[m,n]   = bf16_rint( (float(acc) * sB[n]) * sA[m] + float(bias[n]) )
+ * A [M,K] row-major int8; B [N,K] row-major ("K-major", SetTensorB(..., isTransposeB=true)).
+ * sA fp32 [M] or NULL (=1), sB fp32 [N] or NULL (=1), bias bf16 [N] or NULL.  The bf16 bias added
+ * after the dequantisation is this library's definition (the reference's bias is int32, added
+ * before it).  ldc = row stride of C in elements (>= N).  accDump (optional) receives the raw
+ * int32 accumulators, [M,N] row-major; C may be NULL when only accDump is wanted.
+ * K % 16 == 0; A, B 16-byte aligned (TMA).
+ */
+ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int8_t* B_nk, const float* sA_m,
+                             const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc,
+                             int32_t* accDump, void* stream);
+
+/*
+ * Synchronises `stream`, then reads and clears the status word the matmul kernels keep on the
+ * current device.  ASCQ_ERR_TIMEOUT when a kernel gave up a bounded wait (its output is then
+ * undefined); no counterpart in the reference, whose kernels cannot report.
+ */
+ascq_status ascq_matmul_status(void* stream);
+
+/*
  * Host-side temporary-buffer size queries, kept for API parity (the CUDA kernels need no
  * temporary buffer).  Formulas: impl/adv_api/tiling/quantization/ascend_quant_tiling_impl.cpp:31-69,
  * ascend_dequant_tiling_impl.cpp:31-106, ascend_antiquant_tiling_impl.cpp:71-181.

@@ -1,0 +1,99 @@
+"""GPU parity of the W8A8 matmul: int32 accumulators bit-exact, bf16 epilogue bit-exact (same fp32 operation
+order as the oracle), against the CPU oracle and, at full size, against an exact integer reference on the GPU."""
+import numpy as np
+import pytest
+import torch
+
+from asc_devkit_b200 import ops
+from oracle import oracle as O
+from tests.gpu_util import DEV, assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(M, N, K, seed):
+    rng = np.random.default_rng(seed)
+    A = np.clip(np.rint(rng.normal(0, 30, (M, K))), -127, 127).astype(np.int8)
+    B = rng.integers(-127, 128, (N, K)).astype(np.int8)
+    sA = rng.uniform(0.005, 0.02, M).astype(np.float32)
+    sB = rng.uniform(0.001, 0.01, N).astype(np.float32)
+    bias = O.f32_to_bf16_bits(rng.normal(0, 0.1, N).astype(np.float32))
+    return A, B, sA, sB, bias
+
+
+def run(A, B, sA=None, sB=None, bias=None, ldc=None, want_acc=True):
+    M, K = A.shape
+    N = B.shape[0]
+    ldc = N if ldc is None else ldc
+    dC = torch.full((M, ldc), -1.0, dtype=torch.bfloat16, device=DEV)
+    dAcc = torch.full((M, N), 123456789, dtype=torch.int32, device=DEV) if want_acc else None
+    t = lambda a: None if a is None else torch.from_numpy(a).to(DEV)  # noqa: E731
+    dbias = None if bias is None else torch.from_numpy(bias.view(np.int16)).to(DEV).view(torch.bfloat16)
+    ops.MatmulW8A8(dC[:, :N] if ldc != N else dC, t(A), t(B), t(sA), t(sB), dbias, dAcc)
+    ops.MatmulStatus()
+    return dC.view(torch.int16).cpu().numpy().view(np.uint16), (dAcc.cpu().numpy() if want_acc else None)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (128, 128, 256), (256, 512, 512), (384, 256, 1024),
+                                   (100, 200, 144), (1, 8, 16), (129, 257, 272), (512, 1024, 4096), (2048, 384, 640)])
+def test_parity_small(M, N, K):
+    A, B, sA, sB, bias = make_case(M, N, K, M * 31 + N * 7 + K)
+    want_C, want_acc = O.matmul_w8a8(A, B, sA, sB, bias, want_acc=True)
+    got_C, got_acc = run(A, B, sA, sB, bias)
+    assert_bits_equal(got_acc, want_acc, "int32 accumulators")
+    assert_bits_equal(got_C, want_C, "bf16 epilogue")
+
+
+def test_extreme_values_accumulate_exactly():
+    # +-127 everywhere: |acc| = K * 16129, the largest magnitude the int32 accumulator sees for this K
+    M, N, K = 128, 256, 8192
+    A = np.full((M, K), 127, np.int8)
+    B = np.full((N, K), -127, np.int8)
+    B[::2] = 127
+    _, acc = run(A, B)
+    want = np.where(np.arange(N) % 2 == 0, K * 16129, -K * 16129).astype(np.int32)
+    assert np.array_equal(acc, np.broadcast_to(want, (M, N)))
+
+
+def test_optional_operands_and_row_stride():
+    A, B, sA, sB, bias = make_case(192, 320, 256, 5)
+    for kw in (dict(), dict(sA=sA), dict(sB=sB), dict(bias=bias), dict(sA=sA, sB=sB)):
+        want = O.matmul_w8a8(A, B, kw.get("sA"), kw.get("sB"), kw.get("bias"))
+        got, _ = run(A, B, kw.get("sA"), kw.get("sB"), kw.get("bias"))
+        assert_bits_equal(got, want, f"operands {sorted(kw)}")
+    # ldc > N: the columns beyond N keep their previous contents
+    ldc = 328
+    got, _ = run(A, B, sA, sB, bias, ldc=ldc)
+    want = O.matmul_w8a8(A, B, sA, sB, bias, ldc=ldc)
+    assert_bits_equal(got[:, :320], want[:, :320], "strided C")
+    assert (got[:, 320:] == np.array([-1.0], np.float32).view(np.uint32)[0] >> 16).all()
+
+
+def test_invalid_arguments():
+    a = torch.zeros((16, 24), dtype=torch.int8, device=DEV)
+    b = torch.zeros((16, 24), dtype=torch.int8, device=DEV)
+    c = torch.zeros((16, 16), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.AscqError) as e:
+        ops.MatmulW8A8(c, a, b)
+    assert "multiple of 16" in e.value.message
+
+
+def test_cfg4_full_size_exact():
+    # BASELINE config 4 at full size; the integer reference is computed on the GPU in fp64-free exact arithmetic:
+    # int8 products summed in float32 blocks of K=256 stay below 2^24 and are therefore exact.
+    M = N = K = 4096
+    A, B, sA, sB, bias = make_case(M, N, K, 20251125 + 4)
+    dA, dB = torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV)
+    acc = torch.zeros((M, N), dtype=torch.int32, device=DEV)
+    for k0 in range(0, K, 256):
+        part = dA[:, k0:k0 + 256].float() @ dB[:, k0:k0 + 256].float().T   # |sum| <= 256*127*127 < 2^24: exact
+        acc += part.to(torch.int32)
+    got_C, got_acc = run(A, B, sA, sB, bias)
+    assert np.array_equal(got_acc, acc.cpu().numpy())
+    # epilogue on the exact accumulators with the oracle's scalar order, vectorised in numpy
+    f = acc.cpu().numpy().astype(np.float32)
+    f = (f * sB[None, :]) * sA[:, None] + O.bf16_bits_to_f32(bias)[None, :]
+    assert_bits_equal(got_C, O.f32_to_bf16_bits(f), "cfg4 epilogue")
+    # and a row block through the oracle itself
+    want_C = O.matmul_w8a8(np.ascontiguousarray(A[:64]), B, sA[:64].copy(), sB, bias)
+    assert_bits_equal(got_C[:64], want_C, "cfg4 rows 0..63 vs oracle")
