@@ -8,6 +8,8 @@
 
 #include "../../include/ascq.h"
 
+struct CUstream_st;
+
 namespace ascq {
 
 // Records a printf-style message in the thread-local slot behind ascq_last_error() and returns `s`.
@@ -25,6 +27,9 @@ inline int dtype_size(ascq_dtype t)
     }
     return 0;
 }
+// Defined in gemm_mxfp4.cu: reads and clears that kernel's device status word (synchronises the stream).
+ascq_status mxfp4_read_status(::CUstream_st* stream);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace ascq

@@ -1,0 +1,459 @@
+// ascq_group_matmul_mxfp4: grouped matmul on MX-FP4 operands (E2M1 values, one E8M0 scale per 32 K-elements)
+// with tcgen05.mma kind::mxf4.block_scale, fp32 accumulation in tensor memory and a bf16 epilogue.
+//
+// Data layout in HBM (caller): A [sumM, K/2] bytes, sA [sumM, K/32]; B [G, N, K/2] bytes, sB [G, N, K/32]
+// (both operands K-major, two E2M1 codes per byte, element 2i in the low nibble); C [sumM, N] bf16.
+//
+// Scratch (caller-provided workspace):
+//   tile table   one entry per 128-row tile of A: first row, valid rows, group
+//   packed sA    per A tile and per 256-element k-block, 1 KiB in the order tcgen05.cp wants:
+//                two 512-byte chunks (K = 128 elements each), byte (l*16 + c*4 + j) = scale of row 32c+l,
+//                k-group j of the chunk
+//   packed sB    per (group, 128-row tile of N), same chunk format
+// A repack kernel writes the packed scales once per call; the matmul kernel then moves them with one bulk
+// copy per operand per k-block and hands them to tensor memory with tcgen05.cp.32x128b.warpx4.
+//
+// Matmul kernel: persistent CTAs over (A tile, N tile); warp 0 TMA producer, warp 1 MMA issuer, warps 2..5
+// epilogue.  Per k-block: A 128x128 B and B BNx128 B tiles (128B swizzle) + scale chunks into one of kStages
+// shared-memory stages; four MMAs of K = 64.  Rows of a tile that belong to the next group are computed and
+// dropped at the store.
+//
+// Roofline: dense FP4 tensor throughput; 2*sumM*N*K flops per call.
+#include <cuda_bf16.h>
+
+#include <vector>
+
+#include "ascq_internal.h"
+#include "numerics.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_host.h"
+
+namespace ascq {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;
+constexpr int kBKBytes = 128;   // 256 E2M1 elements per k-block row: one 128B swizzle atom
+constexpr int kBKElems = 256;
+constexpr int kChunkBytes = 512;  // packed scales of 128 rows x 128 K-elements
+constexpr int kThreads = 192;
+
+__device__ int g_mxfp4_status = 0;
+
+struct TileInfo {
+    int rowStart;   // first row of the tile in A / C
+    int rowsValid;  // rows of this tile that belong to its group
+    int group;
+    int pad;
+};
+
+template <int BN> struct Cfg {
+    static constexpr int kAccStages = (BN == 256) ? 1 : 2;
+    static constexpr int kABytes = kBM * kBKBytes;
+    static constexpr int kBBytes = BN * kBKBytes;
+    static constexpr int kSfaBytes = 2 * kChunkBytes;
+    static constexpr int kSfbBytes = (BN / 128) * 2 * kChunkBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kSfaCols = 8;               // 2 chunks x 4 columns
+    static constexpr int kSfbCols = 2 * (BN / 32);   // 2 chunks x N/32 columns
+    static constexpr int kAccCols = kAccStages * BN;
+    static constexpr int kTmemCols = 512;
+    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
+    static_assert(kAccCols + kSfaCols + kSfbCols <= 512, "tensor memory budget");
+};
+
+struct Params {
+    __nv_bfloat16* C;
+    const TileInfo* tiles;
+    const uint8_t* sfaPacked;
+    const uint8_t* sfbPacked;
+    int numTilesM, tilesN, N, K, kBlocks, nTilesPerGroup128;  // nTilesPerGroup128 = ceil(N/128)
+};
+
+// ---- scale repack ----------------------------------------------------------------------------------
+// One thread per 32-bit word of the packed layout.  `rowBase(tile)` comes from the tile table (A) or is
+// group*N + tile128*128 (B); rows past `rowLimit(tile)` read as zero.
+__global__ void __launch_bounds__(256)
+repack_sf_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, const TileInfo* __restrict__ tiles, int numTiles,
+                 int kChunks, int kChunksValid, int sfRowBytes, int N, int tilesPerGroup, long long totalRows)
+{
+    const long long word = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long total = static_cast<long long>(numTiles) * kChunks * (kChunkBytes / 4);
+    if (word >= total) return;
+    const int w = static_cast<int>(word % (kChunkBytes / 4));
+    const long long tc = word / (kChunkBytes / 4);
+    const int chunk = static_cast<int>(tc % kChunks);
+    const int tile = static_cast<int>(tc / kChunks);
+    const int l = w >> 2, c = w & 3;
+    const int r = c * 32 + l;
+    long long row;
+    bool valid;
+    if (tiles != nullptr) {  // A: tiles follow the group boundaries
+        row = static_cast<long long>(tiles[tile].rowStart) + r;
+        valid = row < totalRows;
+    } else {  // B: 128-row tiles inside each group's [N, K] block
+        const int g = tile / tilesPerGroup, t = tile % tilesPerGroup;
+        const int n = t * 128 + r;
+        row = static_cast<long long>(g) * N + n;
+        valid = n < N;
+    }
+    uint32_t v = 0x7F7F7F7Fu;  // scale 1.0 where there is no data (the operand bytes there are zero)
+    if (valid && chunk < kChunksValid) v = *reinterpret_cast<const uint32_t*>(src + row * sfRowBytes + chunk * 4);
+    reinterpret_cast<uint32_t*>(dst)[word] = v;
+}
+
+// ---- matmul ----------------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
+{
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+    uint64_t* fullBar = bars;
+    uint64_t* emptyBar = bars + C::kStages;
+    uint64_t* tmemFull = bars + 2 * C::kStages;
+    uint64_t* tmemEmpty = tmemFull + 2;
+    uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
+    volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int numTiles = p.numTilesM * p.tilesN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&fullBar[s], 1);
+            mbar_init(&emptyBar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmemFull[a], 1);
+            mbar_init(&tmemEmpty[a], 4);
+        }
+        *abortFlag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tmapA);
+        prefetch_tensormap(&tmapB);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmemBaseSlot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmemBase = *tmemBaseSlot;
+    const uint32_t sfaCol = tmemBase + C::kAccCols;
+    const uint32_t sfbCol = sfaCol + C::kSfaCols;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x) {
+                const int mt = tile % p.numTilesM, nt = tile / p.numTilesM;
+                const TileInfo ti = p.tiles[mt];
+                const int n0 = nt * BN;
+                const uint8_t* sfa = p.sfaPacked + static_cast<size_t>(mt) * p.kBlocks * C::kSfaBytes;
+                const uint8_t* sfb = p.sfbPacked +
+                                     (static_cast<size_t>(ti.group) * p.nTilesPerGroup128 + n0 / 128) * p.kBlocks * 2 * kChunkBytes;
+                for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!(ok = mbar_wait_bounded(&emptyBar[s], ph ^ 1, abortFlag))) break;
+                    uint8_t* st = smem + s * C::kStageBytes;
+                    mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
+                    tma_load_2d(st, &tmapA, &fullBar[s], kb * kBKBytes, ti.rowStart);
+                    tma_load_2d(st + C::kABytes, &tmapB, &fullBar[s], kb * kBKBytes, ti.group * p.N + n0);
+                    bulk_load(st + C::kABytes + C::kBBytes, sfa + static_cast<size_t>(kb) * C::kSfaBytes, C::kSfaBytes, &fullBar[s]);
+#pragma unroll
+                    for (int t = 0; t < BN / 128; ++t)
+                        bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2 * kChunkBytes,
+                                  sfb + (static_cast<size_t>(t) * p.kBlocks + kb) * 2 * kChunkBytes, 2 * kChunkBytes, &fullBar[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+                const int acc = local % C::kAccStages;
+                const uint32_t accPh = (local / C::kAccStages) & 1;
+                if (!(ok = mbar_wait_bounded(&tmemEmpty[acc], accPh ^ 1, abortFlag))) break;
+                tc_fence_after();
+                const uint32_t tmemD = tmemBase + acc * BN;
+                for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!(ok = mbar_wait_bounded(&fullBar[s], ph, abortFlag))) break;
+                    tc_fence_after();
+                    const uint32_t base = smem_u32(smem + s * C::kStageBytes);
+                    const uint32_t sfaSmem = base + C::kABytes + C::kBBytes;
+                    const uint32_t sfbSmem = sfaSmem + C::kSfaBytes;
+                    // scales: shared -> tensor memory.  Chunk q of A -> columns sfaCol + 4q; chunk q of the
+                    // 128-row tile t of B -> columns sfbCol + q*(BN/32) + 4t.
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        tc_cp_32x128b_warpx4(sfaCol + 4 * q, smem_desc_noswizzle(sfaSmem + q * kChunkBytes, 0, 128));
+#pragma unroll
+                        for (int t = 0; t < BN / 128; ++t)
+                            tc_cp_32x128b_warpx4(sfbCol + q * (BN / 32) + 4 * t,
+                                                 smem_desc_noswizzle(sfbSmem + (t * 2 + q) * kChunkBytes, 0, 128));
+                    }
+                    const uint64_t descA = smem_desc_sw128(base);
+                    const uint64_t descB = smem_desc_sw128(base + C::kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // K = 64 per MMA = 32 bytes: chunk k/2, scale bytes (k%2)*2 and (k%2)*2+1 of each column
+                        const uint32_t sfId = (k & 1) * 2;
+                        mma_mxf4(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kBM, BN, sfId, sfId), (kb | k) != 0,
+                                 sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
+                    }
+                    tc_commit(&emptyBar[s]);
+                }
+                if (ok) tc_commit(&tmemFull[acc]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+            const int acc = local % C::kAccStages;
+            const uint32_t accPh = (local / C::kAccStages) & 1;
+            const int mt = tile % p.numTilesM, nt = tile / p.numTilesM;
+            const TileInfo ti = p.tiles[mt];
+            const int n0 = nt * BN;
+            if (!(ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag))) break;
+            tc_fence_after();
+            const int rIn = q * 32 + lane;
+            const bool rowOk = rIn < ti.rowsValid;
+            __nv_bfloat16* crow = p.C + static_cast<size_t>(ti.rowStart + rIn) * p.N + n0;
+            const uint32_t taddr = tmemBase + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+            const bool vecStore = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const int n = n0 + c * 32;
+                if (rowOk && n < p.N) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2_sat(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    if (n + 32 <= p.N && vecStore) {
+                        uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n + j < p.N)
+                                crow[c * 32 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[j >> 1] >> ((j & 1) * 16)));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmemEmpty[acc]);
+        }
+    }
+
+    __syncthreads();
+    if (*abortFlag) {
+        if (threadIdx.x == 0) atomicExch(&g_mxfp4_status, 1);
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {}
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmemBase, C::kTmemCols);
+    }
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Layout {
+    size_t tileOff, sfaOff, sfbOff, total;
+    int tilesM, kBlocks, nTiles128;
+};
+Layout make_layout(int64_t sumM, int G, int K, int N)
+{
+    Layout L{};
+    L.tilesM = static_cast<int>((sumM + kBM - 1) / kBM + G);  // upper bound: every group may add one partial tile
+    L.kBlocks = (K + kBKElems - 1) / kBKElems;
+    L.nTiles128 = 2 * ((N + 255) / 256);  // even, so a 256-wide N tile always finds both of its 128-row halves
+    L.tileOff = 0;
+    L.sfaOff = align_up(static_cast<size_t>(L.tilesM) * sizeof(TileInfo), 256);
+    L.sfbOff = L.sfaOff + align_up(static_cast<size_t>(L.tilesM) * L.kBlocks * 2 * kChunkBytes, 256);
+    L.total = L.sfbOff + align_up(static_cast<size_t>(G) * L.nTiles128 * L.kBlocks * 2 * kChunkBytes, 256);
+    return L;
+}
+
+template <int BN>
+ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
+{
+    using C = Cfg<BN>;
+    static bool attrSet = false;
+    if (!attrSet) {
+        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(C::kSmemBytes)));
+        attrSet = true;
+    }
+    p.tilesN = (p.N + BN - 1) / BN;
+    const int tiles = p.numTilesM * p.tilesN;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    mxfp4_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}
+
+}  // namespace
+}  // namespace ascq
+
+using namespace ascq;
+
+extern "C" size_t ascq_group_matmul_mxfp4_workspace_size(int64_t sumM, int G, int K, int N)
+{
+    if (sumM < 0 || G <= 0 || K <= 0 || N <= 0) return 0;
+    return make_layout(sumM, G, K, N).total;
+}
+
+extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
+                                               const uint8_t* B_fp4, const uint8_t* sB_e8m0, const int64_t* groupList_host,
+                                               int G, int K, int N, void* workspace, size_t workspaceBytes, void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!C_bf16 || !A_fp4 || !sA_e8m0 || !B_fp4 || !sB_e8m0 || !groupList_host)
+        return fail(ASCQ_ERR_INVALID_ARG, "C, A, sA, B, sB and groupList must not be NULL");
+    if (G <= 0 || N <= 0 || K <= 0) return fail(ASCQ_ERR_INVALID_ARG, "G, N, K must be positive");
+    if (K % 128 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of 128", K);
+    if (!aligned16(A_fp4) || !aligned16(B_fp4)) return fail(ASCQ_ERR_ALIGNMENT, "A and B must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(sA_e8m0) & 3u) || (reinterpret_cast<uintptr_t>(sB_e8m0) & 3u))
+        return fail(ASCQ_ERR_ALIGNMENT, "scale tensors must be 4-byte aligned");
+    int64_t sumM = 0;
+    for (int g = 0; g < G; ++g) {
+        if (groupList_host[g] < 0) return fail(ASCQ_ERR_INVALID_ARG, "groupList[%d] is negative", g);
+        sumM += groupList_host[g];
+    }
+    if (sumM == 0) return ASCQ_OK;
+    if (sumM > 0x7FFFFFFF - 256 || static_cast<int64_t>(G) * N > 0x7FFFFFFF)
+        return fail(ASCQ_ERR_INVALID_ARG, "problem too large for 32-bit row indices");
+    const Layout L = make_layout(sumM, G, K, N);
+    if (!workspace || workspaceBytes < L.total)
+        return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", L.total, workspaceBytes);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(ASCQ_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+
+    // tile table: zero-row groups are skipped (quant_group_matmul_custom.asc:265-267)
+    std::vector<TileInfo> tiles;
+    tiles.reserve(L.tilesM);
+    int64_t start = 0;
+    for (int g = 0; g < G; ++g) {
+        const int64_t mg = groupList_host[g];
+        for (int64_t r = 0; r < mg; r += kBM) {
+            TileInfo t{static_cast<int>(start + r), static_cast<int>(mg - r < kBM ? mg - r : kBM), g, 0};
+            tiles.push_back(t);
+        }
+        start += mg;
+    }
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    ASCQ_CUDA_CHECK(cudaMemcpyAsync(ws + L.tileOff, tiles.data(), tiles.size() * sizeof(TileInfo), cudaMemcpyHostToDevice, st));
+    // the copy above stages pageable memory before returning, so `tiles` may go out of scope afterwards
+
+    const int numTilesM = static_cast<int>(tiles.size());
+    const int kChunks = L.kBlocks * 2;
+    const int sfRowBytes = K / 32;
+    {
+        const long long words = static_cast<long long>(numTilesM) * kChunks * (kChunkBytes / 4);
+        repack_sf_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, st>>>(
+            ws + L.sfaOff, sA_e8m0, reinterpret_cast<const TileInfo*>(ws + L.tileOff), numTilesM, kChunks, K / 128, sfRowBytes, N, 0, sumM);
+        const long long wordsB = static_cast<long long>(G) * L.nTiles128 * kChunks * (kChunkBytes / 4);
+        repack_sf_kernel<<<static_cast<unsigned>((wordsB + 255) / 256), 256, 0, st>>>(
+            ws + L.sfbOff, sB_e8m0, nullptr, G * L.nTiles128, kChunks, K / 128, sfRowBytes, N, L.nTiles128, 0);
+        ASCQ_CUDA_CHECK(cudaGetLastError());
+    }
+
+    Params p{};
+    p.C = static_cast<__nv_bfloat16*>(C_bf16);
+    p.tiles = reinterpret_cast<const TileInfo*>(ws + L.tileOff);
+    p.sfaPacked = ws + L.sfaOff;
+    p.sfbPacked = ws + L.sfbOff;
+    p.numTilesM = numTilesM;
+    p.N = N; p.K = K; p.kBlocks = L.kBlocks; p.nTilesPerGroup128 = L.nTiles128;
+
+    const bool wide = N >= 256;
+    CUtensorMap ta, tb;
+    ascq_status rc = make_tmap_u8(&ta, A_fp4, static_cast<uint64_t>(sumM), static_cast<uint64_t>(K / 2), kBM);
+    if (rc != ASCQ_OK) return rc;
+    rc = make_tmap_u8(&tb, B_fp4, static_cast<uint64_t>(G) * N, static_cast<uint64_t>(K / 2), wide ? 256 : 128);
+    if (rc != ASCQ_OK) return rc;
+    return wide ? launch<256>(ta, tb, p, st) : launch<128>(ta, tb, p, st);
+}
+
+// Reads and clears this translation unit's device status word (used by ascq_matmul_status).
+ascq_status ascq::mxfp4_read_status(cudaStream_t st)
+{
+    int v = 0, zero = 0;
+    ASCQ_CUDA_CHECK(cudaMemcpyFromSymbolAsync(&v, g_mxfp4_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+    ASCQ_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (v != 0) {
+        ASCQ_CUDA_CHECK(cudaMemcpyToSymbolAsync(g_mxfp4_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+        return fail(ASCQ_ERR_TIMEOUT, "a bounded wait inside the MX-FP4 matmul kernel expired (status %d)", v);
+    }
+    return ASCQ_OK;
+}
+
+// ---- reference layout adapters -----------------------------------------------------------------------
+namespace ascq {
+namespace {
+// B [K, N/2] bytes (pairs along N) -> B [N, K/2] bytes (pairs along K).  One thread per output byte.
+__global__ void __launch_bounds__(256) repack_b_kn_to_nk_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, int K, int N)
+{
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long total = static_cast<long long>(N) * (K / 2);
+    if (i >= total) return;
+    const int n = static_cast<int>(i / (K / 2));
+    const int k = static_cast<int>(i % (K / 2)) * 2;
+    const size_t rowBytes = static_cast<size_t>(N) / 2;
+    const uint8_t b0 = src[static_cast<size_t>(k) * rowBytes + n / 2];
+    const uint8_t b1 = src[static_cast<size_t>(k + 1) * rowBytes + n / 2];
+    const uint32_t lo = (n & 1) ? (b0 >> 4) : (b0 & 0x0Fu);
+    const uint32_t hi = (n & 1) ? (b1 >> 4) : (b1 & 0x0Fu);
+    dst[i] = static_cast<uint8_t>(lo | (hi << 4));
+}
+// scaleB stored [sK/2, N, 2] -> [N, sK].
+__global__ void __launch_bounds__(256) repack_scale_b_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, int sK, int N)
+{
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<long long>(N) * sK) return;
+    const int n = static_cast<int>(i / sK), sk = static_cast<int>(i % sK);
+    dst[i] = src[(static_cast<size_t>(sk / 2) * N + n) * 2 + (sk & 1)];
+}
+}  // namespace
+}  // namespace ascq
+
+extern "C" ascq_status ascq_mx_repack_b_kn_to_nk(uint8_t* B_nk, const uint8_t* B_kn, int K, int N, void* stream)
+{
+    if (!B_nk || !B_kn) return fail(ASCQ_ERR_INVALID_ARG, "null pointer");
+    if (K <= 0 || N <= 0 || K % 2 || N % 2) return fail(ASCQ_ERR_INVALID_ARG, "K and N must be positive and even");
+    const long long total = static_cast<long long>(N) * (K / 2);
+    repack_b_kn_to_nk_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(B_nk, B_kn, K, N);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}
+
+extern "C" ascq_status ascq_mx_repack_scale_b(uint8_t* sB_nk, const uint8_t* sB_ref, int sK, int N, void* stream)
+{
+    if (!sB_nk || !sB_ref) return fail(ASCQ_ERR_INVALID_ARG, "null pointer");
+    if (sK <= 0 || N <= 0 || sK % 2) return fail(ASCQ_ERR_INVALID_ARG, "sK must be positive and even, N positive");
+    const long long total = static_cast<long long>(N) * sK;
+    repack_scale_b_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(sB_nk, sB_ref, sK, N);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}

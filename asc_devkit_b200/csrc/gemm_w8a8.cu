@@ -19,6 +19,7 @@
 #include "ascq_internal.h"
 #include "numerics.cuh"
 #include "sm100_ptx.cuh"
+#include "tma_host.h"
 
 namespace ascq {
 namespace {
@@ -231,49 +232,6 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 }
 
 // ---- host side -------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            sym = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(sym);
-    }();
-    return fn;
-}
-
-// uint8 [rows, colsBytes] row-major tensor map with a [boxRows, 128-byte] box and 128B swizzle.
-ascq_status make_tmap_u8(CUtensorMap* out, const void* base, uint64_t rows, uint64_t colsBytes, uint32_t boxRows)
-{
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-    const cuuint64_t dims[2] = {colsBytes, rows};
-    const cuuint64_t strides[1] = {colsBytes};
-    const cuuint32_t box[2] = {128, boxRows};
-    const cuuint32_t elemStrides[2] = {1, 1};
-    const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elemStrides,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(rc));
-    return ASCQ_OK;
-}
-
-int sm_count()
-{
-    static int n = [] {
-        int dev = 0, v = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-        return v;
-    }();
-    return n;
-}
-
 template <int BN> ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
 {
     using C = Cfg<BN>;
@@ -339,7 +297,7 @@ extern "C" ascq_status ascq_matmul_status(void* stream)
     ASCQ_CUDA_CHECK(cudaStreamSynchronize(st));
     if (v != 0) {
         ASCQ_CUDA_CHECK(cudaMemcpyToSymbolAsync(g_w8a8_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
-        return fail(ASCQ_ERR_TIMEOUT, "a bounded wait inside the matmul kernel expired (status %d)", v);
+        return fail(ASCQ_ERR_TIMEOUT, "a bounded wait inside the W8A8 matmul kernel expired (status %d)", v);
     }
-    return ASCQ_OK;
+    return mxfp4_read_status(st);
 }

@@ -8,6 +8,7 @@ arguments.  Each function forwards device pointers to the C ABI (``include/ascq.
 from __future__ import annotations
 
 import ctypes as C
+from ctypes import c_int64 as C_int64
 from dataclasses import dataclass
 from typing import Optional
 
@@ -178,6 +179,35 @@ def MatmulW8A8(C: Optional[torch.Tensor], A: torch.Tensor, B_nk: torch.Tensor, s
     L.check(L.lib().ascq_matmul_w8a8(cptr, _ptr(A), _ptr(B_nk), _ptr(scaleA), _ptr(scaleB), _ptr(bias), M, N, K, ldc,
                                      _ptr(accDump), _stream(stream)))
     return C
+
+
+def GroupMatmulMxfp4Workspace(sumM: int, G: int, K: int, N: int) -> int:
+    return int(L.lib().ascq_group_matmul_mxfp4_workspace_size(sumM, G, K, N))
+
+
+def GroupMatmulMxfp4(C: torch.Tensor, A: torch.Tensor, scaleA: torch.Tensor, B: torch.Tensor, scaleB: torch.Tensor,
+                     groupList, K: int, N: int, workspace: Optional[torch.Tensor] = None, stream=None):
+    """MX-FP4 grouped matmul (``ascq_group_matmul_mxfp4``).  A [sumM, K/2] uint8, scaleA [sumM, K/32] uint8 (e8m0),
+    B [G, N, K/2] uint8, scaleB [G, N, K/32] uint8, groupList = rows per group (host sequence), C [sumM, N] bf16.
+    ``workspace`` (uint8, CUDA) is allocated here when not given; the C entry point itself never allocates."""
+    gl = (C_int64 * len(groupList))(*[int(v) for v in groupList])
+    G = len(groupList)
+    need = GroupMatmulMxfp4Workspace(int(sum(int(v) for v in groupList)), G, K, N)
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=C.device)
+    L.check(L.lib().ascq_group_matmul_mxfp4(_ptr(C), _ptr(A), _ptr(scaleA), _ptr(B), _ptr(scaleB), gl, G, K, N,
+                                            _ptr(workspace), workspace.numel(), _stream(stream)))
+    return C
+
+
+def MxRepackBKnToNk(B_nk: torch.Tensor, B_kn: torch.Tensor, K: int, N: int, stream=None):
+    L.check(L.lib().ascq_mx_repack_b_kn_to_nk(_ptr(B_nk), _ptr(B_kn), K, N, _stream(stream)))
+    return B_nk
+
+
+def MxRepackScaleB(sB_nk: torch.Tensor, sB_ref: torch.Tensor, sK: int, N: int, stream=None):
+    L.check(L.lib().ascq_mx_repack_scale_b(_ptr(sB_nk), _ptr(sB_ref), sK, N, _stream(stream)))
+    return sB_nk
 
 
 def MatmulStatus(stream=None):

@@ -210,6 +210,31 @@ ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int8_t* B_nk, 
                              int32_t* accDump, void* stream);
 
 /*
+ * MX-FP4 grouped matmul (MatmulWithScalePolicy, impl/adv_api/detail/matmul/mx_matmul_impl.h:29-181;
+ * grouping examples/.../quant_group_matmul_custom.asc:257-289):
+ *   for each group g with rows [s_g, s_g + groupList[g]):
+ *     C[r, n] = bf16( sum_k (A[r,k] * 2^(sA[r,k/32]-127)) * (B[g,n,k] * 2^(sB[g,n,k/32]-127)) )
+ * A  fp4x2 [sumM, K/2] bytes, sA e8m0 [sumM, K/32];
+ * B  fp4x2 [G, N, K/2] bytes (K-major), sB e8m0 [G, N, K/32];
+ * groupList int64 [G] on the HOST = rows per group (not cumulative); zero-row groups are skipped.
+ * C bf16 [sumM, N].  fp32 accumulation.  K % 128 == 0, N % 8 == 0.
+ * workspace: device scratch of at least ascq_group_matmul_mxfp4_workspace_size() bytes, 256-byte
+ * aligned, private to this call until the stream reaches the end of it.
+ */
+ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
+                                    const uint8_t* B_fp4, const uint8_t* sB_e8m0,
+                                    const int64_t* groupList_host, int G, int K, int N,
+                                    void* workspace, size_t workspaceBytes, void* stream);
+size_t ascq_group_matmul_mxfp4_workspace_size(int64_t sumM, int G, int K, int N);
+
+/* Reference layout adapters for the MX matmul (one-off weight preparation):
+ * B given as [K, N] fp4 pairs along N and scaleB stored [sK/2, N, 2]
+ * (examples/.../matmul_mxfp4_high_performance/README_en.md:64-67, scripts/gen_data.py:65)
+ * are rewritten into the K-major form ascq_group_matmul_mxfp4 takes. */
+ascq_status ascq_mx_repack_b_kn_to_nk(uint8_t* B_nk, const uint8_t* B_kn, int K, int N, void* stream);
+ascq_status ascq_mx_repack_scale_b(uint8_t* sB_nk, const uint8_t* sB_ref, int sK, int N, void* stream);
+
+/*
  * Synchronises `stream`, then reads and clears the status word the matmul kernels keep on the
  * current device.  ASCQ_ERR_TIMEOUT when a kernel gave up a bounded wait (its output is then
  * undefined); no counterpart in the reference, whose kernels cannot report.

@@ -1,0 +1,137 @@
+"""GPU parity of the MX-FP4 grouped matmul against the CPU oracle (fp64 accumulation, the reference's golden
+semantics).  The GPU accumulates in fp32, so general inputs are compared with rtol 1e-2 (plus a small absolute
+term for cancellations); inputs whose partial sums are exactly representable must match bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from asc_devkit_b200 import ops
+from oracle import oracle as O
+from tests.gpu_util import DEV, assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(groups, N, K, seed, exp_span=4, codes=None):
+    rng = np.random.default_rng(seed)
+    sumM, G = int(sum(groups)), len(groups)
+    if codes is None:
+        A = rng.integers(0, 256, (sumM, K // 2)).astype(np.uint8)
+        B = rng.integers(0, 256, (G, N, K // 2)).astype(np.uint8)
+    else:
+        pick = lambda shape: (rng.choice(codes, shape) | (rng.choice(codes, shape) << 4)).astype(np.uint8)  # noqa: E731
+        A, B = pick((sumM, K // 2)), pick((G, N, K // 2))
+    sA = (127 + rng.integers(-exp_span, exp_span + 1, (sumM, K // 32))).astype(np.uint8)
+    sB = (127 + rng.integers(-exp_span, exp_span + 1, (G, N, K // 32))).astype(np.uint8)
+    return A, sA, B, sB
+
+
+def run(A, sA, B, sB, groups, K, N):
+    sumM = int(sum(groups))
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    dC = torch.full((max(sumM, 1), N), -1.0, dtype=torch.bfloat16, device=DEV)
+    ops.GroupMatmulMxfp4(dC, t(A), t(sA), t(B), t(sB), groups, K, N)
+    ops.MatmulStatus()
+    return dC.view(torch.int16).cpu().numpy().view(np.uint16)[:sumM]
+
+
+def check_close(got_bits, want_f32, what):
+    got = O.bf16_bits_to_f32(got_bits).astype(np.float64)
+    want = want_f32.astype(np.float64)
+    tol = 1e-2 * np.abs(want) + 1e-3 * np.abs(want).max()
+    bad = np.abs(got - want) > tol
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside rtol 1e-2; worst {np.abs(got - want).max()}"
+
+
+@pytest.mark.parametrize("groups,N,K", [([128], 256, 256), ([128], 128, 128), ([256], 512, 1024), ([64], 256, 512),
+                                        ([100, 0, 300, 129], 384, 384), ([1, 1, 1], 8, 128), ([257], 2048, 7168)])
+def test_parity(groups, N, K):
+    A, sA, B, sB = make_case(groups, N, K, sum(groups) + N + K)
+    want_bits, want_f32 = O.group_matmul_mxfp4(A, sA, B, sB, np.array(groups, np.int64), K, N, want_f32=True)
+    got = run(A, sA, B, sB, groups, K, N)
+    check_close(got, want_f32, f"groups {groups}")
+    ulp = O.bf16_ulp_diff(got, want_bits)
+    assert ulp.max_ulp <= 2 or ulp.mismatches < 0.02 * ulp.total, ulp
+
+
+@pytest.mark.parametrize("groups,N,K", [([128, 200], 256, 512), ([77], 320, 256)])
+def test_exact_when_sums_are_representable(groups, N, K):
+    # codes {0, +-0.5, +-1, +-2} with unit scales: every partial sum is a small multiple of 0.25 -> exact in fp32
+    A, sA, B, sB = make_case(groups, N, K, 7, exp_span=0, codes=np.array([0, 1, 2, 4, 9, 10, 12], np.uint8))
+    want = O.group_matmul_mxfp4(A, sA, B, sB, np.array(groups, np.int64), K, N)
+    assert_bits_equal(run(A, sA, B, sB, groups, K, N), want, "exact case")
+
+
+def test_scale_bytes_are_applied_per_32_elements():
+    # one-hot operands: A row r has a single 1.0 at k = 32*r, B row n has 1.0 everywhere; the product picks out
+    # exactly sA[r, r] * sB[n, r], so every scale byte position is checked individually
+    M, N, K = 128, 256, 4096
+    A = np.zeros((M, K // 2), np.uint8)
+    for r in range(M):
+        A[r, (32 * r) // 2] = 2  # code 2 = 1.0 in the low nibble
+    B = np.full((1, N, K // 2), 0x22, np.uint8)
+    rng = np.random.default_rng(3)
+    sA = (127 + rng.integers(-6, 7, (M, K // 32))).astype(np.uint8)
+    sB = (127 + rng.integers(-6, 7, (1, N, K // 32))).astype(np.uint8)
+    got = O.bf16_bits_to_f32(run(A, sA, B, sB, [M], K, N))
+    want = np.exp2(sA[np.arange(M), np.arange(M)].astype(np.float64) - 127)[:, None] * \
+        np.exp2(sB[0][:, :M].T.astype(np.float64) - 127)
+    assert np.array_equal(got.astype(np.float64), want)
+
+
+def test_reference_layout_adapters():
+    # B [K, N] with pairs along N and scaleB stored [sK/2, N, 2] (examples/.../matmul_mxfp4_high_performance)
+    K, N = 256, 64
+    rng = np.random.default_rng(11)
+    codes = rng.integers(0, 16, (K, N)).astype(np.uint8)
+    b_kn = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    b_nk_want = (codes.T[:, 0::2] | (codes.T[:, 1::2] << 4)).astype(np.uint8)
+    d = torch.zeros((N, K // 2), dtype=torch.uint8, device=DEV)
+    ops.MxRepackBKnToNk(d, torch.from_numpy(b_kn).to(DEV), K, N)
+    assert np.array_equal(d.cpu().numpy(), b_nk_want)
+    sK = K // 32
+    s = rng.integers(100, 150, (sK, N)).astype(np.uint8)
+    s_ref = np.ascontiguousarray(s.reshape(sK // 2, 2, N).transpose(0, 2, 1))
+    d = torch.zeros((N, sK), dtype=torch.uint8, device=DEV)
+    ops.MxRepackScaleB(d, torch.from_numpy(s_ref).to(DEV), sK, N)
+    assert np.array_equal(d.cpu().numpy(), s.T)
+
+
+def test_invalid_arguments():
+    z = torch.zeros(1 << 16, dtype=torch.uint8, device=DEV)
+    c = torch.zeros((128, 64), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.AscqError) as e:
+        ops.GroupMatmulMxfp4(c, z, z, z, z, [128], 96, 64)
+    assert "multiple of 128" in e.value.message
+    with pytest.raises(ops.AscqError):
+        ops.GroupMatmulMxfp4(c, z, z, z, z, [128, -1], 128, 64)
+    with pytest.raises(ops.AscqError) as e:
+        ops.GroupMatmulMxfp4(c, z, z, z, z, [128], 128, 64, workspace=torch.zeros(256, dtype=torch.uint8, device=DEV))
+    assert "workspace" in e.value.message
+
+
+def test_cfg5_full_size():
+    # BASELINE config 5: G=16, 16384 tokens split by a seeded multinomial, K=7168, N=2048
+    G, K, N, total = 16, 7168, 2048, 16384
+    rng = np.random.default_rng(20251125 + 5)
+    groups = rng.multinomial(total, np.full(G, 1.0 / G)).astype(np.int64)
+    A, sA, B, sB = make_case(list(groups), N, K, 20251125 + 5)
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    dA, dsA, dB, dsB = t(A), t(sA), t(B), t(sB)
+    C1 = torch.empty((total, N), dtype=torch.bfloat16, device=DEV)
+    ops.GroupMatmulMxfp4(C1, dA, dsA, dB, dsB, list(groups), K, N)
+    ops.MatmulStatus()
+    # rows sampled from the start, a group boundary and the end, against the oracle
+    starts = np.concatenate([[0], np.cumsum(groups)])
+    got = C1.view(torch.int16).cpu().numpy().view(np.uint16)
+    for g, lo, cnt in [(0, 0, 24), (5, int(groups[5]) - 24, 24), (G - 1, int(groups[G - 1]) - 24, 24)]:
+        r0 = int(starts[g]) + lo
+        _, want = O.group_matmul_mxfp4(np.ascontiguousarray(A[r0:r0 + cnt]), np.ascontiguousarray(sA[r0:r0 + cnt]),
+                                       np.ascontiguousarray(B[g:g + 1]), np.ascontiguousarray(sB[g:g + 1]),
+                                       np.array([cnt], np.int64), K, N, want_f32=True)
+        check_close(got[r0:r0 + cnt], want, f"cfg5 group {g}")
+    # size-independent property: raising every A scale exponent by one doubles the result exactly
+    C2 = torch.empty_like(C1)
+    ops.GroupMatmulMxfp4(C2, dA, dsA + 1, dB, dsB, list(groups), K, N)
+    ops.MatmulStatus()
+    assert torch.equal(C2.float(), C1.float() * 2.0)
