@@ -58,6 +58,8 @@ SIGNATURES = {
     "ascq_matmul_status": (_i, [_vp]),
     "ascq_group_matmul_mxfp4": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp4_workspace_size": (C.c_size_t, [C.c_int64, _i, _i, _i]),
+    "ascq_group_matmul_mxfp4_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp]),
+    "ascq_group_matmul_mxfp4_noalloc_max_scratch": (C.c_size_t, []),
     "ascq_mx_repack_b_kn_to_nk": (_i, [_vp, _vp, _i, _i, _vp]),
     "ascq_mx_repack_scale_b": (_i, [_vp, _vp, _i, _i, _vp]),
     "ascq_get_ascend_quant_max_min_tmp_size": (_i, [_P64, _i, _u32, _PU32, _PU32]),

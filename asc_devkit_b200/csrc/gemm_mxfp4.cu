@@ -21,6 +21,7 @@
 // Roofline: dense FP4 tensor throughput; 2*sumM*N*K flops per call.
 #include <cuda_bf16.h>
 
+#include <mutex>
 #include <vector>
 
 #include "ascq_internal.h"
@@ -394,6 +395,63 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     rc = make_tmap_u8(&tb, B_fp4, static_cast<uint64_t>(G) * N, static_cast<uint64_t>(K / 2), wide ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
     return wide ? launch<256>(ta, tb, p, st) : launch<128>(ta, tb, p, st);
+}
+
+// ---- entry point for callers that may not allocate device memory ------------------------------------
+// The scratch the grouped matmul needs (tile table + repacked scales) lives in this fixed array instead of a
+// caller buffer.  Every GPU that loads the library carries it for the life of the process.
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;  // 16 MiB: enough for 16 groups x 16384 rows x K 7168 x N 2048
+static __device__ __align__(256) unsigned char g_mxfp4_static_scratch[kStaticScratchBytes];
+
+namespace {
+// Device address of the array on the current device.  The symbol name is only a host-side handle, so the
+// address is asked for once per device (with that device current) and remembered.
+ascq_status static_scratch_address(void** out)
+{
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static void* addr[kMaxDevices] = {};
+    int dev = -1;
+    ASCQ_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(ASCQ_ERR_CUDA, "device ordinal %d is outside the supported range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_mxfp4_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(ASCQ_ERR_CUDA, "cudaGetSymbolAddress for the static scratch failed: %s", cudaGetErrorString(e));
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return ASCQ_OK;
+}
+}  // namespace
+
+extern "C" size_t ascq_group_matmul_mxfp4_noalloc_max_scratch(void) { return kStaticScratchBytes; }
+
+extern "C" ascq_status ascq_group_matmul_mxfp4_noalloc(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
+                                                       const uint8_t* B_fp4, const uint8_t* sB_e8m0,
+                                                       const int64_t* groupList_host, int G, int K, int N, void* stream)
+{
+    if (!groupList_host || G <= 0 || K <= 0 || N <= 0)
+        return fail(ASCQ_ERR_INVALID_ARG, "groupList must not be NULL and G, N, K must be positive");
+    int64_t sumM = 0;
+    for (int g = 0; g < G; ++g) {
+        if (groupList_host[g] < 0) return fail(ASCQ_ERR_INVALID_ARG, "groupList[%d] is negative", g);
+        sumM += groupList_host[g];
+    }
+    const size_t need = ascq_group_matmul_mxfp4_workspace_size(sumM, G, K, N);
+    if (need > kStaticScratchBytes)
+        return fail(ASCQ_ERR_INVALID_ARG,
+                    "this problem needs %zu bytes of scratch but the built-in scratch holds %zu; use "
+                    "ascq_group_matmul_mxfp4 with a caller workspace instead", need, kStaticScratchBytes);
+    void* scratch = nullptr;
+    const ascq_status rc = static_scratch_address(&scratch);
+    if (rc != ASCQ_OK) return rc;
+    // Every byte of scratch the kernels read (tile table, packed scales of the tiles in use) is rewritten by
+    // this call before it is read, so nothing has to be cleared between calls.
+    return ascq_group_matmul_mxfp4(C_bf16, A_fp4, sA_e8m0, B_fp4, sB_e8m0, groupList_host, G, K, N, scratch,
+                                   kStaticScratchBytes, stream);
 }
 
 // Reads and clears this translation unit's device status word (used by ascq_matmul_status).

@@ -227,6 +227,29 @@ ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp4, const ui
                                     void* workspace, size_t workspaceBytes, void* stream);
 size_t ascq_group_matmul_mxfp4_workspace_size(int64_t sumM, int G, int K, int N);
 
+/*
+ * The same grouped matmul for callers that cannot hand over scratch memory.  It has no counterpart in
+ * the reference.  Some hosts of this library must not create device allocations of their own: an
+ * inference server that has given all of HBM to its own memory pool at start-up (a cudaMalloc from a
+ * plug-in then fails, or eats into what the pool counted on), or a latency-critical serving thread that
+ * cannot afford the device-wide synchronisation a cudaMalloc / cudaFree implies.  For them the tile
+ * table and the repacked scales go into an array that is compiled into the library (16 MiB, reported by
+ * ascq_group_matmul_mxfp4_noalloc_max_scratch(); every GPU that loads the library keeps it until the
+ * process exits).  The call makes no cudaMalloc, cudaFree or other allocating call.
+ *   - Problems whose scratch need (ascq_group_matmul_mxfp4_workspace_size) exceeds the array are
+ *     rejected with ASCQ_ERR_INVALID_ARG; use the workspace variant for those.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps what the previous call left there.  Each
+ *     call rewrites everything it later reads, so no clearing is needed, but two calls whose kernels can
+ *     overlap on the GPU (different streams, no ordering between them) race on it: serialise them.
+ * Arguments and results are those of ascq_group_matmul_mxfp4.
+ */
+ascq_status ascq_group_matmul_mxfp4_noalloc(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
+                                            const uint8_t* B_fp4, const uint8_t* sB_e8m0,
+                                            const int64_t* groupList_host, int G, int K, int N, void* stream);
+size_t ascq_group_matmul_mxfp4_noalloc_max_scratch(void);
+
 /* Reference layout adapters for the MX matmul (one-off weight preparation):
  * B given as [K, N] fp4 pairs along N and scaleB stored [sK/2, N, 2]
  * (examples/.../matmul_mxfp4_high_performance/README_en.md:64-67, scripts/gen_data.py:65)

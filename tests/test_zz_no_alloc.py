@@ -1,0 +1,75 @@
+"""The grouped MX-FP4 matmul through the entry point that brings its own scratch memory.
+
+Some programs that embed this library are not allowed to allocate device memory themselves -- a serving
+process whose memory pool already owns all of HBM, or a thread that cannot tolerate the device-wide stall of a
+cudaMalloc.  ``ascq_group_matmul_mxfp4_noalloc`` serves them from a fixed array inside the library.  Here it is
+called through the C ABI, twice in a row with different problems (the second call finds the first one's
+leftovers in the shared scratch) and once more with the first problem, and each result must equal, bit for bit,
+what the workspace-taking entry point produces.  Oversized problems must be refused with a clear message.
+
+The file name sorts last so that a run that stops at the first failure has already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from asc_devkit_b200 import _lib as L
+from asc_devkit_b200 import ops
+from tests.gpu_util import DEV
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(groups, N, K, seed):
+    rng = np.random.default_rng(seed)
+    sumM, G = int(sum(groups)), len(groups)
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    return dict(groups=groups, N=N, K=K,
+                A=t(rng.integers(0, 256, (sumM, K // 2)).astype(np.uint8)),
+                sA=t((127 + rng.integers(-4, 5, (sumM, K // 32))).astype(np.uint8)),
+                B=t(rng.integers(0, 256, (G, N, K // 2)).astype(np.uint8)),
+                sB=t((127 + rng.integers(-4, 5, (G, N, K // 32))).astype(np.uint8)))
+
+
+def _with_workspace(p):
+    out = torch.zeros((sum(p["groups"]), p["N"]), dtype=torch.bfloat16, device=DEV)
+    ops.GroupMatmulMxfp4(out, p["A"], p["sA"], p["B"], p["sB"], p["groups"], p["K"], p["N"])
+    ops.MatmulStatus()
+    return out
+
+
+def _no_alloc(p):
+    out = torch.zeros((sum(p["groups"]), p["N"]), dtype=torch.bfloat16, device=DEV)
+    gl = (C.c_int64 * len(p["groups"]))(*p["groups"])
+    before = torch.cuda.memory_allocated()
+    rc = L.lib().ascq_group_matmul_mxfp4_noalloc(ops._ptr(out), ops._ptr(p["A"]), ops._ptr(p["sA"]), ops._ptr(p["B"]),
+                                                 ops._ptr(p["sB"]), gl, len(p["groups"]), p["K"], p["N"],
+                                                 ops._stream(None))
+    L.check(rc)
+    ops.MatmulStatus()
+    assert torch.cuda.memory_allocated() == before
+    return out
+
+
+def test_two_calls_in_a_row_match_the_workspace_entry_point():
+    first = _problem([100, 0, 300, 129], 384, 384, 1)
+    second = _problem([128, 40], 256, 1024, 2)
+    want_first, want_second = _with_workspace(first), _with_workspace(second)
+    assert torch.equal(_no_alloc(first), want_first)
+    assert torch.equal(_no_alloc(second), want_second)     # scratch still holds the first call's tables
+    assert torch.equal(_no_alloc(first), want_first)       # and now the second call's
+
+
+def test_problems_beyond_the_built_in_scratch_are_refused():
+    limit = L.lib().ascq_group_matmul_mxfp4_noalloc_max_scratch()
+    assert limit == 16 << 20
+    G, K, N = 16, 14336, 2048
+    groups = [1024] * G
+    assert L.lib().ascq_group_matmul_mxfp4_workspace_size(sum(groups), G, K, N) > limit
+    gl = (C.c_int64 * G)(*groups)
+    dummy = C.c_void_p(0x1000)  # never dereferenced: the size check comes first
+    rc = L.lib().ascq_group_matmul_mxfp4_noalloc(dummy, dummy, dummy, dummy, dummy, gl, G, K, N, None)
+    assert rc == L.ERR_INVALID_ARG
+    assert b"built-in scratch" in L.lib().ascq_last_error()
