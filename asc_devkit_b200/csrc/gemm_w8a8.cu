@@ -29,7 +29,8 @@ using namespace ptx;
 constexpr int kBM = 128;
 constexpr int kBK = 128;        // bytes == int8 elements per k-block: one 128B swizzle atom
 constexpr int kUmmaK = 32;      // K per tcgen05.mma for 8-bit operands
-constexpr int kThreads = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int kEpiWarps = 16;   // four warps per TMEM lane quarter, each draining a quarter of the accumulator columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..17: epilogue
 
 __device__ int g_w8a8_status = 0;  // 0 ok, 1 = a bounded wait expired
 
@@ -39,7 +40,9 @@ template <int BN> struct Cfg {
     static constexpr int kBBytes = BN * kBK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
-    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kEpiBytes = 2 * 2 * BN * 4;  // per accumulator: sB[BN] and bias[BN] as fp32
+    static constexpr size_t kSmemBytes =
+        static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes;
 };
 
 struct Params {
@@ -67,6 +70,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     uint64_t* tmemEmpty = tmemFull + 2;            // [2] epilogue -> MMA
     uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
+    float* epiScale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + 256);  // [2][2][BN]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -80,7 +84,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmemFull[a], 1);
-            mbar_init(&tmemEmpty[a], 4);  // one arrival per epilogue warp
+            mbar_init(&tmemEmpty[a], kEpiWarps);  // one arrival per epilogue warp
         }
         *abortFlag = 0;
         fence_barrier_init();
@@ -146,8 +150,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----------------
+        // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4)..; the kEpiWarps/4 warps of a lane quarter
+        // take the 32-column chunks round-robin ----------------
         const int q = warp & 3;
+        const int sub = (warp - 2) >> 2;
         uint32_t local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
@@ -155,14 +161,42 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             const uint32_t accPh = (local >> 1) & 1;
             const int m0 = (tile % p.tilesM) * kBM;
             const int n0 = (tile / p.tilesM) * BN;
-            if (!(ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag))) break;
+            ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
             tc_fence_after();
             const int m = m0 + q * 32 + lane;
             const float sa = (p.sA != nullptr && m < p.M) ? __ldg(p.sA + m) : 1.0f;
+            // this tile's per-channel scale and bias, once, into shared memory (fp32): every thread needs all BN of
+            // them and reads them back as warp-wide broadcasts
+            float* sBs = epiScale + acc * 2 * BN;
+            float* biasS = sBs + BN;
+            {
+                const int t = threadIdx.x - 64;  // index over the epilogue threads
+                for (int j = t; j < BN; j += 32 * kEpiWarps) {
+                    const int n = n0 + j;
+                    sBs[j] = (p.sB != nullptr && n < p.N) ? __ldg(p.sB + n) : 1.0f;
+                    biasS[j] = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+                }
+                // barrier of the epilogue warps only; it also makes the give-up decision uniform, so that no warp is
+                // left waiting at it for one that stopped
+                uint32_t anyFail;
+                asm volatile(
+                    "{\n\t.reg .pred pin, pout;\n\t"
+                    "setp.ne.u32 pin, %1, 0;\n\t"
+                    "bar.red.or.pred pout, 1, %2, pin;\n\t"
+                    "selp.u32 %0, 1, 0, pout;\n\t}"
+                    : "=r"(anyFail)
+                    : "r"(ok ? 0u : 1u), "n"(32 * kEpiWarps)
+                    : "memory");
+                if (anyFail) {
+                    ok = false;
+                    break;
+                }
+            }
+            const bool hasBias = p.bias != nullptr;
             const uint32_t taddr = tmemBase + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
             const bool vecStore = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = sub; c < BN / 32; c += kEpiWarps / 4) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
@@ -176,27 +210,24 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     }
                     if (p.C != nullptr) {
                         __nv_bfloat16* crow = p.C + static_cast<size_t>(m) * p.ldc + n;
-                        const bool full = (n + 32 <= p.N);
+                        const float4* sb4 = reinterpret_cast<const float4*>(sBs + c * 32);
+                        const float4* bi4 = reinterpret_cast<const float4*>(biasS + c * 32);
                         uint32_t packed[16];
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            float f0 = __int2float_rn(static_cast<int32_t>(r[j]));
-                            float f1 = __int2float_rn(static_cast<int32_t>(r[j + 1]));
-                            const int n0j = full ? n + j : min(n + j, p.N - 1);
-                            const int n1j = full ? n + j + 1 : min(n + j + 1, p.N - 1);
-                            if (p.sB != nullptr) {
-                                f0 = __fmul_rn(f0, __ldg(p.sB + n0j));
-                                f1 = __fmul_rn(f1, __ldg(p.sB + n1j));
+                        for (int v = 0; v < 8; ++v) {
+                            const float4 s4 = sb4[v];
+                            const float4 b4 = bi4[v];
+                            float f0 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 0])), s4.x), sa);
+                            float f1 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 1])), s4.y), sa);
+                            float f2 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 2])), s4.z), sa);
+                            float f3 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 3])), s4.w), sa);
+                            if (hasBias) {
+                                f0 = __fadd_rn(f0, b4.x); f1 = __fadd_rn(f1, b4.y); f2 = __fadd_rn(f2, b4.z); f3 = __fadd_rn(f3, b4.w);
                             }
-                            f0 = __fmul_rn(f0, sa);
-                            f1 = __fmul_rn(f1, sa);
-                            if (p.bias != nullptr) {
-                                f0 = __fadd_rn(f0, __bfloat162float(p.bias[n0j]));
-                                f1 = __fadd_rn(f1, __bfloat162float(p.bias[n1j]));
-                            }
-                            packed[j >> 1] = pack_bf16x2_sat(f0, f1);
+                            packed[2 * v] = pack_bf16x2_sat(f0, f1);
+                            packed[2 * v + 1] = pack_bf16x2_sat(f2, f3);
                         }
-                        if (full && vecStore) {
+                        if (n + 32 <= p.N && vecStore) {
                             uint4* dst = reinterpret_cast<uint4*>(crow);
 #pragma unroll
                             for (int v = 0; v < 4; ++v)

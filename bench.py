@@ -75,6 +75,16 @@ def gen_w8a8_cfg4(M=4096, N=4096, K=4096):
             "bias": f32_to_bf16_bits(rng.normal(0, 0.1, N).astype(np.float32))}
 
 
+def gen_mxfp4_cfg5(G=16, total=16384, K=7168, N=2048):
+    rng = np.random.default_rng(SEED + 5)
+    groups = rng.multinomial(total, np.full(G, 1.0 / G)).astype(np.int64)
+    return {"groups": groups,
+            "A": rng.integers(0, 256, (total, K // 2), dtype=np.uint8),          # all 16 E2M1 codes, two per byte
+            "sA": (127 + rng.integers(-4, 5, (total, K // 32))).astype(np.uint8),
+            "B": rng.integers(0, 256, (G, N, K // 2), dtype=np.uint8),
+            "sB": (127 + rng.integers(-4, 5, (G, N, K // 32))).astype(np.uint8)}
+
+
 # ------------------------------------------------------------------------------------------------
 # Workloads.  Each owns `nsets` rotating device buffer sets and knows its algorithmic bytes.
 # ------------------------------------------------------------------------------------------------
@@ -324,7 +334,74 @@ class W8A8Cfg4(Workload):
         return bool(np.array_equal(got, want))
 
 
-WORKLOADS = {"w8a8_cfg4": W8A8Cfg4, "antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3, "quant_scaled": QuantScaled}
+class Mxfp4Cfg5(Workload):
+    name = "MX-FP4 grouped matmul G=16, 16384 tokens (multinomial), K=7168, N=2048 -> bf16 (config 5)"
+    dtype = "fp4(e2m1)xue8m0, f32 accumulate"
+    unit = "TFLOPS"
+    bound = "tensor"
+    key = "mxfp4_cfg5"
+
+    def __init__(self, torch, ops, dev):
+        self.torch, self.ops = torch, ops
+        self.G, self.total, self.K, self.N = 16, 16384, 7168, 2048
+        h = gen_mxfp4_cfg5(self.G, self.total, self.K, self.N)
+        self.host = h
+        self.groups = [int(v) for v in h["groups"]]
+        per_set = h["A"].nbytes + h["sA"].nbytes + h["B"].nbytes + h["sB"].nbytes + self.total * self.N * 2
+        self.nsets = self.nsets_for(per_set)
+        t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
+        self.A = [t(h["A"]) for _ in range(self.nsets)]
+        self.sA = [t(h["sA"]) for _ in range(self.nsets)]
+        self.B = [t(h["B"]) for _ in range(self.nsets)]
+        self.sB = [t(h["sB"]) for _ in range(self.nsets)]
+        self.C = [torch.empty((self.total, self.N), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
+        self.ws = torch.empty(ops.GroupMatmulMxfp4Workspace(self.total, self.G, self.K, self.N), dtype=torch.uint8, device=dev)
+        self.h_A = torch.from_numpy(h["A"]).pin_memory()
+        self.h_sA = torch.from_numpy(h["sA"]).pin_memory()
+        self.h_C = torch.empty((self.total, self.N), dtype=torch.bfloat16).pin_memory()
+        self.launches_per_step = 3  # two scale-repack launches + the matmul
+
+    def work_per_step(self):
+        return 2 * self.total * self.N * self.K
+
+    def step(self, i):
+        s = i % self.nsets
+        self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
+                                  workspace=self.ws)
+
+    def e2e_step(self, i):
+        s = i % self.nsets
+        self.A[s].copy_(self.h_A, non_blocking=True)      # this step's tokens and their scales; expert weights stay resident
+        self.sA[s].copy_(self.h_sA, non_blocking=True)
+        self.step(i)
+        self.h_C.copy_(self.C[s], non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.host["A"].nbytes + self.host["sA"].nbytes, self.total * self.N * 2
+
+    def cpu_sample(self, O):
+        rows = 16
+        h = self.host
+        t0 = time.perf_counter()
+        O.group_matmul_mxfp4(np.ascontiguousarray(h["A"][:rows]), np.ascontiguousarray(h["sA"][:rows]),
+                             np.ascontiguousarray(h["B"][:1]), np.ascontiguousarray(h["sB"][:1]), np.array([rows], np.int64),
+                             self.K, self.N)
+        dt = time.perf_counter() - t0
+        return 2 * rows * self.N * self.K / dt / 1e12, f"{rows} of {self.total} rows (group 0)"
+
+    def check(self, O):
+        rows = 8
+        h = self.host
+        _, want = O.group_matmul_mxfp4(np.ascontiguousarray(h["A"][:rows]), np.ascontiguousarray(h["sA"][:rows]),
+                                       np.ascontiguousarray(h["B"][:1]), np.ascontiguousarray(h["sB"][:1]),
+                                       np.array([rows], np.int64), self.K, self.N, want_f32=True)
+        got = self.C[0][:rows].float().cpu().numpy()
+        self.ops.MatmulStatus()
+        return bool(np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3 * np.abs(want).max()))
+
+
+WORKLOADS = {"w8a8_cfg4": W8A8Cfg4, "mxfp4_cfg5": Mxfp4Cfg5, "antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3,
+             "quant_scaled": QuantScaled}
 HEADLINE = "w8a8_cfg4"
 
 
@@ -446,6 +523,13 @@ def run_ours(args):
             roof = {"bound": "tensor", "achieved": kern, "peak": peak, "unit": "TOPS", "frac": kern / peak, "traffic": None,
                     "peak_source": "2 x %s dense bf16 cuBLAS burst (int8 runs at twice the bf16 rate; nominal 4500)"
                                    % peaks["source"], "kernel_ms": gsec / args.steps * 1e3}
+        elif wl.bound == "tensor":
+            achieved = work / per / 1e12          # TFLOPS per rank (replicas)
+            total_value = achieved * world
+            peak = 4.0 * peaks["bf16_tflops"]
+            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOPS", "frac": achieved / peak,
+                    "traffic": None, "peak_source": "4 x %s dense bf16 cuBLAS burst (FP4 runs at four times the bf16 rate; "
+                                                    "nominal 9000)" % peaks["source"]}
         else:
             achieved = work / per / 1e9           # GB/s (each rank does the full workload: replicas)
             total_value = achieved * world
@@ -456,7 +540,8 @@ def run_ours(args):
         h2d, d2h = wl.e2e_bytes()
         if sampler:
             clocks = sampler.stop()
-        e2e_value = work / e2e_per / 1e12 if sharded else work / e2e_per / 1e9 * world
+        e2e_value = (work / e2e_per / 1e12 if sharded else
+                     work / e2e_per / 1e12 * world if wl.bound == "tensor" else work / e2e_per / 1e9 * world)
         rec = {"name": wl.name, "value": total_value, "unit": wl.unit, "ms_per_step": per * 1e3,
                "roofline": roof,
                "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
