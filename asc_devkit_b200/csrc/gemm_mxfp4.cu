@@ -38,7 +38,8 @@ constexpr int kBM = 128;
 constexpr int kBKBytes = 128;   // 256 E2M1 elements per k-block row: one 128B swizzle atom
 constexpr int kBKElems = 256;
 constexpr int kChunkBytes = 512;  // packed scales of 128 rows x 128 K-elements
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;   // two per TMEM lane quarter; each drains half of the accumulator columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 
 __device__ int g_mxfp4_status = 0;
 
@@ -132,7 +133,7 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmemFull[a], 1);
-            mbar_init(&tmemEmpty[a], 4);
+            mbar_init(&tmemEmpty[a], kEpiWarps);
         }
         *abortFlag = 0;
         fence_barrier_init();
@@ -220,7 +221,13 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             }
         }
     } else {
+        // epilogue: warp w reads TMEM lanes 32*(w%4)..; warps 2..5 take the lower half of the accumulator columns,
+        // warps 6..9 the upper half.  Each warp first pulls its whole share into registers and hands the accumulator
+        // back to the MMA warp, so the conversion and the stores overlap the next tile's main loop even when there
+        // is only one accumulator stage.
         const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        constexpr int kChunks = BN / 64;  // 32-column chunks per warp
         uint32_t local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
@@ -228,24 +235,30 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             const uint32_t accPh = (local / C::kAccStages) & 1;
             const int mt = tile % p.numTilesM, nt = tile / p.numTilesM;
             const TileInfo ti = p.tiles[mt];
-            const int n0 = nt * BN;
+            const int n0 = nt * BN + half * (BN / 2);
             if (!(ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag))) break;
             tc_fence_after();
+            const uint32_t taddr = tmemBase + acc * BN + half * (BN / 2) + (static_cast<uint32_t>(q * 32) << 16);
+            uint32_t r[kChunks][32];
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) tmem_ld_32x32b_x32(taddr + c * 32, r[c]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmemEmpty[acc]);
+
             const int rIn = q * 32 + lane;
             const bool rowOk = rIn < ti.rowsValid;
             __nv_bfloat16* crow = p.C + static_cast<size_t>(ti.rowStart + rIn) * p.N + n0;
-            const uint32_t taddr = tmemBase + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
             const bool vecStore = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
                 const int n = n0 + c * 32;
                 if (rowOk && n < p.N) {
                     uint32_t packed[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2_sat(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    for (int j = 0; j < 16; ++j)
+                        packed[j] = pack_bf16x2_sat(__uint_as_float(r[c][2 * j]), __uint_as_float(r[c][2 * j + 1]));
                     if (n + 32 <= p.N && vecStore) {
                         uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
 #pragma unroll
@@ -259,9 +272,6 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmemEmpty[acc]);
         }
     }
 

@@ -283,10 +283,10 @@ class W8A8Cfg4(Workload):
         self.sA = torch.from_numpy(h["sA"]).to(dev)
         self.sB = torch.from_numpy(h["sB"][n0:n0 + self.nl].copy()).to(dev)
         self.bias = bf(h["bias"][n0:n0 + self.nl])
-        self.gathered = torch.empty((world, self.M, self.nl), dtype=torch.bfloat16, device=dev) if world > 1 else None
+        self.gathered = torch.empty((world * self.M, self.nl), dtype=torch.bfloat16, device=dev) if world > 1 else None
         self.h_A = torch.from_numpy(h["A"]).pin_memory()
         self.h_sA = torch.from_numpy(h["sA"]).pin_memory()
-        self.h_C = torch.empty((world, self.M, self.nl), dtype=torch.bfloat16).pin_memory()
+        self.h_C = torch.empty((world * self.M, self.nl), dtype=torch.bfloat16).pin_memory()
         self.launches_per_step = 1
 
     def work_per_step(self):
@@ -310,7 +310,7 @@ class W8A8Cfg4(Workload):
         if self.world > 1:
             self.h_C.copy_(self.gathered, non_blocking=True)
         else:
-            self.h_C[0].copy_(self.C[s], non_blocking=True)
+            self.h_C[:self.M].copy_(self.C[s], non_blocking=True)
 
     def e2e_bytes(self):
         return self.M * self.K + self.M * 4, self.M * self.N * 2
@@ -410,7 +410,7 @@ class ClockSampler:
     """nvidia-smi in the background for the length of the timed region (read-only queries)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, gpu_index):
         self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
@@ -436,7 +436,7 @@ class ClockSampler:
             self.proc.kill()
         self.tmp.flush()
         self.tmp.seek(0)
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, busy = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.tmp.read().splitlines():
             f = [x.strip() for x in line.split(",")]
@@ -447,13 +447,19 @@ class ClockSampler:
                 mx.append(float(f[2]))
             except ValueError:
                 continue
+            try:
+                busy.append(float(f[9]) >= 50.0)
+            except (ValueError, IndexError):
+                busy.append(False)
             for nm, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         self.tmp.close()
         os.unlink(self.tmp.name)
         if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+            loaded = [v for v, b in zip(sm, busy) if b] or sm   # median over the samples taken under load
+            out.update(sm_mhz=float(np.median(loaded)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons),
+                       samples=len(sm), samples_under_load=int(sum(busy)))
         return out
 
 
@@ -505,12 +511,11 @@ def run_ours(args):
         names = [HEADLINE] + names if args.workload == "all" else names
     results = {}
     head = None
-    clocks = None
+    sampler = ClockSampler(local) if rank == 0 else None   # runs across every timed region of this process
     for nm in names:
         sharded = nm == "w8a8_cfg4"
         wl = WORKLOADS[nm](torch, ops, dev, dist, world, rank) if sharded else WORKLOADS[nm](torch, ops, dev)
         is_head = nm == (args.workload if args.workload != "all" else HEADLINE)
-        sampler = ClockSampler(local) if (is_head and rank == 0) else None
         sec = time_steps(torch, wl.step, args.steps, args.warmup, dist)
         per = sec / args.steps
         work = wl.work_per_step()
@@ -538,8 +543,6 @@ def run_ours(args):
         e2e_sec = time_steps(torch, wl.e2e_step, max(2, args.steps // 4), 2, dist)
         e2e_per = e2e_sec / max(2, args.steps // 4)
         h2d, d2h = wl.e2e_bytes()
-        if sampler:
-            clocks = sampler.stop()
         e2e_value = (work / e2e_per / 1e12 if sharded else
                      work / e2e_per / 1e12 * world if wl.bound == "tensor" else work / e2e_per / 1e9 * world)
         rec = {"name": wl.name, "value": total_value, "unit": wl.unit, "ms_per_step": per * 1e3,
@@ -559,6 +562,7 @@ def run_ours(args):
             head = (wl, rec)
         del wl
         torch.cuda.empty_cache()
+    clocks = sampler.stop() if sampler else None
     if rank == 0:
         wl, rec = head
         line = {"metric": "W8A8/MXFP4 GEMM TOPS at 1/2/4/8 B200; quant/dequant GB/s vs HBM peak",
