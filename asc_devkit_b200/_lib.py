@@ -55,6 +55,7 @@ SIGNATURES = {
     "ascq_dequant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _i, C.POINTER(DequantParam), _vp]),
     "ascq_antiquant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(AntiQuantParam), _vp]),
     "ascq_matmul_w8a8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "ascq_matmul_w8a8_scatter": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ascq_matmul_status": (_i, [_vp]),
     "ascq_group_matmul_mxfp4": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp4_workspace_size": (C.c_size_t, [C.c_int64, _i, _i, _i]),

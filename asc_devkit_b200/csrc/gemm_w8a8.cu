@@ -29,8 +29,10 @@ using namespace ptx;
 constexpr int kBM = 128;
 constexpr int kBK = 128;        // bytes == int8 elements per k-block: one 128B swizzle atom
 constexpr int kUmmaK = 32;      // K per tcgen05.mma for 8-bit operands
-constexpr int kEpiWarps = 16;   // four warps per TMEM lane quarter, each draining a quarter of the accumulator columns
-constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..17: epilogue
+constexpr int kEpiWarps = 8;    // two warps per TMEM lane quarter, alternating 32-column chunks
+constexpr int kMaxPeers = 8;    // output buffers one launch can write (this GPU's and its peers')
+constexpr int kStagePitch = 80;  // bytes per staged row: 64 B of bf16 + 16 B pad (conflict-free both ways)
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
 
 __device__ int g_w8a8_status = 0;  // 0 ok, 1 = a bounded wait expired
 
@@ -41,12 +43,14 @@ template <int BN> struct Cfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
     static constexpr int kEpiBytes = 2 * 2 * BN * 4;  // per accumulator: sB[BN] and bias[BN] as fp32
+    static constexpr int kOutBytes = kEpiWarps * 32 * kStagePitch;  // per epilogue warp: 32 rows x 32 bf16 columns
     static constexpr size_t kSmemBytes =
-        static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes;
+        static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes + kOutBytes;
 };
 
 struct Params {
-    __nv_bfloat16* C;
+    __nv_bfloat16* C[kMaxPeers];  // output buffers (own first); every one gets this launch's [M, N] block
+    int nPeers, colOffset, firstPeer;  // block goes to columns [colOffset, colOffset + N); stores start at buffer firstPeer
     const float* sA;
     const float* sB;
     const __nv_bfloat16* bias;
@@ -71,6 +75,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
     float* epiScale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + 256);  // [2][2][BN]
+    uint8_t* outStage = reinterpret_cast<uint8_t*>(epiScale) + C::kEpiBytes;                // [kEpiWarps][32][kStagePitch]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -150,10 +155,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             }
         }
     } else {
-        // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4)..; the kEpiWarps/4 warps of a lane quarter
-        // take the 32-column chunks round-robin ----------------
+        // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).. (its 32 rows of the tile) ----------------
         const int q = warp & 3;
         const int sub = (warp - 2) >> 2;
+        uint8_t* stageW = outStage + (warp - 2) * (32 * kStagePitch);
         uint32_t local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
@@ -194,51 +199,83 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             }
             const bool hasBias = p.bias != nullptr;
             const uint32_t taddr = tmemBase + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-            const bool vecStore = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+            const bool haveC = p.C[0] != nullptr;
+            bool vecStore = (p.ldc % 8 == 0) && (p.colOffset % 8 == 0);
+            for (int pi = 0; pi < p.nPeers; ++pi) vecStore = vecStore && ((reinterpret_cast<uintptr_t>(p.C[pi]) & 15u) == 0);
+
+            // 32 accumulator columns of this thread's row -> 16 packed bf16x2 words
+            auto convert32 = [&](const uint32_t(&r)[32], int colInTile, uint32_t* packed) {
+                const float4* sb4 = reinterpret_cast<const float4*>(sBs + colInTile);
+                const float4* bi4 = reinterpret_cast<const float4*>(biasS + colInTile);
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const float4 s4 = sb4[v];
+                    const float4 b4 = bi4[v];
+                    float f0 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 0])), s4.x), sa);
+                    float f1 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 1])), s4.y), sa);
+                    float f2 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 2])), s4.z), sa);
+                    float f3 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 3])), s4.w), sa);
+                    if (hasBias) {
+                        f0 = __fadd_rn(f0, b4.x); f1 = __fadd_rn(f1, b4.y); f2 = __fadd_rn(f2, b4.z); f3 = __fadd_rn(f3, b4.w);
+                    }
+                    packed[2 * v] = pack_bf16x2_sat(f0, f1);
+                    packed[2 * v + 1] = pack_bf16x2_sat(f2, f3);
+                }
+            };
+            // slow path for ragged edges / unaligned outputs: every thread writes its own row segment
+            auto store_direct = [&](const uint32_t* packed, int n) {
+                if (m >= p.M || n >= p.N) return;
+                for (int pi = 0; pi < p.nPeers; ++pi) {
+                    __nv_bfloat16* crow = p.C[pi] + static_cast<size_t>(m) * p.ldc + p.colOffset + n;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n + j < p.N)
+                            crow[j] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[j >> 1] >> ((j & 1) * 16)));
+                }
+            };
 #pragma unroll 1
             for (int c = sub; c < BN / 32; c += kEpiWarps / 4) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                uint32_t r0[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r0);
                 tmem_ld_wait();
                 const int n = n0 + c * 32;
-                if (m < p.M && n < p.N) {
-                    if (p.accDump != nullptr) {
-                        int32_t* d = p.accDump + static_cast<size_t>(m) * p.N + n;
+                if (n >= p.N) continue;  // uniform over the warp
+                if (p.accDump != nullptr && m < p.M) {
+                    int32_t* d = p.accDump + static_cast<size_t>(m) * p.N + n;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n + j < p.N) d[j] = static_cast<int32_t>(r[j]);
-                    }
-                    if (p.C != nullptr) {
-                        __nv_bfloat16* crow = p.C + static_cast<size_t>(m) * p.ldc + n;
-                        const float4* sb4 = reinterpret_cast<const float4*>(sBs + c * 32);
-                        const float4* bi4 = reinterpret_cast<const float4*>(biasS + c * 32);
-                        uint32_t packed[16];
+                    for (int j = 0; j < 32; ++j)
+                        if (n + j < p.N) d[j] = static_cast<int32_t>(r0[j]);
+                }
+                if (!haveC) continue;
+                uint32_t packed[16];
+                convert32(r0, c * 32, packed);
+                if (vecStore && n + 32 <= p.N) {
+                    // Transpose through this warp's staging rows so that every store instruction writes eight complete
+                    // 64-byte row segments (instead of thirty-two 16-byte pieces): the output leaves the SM in whole
+                    // sectors, which is what both the L1 path and NVLink want.
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            const float4 s4 = sb4[v];
-                            const float4 b4 = bi4[v];
-                            float f0 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 0])), s4.x), sa);
-                            float f1 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 1])), s4.y), sa);
-                            float f2 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 2])), s4.z), sa);
-                            float f3 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 3])), s4.w), sa);
-                            if (hasBias) {
-                                f0 = __fadd_rn(f0, b4.x); f1 = __fadd_rn(f1, b4.y); f2 = __fadd_rn(f2, b4.z); f3 = __fadd_rn(f3, b4.w);
+                    for (int v = 0; v < 4; ++v)
+                        *reinterpret_cast<uint4*>(stageW + lane * kStagePitch + v * 16) =
+                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    __syncwarp();
+                    const int piece = lane & 3;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int row = i * 8 + (lane >> 2);
+                        const uint4 val = *reinterpret_cast<const uint4*>(stageW + row * kStagePitch + piece * 16);
+                        const int gm = m0 + q * 32 + row;
+                        if (gm < p.M) {
+                            const size_t off = static_cast<size_t>(gm) * p.ldc + p.colOffset + n + piece * 8;
+                            for (int pi = 0; pi < p.nPeers; ++pi) {
+                                int b = p.firstPeer + pi;
+                                if (b >= p.nPeers) b -= p.nPeers;
+                                *reinterpret_cast<uint4*>(p.C[b] + off) = val;
                             }
-                            packed[2 * v] = pack_bf16x2_sat(f0, f1);
-                            packed[2 * v + 1] = pack_bf16x2_sat(f2, f3);
-                        }
-                        if (n + 32 <= p.N && vecStore) {
-                            uint4* dst = reinterpret_cast<uint4*>(crow);
-#pragma unroll
-                            for (int v = 0; v < 4; ++v)
-                                dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (n + j < p.N)
-                                    crow[j] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[j >> 1] >> ((j & 1) * 16)));
                         }
                     }
+                    __syncwarp();
+                } else {
+                    store_direct(packed, n);
                 }
             }
             tc_fence_before();
@@ -284,24 +321,33 @@ template <int BN> ascq_status launch(const CUtensorMap& ta, const CUtensorMap& t
 }  // namespace
 }  // namespace ascq
 
-using namespace ascq;
 
-extern "C" ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int8_t* B_nk, const float* sA_m,
-                                        const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc,
-                                        int32_t* accDump, void* stream)
+
+namespace ascq {
+namespace {
+ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
+                     const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc, int32_t* accDump,
+                     cudaStream_t st)
 {
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!A || !B_nk) return fail(ASCQ_ERR_INVALID_ARG, "A and B must not be NULL");
-    if (!C_bf16 && !accDump) return fail(ASCQ_ERR_INVALID_ARG, "one of C and accDump must be given");
-    if (M < 0 || N < 0 || K < 0) return fail(ASCQ_ERR_INVALID_ARG, "M, N, K must be non-negative");
-    if (C_bf16 && ldc < N) return fail(ASCQ_ERR_INVALID_ARG, "ldc %d is smaller than N %d", ldc, N);
+    if (nBufs < 0 || nBufs > kMaxPeers) return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
+    const bool haveC = nBufs > 0 && outBufs != nullptr && outBufs[0] != nullptr;
+    if (!haveC && !accDump) return fail(ASCQ_ERR_INVALID_ARG, "one of C and accDump must be given");
+    if (M < 0 || N < 0 || K < 0 || colOffset < 0) return fail(ASCQ_ERR_INVALID_ARG, "M, N, K, colOffset must be non-negative");
+    if (haveC && ldc < colOffset + N) return fail(ASCQ_ERR_INVALID_ARG, "ldc %d is smaller than colOffset + N = %d", ldc, colOffset + N);
     if (M == 0 || N == 0) return ASCQ_OK;
     if (K == 0) return fail(ASCQ_ERR_INVALID_ARG, "K must be positive");
     if (K % 16 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of 16 (TMA row pitch)", K);
     if (!aligned16(A) || !aligned16(B_nk)) return fail(ASCQ_ERR_ALIGNMENT, "A and B must be 16-byte aligned");
 
     Params p{};
-    p.C = static_cast<__nv_bfloat16*>(C_bf16);
+    p.nPeers = haveC ? nBufs : 1;
+    for (int i = 0; i < p.nPeers; ++i) {
+        p.C[i] = haveC ? static_cast<__nv_bfloat16*>(outBufs[i]) : nullptr;
+        if (haveC && !p.C[i]) return fail(ASCQ_ERR_INVALID_ARG, "output buffer %d is NULL", i);
+    }
+    p.firstPeer = (p.nPeers > 0) ? ((firstBuf % p.nPeers) + p.nPeers) % p.nPeers : 0;
+    p.colOffset = colOffset;
     p.sA = sA_m;
     p.sB = sB_n;
     p.bias = static_cast<const __nv_bfloat16*>(bias_bf16);
@@ -317,6 +363,27 @@ extern "C" ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int
     rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), wide ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
     return wide ? launch<256>(ta, tb, p, st) : launch<128>(ta, tb, p, st);
+}
+}  // namespace
+}  // namespace ascq
+
+using namespace ascq;
+
+extern "C" ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int8_t* B_nk, const float* sA_m,
+                                        const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc,
+                                        int32_t* accDump, void* stream)
+{
+    void* bufs[1] = {C_bf16};
+    return run_w8a8(bufs, 1, 0, 0, A, B_nk, sA_m, sB_n, bias_bf16, M, N, K, ldc, accDump, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" ascq_status ascq_matmul_w8a8_scatter(void* const* C_bufs, int nBufs, int firstBuf, int colOffset, int ldc,
+                                                const int8_t* A, const int8_t* B_nk, const float* sA_m, const float* sB_n,
+                                                const void* bias_bf16, int M, int N, int K, void* stream)
+{
+    if (!C_bufs || nBufs < 1) return fail(ASCQ_ERR_INVALID_ARG, "at least one output buffer is needed");
+    return run_w8a8(C_bufs, nBufs, firstBuf, colOffset, A, B_nk, sA_m, sB_n, bias_bf16, M, N, K, ldc, nullptr,
+                    static_cast<cudaStream_t>(stream));
 }
 
 // Reads and clears the device status word of the GEMM kernels on the current device (synchronises `stream`).

@@ -210,6 +210,18 @@ def MxRepackScaleB(sB_nk: torch.Tensor, sB_ref: torch.Tensor, sK: int, N: int, s
     return sB_nk
 
 
+def MatmulW8A8Scatter(buffer_ptrs, first_buf: int, col_offset: int, ldc: int, A: torch.Tensor, B_nk: torch.Tensor,
+                      scaleA=None, scaleB=None, bias=None, stream=None):
+    """W8A8 matmul whose epilogue writes the [M, N_local] block into columns [col_offset, col_offset + N_local) of every
+    bf16 [M, ldc] buffer in ``buffer_ptrs`` (device addresses; this GPU's buffer and peer-mapped ones):
+    ``ascq_matmul_w8a8_scatter``."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    arr = (C.c_void_p * len(buffer_ptrs))(*[C.c_void_p(int(v)) for v in buffer_ptrs])
+    L.check(L.lib().ascq_matmul_w8a8_scatter(arr, len(buffer_ptrs), first_buf, col_offset, ldc, _ptr(A), _ptr(B_nk),
+                                             _ptr(scaleA), _ptr(scaleB), _ptr(bias), M, N, K, _stream(stream)))
+
+
 def MatmulStatus(stream=None):
     """Synchronise and raise AscqError(ERR_TIMEOUT) if a matmul kernel gave up a bounded wait."""
     L.check(L.lib().ascq_matmul_status(_stream(stream)))

@@ -258,6 +258,22 @@ ascq_status ascq_mx_repack_b_kn_to_nk(uint8_t* B_nk, const uint8_t* B_kn, int K,
 ascq_status ascq_mx_repack_scale_b(uint8_t* sB_nk, const uint8_t* sB_ref, int sK, int N, void* stream);
 
 /*
+ * The same matmul with the all-gather of a column-parallel layout fused into its epilogue: the [M, N]
+ * block this call computes is written to columns [colOffset, colOffset + N) of EVERY buffer in
+ * C_bufs (each a bf16 [M, ldc] matrix, ldc >= colOffset + N).  With one process per GPU, C_bufs holds
+ * this GPU's output matrix and the peer-mapped addresses of the other GPUs' output matrices (CUDA IPC /
+ * symmetric memory); the tiles then cross NVLink as plain stores while the tensor cores work on the
+ * next tile, and no separate collective is needed.  Stores start with buffer `firstBuf` and wrap
+ * around, so ranks passing their own rank + 1 do not all write to the same GPU at once.  nBufs <= 8.
+ * The call returns when the kernel is enqueued; a cross-GPU barrier after it (after all ranks' kernels)
+ * is the caller's job before anyone reads the assembled matrix.  The reference reassembles with a
+ * separate HCCL AllGather (include/adv_api/hccl/hccl.h:77-253); this entry point has no counterpart.
+ */
+ascq_status ascq_matmul_w8a8_scatter(void* const* C_bufs, int nBufs, int firstBuf, int colOffset, int ldc,
+                                     const int8_t* A, const int8_t* B_nk, const float* sA_m, const float* sB_n,
+                                     const void* bias_bf16, int M, int N, int K, void* stream);
+
+/*
  * Synchronises `stream`, then reads and clears the status word the matmul kernels keep on the
  * current device.  ASCQ_ERR_TIMEOUT when a kernel gave up a bounded wait (its output is then
  * undefined); no counterpart in the reference, whose kernels cannot report.

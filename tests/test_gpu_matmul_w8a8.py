@@ -97,3 +97,21 @@ def test_cfg4_full_size_exact():
     # and a row block through the oracle itself
     want_C = O.matmul_w8a8(np.ascontiguousarray(A[:64]), B, sA[:64].copy(), sB, bias)
     assert_bits_equal(got_C[:64], want_C, "cfg4 rows 0..63 vs oracle")
+
+
+def test_scatter_writes_the_block_into_every_buffer():
+    # three [M, ldc] matrices stand in for this GPU's and two peers' output: the block must land at colOffset in each
+    M, N, K, ldc, col = 200, 192, 256, 640, 256
+    A, B, sA, sB, bias = make_case(M, N, K, 99)
+    want = O.matmul_w8a8(A, B, sA, sB, bias)
+    bufs = [torch.full((M, ldc), -1.0, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    dbias = torch.from_numpy(bias.view(np.int16)).to(DEV).view(torch.bfloat16)
+    ops.MatmulW8A8Scatter([b.data_ptr() for b in bufs], 1, col, ldc, t(A), t(B), t(sA), t(sB), dbias)
+    ops.MatmulStatus()
+    for b in bufs:
+        got = b.view(torch.int16).cpu().numpy().view(np.uint16)
+        assert_bits_equal(np.ascontiguousarray(got[:, col:col + N]), want, "scattered block")
+        assert (got[:, :col] == 0xBF80).all() and (got[:, col + N:] == 0xBF80).all(), "columns outside the block changed"
+    with pytest.raises(ops.AscqError):
+        ops.MatmulW8A8Scatter([bufs[0].data_ptr()] * 9, 0, 0, ldc, t(A), t(B))
