@@ -16,6 +16,9 @@
 // TMEM allocation is released and a device status word reports the timeout.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "ascq_internal.h"
 #include "numerics.cuh"
 #include "sm100_ptx.cuh"
@@ -36,11 +39,14 @@ constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA + TME
 
 __device__ int g_w8a8_status = 0;  // 0 ok, 1 = a bounded wait expired
 
-template <int BN> struct Cfg {
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+// PAIR: two CTAs of a cluster drive one tcgen05.mma.cta_group::2 on a 256 x BN tile; each CTA loads its 128 rows of A
+// and its half (BN/2 rows) of B, so every byte of B is fetched from L2 once per pair instead of once per CTA.
+template <int BN, bool PAIR> struct Cfg {
+    static constexpr int kBRows = PAIR ? BN / 2 : BN;          // rows of B this CTA loads
     static constexpr int kABytes = kBM * kBK;
-    static constexpr int kBBytes = BN * kBK;
+    static constexpr int kBBytes = kBRows * kBK;
     static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 x 48 KiB, or 6 x 32 KiB
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
     static constexpr int kEpiBytes = 2 * 2 * BN * 4;  // per accumulator: sB[BN] and bias[BN] as fp32
     static constexpr int kOutBytes = kEpiWarps * 32 * kStagePitch;  // per epilogue warp: 32 rows x 32 bf16 columns
@@ -59,11 +65,11 @@ struct Params {
     int tilesM, tilesN;
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     // stage buffers need 1024-byte alignment for the 128B swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -81,6 +87,11 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     const int lane = threadIdx.x & 31;
     const int numTiles = p.tilesM * p.tilesN;
     const int kBlocks = (p.K + kBK - 1) / kBK;
+    // work unit = CTA (single) or cluster of two CTAs (PAIR); rank = position inside the pair, rank 0 issues the MMAs
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int numUnits = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    constexpr int kTileM = PAIR ? 2 * kBM : kBM;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -89,7 +100,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmemFull[a], 1);
-            mbar_init(&tmemEmpty[a], kEpiWarps);  // one arrival per epilogue warp
+            mbar_init(&tmemEmpty[a], PAIR ? 2 * kEpiWarps : kEpiWarps);  // one arrival per epilogue warp (of both CTAs)
         }
         *abortFlag = 0;
         fence_barrier_init();
@@ -97,11 +108,20 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         prefetch_tensormap(&tmapB);
     }
     if (warp == 1) {
-        tmem_alloc(tmemBaseSlot, C::kTmemCols);
-        tmem_relinquish();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(tmemBaseSlot, C::kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmemBaseSlot, C::kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) {  // the peer's barriers must be initialised before anything is signalled across the pair
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after();
     const uint32_t tmemBase = *tmemBaseSlot;
 
@@ -110,27 +130,35 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         if (elect_one()) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % p.tilesM) * kBM;
-                const int n0 = (tile / p.tilesM) * BN;
+            for (int tile = unit; tile < numTiles && ok; tile += numUnits) {
+                const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
+                const int n0 = (tile / p.tilesM) * BN + (PAIR ? static_cast<int>(rank) * C::kBRows : 0);
                 for (int kb = 0; kb < kBlocks; ++kb, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait_bounded(&emptyBar[s], ph ^ 1, abortFlag))) break;
                     uint8_t* sa = smem + s * C::kStageBytes;
-                    mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
-                    tma_load_2d(sa, &tmapA, &fullBar[s], kb * kBK, m0);
-                    tma_load_2d(sa + C::kABytes, &tmapB, &fullBar[s], kb * kBK, n0);
+                    if constexpr (PAIR) {
+                        // both CTAs' loads are counted on the leader's barrier; the leader announces the bytes of both
+                        if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], 2 * C::kStageBytes);
+                        const uint32_t leaderBar = mapa_u32(smem_u32(&fullBar[s]), 0);
+                        tma_load_2d_pair(sa, &tmapA, leaderBar, kb * kBK, m0);
+                        tma_load_2d_pair(sa + C::kABytes, &tmapB, leaderBar, kb * kBK, n0);
+                    } else {
+                        mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
+                        tma_load_2d(sa, &tmapA, &fullBar[s], kb * kBK, m0);
+                        tma_load_2d(sa + C::kABytes, &tmapB, &fullBar[s], kb * kBK, n0);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (elect_one()) {
-            constexpr uint32_t idesc = idesc_i8(kBM, BN);
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = idesc_i8(kTileM, BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+            for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
                 const int acc = local & 1;
                 const uint32_t accPh = (local >> 1) & 1;
                 if (!(ok = mbar_wait_bounded(&tmemEmpty[acc], accPh ^ 1, abortFlag))) break;
@@ -147,11 +175,17 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         // advancing K inside the swizzle atom: +32 bytes on the start address (>> 4 = 2)
-                        mma_i8(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                        if constexpr (PAIR) mma_i8_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                        else mma_i8(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
                     }
-                    tc_commit(&emptyBar[s]);  // the stage is free once these MMAs have read it
+                    // the stage is free (in both CTAs of a pair) once these MMAs have read it
+                    if constexpr (PAIR) tc_commit_pair(&emptyBar[s], 3);
+                    else tc_commit(&emptyBar[s]);
                 }
-                if (ok) tc_commit(&tmemFull[acc]);
+                if (ok) {
+                    if constexpr (PAIR) tc_commit_pair(&tmemFull[acc], 3);
+                    else tc_commit(&tmemFull[acc]);
+                }
             }
         }
     } else {
@@ -161,10 +195,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         uint8_t* stageW = outStage + (warp - 2) * (32 * kStagePitch);
         uint32_t local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+        for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
             const int acc = local & 1;
             const uint32_t accPh = (local >> 1) & 1;
-            const int m0 = (tile % p.tilesM) * kBM;
+            const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
             const int n0 = (tile / p.tilesM) * BN;
             ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
             tc_fence_after();
@@ -280,12 +314,19 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmemEmpty[acc]);
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&tmemEmpty[acc]), 0));  // the leader's barrier
+                else mbar_arrive(&tmemEmpty[acc]);
+            }
         }
     }
 
     // ---------------- teardown ----------------
     __syncthreads();
+    if constexpr (PAIR) {  // neither CTA may leave (or free tensor memory) while its partner can still touch it
+        cluster_arrive();
+        cluster_wait();
+    }
     if (*abortFlag) {
         if (threadIdx.x == 0) atomicExch(&g_w8a8_status, 1);
         // give bulk copies that may still be in flight time to land before the shared memory is handed back
@@ -295,25 +336,43 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmemBase, C::kTmemCols);
+        if constexpr (PAIR) tmem_dealloc_pair(tmemBase, C::kTmemCols);
+        else tmem_dealloc(tmemBase, C::kTmemCols);
     }
 }
 
 // ---- host side -------------------------------------------------------------------------------------
-template <int BN> ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
+template <int BN, bool PAIR> ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, PAIR>;
     static bool attrSet = false;
     if (!attrSet) {
-        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(C::kSmemBytes)));
         attrSet = true;
     }
-    p.tilesM = (p.M + kBM - 1) / kBM;
+    p.tilesM = (p.M + (PAIR ? 2 * kBM : kBM) - 1) / (PAIR ? 2 * kBM : kBM);
     p.tilesN = (p.N + BN - 1) / BN;
     const int tiles = p.tilesM * p.tilesN;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    w8a8_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+    if constexpr (PAIR) {
+        const int clusters = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR>, ta, tb, p));
+    } else {
+        const int grid = tiles < sm_count() ? tiles : sm_count();
+        w8a8_kernel<BN, PAIR><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+    }
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
@@ -354,15 +413,23 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     p.accDump = accDump;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc;
 
-    // wide tiles when they fill the machine, narrower ones for small problems (e.g. a column shard)
+    // CTA pairs on 256 x 256 tiles when they fill the machine; single CTAs on 128 x 256, or 128 x 128 for small
+    // problems (e.g. a column shard).  ASCQ_W8A8_TILE=pair|wide|narrow overrides the choice.
     const int tiles256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
-    const bool wide = tiles256 >= sm_count();
+    const int tilesPair = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
+    int mode = tilesPair >= sm_count() / 2 ? 2 : (tiles256 >= sm_count() ? 1 : 0);
+    if (const char* e = getenv("ASCQ_W8A8_TILE")) {
+        if (!strcmp(e, "pair")) mode = 2;
+        else if (!strcmp(e, "wide")) mode = 1;
+        else if (!strcmp(e, "narrow")) mode = 0;
+    }
     CUtensorMap ta, tb;
     ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K), kBM);
     if (rc != ASCQ_OK) return rc;
-    rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), wide ? 256 : 128);
+    rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
-    return wide ? launch<256>(ta, tb, p, st) : launch<128>(ta, tb, p, st);
+    if (mode == 2) return launch<256, true>(ta, tb, p, st);
+    return mode == 1 ? launch<256, false>(ta, tb, p, st) : launch<128, false>(ta, tb, p, st);
 }
 }  // namespace
 }  // namespace ascq
