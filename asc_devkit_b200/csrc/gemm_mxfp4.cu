@@ -21,6 +21,8 @@
 // Roofline: dense FP4 tensor throughput; 2*sumM*N*K flops per call.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -50,20 +52,25 @@ struct TileInfo {
     int pad;
 };
 
-template <int BN> struct Cfg {
+// PAIR: two CTAs of a cluster drive one tcgen05.mma.cta_group::2 on a 256 x BN tile.  Each CTA loads its 128 rows
+// of A (with their scales), its half of B's rows, and the scales of ALL BN rows of B (every CTA multiplies its
+// rows with every column), so B's data crosses the L2-to-SM fabric once per pair.
+template <int BN, bool PAIR> struct Cfg {
     static constexpr int kAccStages = (BN == 256) ? 1 : 2;
+    static constexpr int kBRows = PAIR ? BN / 2 : BN;
     static constexpr int kABytes = kBM * kBKBytes;
-    static constexpr int kBBytes = BN * kBKBytes;
+    static constexpr int kBBytes = kBRows * kBKBytes;
     static constexpr int kSfaBytes = 2 * kChunkBytes;
     static constexpr int kSfbBytes = (BN / 128) * 2 * kChunkBytes;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kStages = PAIR ? 5 : ((BN == 256) ? 4 : 6);
     static constexpr int kSfaCols = 8;               // 2 chunks x 4 columns
     static constexpr int kSfbCols = 2 * (BN / 32);   // 2 chunks x N/32 columns
     static constexpr int kAccCols = kAccStages * BN;
     static constexpr int kTmemCols = 512;
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
-    static_assert(kAccCols + kSfaCols + kSfbCols <= 512, "tensor memory budget");
+    static_assert(kAccCols + 2 * (kSfaCols + kSfbCols) <= 512, "tensor memory budget (scale columns are double buffered)");
+    static_assert(kStageBytes % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
 };
 
 struct Params {
@@ -107,11 +114,12 @@ repack_sf_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, con
 }
 
 // ---- matmul ----------------------------------------------------------------------------------------
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
-mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
+mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+             const __grid_constant__ CUtensorMap tmapSfa, const __grid_constant__ CUtensorMap tmapSfb, const Params p)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
@@ -125,6 +133,12 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int numTiles = p.numTilesM * p.tilesN;
+    // work unit = CTA, or cluster of two CTAs (PAIR); rank 0 of a pair issues the MMAs.  In PAIR mode p.numTilesM
+    // counts 256-row tiles and the tile table holds two consecutive 128-row entries per tile.
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int numUnits = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    constexpr int kTileM = PAIR ? 2 * kBM : kBM;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -133,7 +147,7 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmemFull[a], 1);
-            mbar_init(&tmemEmpty[a], kEpiWarps);
+            mbar_init(&tmemEmpty[a], PAIR ? 2 * kEpiWarps : kEpiWarps);
         }
         *abortFlag = 0;
         fence_barrier_init();
@@ -141,48 +155,71 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         prefetch_tensormap(&tmapB);
     }
     if (warp == 1) {
-        tmem_alloc(tmemBaseSlot, C::kTmemCols);
-        tmem_relinquish();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(tmemBaseSlot, C::kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmemBaseSlot, C::kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) {  // the partner's barriers must exist before anything is signalled across the pair
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after();
     const uint32_t tmemBase = *tmemBaseSlot;
-    const uint32_t sfaCol = tmemBase + C::kAccCols;
-    const uint32_t sfbCol = sfaCol + C::kSfaCols;
+    const uint32_t sfCol0 = tmemBase + C::kAccCols;  // two sets of scale columns, alternating per k-block
 
     if (warp == 0) {
         if (elect_one()) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x) {
-                const int mt = tile % p.numTilesM, nt = tile / p.numTilesM;
+            for (int tile = unit; tile < numTiles && ok; tile += numUnits) {
+                const int mt = (tile % p.numTilesM) * (PAIR ? 2 : 1) + static_cast<int>(rank), nt = tile / p.numTilesM;
                 const TileInfo ti = p.tiles[mt];
                 const int n0 = nt * BN;
-                const uint8_t* sfa = p.sfaPacked + static_cast<size_t>(mt) * p.kBlocks * C::kSfaBytes;
-                const uint8_t* sfb = p.sfbPacked +
-                                     (static_cast<size_t>(ti.group) * p.nTilesPerGroup128 + n0 / 128) * p.kBlocks * 2 * kChunkBytes;
+                const size_t sfaRec = static_cast<size_t>(mt) * p.kBlocks;  // 1 KiB records: [A tile][k-block]
+                const size_t sfbRec = (static_cast<size_t>(ti.group) * p.nTilesPerGroup128 + n0 / 128) * p.kBlocks;
                 for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait_bounded(&emptyBar[s], ph ^ 1, abortFlag))) break;
                     uint8_t* st = smem + s * C::kStageBytes;
-                    mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
-                    tma_load_2d(st, &tmapA, &fullBar[s], kb * kBKBytes, ti.rowStart);
-                    tma_load_2d(st + C::kABytes, &tmapB, &fullBar[s], kb * kBKBytes, ti.group * p.N + n0);
-                    bulk_load(st + C::kABytes + C::kBBytes, sfa + static_cast<size_t>(kb) * C::kSfaBytes, C::kSfaBytes, &fullBar[s]);
+                    uint8_t* stSf = st + C::kABytes + C::kBBytes;
+                    if constexpr (PAIR) {
+                        // all loads of both CTAs are counted on the leader's barrier; the leader announces both shares
+                        if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], 2 * C::kStageBytes);
+                        const uint32_t bar = mapa_u32(smem_u32(&fullBar[s]), 0);
+                        tma_load_2d_pair(st, &tmapA, bar, kb * kBKBytes, ti.rowStart);
+                        tma_load_2d_pair(st + C::kABytes, &tmapB, bar, kb * kBKBytes,
+                                         ti.group * p.N + n0 + static_cast<int>(rank) * C::kBRows);
+                        tma_load_2d_pair(stSf, &tmapSfa, bar, 0, static_cast<int>(sfaRec + kb));
 #pragma unroll
-                    for (int t = 0; t < BN / 128; ++t)
-                        bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2 * kChunkBytes,
-                                  sfb + (static_cast<size_t>(t) * p.kBlocks + kb) * 2 * kChunkBytes, 2 * kChunkBytes, &fullBar[s]);
+                        for (int t = 0; t < BN / 128; ++t)
+                            tma_load_2d_pair(stSf + C::kSfaBytes + t * 2 * kChunkBytes, &tmapSfb, bar, 0,
+                                             static_cast<int>(sfbRec + static_cast<size_t>(t) * p.kBlocks + kb));
+                    } else {
+                        mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
+                        tma_load_2d(st, &tmapA, &fullBar[s], kb * kBKBytes, ti.rowStart);
+                        tma_load_2d(st + C::kABytes, &tmapB, &fullBar[s], kb * kBKBytes, ti.group * p.N + n0);
+                        bulk_load(stSf, p.sfaPacked + (sfaRec + kb) * C::kSfaBytes, C::kSfaBytes, &fullBar[s]);
+#pragma unroll
+                        for (int t = 0; t < BN / 128; ++t)
+                            bulk_load(stSf + C::kSfaBytes + t * 2 * kChunkBytes,
+                                      p.sfbPacked + (sfbRec + static_cast<size_t>(t) * p.kBlocks + kb) * 2 * kChunkBytes,
+                                      2 * kChunkBytes, &fullBar[s]);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        if (elect_one()) {
+        if (rank == 0 && elect_one()) {
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+            for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
                 const int acc = local % C::kAccStages;
                 const uint32_t accPh = (local / C::kAccStages) & 1;
                 if (!(ok = mbar_wait_bounded(&tmemEmpty[acc], accPh ^ 1, abortFlag))) break;
@@ -196,15 +233,22 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                     const uint32_t base = smem_u32(smem + s * C::kStageBytes);
                     const uint32_t sfaSmem = base + C::kABytes + C::kBBytes;
                     const uint32_t sfbSmem = sfaSmem + C::kSfaBytes;
+                    // the copy for this k-block must not wait for the previous k-block's MMAs to finish reading theirs
+                    const uint32_t sfaCol = sfCol0 + (it & 1) * (C::kSfaCols + C::kSfbCols);
+                    const uint32_t sfbCol = sfaCol + C::kSfaCols;
                     // scales: shared -> tensor memory.  Chunk q of A -> columns sfaCol + 4q; chunk q of the
                     // 128-row tile t of B -> columns sfbCol + q*(BN/32) + 4t.
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
-                        tc_cp_32x128b_warpx4(sfaCol + 4 * q, smem_desc_noswizzle(sfaSmem + q * kChunkBytes, 0, 128));
+                        const uint64_t da = smem_desc_noswizzle(sfaSmem + q * kChunkBytes, 0, 128);
+                        if constexpr (PAIR) tc_cp_32x128b_warpx4_pair(sfaCol + 4 * q, da);  // each CTA from its own shared memory
+                        else tc_cp_32x128b_warpx4(sfaCol + 4 * q, da);
 #pragma unroll
-                        for (int t = 0; t < BN / 128; ++t)
-                            tc_cp_32x128b_warpx4(sfbCol + q * (BN / 32) + 4 * t,
-                                                 smem_desc_noswizzle(sfbSmem + (t * 2 + q) * kChunkBytes, 0, 128));
+                        for (int t = 0; t < BN / 128; ++t) {
+                            const uint64_t db = smem_desc_noswizzle(sfbSmem + (t * 2 + q) * kChunkBytes, 0, 128);
+                            if constexpr (PAIR) tc_cp_32x128b_warpx4_pair(sfbCol + q * (BN / 32) + 4 * t, db);
+                            else tc_cp_32x128b_warpx4(sfbCol + q * (BN / 32) + 4 * t, db);
+                        }
                     }
                     const uint64_t descA = smem_desc_sw128(base);
                     const uint64_t descB = smem_desc_sw128(base + C::kABytes);
@@ -212,12 +256,20 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                     for (int k = 0; k < 4; ++k) {
                         // K = 64 per MMA = 32 bytes: chunk k/2, scale bytes (k%2)*2 and (k%2)*2+1 of each column
                         const uint32_t sfId = (k & 1) * 2;
-                        mma_mxf4(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kBM, BN, sfId, sfId), (kb | k) != 0,
-                                 sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
+                        if constexpr (PAIR)
+                            mma_mxf4_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kTileM, BN, sfId, sfId), (kb | k) != 0,
+                                          sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
+                        else
+                            mma_mxf4(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kTileM, BN, sfId, sfId), (kb | k) != 0,
+                                     sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
                     }
-                    tc_commit(&emptyBar[s]);
+                    if constexpr (PAIR) tc_commit_pair(&emptyBar[s], 3);
+                    else tc_commit(&emptyBar[s]);
                 }
-                if (ok) tc_commit(&tmemFull[acc]);
+                if (ok) {
+                    if constexpr (PAIR) tc_commit_pair(&tmemFull[acc], 3);
+                    else tc_commit(&tmemFull[acc]);
+                }
             }
         }
     } else {
@@ -230,10 +282,10 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         constexpr int kChunks = BN / 64;  // 32-column chunks per warp
         uint32_t local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x, ++local) {
+        for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
             const int acc = local % C::kAccStages;
             const uint32_t accPh = (local / C::kAccStages) & 1;
-            const int mt = tile % p.numTilesM, nt = tile / p.numTilesM;
+            const int mt = (tile % p.numTilesM) * (PAIR ? 2 : 1) + static_cast<int>(rank), nt = tile / p.numTilesM;
             const TileInfo ti = p.tiles[mt];
             const int n0 = nt * BN + half * (BN / 2);
             if (!(ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag))) break;
@@ -245,7 +297,10 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmemEmpty[acc]);
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&tmemEmpty[acc]), 0));  // the leader's barrier
+                else mbar_arrive(&tmemEmpty[acc]);
+            }
 
             const int rIn = q * 32 + lane;
             const bool rowOk = rIn < ti.rowsValid;
@@ -276,6 +331,10 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     }
 
     __syncthreads();
+    if constexpr (PAIR) {  // neither CTA may leave (or free tensor memory) while its partner can still touch it
+        cluster_arrive();
+        cluster_wait();
+    }
     if (*abortFlag) {
         if (threadIdx.x == 0) atomicExch(&g_mxfp4_status, 1);
         const long long t0 = clock64();
@@ -284,7 +343,8 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     }
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmemBase, C::kTmemCols);
+        if constexpr (PAIR) tmem_dealloc_pair(tmemBase, C::kTmemCols);
+        else tmem_dealloc(tmemBase, C::kTmemCols);
     }
 }
 
@@ -297,7 +357,8 @@ struct Layout {
 Layout make_layout(int64_t sumM, int G, int K, int N)
 {
     Layout L{};
-    L.tilesM = static_cast<int>((sumM + kBM - 1) / kBM + G);  // upper bound: every group may add one partial tile
+    // upper bound on 128-row entries: with 256-row pair tiles every group may add up to two partly filled entries
+    L.tilesM = static_cast<int>((sumM + kBM - 1) / kBM + 2 * static_cast<int64_t>(G) + 2);
     L.kBlocks = (K + kBKElems - 1) / kBKElems;
     L.nTiles128 = 2 * ((N + 255) / 256);  // even, so a 256-wide N tile always finds both of its 128-row halves
     L.tileOff = 0;
@@ -307,20 +368,38 @@ Layout make_layout(int64_t sumM, int G, int K, int N)
     return L;
 }
 
-template <int BN>
-ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
+template <int BN, bool PAIR>
+ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb, Params p,
+                   cudaStream_t st)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, PAIR>;
     static bool attrSet = false;
     if (!attrSet) {
-        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(C::kSmemBytes)));
         attrSet = true;
     }
     p.tilesN = (p.N + BN - 1) / BN;
     const int tiles = p.numTilesM * p.tilesN;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    mxfp4_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+    if constexpr (PAIR) {
+        const int clusters = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mxfp4_kernel<BN, PAIR>, ta, tb, tsa, tsb, p));
+    } else {
+        const int grid = tiles < sm_count() ? tiles : sm_count();
+        mxfp4_kernel<BN, PAIR><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, tsa, tsb, p);
+    }
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
@@ -361,15 +440,27 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
         return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", L.total, workspaceBytes);
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(ASCQ_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
 
-    // tile table: zero-row groups are skipped (quant_group_matmul_custom.asc:265-267)
+    // Single CTAs on 128-row tiles by default.  The CTA-pair variant (256-row tiles, B fetched once per pair) is
+    // measured no faster on this problem class so far; ASCQ_MXFP4_TILE=pair selects it.
+    bool pair = false;
+    if (const char* e = getenv("ASCQ_MXFP4_TILE")) {
+        if (!strcmp(e, "pair")) pair = N >= 256;
+        else if (!strcmp(e, "single")) pair = false;
+    }
+    // tile table: zero-row groups are skipped (quant_group_matmul_custom.asc:265-267).  One entry per 128 rows;
+    // in pair mode entries come in twos (the two halves of a 256-row tile, the second possibly empty).
     std::vector<TileInfo> tiles;
     tiles.reserve(L.tilesM);
     int64_t start = 0;
+    const int64_t step = pair ? 2 * kBM : kBM;
     for (int g = 0; g < G; ++g) {
         const int64_t mg = groupList_host[g];
-        for (int64_t r = 0; r < mg; r += kBM) {
-            TileInfo t{static_cast<int>(start + r), static_cast<int>(mg - r < kBM ? mg - r : kBM), g, 0};
-            tiles.push_back(t);
+        for (int64_t r = 0; r < mg; r += step) {
+            for (int64_t h = 0; h < step; h += kBM) {
+                const int64_t left = mg - (r + h);
+                TileInfo t{static_cast<int>(start + r + h), static_cast<int>(left <= 0 ? 0 : (left < kBM ? left : kBM)), g, 0};
+                tiles.push_back(t);
+            }
         }
         start += mg;
     }
@@ -395,16 +486,23 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     p.tiles = reinterpret_cast<const TileInfo*>(ws + L.tileOff);
     p.sfaPacked = ws + L.sfaOff;
     p.sfbPacked = ws + L.sfbOff;
-    p.numTilesM = numTilesM;
+    p.numTilesM = pair ? numTilesM / 2 : numTilesM;
     p.N = N; p.K = K; p.kBlocks = L.kBlocks; p.nTilesPerGroup128 = L.nTiles128;
 
     const bool wide = N >= 256;
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tsa, tsb;
     ascq_status rc = make_tmap_u8(&ta, A_fp4, static_cast<uint64_t>(sumM), static_cast<uint64_t>(K / 2), kBM);
     if (rc != ASCQ_OK) return rc;
-    rc = make_tmap_u8(&tb, B_fp4, static_cast<uint64_t>(G) * N, static_cast<uint64_t>(K / 2), wide ? 256 : 128);
+    rc = make_tmap_u8(&tb, B_fp4, static_cast<uint64_t>(G) * N, static_cast<uint64_t>(K / 2), pair ? 128 : (wide ? 256 : 128));
     if (rc != ASCQ_OK) return rc;
-    return wide ? launch<256>(ta, tb, p, st) : launch<128>(ta, tb, p, st);
+    // the packed scales as 1 KiB records (pair mode loads them with tensor copies so that the partner CTA's loads
+    // can be counted on the leader's barrier)
+    rc = make_tmap_kib_rows(&tsa, ws + L.sfaOff, static_cast<uint64_t>(numTilesM) * L.kBlocks);
+    if (rc != ASCQ_OK) return rc;
+    rc = make_tmap_kib_rows(&tsb, ws + L.sfbOff, static_cast<uint64_t>(G) * L.nTiles128 * L.kBlocks);
+    if (rc != ASCQ_OK) return rc;
+    if (pair) return launch<256, true>(ta, tb, tsa, tsb, p, st);
+    return wide ? launch<256, false>(ta, tb, tsa, tsb, p, st) : launch<128, false>(ta, tb, tsa, tsb, p, st);
 }
 
 // ---- entry point for callers that may not allocate device memory ------------------------------------

@@ -213,6 +213,21 @@ __device__ __forceinline__ void mma_i8_pair(uint32_t tmemD, uint64_t descA, uint
         ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ void mma_mxf4_pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate,
+                                              uint32_t tmemSfa, uint32_t tmemSfb)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(tmemSfa), "r"(tmemSfb)
+        : "memory");
+}
+// shared -> tensor memory in both CTAs of the pair (each from its own shared memory, same offsets)
+__device__ __forceinline__ void tc_cp_32x128b_warpx4_pair(uint32_t tmemDst, uint64_t smemDesc)
+{
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmemDst), "l"(smemDesc) : "memory");
+}
 // Arrives (once the issued MMAs are done) on the mbarrier at this shared-memory offset in every CTA of `ctaMask`.
 __device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t ctaMask)
 {
