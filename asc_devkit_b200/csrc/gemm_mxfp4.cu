@@ -42,6 +42,7 @@ constexpr int kBKElems = 256;
 constexpr int kChunkBytes = 512;  // packed scales of 128 rows x 128 K-elements
 constexpr int kEpiWarps = 8;   // two per TMEM lane quarter; each drains half of the accumulator columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kStagePitch = 80;  // bytes per staged output row: 64 B of bf16 + 16 B pad (conflict-free both ways)
 
 __device__ int g_mxfp4_status = 0;
 
@@ -68,7 +69,9 @@ template <int BN, bool PAIR> struct Cfg {
     static constexpr int kSfbCols = 2 * (BN / 32);   // 2 chunks x N/32 columns
     static constexpr int kAccCols = kAccStages * BN;
     static constexpr int kTmemCols = 512;
-    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
+    static constexpr int kOutBytes = kEpiWarps * 32 * kStagePitch;  // per epilogue warp: 32 rows x 32 bf16 columns
+    static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kOutBytes;
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
     static_assert(kAccCols + 2 * (kSfaCols + kSfbCols) <= 512, "tensor memory budget (scale columns are double buffered)");
     static_assert(kStageBytes % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
 };
@@ -114,6 +117,22 @@ repack_sf_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, con
 }
 
 // ---- matmul ----------------------------------------------------------------------------------------
+// Tile order.  The CTAs of one wave work on consecutive tile indices, so the order decides what the wave keeps
+// in L2.  Columns are cut into bands of kBandN tiles; inside a band the column index runs fastest, then the row
+// tile.  A wave then covers (number of CTAs / kBandN) row tiles x kBandN column tiles: a few MB of A and the
+// matching slice of B of the one or two groups those rows belong to, and every byte of A and B comes from HBM
+// about once.  (Row tile fastest would sweep all of A once per column tile.)
+constexpr int kBandN = 8;
+__device__ __forceinline__ void tile_coords(int tile, int numTilesM, int tilesN, int& mt, int& nt)
+{
+    const int perBand = numTilesM * kBandN;
+    const int band = tile / perBand;
+    const int within = tile - band * perBand;
+    const int width = min(kBandN, tilesN - band * kBandN);
+    mt = within / width;
+    nt = band * kBandN + (within - mt * width);
+}
+
 template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
@@ -129,6 +148,7 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     uint64_t* tmemEmpty = tmemFull + 2;
     uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
+    uint8_t* outStage = reinterpret_cast<uint8_t*>(bars) + 256;  // [kEpiWarps][32][kStagePitch]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -178,7 +198,9 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             uint32_t it = 0;
             bool ok = true;
             for (int tile = unit; tile < numTiles && ok; tile += numUnits) {
-                const int mt = (tile % p.numTilesM) * (PAIR ? 2 : 1) + static_cast<int>(rank), nt = tile / p.numTilesM;
+                int mt, nt;
+                tile_coords(tile, p.numTilesM, p.tilesN, mt, nt);
+                mt = mt * (PAIR ? 2 : 1) + static_cast<int>(rank);
                 const TileInfo ti = p.tiles[mt];
                 const int n0 = nt * BN;
                 const size_t sfaRec = static_cast<size_t>(mt) * p.kBlocks;  // 1 KiB records: [A tile][k-block]
@@ -285,7 +307,9 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
             const int acc = local % C::kAccStages;
             const uint32_t accPh = (local / C::kAccStages) & 1;
-            const int mt = (tile % p.numTilesM) * (PAIR ? 2 : 1) + static_cast<int>(rank), nt = tile / p.numTilesM;
+            int mt, nt;
+            tile_coords(tile, p.numTilesM, p.tilesN, mt, nt);
+            mt = mt * (PAIR ? 2 : 1) + static_cast<int>(rank);
             const TileInfo ti = p.tiles[mt];
             const int n0 = nt * BN + half * (BN / 2);
             if (!(ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag))) break;
@@ -306,25 +330,37 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             const bool rowOk = rIn < ti.rowsValid;
             __nv_bfloat16* crow = p.C + static_cast<size_t>(ti.rowStart + rIn) * p.N + n0;
             const bool vecStore = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+            uint8_t* stageW = outStage + (warp - 2) * (32 * kStagePitch);
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
                 const int n = n0 + c * 32;
-                if (rowOk && n < p.N) {
-                    uint32_t packed[16];
+                if (n >= p.N) continue;  // uniform over the warp
+                uint32_t packed[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        packed[j] = pack_bf16x2_sat(__uint_as_float(r[c][2 * j]), __uint_as_float(r[c][2 * j + 1]));
-                    if (n + 32 <= p.N && vecStore) {
-                        uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
+                for (int j = 0; j < 16; ++j)
+                    packed[j] = pack_bf16x2_sat(__uint_as_float(r[c][2 * j]), __uint_as_float(r[c][2 * j + 1]));
+                if (n + 32 <= p.N && vecStore) {
+                    // Transpose through this warp's staging rows: every store instruction then writes eight complete
+                    // 64-byte row segments instead of thirty-two 16-byte pieces of thirty-two different rows.
 #pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    } else {
+                    for (int v = 0; v < 4; ++v)
+                        *reinterpret_cast<uint4*>(stageW + lane * kStagePitch + v * 16) =
+                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    __syncwarp();
+                    const int piece = lane & 3;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (n + j < p.N)
-                                crow[c * 32 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[j >> 1] >> ((j & 1) * 16)));
+                    for (int i = 0; i < 4; ++i) {
+                        const int row = q * 32 + i * 8 + (lane >> 2);
+                        const uint4 val = *reinterpret_cast<const uint4*>(stageW + (i * 8 + (lane >> 2)) * kStagePitch + piece * 16);
+                        if (row < ti.rowsValid)
+                            *reinterpret_cast<uint4*>(p.C + static_cast<size_t>(ti.rowStart + row) * p.N + n + piece * 8) = val;
                     }
+                    __syncwarp();
+                } else if (rowOk) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n + j < p.N)
+                            crow[c * 32 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[j >> 1] >> ((j & 1) * 16)));
                 }
             }
         }
