@@ -85,35 +85,48 @@ struct Params {
 };
 
 // ---- scale repack ----------------------------------------------------------------------------------
-// One thread per 32-bit word of the packed layout.  `rowBase(tile)` comes from the tile table (A) or is
-// group*N + tile128*128 (B); rows past `rowLimit(tile)` read as zero.
+// One launch rewrites the e8m0 scales of A and of B into the records the matmul copies to tensor memory.
+// Block (x, y): x < numTilesA is a 128-row tile of A (rows from the tile table), otherwise a 128-row tile of B
+// (group*N + tile128*128); y selects a slab of kSlab 4-byte chunks along K.  The block reads its rows as they lie
+// in memory (whole rows, coalesced), turns them in shared memory and writes whole 512-byte chunks: word w of a
+// chunk holds the four scale bytes of row 32*(w&3) + (w>>2).  Rows or chunks without data get scale 1.0 (0x7F);
+// the operand bytes there are zero.
+constexpr int kSlab = 64;
 __global__ void __launch_bounds__(256)
-repack_sf_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src, const TileInfo* __restrict__ tiles, int numTiles,
-                 int kChunks, int kChunksValid, int sfRowBytes, int N, int tilesPerGroup, long long totalRows)
+repack_sf_kernel(uint8_t* __restrict__ dstA, uint8_t* __restrict__ dstB, const uint8_t* __restrict__ srcA,
+                 const uint8_t* __restrict__ srcB, const TileInfo* __restrict__ tiles, int numTilesA, int kChunks,
+                 int kChunksValid, int sfRowBytes, int N, int tilesPerGroup, long long totalRowsA)
 {
-    const long long word = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    const long long total = static_cast<long long>(numTiles) * kChunks * (kChunkBytes / 4);
-    if (word >= total) return;
-    const int w = static_cast<int>(word % (kChunkBytes / 4));
-    const long long tc = word / (kChunkBytes / 4);
-    const int chunk = static_cast<int>(tc % kChunks);
-    const int tile = static_cast<int>(tc / kChunks);
-    const int l = w >> 2, c = w & 3;
-    const int r = c * 32 + l;
-    long long row;
-    bool valid;
-    if (tiles != nullptr) {  // A: tiles follow the group boundaries
-        row = static_cast<long long>(tiles[tile].rowStart) + r;
-        valid = row < totalRows;
-    } else {  // B: 128-row tiles inside each group's [N, K] block
-        const int g = tile / tilesPerGroup, t = tile % tilesPerGroup;
-        const int n = t * 128 + r;
-        row = static_cast<long long>(g) * N + n;
-        valid = n < N;
+    __shared__ uint32_t sm[128][kSlab + 1];
+    const int slab0 = blockIdx.y * kSlab;
+    const int nch = min(kSlab, kChunks - slab0);
+    const bool isA = static_cast<int>(blockIdx.x) < numTilesA;
+    const int tile = isA ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) - numTilesA;
+    long long rowBase;
+    int rowsValid;
+    if (isA) {
+        rowBase = tiles[tile].rowStart;
+        const long long left = totalRowsA - rowBase;
+        rowsValid = left < 128 ? static_cast<int>(left) : 128;
+    } else {
+        const int g = tile / tilesPerGroup, t = tile - g * tilesPerGroup;
+        rowBase = static_cast<long long>(g) * N + t * 128;
+        rowsValid = min(128, N - t * 128);
     }
-    uint32_t v = 0x7F7F7F7Fu;  // scale 1.0 where there is no data (the operand bytes there are zero)
-    if (valid && chunk < kChunksValid) v = *reinterpret_cast<const uint32_t*>(src + row * sfRowBytes + chunk * 4);
-    reinterpret_cast<uint32_t*>(dst)[word] = v;
+    const uint8_t* src = isA ? srcA : srcB;
+    for (int idx = threadIdx.x; idx < 128 * nch; idx += blockDim.x) {
+        const int r = idx / nch, ch = idx - r * nch;
+        uint32_t v = 0x7F7F7F7Fu;
+        if (r < rowsValid && slab0 + ch < kChunksValid)
+            v = *reinterpret_cast<const uint32_t*>(src + (rowBase + r) * sfRowBytes + (slab0 + ch) * 4);
+        sm[r][ch] = v;
+    }
+    __syncthreads();
+    uint32_t* dst = reinterpret_cast<uint32_t*>(isA ? dstA : dstB) + (static_cast<size_t>(tile) * kChunks + slab0) * (kChunkBytes / 4);
+    for (int idx = threadIdx.x; idx < 128 * nch; idx += blockDim.x) {
+        const int ch = idx >> 7, w = idx & 127;
+        dst[idx] = sm[(w & 3) * 32 + (w >> 2)][ch];
+    }
 }
 
 // ---- matmul ----------------------------------------------------------------------------------------
@@ -476,12 +489,11 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
         return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", L.total, workspaceBytes);
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(ASCQ_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
 
-    // Single CTAs on 128-row tiles by default.  The CTA-pair variant (256-row tiles, B fetched once per pair) is
-    // measured no faster on this problem class so far; ASCQ_MXFP4_TILE=pair selects it.
-    bool pair = false;
+    // CTA pairs on 256-row tiles (B fetched once per pair) when N allows; ASCQ_MXFP4_TILE=single selects single
+    // CTAs on 128-row tiles, which waste fewer rows when the groups are much shorter than 256 rows.
+    bool pair = N >= 256;
     if (const char* e = getenv("ASCQ_MXFP4_TILE")) {
-        if (!strcmp(e, "pair")) pair = N >= 256;
-        else if (!strcmp(e, "single")) pair = false;
+        if (!strcmp(e, "single")) pair = false;
     }
     // tile table: zero-row groups are skipped (quant_group_matmul_custom.asc:265-267).  One entry per 128 rows;
     // in pair mode entries come in twos (the two halves of a 256-row tile, the second possibly empty).
@@ -508,12 +520,10 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     const int kChunks = L.kBlocks * 2;
     const int sfRowBytes = K / 32;
     {
-        const long long words = static_cast<long long>(numTilesM) * kChunks * (kChunkBytes / 4);
-        repack_sf_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, st>>>(
-            ws + L.sfaOff, sA_e8m0, reinterpret_cast<const TileInfo*>(ws + L.tileOff), numTilesM, kChunks, K / 128, sfRowBytes, N, 0, sumM);
-        const long long wordsB = static_cast<long long>(G) * L.nTiles128 * kChunks * (kChunkBytes / 4);
-        repack_sf_kernel<<<static_cast<unsigned>((wordsB + 255) / 256), 256, 0, st>>>(
-            ws + L.sfbOff, sB_e8m0, nullptr, G * L.nTiles128, kChunks, K / 128, sfRowBytes, N, L.nTiles128, 0);
+        const dim3 grid(static_cast<unsigned>(numTilesM + G * L.nTiles128), static_cast<unsigned>((kChunks + kSlab - 1) / kSlab));
+        repack_sf_kernel<<<grid, 256, 0, st>>>(ws + L.sfaOff, ws + L.sfbOff, sA_e8m0, sB_e8m0,
+                                               reinterpret_cast<const TileInfo*>(ws + L.tileOff), numTilesM, kChunks, K / 128,
+                                               sfRowBytes, N, L.nTiles128, sumM);
         ASCQ_CUDA_CHECK(cudaGetLastError());
     }
 
