@@ -158,6 +158,23 @@ __device__ __forceinline__ void apply_op(CT (&x)[VEC], const CT (&s)[SV], const 
             }
             x2[q] = v;
         }
+    } else if constexpr (std::is_same<CT, float>::value && (VEC % 2 == 0)) {
+#pragma unroll
+        for (int q = 0; q < VEC / 2; ++q) {
+            const int s0 = kVecScale ? 2 * q : 0, s1 = kVecScale ? 2 * q + 1 : 0;
+            float& v0 = x[2 * q];
+            float& v1 = x[2 * q + 1];
+            if constexpr (OP == kOpQuant) {
+                mul2_rn(v0, v1, s[s0], s[s1]);
+                if constexpr (HAS_OFF) add2_rn(v0, v1, o[s0], o[s1]);
+            } else if constexpr (OP == kOpDequant) {
+                mul2_rn(v0, v1, s[s0], s[s1]);
+                if constexpr (HAS_TOK) mul2_rn(v0, v1, tok, tok);
+            } else {
+                if constexpr (HAS_OFF) add2_rn(v0, v1, o[s0], o[s1]);
+                mul2_rn(v0, v1, s[s0], s[s1]);
+            }
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
@@ -178,8 +195,19 @@ __device__ __forceinline__ void apply_op(CT (&x)[VEC], const CT (&s)[SV], const 
     }
 }
 
+// Tuning constants (measured on config 2/3-sized and larger inputs): four resident CTAs per SM (at most 64
+// registers per thread), two row batches in flight per thread, about sixteen CTAs per SM in the grid.
+#ifndef ASCQ_EW_MINB
+#define ASCQ_EW_MINB 4
+#endif
+#ifndef ASCQ_EW_U
+#define ASCQ_EW_U 2
+#endif
+#ifndef ASCQ_EW_TARGET
+#define ASCQ_EW_TARGET 16u
+#endif
 template <int OP, typename Src, typename Dst, typename Sc, typename CT, int SMODE, bool HAS_OFF, bool HAS_TOK>
-__global__ void __launch_bounds__(256) ew_rows_kernel(const EwArgs a)
+__global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs a)
 {
     constexpr int VEC = VecOf<Src, Dst>::value;
     constexpr bool kVecScale = (SMODE == kSColVec || SMODE == kSRowVec);
@@ -209,8 +237,8 @@ __global__ void __launch_bounds__(256) ew_rows_kernel(const EwArgs a)
     const uint32_t sc_col = a.scale.cdiv ? c0 / a.scale.cdiv : 0u;
 
     // Rows are taken U at a time: all U source vectors (and the per-row scalars) are requested before
-    // the first result is stored, so every thread keeps U 128-bit loads in flight.
-    constexpr int U = (SMODE == kSRowVec) ? 1 : 4;
+    // the first result is stored, so every thread keeps U vector loads in flight.
+    constexpr int U = (SMODE == kSRowVec) ? 1 : ASCQ_EW_U;
     const uint32_t gy = gridDim.y;
     for (uint32_t r0 = blockIdx.y; r0 < a.rows; r0 += gy * U) {
         Pack<Src, VEC> in[U];
@@ -258,7 +286,7 @@ __global__ void __launch_bounds__(256) ew_rows_kernel(const EwArgs a)
     }
 }
 
-// Grid shape: x covers the column vectors, y strides the rows; about eight 256-thread CTAs per SM.
+// Grid shape: x covers the column vectors, y strides the rows; about ASCQ_EW_TARGET 256-thread CTAs per SM.
 inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* block)
 {
     const uint32_t nvec = (cols + vec - 1) / vec;
@@ -268,7 +296,7 @@ inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* blo
         if (waste(cand) + nvec / 32 < waste(bx)) bx = cand;
     if (nvec < bx) bx = (nvec + 31) / 32 * 32;
     const uint32_t gx = (nvec + bx - 1) / bx;
-    const uint32_t target = 148u * 8u * 256u / bx;  // CTAs
+    const uint32_t target = 148u * ASCQ_EW_TARGET * 256u / bx;  // CTAs
     uint32_t gy = (target + gx - 1) / gx;
     if (gy > rows) gy = rows;
     if (gy < 1) gy = 1;

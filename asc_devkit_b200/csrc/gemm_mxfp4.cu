@@ -491,9 +491,17 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
 
     // CTA pairs on 256-row tiles (B fetched once per pair) when N allows; ASCQ_MXFP4_TILE=single selects single
     // CTAs on 128-row tiles, which waste fewer rows when the groups are much shorter than 256 rows.
-    bool pair = N >= 256;
+    // The pair variant is taken unless rounding every group up to 256 rows adds more than a tenth to the rows that
+    // rounding up to 128 already computes.
+    int64_t padded128 = 0, padded256 = 0;
+    for (int g = 0; g < G; ++g) {
+        padded128 += (groupList_host[g] + 127) / 128 * 128;
+        padded256 += (groupList_host[g] + 255) / 256 * 256;
+    }
+    bool pair = N >= 256 && padded256 * 10 <= padded128 * 11;
     if (const char* e = getenv("ASCQ_MXFP4_TILE")) {
         if (!strcmp(e, "single")) pair = false;
+        else if (!strcmp(e, "pair")) pair = N >= 256;
     }
     // tile table: zero-row groups are skipped (quant_group_matmul_custom.asc:265-267).  One entry per 128 rows;
     // in pair mode entries come in twos (the two halves of a 256-row tile, the second possibly empty).

@@ -413,11 +413,23 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     p.accDump = accDump;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc;
 
-    // CTA pairs on 256 x 256 tiles when they fill the machine; single CTAs on 128 x 256, or 128 x 128 for small
-    // problems (e.g. a column shard).  ASCQ_W8A8_TILE=pair|wide|narrow overrides the choice.
-    const int tiles256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
-    const int tilesPair = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
-    int mode = tilesPair >= sm_count() / 2 ? 2 : (tiles256 >= sm_count() ? 1 : 0);
+    // Tile shape: the one with the smallest estimated time = waves x time of one wave.  One wave of CTA pairs on
+    // 256 x 256 tiles is the unit; single CTAs on 128 x 256 tiles do the same work per SM about a tenth slower
+    // (B crosses the L2-to-SM fabric once per CTA instead of once per pair), 128 x 128 tiles do half the work per
+    // wave at about four fifths of the rate.  Small problems (a column shard on eight GPUs) so end up on 128 x 128
+    // tiles that occupy every SM.  ASCQ_W8A8_TILE=pair|wide|narrow overrides the choice.
+    const int units = sm_count();
+    const int tilesM = (M + kBM - 1) / kBM;
+    const long long tilesPair = static_cast<long long>((tilesM + 1) / 2) * ((N + 255) / 256);
+    const long long tiles256 = static_cast<long long>(tilesM) * ((N + 255) / 256);
+    const long long tiles128 = static_cast<long long>(tilesM) * ((N + 127) / 128);
+    auto waves = [](long long tiles, int n) { return static_cast<double>((tiles + n - 1) / n); };
+    const double costPair = waves(tilesPair, units / 2) * 1.0;
+    const double costWide = waves(tiles256, units) * 1.11;
+    const double costNarrow = waves(tiles128, units) * 0.62;
+    int mode = 2;
+    if (costWide < costPair && costWide <= costNarrow) mode = 1;
+    else if (costNarrow < costPair) mode = 0;
     if (const char* e = getenv("ASCQ_W8A8_TILE")) {
         if (!strcmp(e, "pair")) mode = 2;
         else if (!strcmp(e, "wide")) mode = 1;

@@ -127,15 +127,31 @@ __device__ __forceinline__ uint32_t pack_i8x4_rni(float x0, float x1, float x2, 
     asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
     return r;
 }
+// Two fp32 lanes per instruction (add.f32x2 / mul.f32x2: each lane rounded on its own, no flush to zero), which
+// halves the issue slots the fp32 paths need.
+__device__ __forceinline__ void add2_rn(float& x0, float& x1, float b0, float b1)
+{
+    asm("{\n\t.reg .b64 a, b, d;\n\tmov.b64 a, {%0, %1};\n\tmov.b64 b, {%2, %3};\n\tadd.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "+f"(x0), "+f"(x1)
+        : "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void mul2_rn(float& x0, float& x1, float b0, float b1)
+{
+    asm("{\n\t.reg .b64 a, b, d;\n\tmov.b64 a, {%0, %1};\n\tmov.b64 b, {%2, %3};\n\tmul.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
+        : "+f"(x0), "+f"(x1)
+        : "f"(b0), "f"(b1));
+}
 // Four int8 of one word -> four floats without the conversion pipe: byte ^ 0x80 placed in the mantissa
 // of 2^23 gives 2^23 + (v + 128); subtracting 2^23 + 128 is exact.
 __device__ __forceinline__ void unpack_i8x4_f32(uint32_t w, float (&f)[4])
 {
     const uint32_t b = w ^ 0x80808080u;
-    f[0] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7650)), -8388736.0f);
-    f[1] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7651)), -8388736.0f);
-    f[2] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7652)), -8388736.0f);
-    f[3] = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7653)), -8388736.0f);
+    f[0] = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7650));
+    f[1] = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7651));
+    f[2] = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7652));
+    f[3] = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7653));
+    add2_rn(f[0], f[1], -8388736.0f, -8388736.0f);
+    add2_rn(f[2], f[3], -8388736.0f, -8388736.0f);
 }
 
 // ---- compute-type algebra: CT in {__half, __nv_bfloat16, float} ------------------------------
