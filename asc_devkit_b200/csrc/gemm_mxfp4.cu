@@ -91,13 +91,42 @@ struct Params {
 // in memory (whole rows, coalesced), turns them in shared memory and writes whole 512-byte chunks: word w of a
 // chunk holds the four scale bytes of row 32*(w&3) + (w>>2).  Rows or chunks without data get scale 1.0 (0x7F);
 // the operand bytes there are zero.
+//
+// The same launch builds the row-tile table the matmul reads: with up to kInlineGroups groups the rows per group
+// travel as a kernel argument, every A block derives its own entry and the blocks of slab 0 store theirs.  (No
+// host-to-device copy is then part of the call.)  With more groups the host builds the table and copies it.
 constexpr int kSlab = 64;
+constexpr int kInlineGroups = 256;
+struct GroupRows {
+    int rows[kInlineGroups];
+};
+// Entry `tile` of the table: groups in order, ceil(rows / stepRows) * (stepRows / 128) entries of 128 rows each per
+// group (stepRows = 256 when CTA pairs work on 256-row tiles; the second half of a pair's tile may be empty).
+__device__ __forceinline__ TileInfo tile_entry(const GroupRows& gr, int G, int stepRows, int tile)
+{
+    int start = 0;
+    const int per = stepRows / 128;
+    for (int g = 0; g < G; ++g) {
+        const int mg = gr.rows[g];
+        const int n = (mg + stepRows - 1) / stepRows * per;
+        if (tile < n) {
+            const int left = mg - tile * 128;
+            return TileInfo{start + tile * 128, left <= 0 ? 0 : (left < 128 ? left : 128), g, 0};
+        }
+        tile -= n;
+        start += mg;
+    }
+    return TileInfo{start, 0, G > 0 ? G - 1 : 0, 0};
+}
+
 __global__ void __launch_bounds__(256)
 repack_sf_kernel(uint8_t* __restrict__ dstA, uint8_t* __restrict__ dstB, const uint8_t* __restrict__ srcA,
-                 const uint8_t* __restrict__ srcB, const TileInfo* __restrict__ tiles, int numTilesA, int kChunks,
-                 int kChunksValid, int sfRowBytes, int N, int tilesPerGroup, long long totalRowsA)
+                 const uint8_t* __restrict__ srcB, TileInfo* __restrict__ tiles, const __grid_constant__ GroupRows gr, int G,
+                 int stepRows, int numTilesA, int kChunks, int kChunksValid, int sfRowBytes, int N, int tilesPerGroup,
+                 long long totalRowsA)
 {
     __shared__ uint32_t sm[128][kSlab + 1];
+    __shared__ TileInfo myTile;
     const int slab0 = blockIdx.y * kSlab;
     const int nch = min(kSlab, kChunks - slab0);
     const bool isA = static_cast<int>(blockIdx.x) < numTilesA;
@@ -105,7 +134,12 @@ repack_sf_kernel(uint8_t* __restrict__ dstA, uint8_t* __restrict__ dstB, const u
     long long rowBase;
     int rowsValid;
     if (isA) {
-        rowBase = tiles[tile].rowStart;
+        if (threadIdx.x == 0) {
+            myTile = G > 0 ? tile_entry(gr, G, stepRows, tile) : tiles[tile];
+            if (G > 0 && blockIdx.y == 0) tiles[tile] = myTile;
+        }
+        __syncthreads();
+        rowBase = myTile.rowStart;
         const long long left = totalRowsA - rowBase;
         rowsValid = left < 128 ? static_cast<int>(left) : 128;
     } else {
@@ -503,35 +537,45 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
         if (!strcmp(e, "single")) pair = false;
         else if (!strcmp(e, "pair")) pair = N >= 256;
     }
-    // tile table: zero-row groups are skipped (quant_group_matmul_custom.asc:265-267).  One entry per 128 rows;
+    // Row-tile table: zero-row groups are skipped (quant_group_matmul_custom.asc:265-267).  One entry per 128 rows;
     // in pair mode entries come in twos (the two halves of a 256-row tile, the second possibly empty).
-    std::vector<TileInfo> tiles;
-    tiles.reserve(L.tilesM);
-    int64_t start = 0;
-    const int64_t step = pair ? 2 * kBM : kBM;
-    for (int g = 0; g < G; ++g) {
-        const int64_t mg = groupList_host[g];
-        for (int64_t r = 0; r < mg; r += step) {
-            for (int64_t h = 0; h < step; h += kBM) {
-                const int64_t left = mg - (r + h);
-                TileInfo t{static_cast<int>(start + r + h), static_cast<int>(left <= 0 ? 0 : (left < kBM ? left : kBM)), g, 0};
-                tiles.push_back(t);
-            }
-        }
-        start += mg;
-    }
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    ASCQ_CUDA_CHECK(cudaMemcpyAsync(ws + L.tileOff, tiles.data(), tiles.size() * sizeof(TileInfo), cudaMemcpyHostToDevice, st));
-    // the copy above stages pageable memory before returning, so `tiles` may go out of scope afterwards
+    const int64_t step = pair ? 2 * kBM : kBM;
+    int numTilesM = 0;
+    GroupRows gr{};
+    const bool inlineGroups = G <= kInlineGroups;
+    if (inlineGroups) {
+        for (int g = 0; g < G; ++g) {
+            gr.rows[g] = static_cast<int>(groupList_host[g]);
+            numTilesM += static_cast<int>((groupList_host[g] + step - 1) / step * (step / kBM));
+        }
+    } else {
+        std::vector<TileInfo> tiles;
+        tiles.reserve(L.tilesM);
+        int64_t start = 0;
+        for (int g = 0; g < G; ++g) {
+            const int64_t mg = groupList_host[g];
+            for (int64_t r = 0; r < mg; r += step) {
+                for (int64_t h = 0; h < step; h += kBM) {
+                    const int64_t left = mg - (r + h);
+                    TileInfo t{static_cast<int>(start + r + h), static_cast<int>(left <= 0 ? 0 : (left < kBM ? left : kBM)), g, 0};
+                    tiles.push_back(t);
+                }
+            }
+            start += mg;
+        }
+        ASCQ_CUDA_CHECK(cudaMemcpyAsync(ws + L.tileOff, tiles.data(), tiles.size() * sizeof(TileInfo), cudaMemcpyHostToDevice, st));
+        // the copy above stages pageable memory before returning, so `tiles` may go out of scope afterwards
+        numTilesM = static_cast<int>(tiles.size());
+    }
 
-    const int numTilesM = static_cast<int>(tiles.size());
     const int kChunks = L.kBlocks * 2;
     const int sfRowBytes = K / 32;
     {
         const dim3 grid(static_cast<unsigned>(numTilesM + G * L.nTiles128), static_cast<unsigned>((kChunks + kSlab - 1) / kSlab));
         repack_sf_kernel<<<grid, 256, 0, st>>>(ws + L.sfaOff, ws + L.sfbOff, sA_e8m0, sB_e8m0,
-                                               reinterpret_cast<const TileInfo*>(ws + L.tileOff), numTilesM, kChunks, K / 128,
-                                               sfRowBytes, N, L.nTiles128, sumM);
+                                               reinterpret_cast<TileInfo*>(ws + L.tileOff), gr, inlineGroups ? G : 0,
+                                               static_cast<int>(step), numTilesM, kChunks, K / 128, sfRowBytes, N, L.nTiles128, sumM);
         ASCQ_CUDA_CHECK(cudaGetLastError());
     }
 

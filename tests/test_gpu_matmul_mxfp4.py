@@ -54,6 +54,25 @@ def test_parity(groups, N, K):
     assert ulp.max_ulp <= 2 or ulp.mismatches < 0.02 * ulp.total, ulp
 
 
+def test_many_groups_use_the_host_built_tile_table():
+    """More than 256 groups: the row-tile table is built on the host and copied (fewer groups build it on the device)."""
+    rng = np.random.default_rng(11)
+    groups = [int(v) for v in rng.choice([0, 1, 3, 17, 130], 300)]
+    N, K = 256, 256
+    A, sA, B, sB = make_case(groups, N, K, 12)
+    _, want_f32 = O.group_matmul_mxfp4(A, sA, B, sB, np.array(groups, np.int64), K, N, want_f32=True)
+    check_close(run(A, sA, B, sB, groups, K, N), want_f32, "300 groups")
+
+
+@pytest.mark.parametrize("tile", ["single", "pair"])
+def test_both_tile_shapes_give_the_same_bits(tile, monkeypatch):
+    groups, N, K = [300, 0, 5, 256, 129], 512, 512
+    A, sA, B, sB = make_case(groups, N, K, 21)
+    _, want_f32 = O.group_matmul_mxfp4(A, sA, B, sB, np.array(groups, np.int64), K, N, want_f32=True)
+    monkeypatch.setenv("ASCQ_MXFP4_TILE", tile)
+    check_close(run(A, sA, B, sB, groups, K, N), want_f32, tile)
+
+
 @pytest.mark.parametrize("groups,N,K", [([128, 200], 256, 512), ([77], 320, 256)])
 def test_exact_when_sums_are_representable(groups, N, K):
     # codes {0, +-0.5, +-1, +-2} with unit scales: every partial sum is a small multiple of 0.25 -> exact in fp32

@@ -10,6 +10,7 @@ what the workspace-taking entry point produces.  Oversized problems must be refu
 The file name sorts last so that a run that stops at the first failure has already run every other test.
 """
 import ctypes as C
+import gc
 
 import numpy as np
 import pytest
@@ -43,13 +44,15 @@ def _with_workspace(p):
 def _no_alloc(p):
     out = torch.zeros((sum(p["groups"]), p["N"]), dtype=torch.bfloat16, device=DEV)
     gl = (C.c_int64 * len(p["groups"]))(*p["groups"])
+    gc.collect()  # tensors of earlier tests must not be released half-way through the measurement
     before = torch.cuda.memory_allocated()
+    reserved = torch.cuda.memory_reserved()
     rc = L.lib().ascq_group_matmul_mxfp4_noalloc(ops._ptr(out), ops._ptr(p["A"]), ops._ptr(p["sA"]), ops._ptr(p["B"]),
                                                  ops._ptr(p["sB"]), gl, len(p["groups"]), p["K"], p["N"],
                                                  ops._stream(None))
     L.check(rc)
     ops.MatmulStatus()
-    assert torch.cuda.memory_allocated() == before
+    assert torch.cuda.memory_allocated() == before and torch.cuda.memory_reserved() == reserved
     return out
 
 
