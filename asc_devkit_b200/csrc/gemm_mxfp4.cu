@@ -127,6 +127,7 @@ repack_sf_kernel(uint8_t* __restrict__ dstA, uint8_t* __restrict__ dstB, const u
 {
     __shared__ uint32_t sm[128][kSlab + 1];
     __shared__ TileInfo myTile;
+    asm volatile("griddepcontrol.launch_dependents;");  // the matmul's CTAs may start their set-up
     const int slab0 = blockIdx.y * kSlab;
     const int nch = min(kSlab, kChunks - slab0);
     const bool isA = static_cast<int>(blockIdx.x) < numTilesA;
@@ -148,18 +149,40 @@ repack_sf_kernel(uint8_t* __restrict__ dstA, uint8_t* __restrict__ dstB, const u
         rowsValid = min(128, N - t * 128);
     }
     const uint8_t* src = isA ? srcA : srcB;
-    for (int idx = threadIdx.x; idx < 128 * nch; idx += blockDim.x) {
-        const int r = idx / nch, ch = idx - r * nch;
-        uint32_t v = 0x7F7F7F7Fu;
-        if (r < rowsValid && slab0 + ch < kChunksValid)
-            v = *reinterpret_cast<const uint32_t*>(src + (rowBase + r) * sfRowBytes + (slab0 + ch) * 4);
-        sm[r][ch] = v;
-    }
-    __syncthreads();
     uint32_t* dst = reinterpret_cast<uint32_t*>(isA ? dstA : dstB) + (static_cast<size_t>(tile) * kChunks + slab0) * (kChunkBytes / 4);
-    for (int idx = threadIdx.x; idx < 128 * nch; idx += blockDim.x) {
-        const int ch = idx >> 7, w = idx & 127;
-        dst[idx] = sm[(w & 3) * 32 + (w >> 2)][ch];
+    // 16 bytes per access when rows and slabs are made of whole groups of four chunks
+    const bool vec4 = (nch % 4 == 0) && (kChunksValid % 4 == 0) && (sfRowBytes % 16 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
+    if (vec4) {
+        const int nq = nch >> 2;
+        for (int idx = threadIdx.x; idx < 128 * nq; idx += blockDim.x) {
+            const int r = idx / nq, q = idx - r * nq;
+            uint4 v = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+            if (r < rowsValid && slab0 + 4 * q < kChunksValid)
+                v = __ldg(reinterpret_cast<const uint4*>(src + (rowBase + r) * sfRowBytes + (slab0 + 4 * q) * 4));
+            sm[r][4 * q] = v.x;
+            sm[r][4 * q + 1] = v.y;
+            sm[r][4 * q + 2] = v.z;
+            sm[r][4 * q + 3] = v.w;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 32 * nch; idx += blockDim.x) {
+            const int ch = idx >> 5, l = idx & 31;  // words 4l .. 4l+3 of the chunk: rows l, 32+l, 64+l, 96+l
+            reinterpret_cast<uint4*>(dst)[idx] = make_uint4(sm[l][ch], sm[32 + l][ch], sm[64 + l][ch], sm[96 + l][ch]);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 128 * nch; idx += blockDim.x) {
+            const int r = idx / nch, ch = idx - r * nch;
+            uint32_t v = 0x7F7F7F7Fu;
+            if (r < rowsValid && slab0 + ch < kChunksValid)
+                v = *reinterpret_cast<const uint32_t*>(src + (rowBase + r) * sfRowBytes + (slab0 + ch) * 4);
+            sm[r][ch] = v;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 128 * nch; idx += blockDim.x) {
+            const int ch = idx >> 7, w = idx & 127;
+            dst[idx] = sm[(w & 3) * 32 + (w >> 2)][ch];
+        }
     }
 }
 
@@ -239,6 +262,8 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmemBase = *tmemBaseSlot;
     const uint32_t sfCol0 = tmemBase + C::kAccCols;  // two sets of scale columns, alternating per k-block
+    // everything below reads what the launch before this one wrote (row-tile table, packed scales)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         if (elect_one()) {
@@ -464,25 +489,31 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     }
     p.tilesN = (p.N + BN - 1) / BN;
     const int tiles = p.numTilesM * p.tilesN;
+    // Programmatic dependent launch: the CTAs may become resident and run their set-up (barriers, tensor memory,
+    // descriptor prefetch) while the scale-repack launch before this one drains; they wait for its results with
+    // griddepcontrol.wait before the first dependent read.
+    const int units = PAIR ? sm_count() / 2 : sm_count();
+    const int grid = (tiles < units ? tiles : units) * (PAIR ? 2 : 1);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
     if constexpr (PAIR) {
-        const int clusters = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
-        cfg.blockDim = dim3(kThreads, 1, 1);
-        cfg.dynamicSmemBytes = C::kSmemBytes;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mxfp4_kernel<BN, PAIR>, ta, tb, tsa, tsb, p));
-    } else {
-        const int grid = tiles < sm_count() ? tiles : sm_count();
-        mxfp4_kernel<BN, PAIR><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, tsa, tsb, p);
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 2;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
     }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mxfp4_kernel<BN, PAIR>, ta, tb, tsa, tsb, p));
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
