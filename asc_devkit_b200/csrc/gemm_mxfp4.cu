@@ -42,7 +42,8 @@ constexpr int kBKElems = 256;
 constexpr int kChunkBytes = 512;  // packed scales of 128 rows x 128 K-elements
 constexpr int kEpiWarps = 8;   // two per TMEM lane quarter; each drains half of the accumulator columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
-constexpr int kStagePitch = 80;  // bytes per staged output row: 64 B of bf16 + 16 B pad (conflict-free both ways)
+constexpr int kStagePitch = 144;  // bytes per staged output row: 128 B of bf16 + 16 B pad (conflict-free both ways)
+constexpr int kNarrowPitch = 80;  // the same for 64-byte rows
 
 __device__ int g_mxfp4_status = 0;
 
@@ -50,7 +51,7 @@ struct TileInfo {
     int rowStart;   // first row of the tile in A / C
     int rowsValid;  // rows of this tile that belong to its group
     int group;
-    int pad;
+    int outRow;     // row of the output matrix the tile's first row is written to
 };
 
 // PAIR: two CTAs of a cluster drive one tcgen05.mma.cta_group::2 on a 256 x BN tile.  Each CTA loads its 128 rows
@@ -69,15 +70,19 @@ template <int BN, bool PAIR> struct Cfg {
     static constexpr int kSfbCols = 2 * (BN / 32);   // 2 chunks x N/32 columns
     static constexpr int kAccCols = kAccStages * BN;
     static constexpr int kTmemCols = 512;
-    static constexpr int kOutBytes = kEpiWarps * 32 * kStagePitch;  // per epilogue warp: 32 rows x 32 bf16 columns
+    static constexpr int kWarpStageBytes = 32 * kNarrowPitch > 16 * kStagePitch ? 32 * kNarrowPitch : 16 * kStagePitch;
+    static constexpr int kOutBytes = kEpiWarps * kWarpStageBytes;  // per epilogue warp: 16 rows x 128 B or 32 rows x 64 B
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kOutBytes;
     static_assert(kSmemBytes <= 232448, "shared memory budget");
     static_assert(kAccCols + 2 * (kSfaCols + kSfbCols) <= 512, "tensor memory budget (scale columns are double buffered)");
     static_assert(kStageBytes % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
 };
 
+constexpr int kMaxPeers = 8;  // output buffers one launch can write (this GPU's and its peers')
 struct Params {
-    __nv_bfloat16* C;
+    __nv_bfloat16* C[kMaxPeers];  // every buffer gets this launch's rows (at the tiles' outRow)
+    int nPeers, firstPeer;        // stores start at buffer firstPeer and go round
+    int wideStores;               // 128-byte row segments (peer buffers) instead of 64-byte ones
     const TileInfo* tiles;
     const uint8_t* sfaPacked;
     const uint8_t* sfbPacked;
@@ -98,7 +103,8 @@ struct Params {
 constexpr int kSlab = 64;
 constexpr int kInlineGroups = 256;
 struct GroupRows {
-    int rows[kInlineGroups];
+    int rows[kInlineGroups];      // rows of A per group
+    int outStart[kInlineGroups];  // output row of each group's first row
 };
 // Entry `tile` of the table: groups in order, ceil(rows / stepRows) * (stepRows / 128) entries of 128 rows each per
 // group (stepRows = 256 when CTA pairs work on 256-row tiles; the second half of a pair's tile may be empty).
@@ -111,12 +117,12 @@ __device__ __forceinline__ TileInfo tile_entry(const GroupRows& gr, int G, int s
         const int n = (mg + stepRows - 1) / stepRows * per;
         if (tile < n) {
             const int left = mg - tile * 128;
-            return TileInfo{start + tile * 128, left <= 0 ? 0 : (left < 128 ? left : 128), g, 0};
+            return TileInfo{start + tile * 128, left <= 0 ? 0 : (left < 128 ? left : 128), g, gr.outStart[g] + tile * 128};
         }
         tile -= n;
         start += mg;
     }
-    return TileInfo{start, 0, G > 0 ? G - 1 : 0, 0};
+    return TileInfo{start, 0, G > 0 ? G - 1 : 0, start};
 }
 
 __global__ void __launch_bounds__(256)
@@ -206,7 +212,7 @@ __device__ __forceinline__ void tile_coords(int tile, int numTilesM, int tilesN,
 template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-             const __grid_constant__ CUtensorMap tmapSfa, const __grid_constant__ CUtensorMap tmapSfb, const Params p)
+             const __grid_constant__ CUtensorMap tmapSfa, const __grid_constant__ CUtensorMap tmapSfb, const __grid_constant__ Params p)
 {
     using C = Cfg<BN, PAIR>;
     extern __shared__ uint8_t smem_raw[];
@@ -218,7 +224,7 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     uint64_t* tmemEmpty = tmemFull + 2;
     uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
-    uint8_t* outStage = reinterpret_cast<uint8_t*>(bars) + 256;  // [kEpiWarps][32][kStagePitch]
+    uint8_t* outStage = reinterpret_cast<uint8_t*>(bars) + 256;  // [kEpiWarps][16][kStagePitch]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -400,39 +406,79 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
 
             const int rIn = q * 32 + lane;
             const bool rowOk = rIn < ti.rowsValid;
-            __nv_bfloat16* crow = p.C + static_cast<size_t>(ti.rowStart + rIn) * p.N + n0;
-            const bool vecStore = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
-            uint8_t* stageW = outStage + (warp - 2) * (32 * kStagePitch);
+            bool vecStore = (p.N % 8 == 0);
+            for (int pi = 0; pi < p.nPeers; ++pi) vecStore = vecStore && ((reinterpret_cast<uintptr_t>(p.C[pi]) & 15u) == 0);
+            uint8_t* stageW = outStage + (warp - 2) * C::kWarpStageBytes;
 #pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-                const int n = n0 + c * 32;
+            for (int cp = 0; cp < kChunks / 2; ++cp) {  // two 32-column chunks = 64 columns = 128 bytes of bf16 per row
+                const int n = n0 + cp * 64;
                 if (n >= p.N) continue;  // uniform over the warp
-                uint32_t packed[16];
+                uint32_t packed[32];
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    packed[j] = pack_bf16x2_sat(__uint_as_float(r[c][2 * j]), __uint_as_float(r[c][2 * j + 1]));
-                if (n + 32 <= p.N && vecStore) {
-                    // Transpose through this warp's staging rows: every store instruction then writes eight complete
-                    // 64-byte row segments instead of thirty-two 16-byte pieces of thirty-two different rows.
+                for (int j = 0; j < 32; ++j)
+                    packed[j] = pack_bf16x2_sat(__uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15)]),
+                                                __uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15) + 1]));
+                if (n + 64 <= p.N && vecStore && !p.wideStores) {
+                    // One output buffer in this GPU's memory: 64-byte row segments, all thirty-two rows in one pass
+                    // (fewer instructions and warp barriers than the 128-byte form below, and L2 merges the halves).
 #pragma unroll
-                    for (int v = 0; v < 4; ++v)
-                        *reinterpret_cast<uint4*>(stageW + lane * kStagePitch + v * 16) =
-                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    __syncwarp();
-                    const int piece = lane & 3;
+                    for (int c = 0; c < 2; ++c) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int row = q * 32 + i * 8 + (lane >> 2);
-                        const uint4 val = *reinterpret_cast<const uint4*>(stageW + (i * 8 + (lane >> 2)) * kStagePitch + piece * 16);
-                        if (row < ti.rowsValid)
-                            *reinterpret_cast<uint4*>(p.C + static_cast<size_t>(ti.rowStart + row) * p.N + n + piece * 8) = val;
+                        for (int v = 0; v < 4; ++v)
+                            *reinterpret_cast<uint4*>(stageW + lane * kNarrowPitch + v * 16) =
+                                make_uint4(packed[16 * c + 4 * v], packed[16 * c + 4 * v + 1], packed[16 * c + 4 * v + 2],
+                                           packed[16 * c + 4 * v + 3]);
+                        __syncwarp();
+                        const int piece = lane & 3;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rl = i * 8 + (lane >> 2);
+                            const uint4 val = *reinterpret_cast<const uint4*>(stageW + rl * kNarrowPitch + piece * 16);
+                            if (q * 32 + rl < ti.rowsValid)
+                                *reinterpret_cast<uint4*>(p.C[0] + static_cast<size_t>(ti.outRow + q * 32 + rl) * p.N + n + c * 32 +
+                                                          piece * 8) = val;
+                        }
+                        __syncwarp();
                     }
-                    __syncwarp();
-                } else if (rowOk) {
+                } else if (n + 64 <= p.N && vecStore) {
+                    // Transpose through this warp's staging rows, sixteen rows at a time: every store instruction then
+                    // writes four complete 128-byte row segments (whole lines, which is what both L2 and NVLink move
+                    // best) instead of thirty-two 16-byte pieces of thirty-two different rows.
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (n + j < p.N)
-                            crow[c * 32 + j] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[j >> 1] >> ((j & 1) * 16)));
+                    for (int h = 0; h < 2; ++h) {
+                        if ((lane >> 4) == h) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                *reinterpret_cast<uint4*>(stageW + (lane & 15) * kStagePitch + v * 16) =
+                                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        }
+                        __syncwarp();
+                        const int piece = lane & 7;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rl = i * 4 + (lane >> 3);
+                            const int row = q * 32 + h * 16 + rl;
+                            const uint4 val = *reinterpret_cast<const uint4*>(stageW + rl * kStagePitch + piece * 16);
+                            if (row < ti.rowsValid) {
+                                const size_t off = static_cast<size_t>(ti.outRow + row) * p.N + n + piece * 8;
+                                for (int pi = 0; pi < p.nPeers; ++pi) {
+                                    int b = p.firstPeer + pi;
+                                    if (b >= p.nPeers) b -= p.nPeers;
+                                    *reinterpret_cast<uint4*>(p.C[b] + off) = val;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                } else if (rowOk) {
+                    for (int pi = 0; pi < p.nPeers; ++pi) {
+                        __nv_bfloat16* crow = p.C[pi] + static_cast<size_t>(ti.outRow + rIn) * p.N + n;
+#pragma unroll
+                        for (int w = 0; w < 32; ++w) {
+                            if (n + 2 * w < p.N) crow[2 * w] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[w] & 0xFFFFu));
+                            if (n + 2 * w + 1 < p.N) crow[2 * w + 1] = __ushort_as_bfloat16(static_cast<unsigned short>(packed[w] >> 16));
+                        }
+                    }
                 }
             }
         }
@@ -529,12 +575,19 @@ extern "C" size_t ascq_group_matmul_mxfp4_workspace_size(int64_t sumM, int G, in
     return make_layout(sumM, G, K, N).total;
 }
 
-extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
-                                               const uint8_t* B_fp4, const uint8_t* sB_e8m0, const int64_t* groupList_host,
-                                               int G, int K, int N, void* workspace, size_t workspaceBytes, void* stream)
+// Shared body of the entry points.  outBufs: nBufs bf16 matrices with row stride N; group g's rows go to rows
+// outRowStart_host[g].. of each (NULL: the groups follow each other as in A).
+static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, const int64_t* outRowStart_host,
+                             const uint8_t* A_fp4, const uint8_t* sA_e8m0, const uint8_t* B_fp4, const uint8_t* sB_e8m0,
+                             const int64_t* groupList_host, int G, int K, int N, void* workspace, size_t workspaceBytes,
+                             void* stream)
 {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (!C_bf16 || !A_fp4 || !sA_e8m0 || !B_fp4 || !sB_e8m0 || !groupList_host)
+    if (!outBufs || nBufs < 1 || nBufs > kMaxPeers)
+        return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
+    for (int i = 0; i < nBufs; ++i)
+        if (!outBufs[i]) return fail(ASCQ_ERR_INVALID_ARG, "output buffer %d is NULL", i);
+    if (!A_fp4 || !sA_e8m0 || !B_fp4 || !sB_e8m0 || !groupList_host)
         return fail(ASCQ_ERR_INVALID_ARG, "C, A, sA, B, sB and groupList must not be NULL");
     if (G <= 0 || N <= 0 || K <= 0) return fail(ASCQ_ERR_INVALID_ARG, "G, N, K must be positive");
     if (K % 128 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of 128", K);
@@ -549,6 +602,10 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     if (sumM == 0) return ASCQ_OK;
     if (sumM > 0x7FFFFFFF - 256 || static_cast<int64_t>(G) * N > 0x7FFFFFFF)
         return fail(ASCQ_ERR_INVALID_ARG, "problem too large for 32-bit row indices");
+    if (outRowStart_host)
+        for (int g = 0; g < G; ++g)
+            if (outRowStart_host[g] < 0 || outRowStart_host[g] > 0x7FFFFFFF - 256)
+                return fail(ASCQ_ERR_INVALID_ARG, "outRowStart[%d] is out of range", g);
     const Layout L = make_layout(sumM, G, K, N);
     if (!workspace || workspaceBytes < L.total)
         return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", L.total, workspaceBytes);
@@ -576,8 +633,11 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     GroupRows gr{};
     const bool inlineGroups = G <= kInlineGroups;
     if (inlineGroups) {
+        int64_t start = 0;
         for (int g = 0; g < G; ++g) {
             gr.rows[g] = static_cast<int>(groupList_host[g]);
+            gr.outStart[g] = static_cast<int>(outRowStart_host ? outRowStart_host[g] : start);
+            start += groupList_host[g];
             numTilesM += static_cast<int>((groupList_host[g] + step - 1) / step * (step / kBM));
         }
     } else {
@@ -589,7 +649,9 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
             for (int64_t r = 0; r < mg; r += step) {
                 for (int64_t h = 0; h < step; h += kBM) {
                     const int64_t left = mg - (r + h);
-                    TileInfo t{static_cast<int>(start + r + h), static_cast<int>(left <= 0 ? 0 : (left < kBM ? left : kBM)), g, 0};
+                    const int64_t out0 = outRowStart_host ? outRowStart_host[g] : start;
+                    TileInfo t{static_cast<int>(start + r + h), static_cast<int>(left <= 0 ? 0 : (left < kBM ? left : kBM)), g,
+                               static_cast<int>(out0 + r + h)};
                     tiles.push_back(t);
                 }
             }
@@ -611,7 +673,11 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     }
 
     Params p{};
-    p.C = static_cast<__nv_bfloat16*>(C_bf16);
+    p.nPeers = nBufs;
+    for (int i = 0; i < nBufs; ++i) p.C[i] = static_cast<__nv_bfloat16*>(outBufs[i]);
+    p.firstPeer = ((firstBuf % nBufs) + nBufs) % nBufs;
+    p.wideStores = nBufs > 1;
+    if (const char* e = getenv("ASCQ_MXFP4_STORE")) p.wideStores = !strcmp(e, "wide") ? 1 : (!strcmp(e, "narrow") && nBufs == 1 ? 0 : p.wideStores);
     p.tiles = reinterpret_cast<const TileInfo*>(ws + L.tileOff);
     p.sfaPacked = ws + L.sfaOff;
     p.sfbPacked = ws + L.sfbOff;
@@ -632,6 +698,26 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     if (rc != ASCQ_OK) return rc;
     if (pair) return launch<256, true>(ta, tb, tsa, tsb, p, st);
     return wide ? launch<256, false>(ta, tb, tsa, tsb, p, st) : launch<128, false>(ta, tb, tsa, tsb, p, st);
+}
+
+extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
+                                               const uint8_t* B_fp4, const uint8_t* sB_e8m0, const int64_t* groupList_host,
+                                               int G, int K, int N, void* workspace, size_t workspaceBytes, void* stream)
+{
+    if (!C_bf16) return fail(ASCQ_ERR_INVALID_ARG, "C, A, sA, B, sB and groupList must not be NULL");
+    void* bufs[1] = {C_bf16};
+    return run_mxfp4(bufs, 1, 0, nullptr, A_fp4, sA_e8m0, B_fp4, sB_e8m0, groupList_host, G, K, N, workspace, workspaceBytes,
+                     stream);
+}
+
+extern "C" ascq_status ascq_group_matmul_mxfp4_scatter(void* const* C_bufs, int nBufs, int firstBuf,
+                                                       const int64_t* outRowStart_host, const uint8_t* A_fp4,
+                                                       const uint8_t* sA_e8m0, const uint8_t* B_fp4, const uint8_t* sB_e8m0,
+                                                       const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                                       size_t workspaceBytes, void* stream)
+{
+    return run_mxfp4(C_bufs, nBufs, firstBuf, outRowStart_host, A_fp4, sA_e8m0, B_fp4, sB_e8m0, groupList_host, G, K, N,
+                     workspace, workspaceBytes, stream);
 }
 
 // ---- entry point for callers that may not allocate device memory ------------------------------------

@@ -34,7 +34,7 @@ constexpr int kBK = 128;        // bytes == int8 elements per k-block: one 128B 
 constexpr int kUmmaK = 32;      // K per tcgen05.mma for 8-bit operands
 constexpr int kEpiWarps = 8;    // two warps per TMEM lane quarter, alternating 32-column chunks
 constexpr int kMaxPeers = 8;    // output buffers one launch can write (this GPU's and its peers')
-constexpr int kStagePitch = 80;  // bytes per staged row: 64 B of bf16 + 16 B pad (conflict-free both ways)
+constexpr int kStagePitch = 144;  // bytes per staged row: 128 B of bf16 + 16 B pad (conflict-free both ways)
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
 
 __device__ int g_w8a8_status = 0;  // 0 ok, 1 = a bounded wait expired
@@ -49,7 +49,7 @@ template <int BN, bool PAIR> struct Cfg {
     static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 x 48 KiB, or 6 x 32 KiB
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
     static constexpr int kEpiBytes = 2 * 2 * BN * 4;  // per accumulator: sB[BN] and bias[BN] as fp32
-    static constexpr int kOutBytes = kEpiWarps * 32 * kStagePitch;  // per epilogue warp: 32 rows x 32 bf16 columns
+    static constexpr int kOutBytes = kEpiWarps * 16 * kStagePitch;  // per epilogue warp: 16 rows x 64 bf16 columns
     static constexpr size_t kSmemBytes =
         static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes + kOutBytes;
 };
@@ -81,7 +81,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
     float* epiScale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + 256);  // [2][2][BN]
-    uint8_t* outStage = reinterpret_cast<uint8_t*>(epiScale) + C::kEpiBytes;                // [kEpiWarps][32][kStagePitch]
+    uint8_t* outStage = reinterpret_cast<uint8_t*>(epiScale) + C::kEpiBytes;                // [kEpiWarps][16][kStagePitch]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -192,7 +192,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).. (its 32 rows of the tile) ----------------
         const int q = warp & 3;
         const int sub = (warp - 2) >> 2;
-        uint8_t* stageW = outStage + (warp - 2) * (32 * kStagePitch);
+        uint8_t* stageW = outStage + (warp - 2) * (16 * kStagePitch);
         uint32_t local = 0;
         bool ok = true;
         for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
@@ -268,48 +268,58 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 }
             };
 #pragma unroll 1
-            for (int c = sub; c < BN / 32; c += kEpiWarps / 4) {
-                uint32_t r0[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r0);
+            for (int c2 = sub; c2 < BN / 64; c2 += kEpiWarps / 4) {  // 64 columns = 128 bytes of bf16 per row at a time
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32b_x32(taddr + c2 * 64, r0);
+                tmem_ld_32x32b_x32(taddr + c2 * 64 + 32, r1);
                 tmem_ld_wait();
-                const int n = n0 + c * 32;
+                const int n = n0 + c2 * 64;
                 if (n >= p.N) continue;  // uniform over the warp
                 if (p.accDump != nullptr && m < p.M) {
                     int32_t* d = p.accDump + static_cast<size_t>(m) * p.N + n;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                    for (int j = 0; j < 32; ++j) {
                         if (n + j < p.N) d[j] = static_cast<int32_t>(r0[j]);
+                        if (n + 32 + j < p.N) d[32 + j] = static_cast<int32_t>(r1[j]);
+                    }
                 }
                 if (!haveC) continue;
-                uint32_t packed[16];
-                convert32(r0, c * 32, packed);
-                if (vecStore && n + 32 <= p.N) {
-                    // Transpose through this warp's staging rows so that every store instruction writes eight complete
-                    // 64-byte row segments (instead of thirty-two 16-byte pieces): the output leaves the SM in whole
-                    // sectors, which is what both the L1 path and NVLink want.
+                uint32_t packed[32];
+                convert32(r0, c2 * 64, packed);
+                convert32(r1, c2 * 64 + 32, packed + 16);
+                if (vecStore && n + 64 <= p.N) {
+                    // Transpose through this warp's staging rows, sixteen rows at a time, so that every store instruction
+                    // writes four complete 128-byte row segments (instead of thirty-two 16-byte pieces): the output leaves
+                    // the SM in whole lines, which is what both L2 and NVLink move best.
 #pragma unroll
-                    for (int v = 0; v < 4; ++v)
-                        *reinterpret_cast<uint4*>(stageW + lane * kStagePitch + v * 16) =
-                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    __syncwarp();
-                    const int piece = lane & 3;
+                    for (int h = 0; h < 2; ++h) {
+                        if ((lane >> 4) == h) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int row = i * 8 + (lane >> 2);
-                        const uint4 val = *reinterpret_cast<const uint4*>(stageW + row * kStagePitch + piece * 16);
-                        const int gm = m0 + q * 32 + row;
-                        if (gm < p.M) {
-                            const size_t off = static_cast<size_t>(gm) * p.ldc + p.colOffset + n + piece * 8;
-                            for (int pi = 0; pi < p.nPeers; ++pi) {
-                                int b = p.firstPeer + pi;
-                                if (b >= p.nPeers) b -= p.nPeers;
-                                *reinterpret_cast<uint4*>(p.C[b] + off) = val;
+                            for (int v = 0; v < 8; ++v)
+                                *reinterpret_cast<uint4*>(stageW + (lane & 15) * kStagePitch + v * 16) =
+                                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        }
+                        __syncwarp();
+                        const int piece = lane & 7;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rl = i * 4 + (lane >> 3);
+                            const uint4 val = *reinterpret_cast<const uint4*>(stageW + rl * kStagePitch + piece * 16);
+                            const int gm = m0 + q * 32 + h * 16 + rl;
+                            if (gm < p.M) {
+                                const size_t off = static_cast<size_t>(gm) * p.ldc + p.colOffset + n + piece * 8;
+                                for (int pi = 0; pi < p.nPeers; ++pi) {
+                                    int b = p.firstPeer + pi;
+                                    if (b >= p.nPeers) b -= p.nPeers;
+                                    *reinterpret_cast<uint4*>(p.C[b] + off) = val;
+                                }
                             }
                         }
+                        __syncwarp();
                     }
-                    __syncwarp();
                 } else {
                     store_direct(packed, n);
+                    store_direct(packed + 16, n + 32);
                 }
             }
             tc_fence_before();

@@ -200,6 +200,24 @@ def GroupMatmulMxfp4(C: torch.Tensor, A: torch.Tensor, scaleA: torch.Tensor, B: 
     return C
 
 
+def GroupMatmulMxfp4Scatter(buffer_ptrs, first_buf: int, out_row_start, A: torch.Tensor, scaleA: torch.Tensor, B: torch.Tensor,
+                            scaleB: torch.Tensor, groupList, K: int, N: int, workspace: Optional[torch.Tensor] = None,
+                            stream=None):
+    """Grouped MX-FP4 matmul whose epilogue writes group g's rows to rows ``out_row_start[g]``.. of every bf16 [*, N]
+    buffer in ``buffer_ptrs`` (device addresses; this GPU's buffer and peer-mapped ones):
+    ``ascq_group_matmul_mxfp4_scatter``."""
+    G = len(groupList)
+    gl = (C_int64 * G)(*[int(v) for v in groupList])
+    rs = (C_int64 * G)(*[int(v) for v in out_row_start]) if out_row_start is not None else None
+    need = GroupMatmulMxfp4Workspace(int(sum(int(v) for v in groupList)), G, K, N)
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=A.device)
+    arr = (C.c_void_p * len(buffer_ptrs))(*[C.c_void_p(int(v)) for v in buffer_ptrs])
+    L.check(L.lib().ascq_group_matmul_mxfp4_scatter(arr, len(buffer_ptrs), first_buf, rs, _ptr(A), _ptr(scaleA), _ptr(B),
+                                                    _ptr(scaleB), gl, G, K, N, _ptr(workspace), workspace.numel(),
+                                                    _stream(stream)))
+
+
 def MxRepackBKnToNk(B_nk: torch.Tensor, B_kn: torch.Tensor, K: int, N: int, stream=None):
     L.check(L.lib().ascq_mx_repack_b_kn_to_nk(_ptr(B_nk), _ptr(B_kn), K, N, _stream(stream)))
     return B_nk

@@ -262,6 +262,7 @@ class W8A8Cfg4(Workload):
     """Config 4.  With `world` > 1 the weight matrix B (and sB, bias) is column-sharded over the ranks: each rank
     computes C[:, shard] and an NCCL all-gather reassembles the output on every rank (strong scaling)."""
     name = "W8A8 int8 matmul M=N=K=4096 + per-token x per-channel dequant + bias -> bf16 (config 4)"
+    sharding_note = "B column-sharded over N"
     dtype = "int8"
     unit = "TOPS"
     bound = "tensor"
@@ -364,45 +365,106 @@ class W8A8Cfg4(Workload):
 
 class Mxfp4Cfg5(Workload):
     name = "MX-FP4 grouped matmul G=16, 16384 tokens (multinomial), K=7168, N=2048 -> bf16 (config 5)"
+    sharding_note = "groups dealt out over the ranks, longest first"
     dtype = "fp4(e2m1)xue8m0, f32 accumulate"
     unit = "TFLOPS"
     bound = "tensor"
     key = "mxfp4_cfg5"
 
-    def __init__(self, torch, ops, dev):
-        self.torch, self.ops = torch, ops
+    def __init__(self, torch, ops, dev, dist=None, world=1, rank=0):
+        """With `world` > 1 the groups are dealt out over the ranks (longest first); each rank holds the tokens and the
+        weights of its groups only and computes their output rows; the full [tokens, N] output is reassembled on every
+        rank inside the step (strong scaling)."""
+        from asc_devkit_b200 import sharding
+        self.torch, self.ops, self.dist, self.world, self.rank = torch, ops, dist, world, rank
         self.G, self.total, self.K, self.N = 16, 16384, 7168, 2048
         h = gen_mxfp4_cfg5(self.G, self.total, self.K, self.N)
+        self.all_groups = [int(v) for v in h["groups"]]
+        starts = np.concatenate([[0], np.cumsum(self.all_groups)]).astype(np.int64)
+        self.plan = sharding.assign_groups_lpt(self.all_groups, world)
+        mine = self.plan.groups_of[rank]
+        rows = np.concatenate([np.arange(starts[g], starts[g + 1]) for g in mine]) if mine else np.zeros(0, np.int64)
+        if world > 1:   # this rank's share, its groups back to back
+            h = dict(h, A=np.ascontiguousarray(h["A"][rows]), sA=np.ascontiguousarray(h["sA"][rows]),
+                     B=np.ascontiguousarray(h["B"][mine]), sB=np.ascontiguousarray(h["sB"][mine]))
         self.host = h
-        self.groups = [int(v) for v in h["groups"]]
-        per_set = h["A"].nbytes + h["sA"].nbytes + h["B"].nbytes + h["sB"].nbytes + self.total * self.N * 2
+        self.groups = [self.all_groups[g] for g in mine]
+        self.out_row_start = [int(starts[g]) for g in mine]
+        self.local_rows = int(sum(self.groups))
+        per_set = h["A"].nbytes + h["sA"].nbytes + h["B"].nbytes + h["sB"].nbytes + self.local_rows * self.N * 2
         self.nsets = self.nsets_for(per_set)
         t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
         self.A = [t(h["A"]) for _ in range(self.nsets)]
         self.sA = [t(h["sA"]) for _ in range(self.nsets)]
         self.B = [t(h["B"]) for _ in range(self.nsets)]
         self.sB = [t(h["sB"]) for _ in range(self.nsets)]
-        self.C = [torch.empty((self.total, self.N), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
-        self.ws = torch.empty(ops.GroupMatmulMxfp4Workspace(self.total, self.G, self.K, self.N), dtype=torch.uint8, device=dev)
+        self.C = [torch.empty((max(self.local_rows, 1), self.N), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
+        self.ws = torch.empty(max(256, ops.GroupMatmulMxfp4Workspace(self.local_rows, max(len(mine), 1), self.K, self.N)),
+                              dtype=torch.uint8, device=dev)
+        self.fused = None
+        if world > 1:
+            self.padded = torch.zeros((self.plan.max_rows, self.N), dtype=torch.bfloat16, device=dev)
+            self.gathered = torch.empty((world * self.plan.max_rows, self.N), dtype=torch.bfloat16, device=dev)
+            try:
+                import torch.distributed._symmetric_memory as symm
+                self.full, self.hdl = [], []
+                for _ in range(2):
+                    tt = symm.empty((self.total, self.N), dtype=torch.bfloat16, device=dev)
+                    self.hdl.append(symm.rendezvous(tt, dist.group.WORLD))
+                    self.full.append(tt)
+                self.fused = True
+            except Exception as e:  # noqa: BLE001
+                self.fused = False
+                self.fused_error = repr(e)[:200]
         self.h_A = torch.from_numpy(h["A"]).pin_memory()
         self.h_sA = torch.from_numpy(h["sA"]).pin_memory()
         self.h_C = torch.empty((self.total, self.N), dtype=torch.bfloat16).pin_memory()
         self.launches_per_step = 2  # one scale-repack launch + the matmul
 
     def work_per_step(self):
-        return 2 * self.total * self.N * self.K
+        return 2 * self.total * self.N * self.K   # whole job (all ranks together)
 
     def step(self, i):
         s = i % self.nsets
-        self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
-                                  workspace=self.ws)
+        if self.world == 1:
+            self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
+                                      workspace=self.ws)
+        elif self.fused:
+            f = i % 2
+            if self.groups:
+                self.ops.GroupMatmulMxfp4Scatter(self.hdl[f].buffer_ptrs, self.rank + 1, self.out_row_start, self.A[s], self.sA[s],
+                                                 self.B[s], self.sB[s], self.groups, self.K, self.N, workspace=self.ws)
+            self.hdl[f].barrier(channel=0)
+        else:
+            self.nccl_step(i)
+
+    def gemm_only_step(self, i):
+        s = i % self.nsets
+        if self.groups:
+            self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
+                                      workspace=self.ws)
+
+    def nccl_step(self, i):
+        """The unfused variant: local matmul, rows padded to the largest share, NCCL all-gather (the ragged blocks
+        still have to be put in order by the consumer)."""
+        s = i % self.nsets
+        self.gemm_only_step(i)
+        self.padded[:self.local_rows].copy_(self.C[s][:self.local_rows])
+        self.dist.all_gather_into_tensor(self.gathered, self.padded)
 
     def e2e_step(self, i):
         s = i % self.nsets
         self.A[s].copy_(self.h_A, non_blocking=True)      # this step's tokens and their scales; expert weights stay resident
         self.sA[s].copy_(self.h_sA, non_blocking=True)
         self.step(i)
-        self.h_C.copy_(self.C[s], non_blocking=True)
+        if self.world == 1:
+            self.h_C.copy_(self.C[s], non_blocking=True)
+        elif self.fused:
+            self.h_C.copy_(self.full[i % 2], non_blocking=True)
+        else:
+            if not hasattr(self, "h_gathered"):
+                self.h_gathered = self.torch.empty(self.gathered.shape, dtype=self.torch.bfloat16).pin_memory()
+            self.h_gathered.copy_(self.gathered, non_blocking=True)
 
     def e2e_bytes(self):
         return self.host["A"].nbytes + self.host["sA"].nbytes, self.total * self.N * 2
@@ -423,9 +485,16 @@ class Mxfp4Cfg5(Workload):
         _, want = O.group_matmul_mxfp4(np.ascontiguousarray(h["A"][:rows]), np.ascontiguousarray(h["sA"][:rows]),
                                        np.ascontiguousarray(h["B"][:1]), np.ascontiguousarray(h["sB"][:1]),
                                        np.array([rows], np.int64), self.K, self.N, want_f32=True)
+        self.gemm_only_step(0)
         got = self.C[0][:rows].float().cpu().numpy()
         self.ops.MatmulStatus()
-        return bool(np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3 * np.abs(want).max()))
+        ok = bool(np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3 * np.abs(want).max()))
+        if self.world > 1 and self.fused:   # the reassembled matrix holds the same bits at this group's rows, on every rank
+            self.step(0)
+            self.torch.cuda.synchronize()
+            r0 = self.out_row_start[0]
+            ok = ok and bool(self.torch.equal(self.full[0][r0:r0 + rows], self.C[0][:rows]))
+        return ok
 
 
 WORKLOADS = {"w8a8_cfg4": W8A8Cfg4, "mxfp4_cfg5": Mxfp4Cfg5, "antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3,
@@ -566,7 +635,7 @@ def run_ours(args):
     head = None
     sampler = ClockSampler(local) if rank == 0 else None   # runs across every timed region of this process
     for nm in names:
-        sharded = nm == "w8a8_cfg4"
+        sharded = nm in ("w8a8_cfg4", "mxfp4_cfg5")
         wl = WORKLOADS[nm](torch, ops, dev, dist, world, rank) if sharded else WORKLOADS[nm](torch, ops, dev)
         is_head = nm == (args.workload if args.workload != "all" else HEADLINE)
         sec = time_steps(torch, wl.step, args.steps, args.warmup, dist)
@@ -579,29 +648,27 @@ def run_ours(args):
         per = sec / args.steps
         work = wl.work_per_step()
         if sharded:
-            achieved = work / per / 1e12          # TOPS of the whole job (strong scaling: work is split over ranks)
+            achieved = work / per / 1e12          # T(FL)OPS of the whole job (strong scaling: work is split over ranks)
             total_value = achieved
             gsec = time_steps(torch, wl.gemm_only_step, args.steps, args.warmup, dist)
             if world == 1:
                 gsec = min(gsec, sec)
-            kern = work / world / (gsec / args.steps) / 1e12   # this rank's matmul kernel alone
-            peak = 2.0 * peaks["bf16_tflops"]
+            # the slowest rank's matmul alone, as a rate per GPU (group shares are not exactly equal)
+            kern = work / world / (gsec / args.steps) / 1e12
+            int8 = nm == "w8a8_cfg4"
+            peak = (2.0 if int8 else 4.0) * peaks["bf16_tflops"]
             extra = {}
             if world > 1:
                 extra["reassembly"] = ("fused epilogue peer stores + symmetric-memory barrier" if wl.fused
                                        else "NCCL all-gather (symmetric memory unavailable: %s)" % getattr(wl, "fused_error", ""))
                 nsec = time_steps(torch, wl.nccl_step, args.steps, args.warmup, dist)
-                extra["nccl_allgather_variant_tops"] = work / (nsec / args.steps) / 1e12
-            roof = {"bound": "tensor", "achieved": kern, "peak": peak, "unit": "TOPS", "frac": kern / peak, "traffic": None,
-                    "peak_source": "2 x %s dense bf16 cuBLAS burst (int8 runs at twice the bf16 rate; nominal 4500)"
+                extra["nccl_allgather_variant"] = work / (nsec / args.steps) / 1e12
+            roof = {"bound": "tensor", "achieved": kern, "peak": peak, "unit": wl.unit, "frac": kern / peak, "traffic": None,
+                    "peak_source": ("2 x %s dense bf16 cuBLAS burst (int8 runs at twice the bf16 rate; nominal 4500)" if int8 else
+                                    "4 x %s dense bf16 cuBLAS burst (FP4 runs at four times the bf16 rate; nominal 9000)")
                                    % peaks["source"], "kernel_ms": gsec / args.steps * 1e3}
         elif wl.bound == "tensor":
-            achieved = work / per / 1e12          # TFLOPS per rank (replicas)
-            total_value = achieved * world
-            peak = 4.0 * peaks["bf16_tflops"]
-            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOPS", "frac": achieved / peak,
-                    "traffic": None, "peak_source": "4 x %s dense bf16 cuBLAS burst (FP4 runs at four times the bf16 rate; "
-                                                    "nominal 9000)" % peaks["source"]}
+            raise AssertionError("every tensor-bound workload shards")
         else:
             achieved = work / per / 1e9           # GB/s (each rank does the full workload: replicas)
             total_value = achieved * world
@@ -644,7 +711,7 @@ def run_ours(args):
                 "dtype": wl.dtype, "data": "synthetic",
                 "config": {"workload": rec["name"], "timing": "buffers rotate over a set larger than L2 (126 MB)",
                            "launch": rec["launch"],
-                           "sharding": ("B column-sharded over N; C reassembled inside the step: " + rec.get("reassembly", "single GPU")
+                           "sharding": ((wl.sharding_note + "; C reassembled inside the step: ") + rec.get("reassembly", "single GPU")
                                         if rec["scaling"] == "strong"
                                         else "replicas only (elementwise operators do not shard)")},
                 "roofline": rec["roofline"], "e2e": rec["e2e"], "gpu_launches": args.steps * rec["launches_per_step"],
@@ -725,10 +792,17 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all"] + list(WORKLOADS))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; the JSON line must be the only thing on
+    # stdout, so everything else is sent to stderr while the run lasts.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real_stdout, "w")
     if args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
+    sys.stdout.flush()
 
 
 if __name__ == "__main__":

@@ -274,6 +274,24 @@ ascq_status ascq_matmul_w8a8_scatter(void* const* C_bufs, int nBufs, int firstBu
                                      const void* bias_bf16, int M, int N, int K, void* stream);
 
 /*
+ * The grouped MX-FP4 matmul with the reassembly of a group-parallel layout fused into its epilogue.  With the
+ * groups dealt out over the GPUs of one box (one process per GPU), every rank computes the output rows of its own
+ * groups and writes them into EVERY buffer of C_bufs: group g's rows go to rows outRowStart_host[g] .. of each bf16
+ * [*, N] matrix.  C_bufs holds this GPU's output matrix and the peer-mapped addresses of the other GPUs' matrices
+ * (plain stores over NVLink; nothing is loaded from a peer).  firstBuf rotates the store order so that the ranks do
+ * not all write to the same peer at the same time.  The caller orders the step: a barrier across the ranks after
+ * the launches, before anyone reads its matrix.  outRowStart_host may be NULL (groups follow each other as in A).
+ * It replaces the all-gather (of ragged row blocks) that the reference's grouped matmul leaves to its caller
+ * (examples/03_libraries/00_matmul/quant_group_matmul_custom: one core group per group, output rows disjoint).
+ * 1 <= nBufs <= 8; all other arguments as for ascq_group_matmul_mxfp4.
+ */
+ascq_status ascq_group_matmul_mxfp4_scatter(void* const* C_bufs, int nBufs, int firstBuf,
+                                            const int64_t* outRowStart_host, const uint8_t* A_fp4,
+                                            const uint8_t* sA_e8m0, const uint8_t* B_fp4, const uint8_t* sB_e8m0,
+                                            const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                            size_t workspaceBytes, void* stream);
+
+/*
  * Synchronises `stream`, then reads and clears the status word the matmul kernels keep on the
  * current device.  ASCQ_ERR_TIMEOUT when a kernel gave up a bounded wait (its output is then
  * undefined); no counterpart in the reference, whose kernels cannot report.

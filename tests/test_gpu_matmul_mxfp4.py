@@ -73,6 +73,26 @@ def test_both_tile_shapes_give_the_same_bits(tile, monkeypatch):
     check_close(run(A, sA, B, sB, groups, K, N), want_f32, tile)
 
 
+def test_scatter_writes_every_buffer_at_the_given_rows():
+    """The fused reassembly of a group-parallel layout, on one GPU: three output matrices stand for this GPU's and two
+    peers'; the groups computed here are placed at their rows of the full output, other rows stay untouched."""
+    groups, N, K = [130, 0, 300, 64], 512, 512
+    out_row_start = [700, 0, 100, 420]           # where each group lives in the full [1000, N] output
+    A, sA, B, sB = make_case(groups, N, K, 31)
+    want = run(A, sA, B, sB, groups, K, N)       # plain entry point: groups one after the other
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    bufs = [torch.full((1000, N), -1.0, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    ops.GroupMatmulMxfp4Scatter([b.data_ptr() for b in bufs], 1, out_row_start, t(A), t(sA), t(B), t(sB), groups, K, N)
+    ops.MatmulStatus()
+    expect = np.full((1000, N), O.f32_to_bf16_bits(np.array([-1.0], np.float32))[0], np.uint16)
+    src = 0
+    for g, mg in enumerate(groups):
+        expect[out_row_start[g]:out_row_start[g] + mg] = want[src:src + mg]
+        src += mg
+    for b in bufs:
+        assert_bits_equal(b.view(torch.int16).cpu().numpy().view(np.uint16), expect, "scatter buffer")
+
+
 @pytest.mark.parametrize("groups,N,K", [([128, 200], 256, 512), ([77], 320, 256)])
 def test_exact_when_sums_are_representable(groups, N, K):
     # codes {0, +-0.5, +-1, +-2} with unit scales: every partial sum is a small multiple of 0.25 -> exact in fp32
