@@ -92,7 +92,7 @@ struct Params {
 // ---- scale repack ----------------------------------------------------------------------------------
 // One launch rewrites the e8m0 scales of A and of B into the records the matmul copies to tensor memory.
 // Block (x, y): x < numTilesA is a 128-row tile of A (rows from the tile table), otherwise a 128-row tile of B
-// (group*N + tile128*128); y selects a slab of kSlab 4-byte chunks along K.  The block reads its rows as they lie
+// (group*N + tile128*128); y selects a slab of kSlab 4-byte chunks along K (128 bytes of every row).  The block reads its rows as they lie
 // in memory (whole rows, coalesced), turns them in shared memory and writes whole 512-byte chunks: word w of a
 // chunk holds the four scale bytes of row 32*(w&3) + (w>>2).  Rows or chunks without data get scale 1.0 (0x7F);
 // the operand bytes there are zero.
@@ -100,7 +100,7 @@ struct Params {
 // The same launch builds the row-tile table the matmul reads: with up to kInlineGroups groups the rows per group
 // travel as a kernel argument, every A block derives its own entry and the blocks of slab 0 store theirs.  (No
 // host-to-device copy is then part of the call.)  With more groups the host builds the table and copies it.
-constexpr int kSlab = 64;
+constexpr int kSlab = 32;
 constexpr int kInlineGroups = 256;
 struct GroupRows {
     int rows[kInlineGroups];      // rows of A per group

@@ -500,6 +500,10 @@ class Mxfp4Cfg5(Workload):
 WORKLOADS = {"w8a8_cfg4": W8A8Cfg4, "mxfp4_cfg5": Mxfp4Cfg5, "antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3,
              "quant_scaled": QuantScaled}
 HEADLINE = "w8a8_cfg4"
+# DRAM bytes read + written by the dominant kernel of one step at full size on one GPU, from the ncu captures
+# summarised in profiles/<workload>_ncu_counters.md (outputs that stay in the 126 MB L2 do not show up as DRAM writes).
+TRAFFIC_BYTES = {"w8a8_cfg4": 36.8e6, "mxfp4_cfg5": 234.5e6, "antiquant_cfg2": 79.4e6, "dequant_cfg3": 33.6e6,
+                 "quant_scaled": 364.1e6}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -674,6 +678,8 @@ def run_ours(args):
             total_value = achieved * world
             roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
+        if world == 1:
+            roof["traffic"] = TRAFFIC_BYTES.get(nm)
         e2e_sec = time_steps(torch, wl.e2e_step, max(2, args.steps // 4), 2, dist)
         e2e_per = e2e_sec / max(2, args.steps // 4)
         h2d, d2h = wl.e2e_bytes()
