@@ -35,6 +35,12 @@ class AntiQuantParam(C.Structure):
                 ("hasOffset", C.c_int32), ("isTranspose", C.c_int32), ("kDim", C.c_int32)]
 
 
+class QuantizeParam(C.Structure):
+    """ascq_quantize_param: QuantizeConfig + QuantizeParams of the unified interface."""
+    _fields_ = [("m", C.c_uint32), ("n", C.c_uint32), ("groupSize", C.c_uint32), ("hasOffset", C.c_int32),
+                ("kDim", C.c_int32), ("roundMode", C.c_int)]
+
+
 class AscqError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"{status_string(status)}: {message}")
@@ -54,6 +60,9 @@ SIGNATURES = {
     "ascq_dynamic_quant_per_token": (_i, [_vp, _vp, _vp, _vp, _i, _u32, _u32, _vp]),
     "ascq_dequant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _i, C.POINTER(DequantParam), _vp]),
     "ascq_antiquant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(AntiQuantParam), _vp]),
+   "ascq_quantize": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(QuantizeParam), _vp]),
+    "ascq_dequantize": (_i, [_vp, _i, _vp, _i, _vp, _i, _f, _i, C.POINTER(QuantizeParam), _vp]),
+    "ascq_antiquantize": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(QuantizeParam), _vp]),
     "ascq_matmul_w8a8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "ascq_matmul_w8a8_scatter": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ascq_matmul_status": (_i, [_vp]),

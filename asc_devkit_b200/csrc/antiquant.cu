@@ -21,6 +21,8 @@ ascq_status dispatch_fast(const EwArgs& a, ascq_dtype dstT, ascq_dtype scT, ascq
     if (ct == ASCQ_DT_F32) {
         if (dstT == ASCQ_DT_BF16 && (scT == ASCQ_DT_BF16 || smode == kSScalar))
             return run_fast<__nv_bfloat16, __nv_bfloat16, float>(a, smode, hasOff, st);
+        if (dstT == ASCQ_DT_F16 && (scT == ASCQ_DT_F16 || smode == kSScalar))  // the unified AntiQuantize interface
+            return run_fast<__half, __half, float>(a, smode, hasOff, st);
         if (scT == ASCQ_DT_F32) {
             if (dstT == ASCQ_DT_F32) return run_fast<float, float, float>(a, smode, hasOff, st);
             if (dstT == ASCQ_DT_F16) return run_fast<__half, float, float>(a, smode, hasOff, st);
@@ -70,9 +72,12 @@ __global__ void __launch_bounds__(256) mx_decode_kernel(Dst* __restrict__ dst, c
 
 using namespace ascq;
 
-extern "C" ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* offset,
-                                      const void* scale, ascq_dtype scaleT, float offsetScalar, float scaleScalar,
-                                      ascq_policy policy, const ascq_antiquant_param* p, void* stream)
+// Shared body.  `unified` selects the numerics of the AntiQuantize interface
+// (impl/adv_api/detail/quantization/antiquantize/antiquantize_3510_impl.h:252-381, antiquantize_impl.h:68-190):
+// every policy widens source, offset and scale to fp32, adds, multiplies and casts once (RINT, saturating).
+static ascq_status antiquant_common(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* offset,
+                                    const void* scale, ascq_dtype scaleT, float offsetScalar, float scaleScalar,
+                                    ascq_policy policy, const ascq_antiquant_param* p, void* stream, bool unified)
 {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!dst || !src || !p) return fail(ASCQ_ERR_INVALID_ARG, "dst, src and param must not be NULL");
@@ -145,7 +150,8 @@ extern "C" ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* sr
         } else {
             if (!scale) return fail(ASCQ_ERR_INVALID_ARG, "scale tensor must not be NULL");
             if (scaleT != dstT) return fail(ASCQ_ERR_UNSUPPORTED, "scale/offset dtype must equal the output dtype");
-            hasOff = offset != nullptr;
+            hasOff = unified ? (p->hasOffset != 0) : (offset != nullptr);
+            if (hasOff && !offset) return fail(ASCQ_ERR_INVALID_ARG, "hasOffset is set but the offset tensor is NULL");
             const uint32_t K = p->isTranspose ? n : rows;
             const uint32_t gs = p->groupSize ? p->groupSize : K;
             if (K % gs != 0) return fail(ASCQ_ERR_INVALID_ARG, "K %u must be a multiple of groupSize %u", K, gs);
@@ -206,6 +212,7 @@ extern "C" ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* sr
         }
     }
 
+    if (unified) ct = ASCQ_DT_F32;
     if (ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {
         bool handled = false;
         ascq_status rc = dispatch_fast(a, dstT, scaleT, ct, smode, hasOff, st, &handled);
@@ -217,4 +224,22 @@ extern "C" ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* sr
     g.scale = a.scale; g.offset = a.offset; g.scaleIsScalar = (smode == kSScalar); g.hasOff = hasOff;
     g.offIsScalar = (smode == kSScalar); g.roundMode = kRoundRint;
     return launch_ew_generic(g, st);
+}
+
+extern "C" ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* offset,
+                                      const void* scale, ascq_dtype scaleT, float offsetScalar, float scaleScalar,
+                                      ascq_policy policy, const ascq_antiquant_param* p, void* stream)
+{
+    return antiquant_common(dst, dstT, src, srcT, offset, scale, scaleT, offsetScalar, scaleScalar, policy, p, stream, false);
+}
+
+extern "C" ascq_status ascq_antiquantize(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* offset,
+                                         const void* scale, ascq_dtype scaleT, float offsetScalar, float scaleScalar,
+                                         ascq_policy policy, const ascq_quantize_param* qp, void* stream)
+{
+    if (!qp) return fail(ASCQ_ERR_INVALID_ARG, "dst, src and param must not be NULL");
+    if (policy < ASCQ_PER_TENSOR || policy > ASCQ_PER_GROUP)
+        return fail(ASCQ_ERR_UNSUPPORTED, "Unsupported AntiQuantize policy on current device");
+    ascq_antiquant_param p{qp->m, qp->n, 0, policy == ASCQ_PER_GROUP ? qp->groupSize : 0, qp->hasOffset, 0, qp->kDim};
+    return antiquant_common(dst, dstT, src, srcT, offset, scale, scaleT, offsetScalar, scaleScalar, policy, &p, stream, true);
 }

@@ -135,3 +135,20 @@ extern "C" ascq_status ascq_dequant(void* dst, ascq_dtype dstT, const void* src,
     g.scale = a.scale; g.scaleIsScalar = (smode == kSScalar); g.hasOff = 0; g.tok = tokScale; g.roundMode = kRoundRint;
     return launch_ew_generic(g, st);
 }
+
+// Dequantize (impl/adv_api/detail/quantization/dequantize/dequantize_impl.h:100-215) forwards to the AscendDequant
+// implementations with whole rows (calCount = n for PER_TENSOR / PER_CHANNEL, m * n otherwise) and has no offset.
+extern "C" ascq_status ascq_dequantize(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
+                                       ascq_dtype scaleT, float scaleScalar, ascq_policy policy,
+                                       const ascq_quantize_param* qp, void* stream)
+{
+    if (!qp) return fail(ASCQ_ERR_INVALID_ARG, "dst, src and param must not be NULL");
+    if (policy < ASCQ_PER_TENSOR || policy > ASCQ_PER_GROUP)
+        return fail(ASCQ_ERR_UNSUPPORTED, "Unsupported Dequantize policy on current device");
+    if (qp->hasOffset) return fail(ASCQ_ERR_UNSUPPORTED, "Dequantize do not support offset currently");
+    const bool rowWise = policy == ASCQ_PER_TENSOR || policy == ASCQ_PER_CHANNEL;
+    const uint64_t total = static_cast<uint64_t>(qp->m) * qp->n;
+    if (total > 0xFFFFFFFFull) return fail(ASCQ_ERR_INVALID_ARG, "m * n does not fit 32 bits");
+    ascq_dequant_param p{qp->m, qp->n, rowWise ? qp->n : static_cast<uint32_t>(total), qp->groupSize, qp->kDim};
+    return ascq_dequant(dst, dstT, src, srcT, scale, nullptr, scaleT, scaleScalar, policy, &p, stream);
+}

@@ -54,11 +54,16 @@ ascq_status dispatch_fast(const EwArgs& a, ascq_dtype srcT, ascq_dtype scT, ascq
         if (srcT == ASCQ_DT_BF16 && scT == ASCQ_DT_BF16)
             return run_fast<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(a, smode, hasOff, st);
     } else {
-        if (scT == ASCQ_DT_F32) {
+        // scalar operands carry no storage type: reuse the float-scale instantiation
+        const ascq_dtype sc = (smode == kSScalar) ? ASCQ_DT_F32 : scT;
+        if (sc == ASCQ_DT_F32) {
             if (srcT == ASCQ_DT_F16) return run_fast<__half, float, float>(a, smode, hasOff, st);
             if (srcT == ASCQ_DT_BF16) return run_fast<__nv_bfloat16, float, float>(a, smode, hasOff, st);
             if (srcT == ASCQ_DT_F32) return run_fast<float, float, float>(a, smode, hasOff, st);
         }
+        // the unified Quantize interface: 16-bit scales widened to fp32
+        if (srcT == ASCQ_DT_F16 && sc == ASCQ_DT_F16) return run_fast<__half, __half, float>(a, smode, hasOff, st);
+        if (srcT == ASCQ_DT_BF16 && sc == ASCQ_DT_BF16) return run_fast<__nv_bfloat16, __nv_bfloat16, float>(a, smode, hasOff, st);
     }
     *handled = false;
     return ASCQ_OK;
@@ -69,9 +74,13 @@ ascq_status dispatch_fast(const EwArgs& a, ascq_dtype srcT, ascq_dtype scT, ascq
 
 using namespace ascq;
 
-extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
-                                  const void* offset, ascq_dtype scaleT, float scaleScalar, float offsetScalar,
-                                  ascq_policy policy, const ascq_quant_param* p, void* stream)
+// Shared body.  `unified` selects the numerics of the Quantize interface
+// (impl/adv_api/detail/quantization/quantize/quantize_impl.h:832-975): every policy computes in fp32 (source and
+// scale/offset widened to fp32, one rounded multiply, one rounded add), honours hasOffset and roundMode, and takes
+// the tensor as m rows of n (calCount = m * n).
+static ascq_status quant_common(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
+                                const void* offset, ascq_dtype scaleT, float scaleScalar, float offsetScalar,
+                                ascq_policy policy, const ascq_quant_param* p, void* stream, bool unified)
 {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!dst || !src || !p) return fail(ASCQ_ERR_INVALID_ARG, "dst, src and param must not be NULL");
@@ -91,6 +100,16 @@ extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, a
     bool hasOff = true;
     ascq_dtype ct = ASCQ_DT_F16;
 
+    if (unified) {
+        if (!is_float_type(scaleT)) return fail(ASCQ_ERR_UNSUPPORTED, "Quantize only support half/float/bfloat16_t scale dtype");
+        if (scaleT != ASCQ_DT_F32 && scaleT != srcT)
+            return fail(ASCQ_ERR_UNSUPPORTED, "Failed to check data type for Quantize: (src, scale) must be (T, T) or (T, float)");
+        if (p->roundMode < ASCQ_CAST_NONE || p->roundMode > ASCQ_CAST_TRUNC)
+            return fail(ASCQ_ERR_INVALID_ARG, "unknown roundMode %d", (int)p->roundMode);
+        ct = ASCQ_DT_F32;
+        hasOff = p->hasOffset != 0;
+        a.roundMode = static_cast<int>(p->roundMode);
+    }
     if (policy == ASCQ_PER_TENSOR) {
         if (dstT != ASCQ_DT_I8) return fail(ASCQ_ERR_UNSUPPORTED, "per-tensor AscendQuant writes int8 only");
         if (scale || offset) return fail(ASCQ_ERR_INVALID_ARG, "per-tensor AscendQuant takes scalar scale/offset; tensors must be NULL");
@@ -109,9 +128,9 @@ extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, a
         a.srcStride = a.dstStride = p->n;
         if (policy == ASCQ_PER_CHANNEL) {
             if (dstT != ASCQ_DT_I8) return fail(ASCQ_ERR_UNSUPPORTED, "per-channel AscendQuant writes int8 only");
-            if (scaleT != ASCQ_DT_F16 && scaleT != ASCQ_DT_F32)
+            if (!unified && scaleT != ASCQ_DT_F16 && scaleT != ASCQ_DT_F32)
                 return fail(ASCQ_ERR_UNSUPPORTED, "per-channel scale dtype must be half or float");
-            if ((static_cast<size_t>(p->n) * dtype_size(scaleT)) % 32 != 0)
+            if (!unified && (static_cast<size_t>(p->n) * dtype_size(scaleT)) % 32 != 0)
                 return fail(ASCQ_ERR_INVALID_ARG, "scaleCount is %u, which should be 32B aligned", p->n);
             smode = kSColVec;
             a.scale.p = scale; a.scale.rdiv = 0; a.scale.cdiv = 1; a.scale.stride = 0;
@@ -122,7 +141,7 @@ extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, a
             if (!is_float_type(scaleT)) return fail(ASCQ_ERR_UNSUPPORTED, "scale dtype must be half, bfloat16_t or float");
             if (scaleT != ASCQ_DT_F32 && scaleT != srcT)
                 return fail(ASCQ_ERR_UNSUPPORTED, "unsupported (src, scale) dtype pair for AscendQuant PER_TOKEN/PER_GROUP");
-            ct = scaleT;
+            ct = unified ? ASCQ_DT_F32 : scaleT;
             hasOff = p->hasOffset != 0;
             if (hasOff && !offset) return fail(ASCQ_ERR_INVALID_ARG, "hasOffset is set but the offset tensor is NULL");
             if (p->roundMode < ASCQ_CAST_NONE || p->roundMode > ASCQ_CAST_TRUNC)
@@ -161,7 +180,7 @@ extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, a
             GenericArgs g{};
             g.op = kOpQuant; g.srcT = srcT; g.dstT = dstT; g.scT = scaleT; g.ct = ct;
             g.src = src; g.dst = dst; g.rows = 1; g.cols = a.cols; g.srcStride = g.dstStride = a.cols;
-            g.scale = a.scale; g.offset = a.offset; g.scaleIsScalar = 1; g.hasOff = 1; g.offIsScalar = 1;
+            g.scale = a.scale; g.offset = a.offset; g.scaleIsScalar = 1; g.hasOff = hasOff; g.offIsScalar = 1;
             g.roundMode = a.roundMode; g.srcBase = g.dstBase = done;
             return launch_ew_generic(g, st);
         }
@@ -180,6 +199,26 @@ extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, a
     g.offIsScalar = (smode == kSScalar) || (policy == ASCQ_PER_CHANNEL && !offset);
     g.roundMode = a.roundMode;
     return launch_ew_generic(g, st);
+}
+
+extern "C" ascq_status ascq_quant(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
+                                  const void* offset, ascq_dtype scaleT, float scaleScalar, float offsetScalar,
+                                  ascq_policy policy, const ascq_quant_param* p, void* stream)
+{
+    return quant_common(dst, dstT, src, srcT, scale, offset, scaleT, scaleScalar, offsetScalar, policy, p, stream, false);
+}
+
+extern "C" ascq_status ascq_quantize(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
+                                     const void* offset, ascq_dtype scaleT, float scaleScalar, float offsetScalar,
+                                     ascq_policy policy, const ascq_quantize_param* qp, void* stream)
+{
+    if (!qp) return fail(ASCQ_ERR_INVALID_ARG, "dst, src and param must not be NULL");
+    if (policy < ASCQ_PER_TENSOR || policy > ASCQ_PER_GROUP)
+        return fail(ASCQ_ERR_UNSUPPORTED, "unsupported policy for Quantize in current device!");
+    const uint64_t total = static_cast<uint64_t>(qp->m) * qp->n;
+    if (total > 0xFFFFFFFFull) return fail(ASCQ_ERR_INVALID_ARG, "m * n does not fit 32 bits");
+    ascq_quant_param p{qp->m, qp->n, static_cast<uint32_t>(total), qp->groupSize, qp->hasOffset, qp->kDim, qp->roundMode};
+    return quant_common(dst, dstT, src, srcT, scale, offset, scaleT, scaleScalar, offsetScalar, policy, &p, stream, true);
 }
 
 // ---- dynamic per-token quantisation -------------------------------------------------------------

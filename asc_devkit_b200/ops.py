@@ -164,6 +164,58 @@ def AscendAntiQuant(dstTensor: torch.Tensor, srcTensor: torch.Tensor, offset, sc
     return dstTensor
 
 
+# ---- the unified interface (include/adv_api/quantization/quantize.h, dequantize.h, antiquantize.h) ---------------
+@dataclass
+class QuantizeParams:
+    """QuantizeParams / DequantizeParams / AntiQuantizeParams (quantize_utils.h:43-47)"""
+    m: int
+    n: int
+    groupSize: int = 0
+
+
+def _scalar_code(dstTensor, scale, override):
+    return dtype_code(scale, override) if isinstance(scale, torch.Tensor) else L.DT_F32
+
+
+def Quantize(dstTensor: torch.Tensor, srcTensor: torch.Tensor, scale, offset, params: QuantizeParams, *, policy: int,
+             hasOffset: bool = False, roundMode: int = CAST_RINT, kDim: int = 1, dst_dtype: int = L.DT_I8, stream=None):
+    """Quantize<config>(dst, src, scale, offset, params) (quantize.h:41-62): fp32 arithmetic for every policy.
+    PER_TENSOR takes Python floats, the other policies tensors (PER_CHANNEL also a float offset)."""
+    st, ot = isinstance(scale, torch.Tensor), isinstance(offset, torch.Tensor)
+    p = L.QuantizeParam(params.m, params.n, params.groupSize, int(bool(hasOffset)), kDim, roundMode)
+    L.check(L.lib().ascq_quantize(_ptr(dstTensor), dst_dtype, _ptr(srcTensor), dtype_code(srcTensor),
+                                  _ptr(scale) if st else None, _ptr(offset) if ot else None,
+                                  dtype_code(scale) if st else L.DT_F32, 0.0 if st else float(scale),
+                                  float(offset) if (offset is not None and not ot) else 0.0, policy, C.byref(p),
+                                  _stream(stream)))
+    return dstTensor
+
+
+def Dequantize(dstTensor: torch.Tensor, srcTensor: torch.Tensor, scale, offset, params: QuantizeParams, *, policy: int,
+               hasOffset: bool = False, kDim: int = 1, scale_dtype: Optional[int] = None, stream=None):
+    """Dequantize<config>(dst, src, scale, offset, params) (dequantize.h): forwards to the AscendDequant kernels on
+    whole rows; the reference accepts no offset yet (``offset`` is ignored, ``hasOffset`` must be False)."""
+    st = isinstance(scale, torch.Tensor)
+    p = L.QuantizeParam(params.m, params.n, params.groupSize, int(bool(hasOffset)), kDim, CAST_RINT)
+    L.check(L.lib().ascq_dequantize(_ptr(dstTensor), dtype_code(dstTensor), _ptr(srcTensor), dtype_code(srcTensor),
+                                    _ptr(scale) if st else None, dtype_code(scale, scale_dtype) if st else L.DT_F32,
+                                    0.0 if st else float(scale), policy, C.byref(p), _stream(stream)))
+    return dstTensor
+
+
+def AntiQuantize(dstTensor: torch.Tensor, srcTensor: torch.Tensor, scale, offset, params: QuantizeParams, *, policy: int,
+                 hasOffset: bool = False, kDim: int = 1, stream=None):
+    """AntiQuantize<config>(dst, src, scale, offset, params) (antiquantize.h): dst = (src + offset) * scale in fp32."""
+    st, ot = isinstance(scale, torch.Tensor), isinstance(offset, torch.Tensor)
+    p = L.QuantizeParam(params.m, params.n, params.groupSize, int(bool(hasOffset)), kDim, CAST_RINT)
+    L.check(L.lib().ascq_antiquantize(_ptr(dstTensor), dtype_code(dstTensor), _ptr(srcTensor), dtype_code(srcTensor),
+                                      _ptr(offset) if ot else None, _ptr(scale) if st else None,
+                                      dtype_code(scale) if st else dtype_code(dstTensor),
+                                      float(offset) if (offset is not None and not ot) else 0.0,
+                                      0.0 if st else float(scale), policy, C.byref(p), _stream(stream)))
+    return dstTensor
+
+
 def MatmulW8A8(C: Optional[torch.Tensor], A: torch.Tensor, B_nk: torch.Tensor, scaleA: Optional[torch.Tensor] = None,
                scaleB: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
                accDump: Optional[torch.Tensor] = None, stream=None):

@@ -192,6 +192,36 @@ ascq_status ascq_antiquant(void* dst, ascq_dtype dstT, const void* src, ascq_dty
                            const ascq_antiquant_param* param, void* stream);
 
 /*
+ * The unified interface Quantize / Dequantize / AntiQuantize (include/adv_api/quantization/quantize.h:41-62,
+ * dequantize.h, antiquantize.h; QuantizeConfig{policy, hasOffset, roundMode, kDim} and QuantizeParams{m, n, groupSize}
+ * in quantize_utils.h:34-47 become one run-time struct).  Same tensors and policies as the Ascend* calls above, but
+ * every policy computes in fp32: operands widened to fp32, one rounded multiply and one rounded add, one final cast
+ * (impl/adv_api/detail/quantization/quantize/quantize_impl.h:832-975,
+ *  antiquantize/antiquantize_3510_impl.h:252-381, dequantize/dequantize_impl.h:100-215).
+ *   ascq_quantize      dst = cast(float(src) * float(scale) [+ float(offset)]), cast with roundMode + saturation;
+ *                      PER_TENSOR: scalars; PER_CHANNEL: scale[n] and offset[n] (or scalar offset when `offset` is
+ *                      NULL); PER_TOKEN: [m]; PER_GROUP: as ascq_quant.  (src, scale) dtypes (T, T) or (T, float).
+ *   ascq_dequantize    forwards to ascq_dequant on whole rows; hasOffset must be 0.
+ *   ascq_antiquantize  dst = cast((float(src) + float(offset)) * float(scale)); int8 source, never transposed;
+ *                      PER_TENSOR: scalars rounded to dstT; PER_CHANNEL: [n] of dstT; PER_TOKEN: [m]; PER_GROUP.
+ */
+typedef struct ascq_quantize_param {
+    uint32_t m, n, groupSize;
+    int32_t hasOffset;
+    int32_t kDim;
+    ascq_round roundMode; /* ascq_quantize only */
+} ascq_quantize_param;
+ascq_status ascq_quantize(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
+                          const void* offset, ascq_dtype scaleT, float scaleScalar, float offsetScalar,
+                          ascq_policy policy, const ascq_quantize_param* param, void* stream);
+ascq_status ascq_dequantize(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
+                            ascq_dtype scaleT, float scaleScalar, ascq_policy policy,
+                            const ascq_quantize_param* param, void* stream);
+ascq_status ascq_antiquantize(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* offset,
+                              const void* scale, ascq_dtype scaleT, float offsetScalar, float scaleScalar,
+                              ascq_policy policy, const ascq_quantize_param* param, void* stream);
+
+/*
  * W8A8 matmul with fused dequant epilogue (AscendC::Matmul<int8,int8,int32> +
  * AscendDequant per-channel x per-token; include/adv_api/matmul/matmul.h:79-398,
  * impl/adv_api/detail/matmul/stage/compute/mmad_compute.h:83, epilogue order

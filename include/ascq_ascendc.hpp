@@ -183,6 +183,85 @@ inline void AscendAntiQuant(const GlobalTensor<dstT>& dst, const GlobalTensor<sr
                                static_cast<ascq_policy>(policy), &p, stream));
 }
 
+// ---- the unified interface (include/adv_api/quantization/quantize.h:41-62, dequantize.h, antiquantize.h) ----------
+enum class QuantizePolicy : int32_t { PER_TENSOR, PER_CHANNEL, PER_TOKEN, PER_GROUP };
+using DequantizePolicy = QuantizePolicy;
+using AntiQuantizePolicy = QuantizePolicy;
+struct QuantizeConfig {
+    QuantizePolicy policy;
+    bool hasOffset = false;
+    RoundMode roundMode = RoundMode::CAST_RINT;
+    int32_t kDim = 1;
+};
+struct DequantizeConfig { DequantizePolicy policy; bool hasOffset = false; int32_t kDim = 1; };
+struct AntiQuantizeConfig { AntiQuantizePolicy policy; bool hasOffset = false; int32_t kDim = 1; };
+struct QuantizeParams { uint32_t m, n, groupSize = 0; };
+using DequantizeParams = QuantizeParams;
+using AntiQuantizeParams = QuantizeParams;
+
+namespace detail {
+inline ascq_quantize_param pack(const QuantizeParams& p, bool hasOffset, int32_t kDim, RoundMode mode)
+{
+    return ascq_quantize_param{p.m, p.n, p.groupSize, hasOffset ? 1 : 0, kDim, static_cast<ascq_round>(mode)};
+}
+}  // namespace detail
+
+// Quantize, scalar scale and offset (PER_TENSOR)
+template <typename DstT, typename SrcT>
+inline void Quantize(const QuantizeConfig& config, const GlobalTensor<DstT>& dst, const GlobalTensor<SrcT>& src, float scale,
+                     float offset, const QuantizeParams& params, void* stream = nullptr)
+{
+    const ascq_quantize_param p = detail::pack(params, config.hasOffset, config.kDim, config.roundMode);
+    ascq::check(ascq_quantize(dst.ptr, ascq::DTypeOf<DstT>::value, src.ptr, ascq::DTypeOf<SrcT>::value, nullptr, nullptr,
+                              ASCQ_DT_F32, scale, offset, static_cast<ascq_policy>(config.policy), &p, stream));
+}
+// Quantize, tensor scale and offset (PER_CHANNEL / PER_TOKEN / PER_GROUP)
+template <typename DstT, typename SrcT, typename ScaleT>
+inline void Quantize(const QuantizeConfig& config, const GlobalTensor<DstT>& dst, const GlobalTensor<SrcT>& src,
+                     const GlobalTensor<ScaleT>& scale, const GlobalTensor<ScaleT>& offset, const QuantizeParams& params,
+                     void* stream = nullptr)
+{
+    const ascq_quantize_param p = detail::pack(params, config.hasOffset, config.kDim, config.roundMode);
+    ascq::check(ascq_quantize(dst.ptr, ascq::DTypeOf<DstT>::value, src.ptr, ascq::DTypeOf<SrcT>::value, scale.ptr,
+                              config.hasOffset ? offset.ptr : nullptr, ascq::DTypeOf<ScaleT>::value, 0.f, 0.f,
+                              static_cast<ascq_policy>(config.policy), &p, stream));
+}
+template <typename DstT, typename SrcT>
+inline void Dequantize(const DequantizeConfig& config, const GlobalTensor<DstT>& dst, const GlobalTensor<SrcT>& src, float scale,
+                       const DequantizeParams& params, void* stream = nullptr)
+{
+    const ascq_quantize_param p = detail::pack(params, config.hasOffset, config.kDim, RoundMode::CAST_RINT);
+    ascq::check(ascq_dequantize(dst.ptr, ascq::DTypeOf<DstT>::value, src.ptr, ascq::DTypeOf<SrcT>::value, nullptr, ASCQ_DT_F32,
+                                scale, static_cast<ascq_policy>(config.policy), &p, stream));
+}
+template <typename DstT, typename SrcT, typename ScaleT>
+inline void Dequantize(const DequantizeConfig& config, const GlobalTensor<DstT>& dst, const GlobalTensor<SrcT>& src,
+                       const GlobalTensor<ScaleT>& scale, const GlobalTensor<ScaleT>& /*offset: not supported by the reference yet*/,
+                       const DequantizeParams& params, void* stream = nullptr)
+{
+    const ascq_quantize_param p = detail::pack(params, config.hasOffset, config.kDim, RoundMode::CAST_RINT);
+    ascq::check(ascq_dequantize(dst.ptr, ascq::DTypeOf<DstT>::value, src.ptr, ascq::DTypeOf<SrcT>::value, scale.ptr,
+                                ascq::DTypeOf<ScaleT>::value, 0.f, static_cast<ascq_policy>(config.policy), &p, stream));
+}
+template <typename DstT, typename SrcT>
+inline void AntiQuantize(const AntiQuantizeConfig& config, const GlobalTensor<DstT>& dst, const GlobalTensor<SrcT>& src, float scale,
+                         float offset, const AntiQuantizeParams& params, void* stream = nullptr)
+{
+    const ascq_quantize_param p = detail::pack(params, config.hasOffset, config.kDim, RoundMode::CAST_RINT);
+    ascq::check(ascq_antiquantize(dst.ptr, ascq::DTypeOf<DstT>::value, src.ptr, ascq::DTypeOf<SrcT>::value, nullptr, nullptr,
+                                  ascq::DTypeOf<DstT>::value, offset, scale, static_cast<ascq_policy>(config.policy), &p, stream));
+}
+template <typename DstT, typename SrcT, typename ScaleT>
+inline void AntiQuantize(const AntiQuantizeConfig& config, const GlobalTensor<DstT>& dst, const GlobalTensor<SrcT>& src,
+                         const GlobalTensor<ScaleT>& scale, const GlobalTensor<ScaleT>& offset, const AntiQuantizeParams& params,
+                         void* stream = nullptr)
+{
+    const ascq_quantize_param p = detail::pack(params, config.hasOffset, config.kDim, RoundMode::CAST_RINT);
+    ascq::check(ascq_antiquantize(dst.ptr, ascq::DTypeOf<DstT>::value, src.ptr, ascq::DTypeOf<SrcT>::value,
+                                  config.hasOffset ? offset.ptr : nullptr, scale.ptr, ascq::DTypeOf<ScaleT>::value, 0.f, 0.f,
+                                  static_cast<ascq_policy>(config.policy), &p, stream));
+}
+
 // Host tiling helpers (include/adv_api/quantization/ascend_quant_tiling.h etc.); shape = dims + rank.
 inline void GetAscendQuantMaxMinTmpSize(const int64_t* dims, int rank, uint32_t typeSize, uint32_t& maxValue, uint32_t& minValue)
 {

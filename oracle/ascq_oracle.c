@@ -304,8 +304,12 @@ static int policy_sref(sref* s, const void* p, int dt, int policy, uint32_t m, u
  * ---------------------------------------------------------------------------------------- */
 typedef struct { uint32_t m, n, calCount, groupSize; int32_t hasOffset, kDim; int32_t roundMode; } quant_param;
 
-int ascq_oracle_quant(void* dst, int dstT, const void* src, int srcT, const void* scale, const void* offset,
-                      int scaleT, float scaleScalar, float offsetScalar, int policy, const quant_param* p)
+/* unified != 0: the Quantize interface (impl/adv_api/detail/quantization/quantize/quantize_impl.h:832-975):
+ * every policy in fp32 -- src and scale/offset widened to fp32, multiply, add (if hasOffset), then the
+ * float -> int16 (roundMode, sat) -> half -> int8 chain (quantize_impl.h:146-157) or, for fp4, float -> bf16 (RINT)
+ * -> e2m1 (roundMode) (:170-185). */
+static int quant_common(void* dst, int dstT, const void* src, int srcT, const void* scale, const void* offset,
+                        int scaleT, float scaleScalar, float offsetScalar, int policy, const quant_param* p, int unified)
 {
     if (!dst || !src || !p) return OR_INVALID;
     if (srcT != DT_F16 && srcT != DT_BF16 && srcT != DT_F32) return OR_UNSUPPORTED;
@@ -318,14 +322,16 @@ int ascq_oracle_quant(void* dst, int dstT, const void* src, int srcT, const void
         ct = DT_F16;
         sref_scalar(&ss, scaleScalar); sref_scalar(&so, offsetScalar);
         n = p->calCount; rows = 1; /* flat */
+        if (unified) { has_off = p->hasOffset; mode = p->roundMode; }
     } else if (policy == PER_CHANNEL) {
         if (dstT != DT_I8) return OR_UNSUPPORTED;
         if (!scale || p->n == 0 || p->calCount % p->n != 0) return OR_INVALID;
-        if (scaleT != DT_F16 && scaleT != DT_F32) return OR_UNSUPPORTED;
+        if (!unified && scaleT != DT_F16 && scaleT != DT_F32) return OR_UNSUPPORTED;
         ct = DT_F16;
         n = p->n; rows = p->calCount / n;
         sref_tensor(&ss, scale, scaleT, 0, 1, 0);
         if (offset) sref_tensor(&so, offset, scaleT, 0, 1, 0); else sref_scalar(&so, offsetScalar);
+        if (unified) { has_off = p->hasOffset; mode = p->roundMode; }
     } else {
         if (!scale || p->n == 0 || p->calCount % p->n != 0) return OR_INVALID;
         if (scaleT != DT_F16 && scaleT != DT_BF16 && scaleT != DT_F32) return OR_UNSUPPORTED;
@@ -338,6 +344,11 @@ int ascq_oracle_quant(void* dst, int dstT, const void* src, int srcT, const void
         if (rc) return rc;
         if (has_off) { if (!offset) return OR_INVALID; policy_sref(&so, offset, scaleT, policy, rows, n, p->groupSize, p->kDim); }
         if (dstT == DT_FP4X2_E2M1 && (policy != PER_GROUP || has_off || (n & 1))) return OR_UNSUPPORTED;
+    }
+    if (unified) {
+        if (scaleT != DT_F16 && scaleT != DT_BF16 && scaleT != DT_F32) return OR_UNSUPPORTED;
+        if (scaleT != DT_F32 && scaleT != srcT) return OR_UNSUPPORTED;
+        ct = DT_F32; legacy = 0;
     }
 #pragma omp parallel for schedule(static)
     for (uint32_t r = 0; r < rows; ++r) {
@@ -365,6 +376,22 @@ int ascq_oracle_quant(void* dst, int dstT, const void* src, int srcT, const void
         }
     }
     return OR_OK;
+}
+
+int ascq_oracle_quant(void* dst, int dstT, const void* src, int srcT, const void* scale, const void* offset,
+                      int scaleT, float scaleScalar, float offsetScalar, int policy, const quant_param* p)
+{
+    return quant_common(dst, dstT, src, srcT, scale, offset, scaleT, scaleScalar, offsetScalar, policy, p, 0);
+}
+
+typedef struct { uint32_t m, n, groupSize; int32_t hasOffset, kDim; int32_t roundMode; } quantize_param;
+
+int ascq_oracle_quantize(void* dst, int dstT, const void* src, int srcT, const void* scale, const void* offset,
+                         int scaleT, float scaleScalar, float offsetScalar, int policy, const quantize_param* q)
+{
+    if (!q) return OR_INVALID;
+    quant_param p = {q->m, q->n, q->m * q->n, q->groupSize, q->hasOffset, q->kDim, q->roundMode};
+    return quant_common(dst, dstT, src, srcT, scale, offset, scaleT, scaleScalar, offsetScalar, policy, &p, 1);
 }
 
 /* Build-defined dynamic per-token quantisation (no reference counterpart): fp32 absmax per row,
@@ -471,8 +498,12 @@ int ascq_oracle_dequant(void* dst, int dstT, const void* src, int srcT, const vo
  * ---------------------------------------------------------------------------------------- */
 typedef struct { uint32_t m, n, calCount, groupSize; int32_t hasOffset, isTranspose, kDim; } antiquant_param;
 
-int ascq_oracle_antiquant(void* dst, int dstT, const void* src, int srcT, const void* offset, const void* scale,
-                          int scaleT, float offsetScalar, float scaleScalar, int policy, const antiquant_param* p)
+/* unified != 0: the AntiQuantize interface (antiquantize/antiquantize_3510_impl.h:252-381, antiquantize_impl.h:
+ * 68-190): int8 -> half -> fp32 (exact), fp32 add of float(offset) when hasOffset, fp32 multiply by float(scale),
+ * one cast to dstT (RINT, sat), for every policy; PER_CHANNEL takes scale[n] / offset[n], never transposed. */
+static int antiquant_common(void* dst, int dstT, const void* src, int srcT, const void* offset, const void* scale,
+                            int scaleT, float offsetScalar, float scaleScalar, int policy, const antiquant_param* p,
+                            int unified)
 {
     if (!dst || !src || !p || p->n == 0) return OR_INVALID;
     uint32_t n = p->n;
@@ -509,7 +540,8 @@ int ascq_oracle_antiquant(void* dst, int dstT, const void* src, int srcT, const 
     if (policy == PER_TENSOR || policy == PER_CHANNEL) {
         if (dstT != DT_F16 && dstT != DT_BF16) return OR_UNSUPPORTED;
         ct = (dstT == DT_F16) ? DT_F16 : DT_F32;
-        has_off = (policy == PER_TENSOR) ? p->hasOffset : (offset != NULL);
+        has_off = (policy == PER_TENSOR || unified) ? p->hasOffset : (offset != NULL);
+        if (unified && policy == PER_CHANNEL && has_off && !offset) return OR_INVALID;
         if (policy == PER_TENSOR) {
             /* the scalars arrive as dstT values (ascend_antiquant.h:136-205) */
             float sc = (dstT == DT_F16) ? orc_f16_to_f32(orc_f32_to_f16_sat(scaleScalar)) : orc_bf16_to_f32(orc_f32_to_bf16_sat(scaleScalar));
@@ -544,6 +576,7 @@ int ascq_oracle_antiquant(void* dst, int dstT, const void* src, int srcT, const 
             policy_sref(&so, offset, scaleT, PER_GROUP, rows, n, p->groupSize, along_cols ? 1 : 0);
         } else return OR_UNSUPPORTED;
     }
+    if (unified) ct = DT_F32;
 #pragma omp parallel for schedule(static)
     for (uint32_t r = 0; r < rows; ++r) {
         for (uint32_t c = 0; c < n; ++c) {
@@ -556,6 +589,20 @@ int ascq_oracle_antiquant(void* dst, int dstT, const void* src, int srcT, const 
         }
     }
     return OR_OK;
+}
+
+int ascq_oracle_antiquant(void* dst, int dstT, const void* src, int srcT, const void* offset, const void* scale,
+                          int scaleT, float offsetScalar, float scaleScalar, int policy, const antiquant_param* p)
+{
+    return antiquant_common(dst, dstT, src, srcT, offset, scale, scaleT, offsetScalar, scaleScalar, policy, p, 0);
+}
+
+int ascq_oracle_antiquantize(void* dst, int dstT, const void* src, int srcT, const void* offset, const void* scale,
+                             int scaleT, float offsetScalar, float scaleScalar, int policy, const quantize_param* q)
+{
+    if (!q) return OR_INVALID;
+    antiquant_param p = {q->m, q->n, 0, policy == PER_GROUP ? q->groupSize : 0, q->hasOffset, 0, q->kDim};
+    return antiquant_common(dst, dstT, src, srcT, offset, scale, scaleT, offsetScalar, scaleScalar, policy, &p, 1);
 }
 
 /* ------------------------------------------------------------------------------------------

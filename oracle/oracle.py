@@ -169,6 +169,38 @@ def ascend_antiquant(src, srcT, dstT, *, policy, m, n, calCount=0, scale=None, o
     return dst
 
 
+class _QuantizeParam(C.Structure):
+    _fields_ = [("m", C.c_uint32), ("n", C.c_uint32), ("groupSize", C.c_uint32), ("hasOffset", C.c_int32),
+                ("kDim", C.c_int32), ("roundMode", C.c_int32)]
+
+
+def quantize(src, srcT, *, policy, m, n, scale=None, offset=None, scaleT=F32, scaleScalar=0.0, offsetScalar=0.0,
+             groupSize=0, hasOffset=False, kDim=1, roundMode=CAST_RINT, dstT=I8):
+    """The unified Quantize interface (fp32 arithmetic for every policy); returns int8 [m, n] (or packed fp4x2)."""
+    dst = np.zeros((m, n), np.int8) if dstT == I8 else np.zeros(m * n // 2, np.uint8)
+    p = _QuantizeParam(m, n, groupSize, int(hasOffset), kDim, roundMode)
+    _check(lib().ascq_oracle_quantize(_p(dst), dstT, _p(src), srcT, _p(scale), _p(offset), scaleT, C.c_float(scaleScalar),
+                                      C.c_float(offsetScalar), policy, C.byref(p)))
+    return dst
+
+
+def dequantize(src, srcT, dstT, *, policy, m, n, scale=None, scaleT=F32, scaleScalar=0.0, groupSize=0, kDim=1, fill=0):
+    """The unified Dequantize interface: AscendDequant on whole rows (dequantize_impl.h:100-215)."""
+    cal = n if policy in (PER_TENSOR, PER_CHANNEL) else m * n
+    return ascend_dequant(src, srcT, dstT, policy=policy, m=m, n=n, calCount=cal, scale=scale, scaleT=scaleT,
+                          scaleScalar=scaleScalar, groupSize=groupSize, kDim=kDim, fill=fill)
+
+
+def antiquantize(src, srcT, dstT, *, policy, m, n, scale=None, offset=None, scaleT=BF16, scaleScalar=0.0,
+                 offsetScalar=0.0, groupSize=0, hasOffset=False, kDim=1):
+    """The unified AntiQuantize interface (fp32 arithmetic for every policy); returns [m, n] of dstT."""
+    dst = np.zeros((m, n), NP_DTYPE[dstT])
+    p = _QuantizeParam(m, n, groupSize, int(hasOffset), kDim, CAST_RINT)
+    _check(lib().ascq_oracle_antiquantize(_p(dst), dstT, _p(src), srcT, _p(offset), _p(scale), scaleT,
+                                          C.c_float(offsetScalar), C.c_float(scaleScalar), policy, C.byref(p)))
+    return dst
+
+
 def matmul_w8a8(A, B_nk, sA=None, sB=None, bias_bf16=None, want_acc=False, ldc=None):
     M, K = A.shape
     N = B_nk.shape[0]

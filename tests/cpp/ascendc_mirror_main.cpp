@@ -1,7 +1,7 @@
 // Drives the C++ host mirror (ascq_ascendc.hpp) end to end: reads operands from files, runs one operator on the
 // GPU, writes the result to a file.  The Python test compares that file with the CPU oracle.
 //   usage: ascendc_mirror_main <op> <dir>
-//   op = quant_tensor | quant_channel | dequant_channel | antiquant_channel
+//   op = quant_tensor | quant_channel | dequant_channel | antiquant_channel | quantize_token
 #include <cuda_runtime_api.h>
 
 #include <cstdio>
@@ -90,6 +90,14 @@ int main(int argc, char** argv)
             auto offset = upload<bfloat16_t>(read_file(dir + "offset.bin"));
             auto dst = device_alloc<bfloat16_t>(src.size, 0);
             AscendAntiQuant<int8_t, bfloat16_t, false>(dst, src, offset, scale, dims[0]);
+            download(dir + "dst.bin", dst);
+        } else if (op == "quantize_token") {  // dims: m, n; unified interface, PER_TOKEN with offset, float scales
+            auto src = upload<half>(read_file(dir + "src.bin"));
+            auto scale = upload<float>(read_file(dir + "scale.bin"));
+            auto offset = upload<float>(read_file(dir + "offset.bin"));
+            auto dst = device_alloc<int8_t>(src.size, 0x55);
+            QuantizeConfig cfg{QuantizePolicy::PER_TOKEN, true, RoundMode::CAST_RINT, 1};
+            Quantize(cfg, dst, src, scale, offset, QuantizeParams{dims[0], dims[1], 0});
             download(dir + "dst.bin", dst);
         } else if (op == "bad_args") {  // the reference asserts scaleCount == offsetCount
             GlobalTensor<int8_t> d;

@@ -99,3 +99,18 @@ def test_mirror_antiquant_channel(mirror_exe, tmp_path):
     want = O.ascend_antiquant(src, O.I8, O.BF16, policy=O.PER_CHANNEL, m=K, n=N, scale=scale, offset=offset, scaleT=O.BF16)
     got = np.fromfile(tmp_path / "dst.bin", np.uint16).reshape(K, N)
     assert np.array_equal(got, want.view(np.uint16))
+
+
+@pytest.mark.gpu
+def test_mirror_unified_quantize_per_token(mirror_exe, tmp_path):
+    rng = np.random.default_rng(9)
+    m, n = 40, 320
+    src = rng.uniform(-9, 9, (m, n)).astype(np.float16)
+    scale = rng.uniform(0.5, 14, m).astype(np.float32)
+    offset = rng.uniform(-3, 3, m).astype(np.float32)
+    for a, f in ((src, "src"), (scale, "scale"), (offset, "offset")):
+        a.tofile(tmp_path / f"{f}.bin")
+    np.array([m, n], np.uint32).tofile(tmp_path / "dims.bin")
+    run(mirror_exe, "quantize_token", tmp_path)
+    want = O.quantize(src, O.F16, policy=O.PER_TOKEN, m=m, n=n, scale=scale, offset=offset, scaleT=O.F32, hasOffset=True)
+    assert np.array_equal(np.fromfile(tmp_path / "dst.bin", np.int8).reshape(m, n), want)

@@ -137,6 +137,44 @@ def test_antiquant_sample_golden_dav3510(golden_dir):
     assert np.array_equal(out.view(np.uint16), g["golden"].view(np.uint16))
 
 
+# ---- the unified interface, which the 950-series samples call ---------------------------------------
+def test_quantize_sample_golden_dav3510(golden_dir):
+    # quant.asc:113-130: Quantize<{PER_TENSOR, hasOffset, CAST_RINT, 1}>(dst, src float, 2.0f, 0.9f, {1, 1024, 0})
+    g = _load(golden_dir, "quant_dav3510")
+    out = O.quantize(g["input"], O.F32, policy=O.PER_TENSOR, m=1, n=1024, scaleScalar=2.0, offsetScalar=0.9, hasOffset=True)
+    assert np.array_equal(out.reshape(-1), g["golden"])
+
+
+def test_antiquantize_sample_golden_dav3510(golden_dir):
+    # antiquant.asc:159-175: AntiQuantize<{PER_CHANNEL, hasOffset}>(dst half, src int8, scale half[128], offset, {8, 128, 0})
+    g = _load(golden_dir, "antiquant_dav3510")
+    out = O.antiquantize(g["input_src"], O.I8, O.F16, policy=O.PER_CHANNEL, m=8, n=128, scale=g["input_scale"].reshape(-1),
+                         offset=g["input_offset"].reshape(-1), scaleT=O.F16, hasOffset=True)
+    assert np.array_equal(out.view(np.uint16), g["golden"].view(np.uint16))
+    # the fp32 intermediates matter: the half-arithmetic legacy operator gives other bits on the same inputs
+    legacy = O.ascend_antiquant(g["input_src"], O.I8, O.F16, policy=O.PER_CHANNEL, m=8, n=128,
+                                scale=g["input_scale"].reshape(-1), offset=g["input_offset"].reshape(-1), scaleT=O.F16)
+    assert not np.array_equal(legacy.view(np.uint16), g["golden"].view(np.uint16))
+
+
+def test_dequantize_sample_golden(golden_dir):
+    # dequant.asc:142-152: Dequantize<{PER_CHANNEL, false, 1}>(dst float, src int32, scale float[32], offset, {128, 32, 0})
+    g = _load(golden_dir, "dequant")
+    out = O.dequantize(g["input"], O.I32, O.F32, policy=O.PER_CHANNEL, m=128, n=32, scale=g["scale"], scaleT=O.F32)
+    assert np.array_equal(out.view(np.uint32), g["golden"].view(np.uint32))
+
+
+def test_quantize_equals_policy_operator_where_both_compute_in_fp32():
+    rng = np.random.default_rng(9)
+    src = rng.normal(0, 3, (16, 64)).astype(np.float16)
+    sc = rng.uniform(1, 20, 16).astype(np.float32)
+    of = rng.uniform(-3, 3, 16).astype(np.float32)
+    for mode in (O.CAST_RINT, O.CAST_FLOOR, O.CAST_CEIL, O.CAST_ROUND, O.CAST_TRUNC):
+        a = O.quantize(src, O.F16, policy=O.PER_TOKEN, m=16, n=64, scale=sc, offset=of, scaleT=O.F32, hasOffset=True, roundMode=mode)
+        b = O.ascend_quant(src, O.F16, policy=O.PER_TOKEN, m=16, n=64, scale=sc, offset=of, scaleT=O.F32, hasOffset=True, roundMode=mode)
+        assert np.array_equal(a, b)
+
+
 # ---- tests/api/adv_api/tiling/test_tiling.cpp:6540-6712 known answers -----------------------------
 TILING_ANTIQUANT = [
     # srcDims, scaleDims, transpose, outT, (max, min), (live, extra)
