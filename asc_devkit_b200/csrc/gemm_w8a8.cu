@@ -63,9 +63,15 @@ struct Params {
     int32_t* accDump;
     int M, N, K, ldc;
     int tilesM, tilesN;
+    // fixpipe-style epilogue (EPI == kEpiFixpipe): C is fp16 = half(acc + biasI32[n]) scaled by quantVec[n] or quantScalar
+    const int32_t* biasI32;
+    const uint64_t* quantVec;   // low word: fp32 bits, of which the hardware keeps sign, exponent and 10 mantissa bits
+    float quantScalar;
 };
+constexpr int kEpiDequant = 0;  // bf16(((float(acc) * sB[n]) * sA[m]) + bias[n])
+constexpr int kEpiFixpipe = 1;  // SetQuantScalar / SetQuantVector of the reference's Matmul (DEQF16)
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
 {
@@ -212,8 +218,16 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 const int t = threadIdx.x - 64;  // index over the epilogue threads
                 for (int j = t; j < BN; j += 32 * kEpiWarps) {
                     const int n = n0 + j;
-                    sBs[j] = (p.sB != nullptr && n < p.N) ? __ldg(p.sB + n) : 1.0f;
-                    biasS[j] = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+                    if constexpr (EPI == kEpiFixpipe) {
+                        const uint32_t bits = (p.quantVec != nullptr && n < p.N)
+                                                  ? static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned long long*>(p.quantVec) + n)) & 0xFFFFE000u
+                                                  : 0x3F800000u;
+                        sBs[j] = __uint_as_float(bits);
+                        biasS[j] = __int_as_float((p.biasI32 != nullptr && n < p.N) ? __ldg(p.biasI32 + n) : 0);
+                    } else {
+                        sBs[j] = (p.sB != nullptr && n < p.N) ? __ldg(p.sB + n) : 1.0f;
+                        biasS[j] = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+                    }
                 }
                 // barrier of the epilogue warps only; it also makes the give-up decision uniform, so that no warp is
                 // left waiting at it for one that stopped
@@ -241,6 +255,30 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             auto convert32 = [&](const uint32_t(&r)[32], int colInTile, uint32_t* packed) {
                 const float4* sb4 = reinterpret_cast<const float4*>(sBs + colInTile);
                 const float4* bi4 = reinterpret_cast<const float4*>(biasS + colInTile);
+                if constexpr (EPI == kEpiFixpipe) {
+                    // matmul_quant/scripts/gen_data.py:26-44: (acc + bias) -> half; scalar mode: half * half(scale);
+                    // vector mode: float(half) * scale (19 significant bits kept) -> half
+                    const bool vec = p.quantVec != nullptr;
+                    const __half hs = __float2half_rn(p.quantScalar);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        const float4 s4 = sb4[v];
+                        const float4 b4 = bi4[v];
+                        const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+                        const float bi[4] = {b4.x, b4.y, b4.z, b4.w};
+                        unsigned short o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int32_t a = static_cast<int32_t>(r[4 * v + e]) + __float_as_int(bi[e]);
+                            const __half h = __int2half_rn(a);
+                            const __half res = vec ? __float2half_rn(__fmul_rn(__half2float(h), sc[e])) : __hmul_rn(h, hs);
+                            o[e] = __half_as_ushort(res);
+                        }
+                        packed[2 * v] = static_cast<uint32_t>(o[0]) | (static_cast<uint32_t>(o[1]) << 16);
+                        packed[2 * v + 1] = static_cast<uint32_t>(o[2]) | (static_cast<uint32_t>(o[3]) << 16);
+                    }
+                    return;
+                }
 #pragma unroll
                 for (int v = 0; v < 8; ++v) {
                     const float4 s4 = sb4[v];
@@ -352,12 +390,13 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 }
 
 // ---- host side -------------------------------------------------------------------------------------
-template <int BN, bool PAIR> ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
+template <int BN, bool PAIR, int EPI = kEpiDequant>
+ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
 {
     using C = Cfg<BN, PAIR>;
     static bool attrSet = false;
     if (!attrSet) {
-        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN, PAIR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(C::kSmemBytes)));
         attrSet = true;
     }
@@ -378,10 +417,10 @@ template <int BN, bool PAIR> ascq_status launch(const CUtensorMap& ta, const CUt
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR>, ta, tb, p));
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI>, ta, tb, p));
     } else {
         const int grid = tiles < sm_count() ? tiles : sm_count();
-        w8a8_kernel<BN, PAIR><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+        w8a8_kernel<BN, PAIR, EPI><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
     }
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
@@ -394,10 +433,17 @@ template <int BN, bool PAIR> ascq_status launch(const CUtensorMap& ta, const CUt
 
 namespace ascq {
 namespace {
+struct FixpipeArgs {
+    const int32_t* biasI32;
+    const uint64_t* quantVec;
+    float quantScalar;
+};
+
 ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
                      const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc, int32_t* accDump,
-                     cudaStream_t st)
+                     cudaStream_t st, const FixpipeArgs* fix = nullptr)
 {
+    const int epi = fix ? kEpiFixpipe : kEpiDequant;
     if (!A || !B_nk) return fail(ASCQ_ERR_INVALID_ARG, "A and B must not be NULL");
     if (nBufs < 0 || nBufs > kMaxPeers) return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
     const bool haveC = nBufs > 0 && outBufs != nullptr && outBufs[0] != nullptr;
@@ -422,6 +468,11 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     p.bias = static_cast<const __nv_bfloat16*>(bias_bf16);
     p.accDump = accDump;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+    if (fix) {
+        p.biasI32 = fix->biasI32;
+        p.quantVec = fix->quantVec;
+        p.quantScalar = fix->quantScalar;
+    }
 
     // Tile shape: the one with the smallest estimated time = waves x time of one wave.  One wave of CTA pairs on
     // 256 x 256 tiles is the unit; single CTAs on 128 x 256 tiles do the same work per SM about a tenth slower
@@ -450,6 +501,10 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     if (rc != ASCQ_OK) return rc;
     rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
+    if (epi == kEpiFixpipe) {
+        if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, p, st);
+        return mode == 1 ? launch<256, false, kEpiFixpipe>(ta, tb, p, st) : launch<128, false, kEpiFixpipe>(ta, tb, p, st);
+    }
     if (mode == 2) return launch<256, true>(ta, tb, p, st);
     return mode == 1 ? launch<256, false>(ta, tb, p, st) : launch<128, false>(ta, tb, p, st);
 }
@@ -487,4 +542,47 @@ extern "C" ascq_status ascq_matmul_status(void* stream)
         return fail(ASCQ_ERR_TIMEOUT, "a bounded wait inside the W8A8 matmul kernel expired (status %d)", v);
     }
     return mxfp4_read_status(st);
+}
+
+// ---- int8 matmul with the reference's fixpipe quantisation of the result (fp16 output) ----------------------------
+extern "C" ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const int8_t* B_nk, const int32_t* bias_i32,
+                                            const uint64_t* quantVector, float quantScalar, int M, int N, int K, int ldc,
+                                            void* stream)
+{
+    if (!C_f16) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
+    if (quantVector && (reinterpret_cast<uintptr_t>(quantVector) & 7u))
+        return fail(ASCQ_ERR_ALIGNMENT, "quantVector must be 8-byte aligned");
+    void* bufs[1] = {C_f16};
+    const FixpipeArgs fix{bias_i32, quantVector, quantScalar};
+    return run_w8a8(bufs, 1, 0, 0, A, B_nk, nullptr, nullptr, nullptr, M, N, K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fix);
+}
+
+// [K, N] row-major int8 (the reference's ND weight, CubeFormat::ND, not transposed) -> [N, K]: one-off weight preparation.
+namespace ascq {
+namespace {
+__global__ void __launch_bounds__(256) transpose_i8_kernel(int8_t* __restrict__ dst, const int8_t* __restrict__ src, int K, int N)
+{
+    __shared__ int8_t tile[64][65];
+    const int k0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
+        const int k = k0 + i / 64, n = n0 + i % 64;
+        tile[i / 64][i % 64] = (k < K && n < N) ? src[static_cast<size_t>(k) * N + n] : 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
+        const int n = n0 + i / 64, k = k0 + i % 64;
+        if (n < N && k < K) dst[static_cast<size_t>(n) * K + k] = tile[i % 64][i / 64];
+    }
+}
+}  // namespace
+}  // namespace ascq
+
+extern "C" ascq_status ascq_transpose_i8_kn_to_nk(int8_t* B_nk, const int8_t* B_kn, int K, int N, void* stream)
+{
+    if (!B_nk || !B_kn) return fail(ASCQ_ERR_INVALID_ARG, "B_nk and B_kn must not be NULL");
+    if (K <= 0 || N <= 0) return fail(ASCQ_ERR_INVALID_ARG, "K and N must be positive");
+    const dim3 grid((N + 63) / 64, (K + 63) / 64);
+    transpose_i8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(B_nk, B_kn, K, N);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
 }

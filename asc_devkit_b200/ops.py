@@ -233,6 +233,24 @@ def MatmulW8A8(C: Optional[torch.Tensor], A: torch.Tensor, B_nk: torch.Tensor, s
     return C
 
 
+def MatmulI8Quant(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  quantVector: Optional[torch.Tensor] = None, quantScalar: float = 1.0, stream=None):
+    """int8 matmul whose result leaves through the fixpipe quantisation of the reference (SetQuantScalar /
+    SetQuantVector, fp16 output): ``ascq_matmul_i8_quant``.  ``quantVector`` is an int64 tensor holding the uint64
+    words (fp32 bits in the low half), ``bias`` int32 [N]."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    L.check(L.lib().ascq_matmul_i8_quant(_ptr(C), _ptr(A), _ptr(B_nk), _ptr(bias), _ptr(quantVector), float(quantScalar),
+                                         M, N, K, C.stride(0), _stream(stream)))
+    return C
+
+
+def TransposeI8KnToNk(B_nk: torch.Tensor, B_kn: torch.Tensor, stream=None):
+    K, N = B_kn.shape
+    L.check(L.lib().ascq_transpose_i8_kn_to_nk(_ptr(B_nk), _ptr(B_kn), K, N, _stream(stream)))
+    return B_nk
+
+
 def GroupMatmulMxfp4Workspace(sumM: int, G: int, K: int, N: int) -> int:
     return int(L.lib().ascq_group_matmul_mxfp4_workspace_size(sumM, G, K, N))
 

@@ -304,6 +304,22 @@ ascq_status ascq_matmul_w8a8_scatter(void* const* C_bufs, int nBufs, int firstBu
                                      const void* bias_bf16, int M, int N, int K, void* stream);
 
 /*
+ * int8 x int8 matmul with the result quantised on the way out the way the reference's fixpipe does it
+ * (Matmul::SetQuantScalar / SetQuantVector, include/adv_api/matmul/matmul.h:150-160,
+ * impl/adv_api/detail/matmul/stage/copy_cube_out/quant/quant_processor_fixpipe.h:80-119, mode DEQF16), with the
+ * arithmetic of the sample's golden (examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_quant/scripts/
+ * gen_data.py:26-44):  h = half(acc + bias_i32[n]);  C = h * half(quantScalar)            (quantVector NULL)
+ *                                                    C = half(float(h) * s19(quantVector[n]))  (per channel),
+ * where s19 keeps sign, exponent and the top 10 mantissa bits of the fp32 held in the low word of the uint64.
+ * A [M,K], B_nk [N,K] int8 K-major, bias_i32 [N] or NULL, C fp16 [M, ldc].  A weight stored [K,N] (the sample's
+ * CubeFormat::ND B) is turned once with ascq_transpose_i8_kn_to_nk.
+ */
+ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const int8_t* B_nk, const int32_t* bias_i32,
+                                 const uint64_t* quantVector, float quantScalar, int M, int N, int K, int ldc,
+                                 void* stream);
+ascq_status ascq_transpose_i8_kn_to_nk(int8_t* B_nk, const int8_t* B_kn, int K, int N, void* stream);
+
+/*
  * The grouped MX-FP4 matmul with the reassembly of a group-parallel layout fused into its epilogue.  With the
  * groups dealt out over the GPUs of one box (one process per GPU), every rank computes the output rows of its own
  * groups and writes them into EVERY buffer of C_bufs: group g's rows go to rows outRowStart_host[g] .. of each bf16

@@ -639,6 +639,46 @@ int ascq_oracle_matmul_w8a8(uint16_t* C, const int8_t* A, const int8_t* B, const
 }
 
 /* ------------------------------------------------------------------------------------------
+ * int8 matmul leaving through the fixpipe quantisation (Matmul::SetQuantScalar / SetQuantVector, mode DEQF16:
+ * impl/adv_api/detail/matmul/stage/copy_cube_out/quant/quant_processor_fixpipe.h:80-119), with the arithmetic of
+ * the sample's golden, examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_quant/scripts/gen_data.py:26-44:
+ *   y = A.B + bias (int32);  h = half(y) (RINT, overflow -> inf);
+ *   scalar mode: C = h * half(quantScalar) in half;
+ *   vector mode: C = half(float(h) * s), s = fp32 from the low word of quantVec[n] with the low 13 mantissa bits
+ *                cleared ("1 sign bit, 8 exponent bits and 10 mantissa bits").
+ * A [M,K], B [N,K] int8 row-major (the sample stores B [K,N]; the caller transposes).
+ * ---------------------------------------------------------------------------------------- */
+static uint16_t i32_to_f16_rint(int32_t v) { return f64_to_f16_ieee((double)v); } /* one rounding, IEEE overflow */
+
+int ascq_oracle_matmul_i8_quant(uint16_t* C, const int8_t* A, const int8_t* B, const int32_t* bias,
+                                const uint64_t* quantVec, float quantScalar, int M, int N, int K, int ldc)
+{
+    if (!C || !A || !B || M < 0 || N < 0 || K < 0) return OR_INVALID;
+    const uint16_t hs = orc_f32_to_f16_sat(quantScalar);
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        for (int n = 0; n < N; ++n) {
+            int32_t acc = 0;
+            const int8_t* a = A + (size_t)m * K;
+            const int8_t* b = B + (size_t)n * K;
+            for (int k = 0; k < K; ++k) acc += (int32_t)a[k] * (int32_t)b[k];
+            if (bias) acc = (int32_t)((uint32_t)acc + (uint32_t)bias[n]);
+            uint16_t h = i32_to_f16_rint(acc);
+            uint16_t out;
+            if (quantVec) {
+                uint32_t bits = (uint32_t)(quantVec[n] & 0xFFFFFFFFull) & 0xFFFFE000u;
+                float s; memcpy(&s, &bits, 4);
+                out = f64_to_f16_ieee((double)(orc_f16_to_f32(h) * s)); /* fp32 product, then half (IEEE overflow) */
+            } else {
+                out = orc_f16_mul(h, hs);
+            }
+            C[(size_t)m * ldc + n] = out;
+        }
+    }
+    return OR_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
  * MX-FP4 grouped matmul.  Golden semantics of
  * examples/.../matmul_mxfp4_high_performance/scripts/gen_data.py:38-72 and
  * examples/.../03_matrix_compute/mmad_mx/scripts/gen_data.py: operands are dequantised

@@ -212,6 +212,16 @@ def matmul_w8a8(A, B_nk, sA=None, sB=None, bias_bf16=None, want_acc=False, ldc=N
     return (Cb, acc) if want_acc else Cb
 
 
+def matmul_i8_quant(A, B_nk, bias=None, quantVector=None, quantScalar=1.0):
+    """int8 matmul + int32 bias, result quantised as the fixpipe does (fp16); returns [M, N] float16."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    Cq = np.zeros((M, N), np.float16)
+    _check(lib().ascq_oracle_matmul_i8_quant(_p(Cq), _p(A), _p(B_nk), _p(bias), _p(quantVector), C.c_float(quantScalar),
+                                             M, N, K, N))
+    return Cq
+
+
 def group_matmul_mxfp4(A, sA, B, sB, groupList, K, N, want_f32=False):
     """A [sumM, K/2] u8, sA [sumM, K/32] u8, B [G, N, K/2] u8, sB [G, N, K/32] u8, groupList int64 [G]."""
     G = int(len(groupList))

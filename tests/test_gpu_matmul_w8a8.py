@@ -115,3 +115,38 @@ def test_scatter_writes_the_block_into_every_buffer():
         assert (got[:, :col] == 0xBF80).all() and (got[:, col + N:] == 0xBF80).all(), "columns outside the block changed"
     with pytest.raises(ops.AscqError):
         ops.MatmulW8A8Scatter([bufs[0].data_ptr()] * 9, 0, 0, ldc, t(A), t(B))
+
+
+# ---- fixpipe quantisation of the result (SetQuantScalar / SetQuantVector, fp16 output) ----------------------------
+@pytest.mark.parametrize("name", ["matmul_quant_scalar", "matmul_quant_vector"])
+def test_matmul_quant_sample_golden_through_the_gpu(name):
+    """The reference sample's own vectors (its gen_data.py, first 96 rows of A): transpose B once, one call, same bits."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name + ".npz"))
+    A = torch.from_numpy(g["x1_gm"]).to(DEV)
+    B_kn = torch.from_numpy(g["x2_gm"]).to(DEV)
+    B_nk = torch.empty((1024, 1024), dtype=torch.int8, device=DEV)
+    ops.TransposeI8KnToNk(B_nk, B_kn)
+    assert torch.equal(B_nk, B_kn.t().contiguous())
+    qv = torch.from_numpy(g["quant_vector_gm"].view(np.int64)).to(DEV) if "quant_vector_gm" in g else None
+    C = torch.zeros((A.shape[0], 1024), dtype=torch.float16, device=DEV)
+    ops.MatmulI8Quant(C, A, B_nk, torch.from_numpy(g["bias_gm"]).to(DEV), qv, 0.1)
+    ops.MatmulStatus()
+    assert_bits_equal(C.cpu().numpy().view(np.uint16), g["golden"].view(np.uint16), name)
+
+
+@pytest.mark.parametrize("M,N,K,vector", [(128, 128, 128, True), (300, 520, 272, True), (257, 384, 1024, False), (4096, 512, 512, True)])
+@pytest.mark.parametrize("tile", ["pair", "wide", "narrow"])
+def test_matmul_quant_matches_oracle(M, N, K, vector, tile, monkeypatch):
+    monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
+    rng = np.random.default_rng(M + N + K)
+    A = rng.integers(-20, 21, (M, K), dtype=np.int8)
+    B = rng.integers(-20, 21, (N, K), dtype=np.int8)
+    bias = rng.integers(-50, 50, N, dtype=np.int32)
+    qv = rng.uniform(0.01, 2.0, N).astype(np.float32).view(np.uint32).astype(np.uint64) if vector else None
+    want = O.matmul_i8_quant(A, B, bias, qv, 0.37)
+    C = torch.zeros((M, N), dtype=torch.float16, device=DEV)
+    ops.MatmulI8Quant(C, torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV), torch.from_numpy(bias).to(DEV),
+                      torch.from_numpy(qv.view(np.int64)).to(DEV) if vector else None, 0.37)
+    ops.MatmulStatus()
+    assert_bits_equal(C.cpu().numpy().view(np.uint16), want.view(np.uint16), f"{M}x{N}x{K}")

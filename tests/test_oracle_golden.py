@@ -175,6 +175,17 @@ def test_quantize_equals_policy_operator_where_both_compute_in_fp32():
         assert np.array_equal(a, b)
 
 
+# ---- int8 matmul with the fixpipe quantisation of the result (matmul_quant sample) ---------------------
+@pytest.mark.parametrize("name", ["matmul_quant_scalar", "matmul_quant_vector"])
+def test_matmul_quant_sample_golden(golden_dir, name):
+    # matmul_quant.asc:113-117 SetQuantVector / SetQuantScalar(0.1); golden by the sample's gen_data.py (-m 0 / -m 1);
+    # the fixture keeps the first 96 rows of A and of the golden
+    g = _load(golden_dir, name)
+    qv = g["quant_vector_gm"] if "quant_vector_gm" in g else None
+    out = O.matmul_i8_quant(g["x1_gm"], np.ascontiguousarray(g["x2_gm"].T), g["bias_gm"], qv, 0.1)
+    assert np.array_equal(out.view(np.uint16), g["golden"].view(np.uint16))
+
+
 # ---- tests/api/adv_api/tiling/test_tiling.cpp:6540-6712 known answers -----------------------------
 TILING_ANTIQUANT = [
     # srcDims, scaleDims, transpose, outT, (max, min), (live, extra)
