@@ -57,17 +57,19 @@ struct TileInfo {
 // PAIR: two CTAs of a cluster drive one tcgen05.mma.cta_group::2 on a 256 x BN tile.  Each CTA loads its 128 rows
 // of A (with their scales), its half of B's rows, and the scales of ALL BN rows of B (every CTA multiplies its
 // rows with every column), so B's data crosses the L2-to-SM fabric once per pair.
-template <int BN, bool PAIR> struct Cfg {
+// SFC: 512-byte scale chunks (128 elements of K each) per k-block row of 128 bytes: 2 for 4-bit, 1 for 8-bit operands.
+template <int BN, bool PAIR, int SFC> struct Cfg {
     static constexpr int kAccStages = (BN == 256) ? 1 : 2;
     static constexpr int kBRows = PAIR ? BN / 2 : BN;
     static constexpr int kABytes = kBM * kBKBytes;
     static constexpr int kBBytes = kBRows * kBKBytes;
-    static constexpr int kSfaBytes = 2 * kChunkBytes;
-    static constexpr int kSfbBytes = (BN / 128) * 2 * kChunkBytes;
-    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kSfaBytes = SFC * kChunkBytes;
+    static constexpr int kSfbBytes = (BN / 128) * SFC * kChunkBytes;
+    static constexpr int kLoadBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;  // what the copies of one stage bring
+    static constexpr int kStageBytes = (kLoadBytes + 1023) / 1024 * 1024;         // swizzled tiles start 1024-byte aligned
     static constexpr int kStages = PAIR ? 5 : ((BN == 256) ? 4 : 6);
-    static constexpr int kSfaCols = 8;               // 2 chunks x 4 columns
-    static constexpr int kSfbCols = 2 * (BN / 32);   // 2 chunks x N/32 columns
+    static constexpr int kSfaCols = 4 * SFC;         // 4 columns per chunk
+    static constexpr int kSfbCols = SFC * (BN / 32); // N/32 columns per chunk
     static constexpr int kAccCols = kAccStages * BN;
     static constexpr int kTmemCols = 512;
     static constexpr int kWarpStageBytes = 32 * kNarrowPitch > 16 * kStagePitch ? 32 * kNarrowPitch : 16 * kStagePitch;
@@ -83,6 +85,8 @@ struct Params {
     __nv_bfloat16* C[kMaxPeers];  // every buffer gets this launch's rows (at the tiles' outRow)
     int nPeers, firstPeer;        // stores start at buffer firstPeer and go round
     int wideStores;               // 128-byte row segments (peer buffers) instead of 64-byte ones
+    int outF32;                   // the output matrices hold fp32 instead of bf16 (8-bit operands only)
+    uint32_t aFmt, bFmt;          // 8-bit operands: 0 = E4M3, 1 = E5M2
     const TileInfo* tiles;
     const uint8_t* sfaPacked;
     const uint8_t* sfbPacked;
@@ -209,12 +213,12 @@ __device__ __forceinline__ void tile_coords(int tile, int numTilesM, int tilesN,
     nt = band * kBandN + (within - mt * width);
 }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int SFC>
 __global__ void __launch_bounds__(kThreads, 1)
 mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
              const __grid_constant__ CUtensorMap tmapSfa, const __grid_constant__ CUtensorMap tmapSfb, const __grid_constant__ Params p)
 {
-    using C = Cfg<BN, PAIR>;
+    using C = Cfg<BN, PAIR, SFC>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
@@ -291,7 +295,7 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                     uint8_t* stSf = st + C::kABytes + C::kBBytes;
                     if constexpr (PAIR) {
                         // all loads of both CTAs are counted on the leader's barrier; the leader announces both shares
-                        if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], 2 * C::kStageBytes);
+                        if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], 2 * C::kLoadBytes);
                         const uint32_t bar = mapa_u32(smem_u32(&fullBar[s]), 0);
                         tma_load_2d_pair(st, &tmapA, bar, kb * kBKBytes, ti.rowStart);
                         tma_load_2d_pair(st + C::kABytes, &tmapB, bar, kb * kBKBytes,
@@ -299,18 +303,18 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                         tma_load_2d_pair(stSf, &tmapSfa, bar, 0, static_cast<int>(sfaRec + kb));
 #pragma unroll
                         for (int t = 0; t < BN / 128; ++t)
-                            tma_load_2d_pair(stSf + C::kSfaBytes + t * 2 * kChunkBytes, &tmapSfb, bar, 0,
+                            tma_load_2d_pair(stSf + C::kSfaBytes + t * SFC * kChunkBytes, &tmapSfb, bar, 0,
                                              static_cast<int>(sfbRec + static_cast<size_t>(t) * p.kBlocks + kb));
                     } else {
-                        mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
+                        mbar_arrive_expect_tx(&fullBar[s], C::kLoadBytes);
                         tma_load_2d(st, &tmapA, &fullBar[s], kb * kBKBytes, ti.rowStart);
                         tma_load_2d(st + C::kABytes, &tmapB, &fullBar[s], kb * kBKBytes, ti.group * p.N + n0);
                         bulk_load(stSf, p.sfaPacked + (sfaRec + kb) * C::kSfaBytes, C::kSfaBytes, &fullBar[s]);
 #pragma unroll
                         for (int t = 0; t < BN / 128; ++t)
-                            bulk_load(stSf + C::kSfaBytes + t * 2 * kChunkBytes,
-                                      p.sfbPacked + (sfbRec + static_cast<size_t>(t) * p.kBlocks + kb) * 2 * kChunkBytes,
-                                      2 * kChunkBytes, &fullBar[s]);
+                            bulk_load(stSf + C::kSfaBytes + t * SFC * kChunkBytes,
+                                      p.sfbPacked + (sfbRec + static_cast<size_t>(t) * p.kBlocks + kb) * SFC * kChunkBytes,
+                                      SFC * kChunkBytes, &fullBar[s]);
                     }
                 }
             }
@@ -339,13 +343,13 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                     // scales: shared -> tensor memory.  Chunk q of A -> columns sfaCol + 4q; chunk q of the
                     // 128-row tile t of B -> columns sfbCol + q*(BN/32) + 4t.
 #pragma unroll
-                    for (int q = 0; q < 2; ++q) {
+                    for (int q = 0; q < SFC; ++q) {
                         const uint64_t da = smem_desc_noswizzle(sfaSmem + q * kChunkBytes, 0, 128);
                         if constexpr (PAIR) tc_cp_32x128b_warpx4_pair(sfaCol + 4 * q, da);  // each CTA from its own shared memory
                         else tc_cp_32x128b_warpx4(sfaCol + 4 * q, da);
 #pragma unroll
                         for (int t = 0; t < BN / 128; ++t) {
-                            const uint64_t db = smem_desc_noswizzle(sfbSmem + (t * 2 + q) * kChunkBytes, 0, 128);
+                            const uint64_t db = smem_desc_noswizzle(sfbSmem + (t * SFC + q) * kChunkBytes, 0, 128);
                             if constexpr (PAIR) tc_cp_32x128b_warpx4_pair(sfbCol + q * (BN / 32) + 4 * t, db);
                             else tc_cp_32x128b_warpx4(sfbCol + q * (BN / 32) + 4 * t, db);
                         }
@@ -354,14 +358,21 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                     const uint64_t descB = smem_desc_sw128(base + C::kABytes);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        // K = 64 per MMA = 32 bytes: chunk k/2, scale bytes (k%2)*2 and (k%2)*2+1 of each column
-                        const uint32_t sfId = (k & 1) * 2;
-                        if constexpr (PAIR)
-                            mma_mxf4_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kTileM, BN, sfId, sfId), (kb | k) != 0,
-                                          sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
-                        else
-                            mma_mxf4(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kTileM, BN, sfId, sfId), (kb | k) != 0,
-                                     sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
+                        if constexpr (SFC == 2) {
+                            // 4-bit: K = 64 per MMA = 32 bytes: chunk k/2, scale bytes (k%2)*2 and (k%2)*2+1 of each column
+                            const uint32_t sfId = (k & 1) * 2;
+                            if constexpr (PAIR)
+                                mma_mxf4_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kTileM, BN, sfId, sfId), (kb | k) != 0,
+                                              sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
+                            else
+                                mma_mxf4(tmemD, descA + 2 * k, descB + 2 * k, idesc_mxf4(kTileM, BN, sfId, sfId), (kb | k) != 0,
+                                         sfaCol + 4 * (k >> 1), sfbCol + (k >> 1) * (BN / 32));
+                        } else {
+                            // 8-bit: K = 32 per MMA = 32 bytes: one chunk per k-block, scale byte k of each column
+                            const uint32_t id = idesc_mxf8(kTileM, BN, p.aFmt, p.bFmt, k, k);
+                            if constexpr (PAIR) mma_mxf8_pair(tmemD, descA + 2 * k, descB + 2 * k, id, (kb | k) != 0, sfaCol, sfbCol);
+                            else mma_mxf8(tmemD, descA + 2 * k, descB + 2 * k, id, (kb | k) != 0, sfaCol, sfbCol);
+                        }
                     }
                     if constexpr (PAIR) tc_commit_pair(&emptyBar[s], 3);
                     else tc_commit(&emptyBar[s]);
@@ -413,6 +424,17 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             for (int cp = 0; cp < kChunks / 2; ++cp) {  // two 32-column chunks = 64 columns = 128 bytes of bf16 per row
                 const int n = n0 + cp * 64;
                 if (n >= p.N) continue;  // uniform over the warp
+                if (p.outF32) {  // fp32 output: every thread writes its own row (no conversion, no transpose)
+                    if (rowOk) {
+                        for (int pi = 0; pi < p.nPeers; ++pi) {
+                            float* crow = reinterpret_cast<float*>(p.C[pi]) + static_cast<size_t>(ti.outRow + rIn) * p.N + n;
+#pragma unroll
+                            for (int j = 0; j < 64; ++j)
+                                if (n + j < p.N) crow[j] = __uint_as_float(r[2 * cp + (j >> 5)][j & 31]);
+                        }
+                    }
+                    continue;
+                }
                 uint32_t packed[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
@@ -508,28 +530,28 @@ struct Layout {
     size_t tileOff, sfaOff, sfbOff, total;
     int tilesM, kBlocks, nTiles128;
 };
-Layout make_layout(int64_t sumM, int G, int K, int N)
+Layout make_layout(int64_t sumM, int G, int K, int N, int sfc = 2)
 {
     Layout L{};
     // upper bound on 128-row entries: with 256-row pair tiles every group may add up to two partly filled entries
     L.tilesM = static_cast<int>((sumM + kBM - 1) / kBM + 2 * static_cast<int64_t>(G) + 2);
-    L.kBlocks = (K + kBKElems - 1) / kBKElems;
+    L.kBlocks = (K + 128 * sfc - 1) / (128 * sfc);  // a k-block row is 128 bytes: 256 4-bit or 128 8-bit elements
     L.nTiles128 = 2 * ((N + 255) / 256);  // even, so a 256-wide N tile always finds both of its 128-row halves
     L.tileOff = 0;
     L.sfaOff = align_up(static_cast<size_t>(L.tilesM) * sizeof(TileInfo), 256);
-    L.sfbOff = L.sfaOff + align_up(static_cast<size_t>(L.tilesM) * L.kBlocks * 2 * kChunkBytes, 256);
-    L.total = L.sfbOff + align_up(static_cast<size_t>(G) * L.nTiles128 * L.kBlocks * 2 * kChunkBytes, 256);
+    L.sfbOff = L.sfaOff + align_up(static_cast<size_t>(L.tilesM) * L.kBlocks * sfc * kChunkBytes, 256);
+    L.total = L.sfbOff + align_up(static_cast<size_t>(G) * L.nTiles128 * L.kBlocks * sfc * kChunkBytes, 256);
     return L;
 }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int SFC = 2>
 ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb, Params p,
                    cudaStream_t st)
 {
-    using C = Cfg<BN, PAIR>;
+    using C = Cfg<BN, PAIR, SFC>;
     static bool attrSet = false;
     if (!attrSet) {
-        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_kernel<BN, PAIR, SFC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(C::kSmemBytes)));
         attrSet = true;
     }
@@ -559,7 +581,7 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mxfp4_kernel<BN, PAIR>, ta, tb, tsa, tsb, p));
+    ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mxfp4_kernel<BN, PAIR, SFC>, ta, tb, tsa, tsb, p));
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
@@ -577,11 +599,16 @@ extern "C" size_t ascq_group_matmul_mxfp4_workspace_size(int64_t sumM, int G, in
 
 // Shared body of the entry points.  outBufs: nBufs bf16 matrices with row stride N; group g's rows go to rows
 // outRowStart_host[g].. of each (NULL: the groups follow each other as in A).
+struct Mx8Args {  // 8-bit operands (kind::mxf8f6f4): formats 0 = E4M3, 1 = E5M2; output bf16 or fp32
+    uint32_t aFmt, bFmt;
+    int outF32;
+};
 static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, const int64_t* outRowStart_host,
                              const uint8_t* A_fp4, const uint8_t* sA_e8m0, const uint8_t* B_fp4, const uint8_t* sB_e8m0,
                              const int64_t* groupList_host, int G, int K, int N, void* workspace, size_t workspaceBytes,
-                             void* stream)
+                             void* stream, const Mx8Args* mx8 = nullptr)
 {
+    const int sfc = mx8 ? 1 : 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!outBufs || nBufs < 1 || nBufs > kMaxPeers)
         return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
@@ -606,7 +633,7 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
         for (int g = 0; g < G; ++g)
             if (outRowStart_host[g] < 0 || outRowStart_host[g] > 0x7FFFFFFF - 256)
                 return fail(ASCQ_ERR_INVALID_ARG, "outRowStart[%d] is out of range", g);
-    const Layout L = make_layout(sumM, G, K, N);
+    const Layout L = make_layout(sumM, G, K, N, sfc);
     if (!workspace || workspaceBytes < L.total)
         return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", L.total, workspaceBytes);
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(ASCQ_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
@@ -662,7 +689,7 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
         numTilesM = static_cast<int>(tiles.size());
     }
 
-    const int kChunks = L.kBlocks * 2;
+    const int kChunks = L.kBlocks * sfc;
     const int sfRowBytes = K / 32;
     {
         const dim3 grid(static_cast<unsigned>(numTilesM + G * L.nTiles128), static_cast<unsigned>((kChunks + kSlab - 1) / kSlab));
@@ -677,6 +704,7 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
     for (int i = 0; i < nBufs; ++i) p.C[i] = static_cast<__nv_bfloat16*>(outBufs[i]);
     p.firstPeer = ((firstBuf % nBufs) + nBufs) % nBufs;
     p.wideStores = nBufs > 1;
+    if (mx8) { p.aFmt = mx8->aFmt; p.bFmt = mx8->bFmt; p.outF32 = mx8->outF32; }
     if (const char* e = getenv("ASCQ_MXFP4_STORE")) p.wideStores = !strcmp(e, "wide") ? 1 : (!strcmp(e, "narrow") && nBufs == 1 ? 0 : p.wideStores);
     p.tiles = reinterpret_cast<const TileInfo*>(ws + L.tileOff);
     p.sfaPacked = ws + L.sfaOff;
@@ -686,16 +714,21 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
 
     const bool wide = N >= 256;
     CUtensorMap ta, tb, tsa, tsb;
-    ascq_status rc = make_tmap_u8(&ta, A_fp4, static_cast<uint64_t>(sumM), static_cast<uint64_t>(K / 2), kBM);
+    const uint64_t rowBytes = mx8 ? static_cast<uint64_t>(K) : static_cast<uint64_t>(K / 2);
+    ascq_status rc = make_tmap_u8(&ta, A_fp4, static_cast<uint64_t>(sumM), rowBytes, kBM);
     if (rc != ASCQ_OK) return rc;
-    rc = make_tmap_u8(&tb, B_fp4, static_cast<uint64_t>(G) * N, static_cast<uint64_t>(K / 2), pair ? 128 : (wide ? 256 : 128));
+    rc = make_tmap_u8(&tb, B_fp4, static_cast<uint64_t>(G) * N, rowBytes, pair ? 128 : (wide ? 256 : 128));
     if (rc != ASCQ_OK) return rc;
     // the packed scales as 1 KiB records (pair mode loads them with tensor copies so that the partner CTA's loads
     // can be counted on the leader's barrier)
-    rc = make_tmap_kib_rows(&tsa, ws + L.sfaOff, static_cast<uint64_t>(numTilesM) * L.kBlocks);
+    rc = make_tmap_kib_rows(&tsa, ws + L.sfaOff, static_cast<uint64_t>(numTilesM) * L.kBlocks, sfc * kChunkBytes);
     if (rc != ASCQ_OK) return rc;
-    rc = make_tmap_kib_rows(&tsb, ws + L.sfbOff, static_cast<uint64_t>(G) * L.nTiles128 * L.kBlocks);
+    rc = make_tmap_kib_rows(&tsb, ws + L.sfbOff, static_cast<uint64_t>(G) * L.nTiles128 * L.kBlocks, sfc * kChunkBytes);
     if (rc != ASCQ_OK) return rc;
+    if (mx8) {
+        if (pair) return launch<256, true, 1>(ta, tb, tsa, tsb, p, st);
+        return wide ? launch<256, false, 1>(ta, tb, tsa, tsb, p, st) : launch<128, false, 1>(ta, tb, tsa, tsb, p, st);
+    }
     if (pair) return launch<256, true>(ta, tb, tsa, tsb, p, st);
     return wide ? launch<256, false>(ta, tb, tsa, tsb, p, st) : launch<128, false>(ta, tb, tsa, tsb, p, st);
 }
@@ -718,6 +751,27 @@ extern "C" ascq_status ascq_group_matmul_mxfp4_scatter(void* const* C_bufs, int 
 {
     return run_mxfp4(C_bufs, nBufs, firstBuf, outRowStart_host, A_fp4, sA_e8m0, B_fp4, sB_e8m0, groupList_host, G, K, N,
                      workspace, workspaceBytes, stream);
+}
+
+extern "C" size_t ascq_group_matmul_mxfp8_workspace_size(int64_t sumM, int G, int K, int N)
+{
+    if (sumM < 0 || G <= 0 || K <= 0 || N <= 0) return 0;
+    return make_layout(sumM, G, K, N, 1).total;
+}
+
+extern "C" ascq_status ascq_group_matmul_mxfp8(void* C, ascq_dtype cT, const uint8_t* A_fp8, ascq_dtype aT, const uint8_t* sA_e8m0,
+                                               const uint8_t* B_fp8, ascq_dtype bT, const uint8_t* sB_e8m0,
+                                               const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                               size_t workspaceBytes, void* stream)
+{
+    if (!C) return fail(ASCQ_ERR_INVALID_ARG, "C, A, sA, B, sB and groupList must not be NULL");
+    if ((aT != ASCQ_DT_FP8_E4M3 && aT != ASCQ_DT_FP8_E5M2) || (bT != ASCQ_DT_FP8_E4M3 && bT != ASCQ_DT_FP8_E5M2))
+        return fail(ASCQ_ERR_UNSUPPORTED, "operands must be fp8_e4m3fn or fp8_e5m2");
+    if (cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32) return fail(ASCQ_ERR_UNSUPPORTED, "output must be bfloat16_t or float");
+    void* bufs[1] = {C};
+    const Mx8Args mx8{aT == ASCQ_DT_FP8_E5M2 ? 1u : 0u, bT == ASCQ_DT_FP8_E5M2 ? 1u : 0u, cT == ASCQ_DT_F32 ? 1 : 0};
+    return run_mxfp4(bufs, 1, 0, nullptr, A_fp8, sA_e8m0, B_fp8, sB_e8m0, groupList_host, G, K, N, workspace, workspaceBytes,
+                     stream, &mx8);
 }
 
 // ---- entry point for callers that may not allocate device memory ------------------------------------

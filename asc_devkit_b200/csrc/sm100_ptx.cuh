@@ -137,6 +137,17 @@ __device__ __forceinline__ void mma_mxf4(uint32_t tmemD, uint64_t descA, uint64_
         ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(tmemSfa), "r"(tmemSfb)
         : "memory");
 }
+// 8-bit (and 6/4-bit padded) operands with one E8M0 scale per 32 elements: K = 32 per instruction
+__device__ __forceinline__ void mma_mxf8(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate,
+                                         uint32_t tmemSfa, uint32_t tmemSfb)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(tmemSfa), "r"(tmemSfb)
+        : "memory");
+}
 // The mbarrier receives one arrival when every tcgen05 operation issued so far by this thread is done.
 __device__ __forceinline__ void tc_commit(uint64_t* bar)
 {
@@ -223,6 +234,16 @@ __device__ __forceinline__ void mma_mxf4_pair(uint32_t tmemD, uint64_t descA, ui
         ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(tmemSfa), "r"(tmemSfb)
         : "memory");
 }
+__device__ __forceinline__ void mma_mxf8_pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate,
+                                              uint32_t tmemSfa, uint32_t tmemSfb)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(tmemSfa), "r"(tmemSfb)
+        : "memory");
+}
 // shared -> tensor memory in both CTAs of the pair (each from its own shared memory, same offsets)
 __device__ __forceinline__ void tc_cp_32x128b_warpx4_pair(uint32_t tmemDst, uint64_t smemDesc)
 {
@@ -265,6 +286,13 @@ __host__ __device__ constexpr uint32_t idesc_i8(uint32_t M, uint32_t N)
 __host__ __device__ constexpr uint32_t idesc_mxf4(uint32_t M, uint32_t N, uint32_t sfaId, uint32_t sfbId)
 {
     return (sfbId << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (sfaId << 29);
+}
+
+// Block-scaled descriptor for kind::mxf8f6f4: A/B format 0 = E4M3, 1 = E5M2; the scale-factor ids pick one of the
+// four bytes of a 32-bit scale column (one byte per 32 elements of K).
+__host__ __device__ constexpr uint32_t idesc_mxf8(uint32_t M, uint32_t N, uint32_t aFmt, uint32_t bFmt, uint32_t sfaId, uint32_t sfbId)
+{
+    return (sfbId << 4) | (aFmt << 7) | (bFmt << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (sfaId << 29);
 }
 
 }  // namespace ptx

@@ -44,14 +44,14 @@ inline ascq_status make_tmap_u8(CUtensorMap* out, const void* base, uint64_t row
     return ASCQ_OK;
 }
 
-// uint32 [rows, 256] tensor map (1 KiB rows, no swizzle) with a one-row box: one load moves one 1 KiB record.
-inline ascq_status make_tmap_kib_rows(CUtensorMap* out, const void* base, uint64_t rows)
+// uint32 [rows, words] tensor map (rows of recordBytes, no swizzle) with a one-row box: one load moves one record.
+inline ascq_status make_tmap_kib_rows(CUtensorMap* out, const void* base, uint64_t rows, uint32_t recordBytes = 1024)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-    const cuuint64_t dims[2] = {256, rows};
-    const cuuint64_t strides[1] = {1024};
-    const cuuint32_t box[2] = {256, 1};
+    const cuuint64_t dims[2] = {recordBytes / 4, rows};
+    const cuuint64_t strides[1] = {recordBytes};
+    const cuuint32_t box[2] = {recordBytes / 4, 1};
     const cuuint32_t elemStrides[2] = {1, 1};
     const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elemStrides,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

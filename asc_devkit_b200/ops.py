@@ -270,6 +270,20 @@ def GroupMatmulMxfp4(C: torch.Tensor, A: torch.Tensor, scaleA: torch.Tensor, B: 
     return C
 
 
+def GroupMatmulMxfp8(C: torch.Tensor, A: torch.Tensor, a_dtype: int, scaleA: torch.Tensor, B: torch.Tensor, b_dtype: int,
+                     scaleB: torch.Tensor, groupList, K: int, N: int, workspace: Optional[torch.Tensor] = None, stream=None):
+    """MX matmul with fp8 operands (``ascq_group_matmul_mxfp8``).  A [sumM, K] uint8 (fp8 codes), B [G, N, K] uint8,
+    scales [rows, K/32] uint8 (e8m0), ``a_dtype`` / ``b_dtype`` = DT_FP8_E4M3 or DT_FP8_E5M2, C bf16 or fp32 [sumM, N]."""
+    G = len(groupList)
+    gl = (C_int64 * G)(*[int(v) for v in groupList])
+    need = int(L.lib().ascq_group_matmul_mxfp8_workspace_size(int(sum(int(v) for v in groupList)), G, K, N))
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=C.device)
+    L.check(L.lib().ascq_group_matmul_mxfp8(_ptr(C), dtype_code(C), _ptr(A), a_dtype, _ptr(scaleA), _ptr(B), b_dtype,
+                                            _ptr(scaleB), gl, G, K, N, _ptr(workspace), workspace.numel(), _stream(stream)))
+    return C
+
+
 def GroupMatmulMxfp4Scatter(buffer_ptrs, first_buf: int, out_row_start, A: torch.Tensor, scaleA: torch.Tensor, B: torch.Tensor,
                             scaleB: torch.Tensor, groupList, K: int, N: int, workspace: Optional[torch.Tensor] = None,
                             stream=None):

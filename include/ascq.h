@@ -320,6 +320,22 @@ ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const int8_t* B_n
 ascq_status ascq_transpose_i8_kn_to_nk(int8_t* B_nk, const int8_t* B_kn, int K, int N, void* stream);
 
 /*
+ * The grouped MX matmul with 8-bit operands (fp8_e4m3fn / fp8_e5m2 in any combination, one E8M0 scale per 32 elements
+ * of K): MatmulWithScalePolicy on fp8 types (impl/adv_api/detail/matmul/mx_matmul_impl.h:29-181, sample
+ * examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx, basic-API form .../03_matrix_compute/mmad_mx).
+ * tcgen05 kind::mxf8f6f4.block_scale; same kernel, tile shapes, scratch scheme and grouping as ascq_group_matmul_mxfp4.
+ * A [sumM, K], B [G, N, K] one byte per element, K-major; scales [rows, K/32]; K % 128 == 0; C [sumM, N] of
+ * cT = ASCQ_DT_BF16 or ASCQ_DT_F32 (the samples' output type); aT / bT = ASCQ_DT_FP8_E4M3 or ASCQ_DT_FP8_E5M2.
+ * A weight stored [K, N] is turned once with ascq_transpose_i8_kn_to_nk (bytes), scales stored [sK/2, N, 2] with
+ * ascq_mx_repack_scale_b.
+ */
+ascq_status ascq_group_matmul_mxfp8(void* C, ascq_dtype cT, const uint8_t* A_fp8, ascq_dtype aT, const uint8_t* sA_e8m0,
+                                    const uint8_t* B_fp8, ascq_dtype bT, const uint8_t* sB_e8m0,
+                                    const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                    size_t workspaceBytes, void* stream);
+size_t ascq_group_matmul_mxfp8_workspace_size(int64_t sumM, int G, int K, int N);
+
+/*
  * The grouped MX-FP4 matmul with the reassembly of a group-parallel layout fused into its epilogue.  With the
  * groups dealt out over the GPUs of one box (one process per GPU), every rank computes the output rows of its own
  * groups and writes them into EVERY buffer of C_bufs: group g's rows go to rows outRowStart_host[g] .. of each bf16

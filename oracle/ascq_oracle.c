@@ -732,6 +732,58 @@ int ascq_oracle_group_matmul_mxfp4(uint16_t* C, float* C_f32, const uint8_t* A, 
     return OR_OK;
 }
 
+/* MX matmul with 8-bit operands (fp8_e4m3fn / fp8_e5m2, one E8M0 scale per 32 elements of K), grouped like the fp4
+ * one.  Golden formula: examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py:52-66 and
+ * examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/mmad_mx/scripts/gen_data.py (mx_decompress, fp64 matmul,
+ * result cast to fp32).  aFmt / bFmt: 0 = E4M3 (bias 7, no infinity, S.1111.111 = NaN), 1 = E5M2 (the top byte of a half). */
+double orc_fp8_to_f64(uint8_t v, int fmt)
+{
+    if (fmt == 1) return (double)orc_f16_to_f32((uint16_t)((uint16_t)v << 8));
+    int sign = v >> 7, e = (v >> 3) & 0xF, m = v & 7;
+    double r;
+    if (e == 0xF && m == 7) return NAN;
+    if (e == 0) r = ldexp((double)m, -9);            /* subnormal: m/8 * 2^-6 */
+    else r = ldexp(1.0 + (double)m / 8.0, e - 7);
+    return sign ? -r : r;
+}
+
+int ascq_oracle_group_matmul_mxfp8(uint16_t* C, float* C_f32, const uint8_t* A, int aFmt, const uint8_t* sA, const uint8_t* B,
+                                   int bFmt, const uint8_t* sB, const int64_t* groupList, int G, int K, int N)
+{
+    if (!A || !B || !sA || !sB || !groupList || K % 32 != 0) return OR_INVALID;
+    int64_t start = 0;
+    const int KS = K / 32;
+    for (int g = 0; g < G; ++g) {
+        int64_t mg = groupList[g];
+        if (mg < 0) return OR_INVALID;
+        const uint8_t* Bg = B + (size_t)g * N * K;
+        const uint8_t* sBg = sB + (size_t)g * N * KS;
+#pragma omp parallel
+        {
+            double* arow = (double*)malloc(sizeof(double) * (size_t)K);
+#pragma omp for schedule(dynamic, 4)
+            for (int64_t r = start; r < start + mg; ++r) {
+                for (int k = 0; k < K; ++k)
+                    arow[k] = orc_fp8_to_f64(A[(size_t)r * K + k], aFmt) * e8m0_to_f64(sA[(size_t)r * KS + k / 32]);
+                for (int n = 0; n < N; ++n) {
+                    double acc = 0.0;
+                    const uint8_t* brow = Bg + (size_t)n * K;
+                    for (int kb = 0; kb < KS; ++kb) {
+                        double part = 0.0;
+                        for (int k = kb * 32; k < kb * 32 + 32; ++k) part += arow[k] * orc_fp8_to_f64(brow[k], bFmt);
+                        acc += part * e8m0_to_f64(sBg[(size_t)n * KS + kb]);
+                    }
+                    if (C) C[(size_t)r * N + n] = orc_f32_to_bf16_sat((float)acc);
+                    if (C_f32) C_f32[(size_t)r * N + n] = (float)acc;
+                }
+            }
+            free(arow);
+        }
+        start += mg;
+    }
+    return OR_OK;
+}
+
 /* ------------------------------------------------------------------------------------------
  * Host tmp-size formulas.
  *   impl/adv_api/tiling/quantization/ascend_quant_tiling_impl.cpp:31-69

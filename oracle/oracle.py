@@ -233,6 +233,18 @@ def group_matmul_mxfp4(A, sA, B, sB, groupList, K, N, want_f32=False):
     return (Cb, Cf) if want_f32 else Cb
 
 
+def group_matmul_mxfp8(A, aFmt, sA, B, bFmt, sB, groupList, K, N):
+    """A [sumM, K] u8 (fp8 codes), sA [sumM, K/32] u8, B [G, N, K] u8, sB [G, N, K/32] u8; aFmt/bFmt 0 = e4m3fn, 1 = e5m2.
+    Returns (bf16 bits, fp32)."""
+    G = int(len(groupList))
+    sumM = int(np.sum(groupList))
+    Cb = np.zeros((sumM, N), np.uint16)
+    Cf = np.zeros((sumM, N), np.float32)
+    gl = np.ascontiguousarray(groupList, np.int64)
+    _check(lib().ascq_oracle_group_matmul_mxfp8(_p(Cb), _p(Cf), _p(A), aFmt, _p(sA), _p(B), bFmt, _p(sB), _p(gl), G, K, N))
+    return Cb, Cf
+
+
 def _dims(d):
     arr = (C.c_int64 * len(d))(*d)
     return arr, len(d)

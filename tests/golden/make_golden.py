@@ -40,6 +40,20 @@ CASES = [
      {"input/x1_gm.bin": (np.int8, (1024, 1024)), "input/x2_gm.bin": (np.int8, (1024, 1024)),
       "input/bias_gm.bin": (np.int32, (1024,)), "input/quant_vector_gm.bin": (np.uint64, (1024,)),
       "output/golden.bin": (np.float16, (1024, 1024))}),
+    ("matmul_mx_e5m2", "examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py", [], 106,
+     {"input/x1_gm.bin": (np.uint8, (32, 128)), "input/x2_gm.bin": (np.uint8, (128, 128)),
+      "input/x1_mx_gm.bin": (np.uint8, (32, 4)), "input/x2_mx_gm.bin": (np.uint8, (2, 128, 2)),
+      "output/golden.bin": (np.float32, (32, 128))}),
+    ("mmad_mx_scenario3", "examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/mmad_mx/scripts/gen_data.py",
+     ["scenario_num=3"], 107,
+     {"input/x1_gm.bin": (np.uint8, (40, 70)), "input/x2_gm.bin": (np.uint8, (50, 70)),
+      "input/x1_scale_gm.bin": (np.uint8, (40, 4)), "input/x2_scale_gm.bin": (np.uint8, (50, 4)),
+      "output/golden.bin": (np.float32, (40, 50))}),
+    ("mmad_mx_scenario4", "examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/mmad_mx/scripts/gen_data.py",
+     ["scenario_num=4"], 108,
+     {"input/x1_gm.bin": (np.uint8, (40, 70)), "input/x2_gm.bin": (np.uint8, (50, 70)),
+      "input/x1_scale_gm.bin": (np.uint8, (40, 4)), "input/x2_scale_gm.bin": (np.uint8, (50, 4)),
+      "input/bias_gm.bin": (np.float32, (50,)), "output/golden.bin": (np.float32, (40, 50))}),
     ("antiquant_dav3510", f"{EX}/antiquant/scripts/gen_data.py", ["dav-3510"], None,
      {"input/input_src.bin": (np.int8, (8, 128)), "input/input_offset.bin": (np.float16, (1, 128)),
       "input/input_scale.bin": (np.float16, (1, 128)), "output/golden.bin": (np.float16, (8, 128))}),

@@ -186,6 +186,53 @@ def test_matmul_quant_sample_golden(golden_dir, name):
     assert np.array_equal(out.view(np.uint16), g["golden"].view(np.uint16))
 
 
+# ---- MX matmul with fp8 operands (matmul_mx and mmad_mx samples) --------------------------------------
+def test_matmul_mx_sample_golden(golden_dir):
+    # matmul_mx/scripts/gen_data.py: e5m2 x e5m2, m=32 n=k=128, B stored [K,N], scaleB stored [sk/2, n, 2]
+    g = _load(golden_dir, "matmul_mx_e5m2")
+    B_nk = np.ascontiguousarray(g["x2_gm"].T)
+    sB = np.ascontiguousarray(g["x2_mx_gm"].transpose(1, 0, 2).reshape(128, 4))
+    _, out = O.group_matmul_mxfp8(g["x1_gm"], 1, g["x1_mx_gm"], B_nk[None], 1, sB[None], np.array([32]), 128, 128)
+    assert np.array_equal(out.view(np.uint32), g["golden"].view(np.uint32))
+
+
+@pytest.mark.parametrize("scenario,aFmt,bFmt", [(3, 0, 1), (4, 1, 0)])
+def test_mmad_mx_sample_golden(golden_dir, scenario, aFmt, bFmt):
+    # mmad_mx/scripts/gen_data.py scenario 3 (e4m3 x e5m2, result doubled) and 4 (e5m2 x e4m3, fp32 bias added);
+    # m, n, k = 40, 50, 70: K is padded with zero codes to the next multiple of 128, as the scale arrays already are
+    g = _load(golden_dir, f"mmad_mx_scenario{scenario}")
+    A = np.zeros((40, 128), np.uint8)
+    A[:, :70] = g["x1_gm"]
+    B = np.zeros((50, 128), np.uint8)
+    B[:, :70] = g["x2_gm"]
+    _, out = O.group_matmul_mxfp8(A, aFmt, g["x1_scale_gm"], B[None], bFmt, g["x2_scale_gm"][None], np.array([40]), 128, 50)
+    want = out * np.float32(2) if scenario == 3 else out + g["bias_gm"]
+    assert np.array_equal(want.view(np.uint32), g["golden"].view(np.uint32))
+
+
+def test_fp8_decode_matches_ml_dtypes():
+    ml_dtypes = pytest.importorskip("ml_dtypes")
+    codes = np.arange(256, dtype=np.uint8)
+    for fmt, dt in ((0, ml_dtypes.float8_e4m3fn), (1, ml_dtypes.float8_e5m2)):
+        want = codes.view(dt).astype(np.float64)
+        A = codes.reshape(2, 128)
+        ones = np.full((2, 4), 127, np.uint8)
+        # one-hot B rows pick out every decoded value: B[n] has 1.0 at k = n
+        one = {0: 0x38, 1: 0x3C}[fmt]
+        B = np.zeros((128, 128), np.uint8)
+        B[np.arange(128), np.arange(128)] = one
+        _, out = O.group_matmul_mxfp8(A, fmt, ones, B[None], fmt, np.full((1, 128, 4), 127, np.uint8), np.array([2]), 128, 128)
+        got = out.reshape(-1).astype(np.float64)
+        ok = (got == want) | (np.isnan(got) & np.isnan(want))
+        # a NaN operand poisons its whole row of sums: compare only rows without NaN codes exactly, NaN rows as NaN
+        for r in range(2):
+            rowcodes = want[r * 128:(r + 1) * 128]
+            if np.isnan(rowcodes).any():
+                assert np.isnan(got[r * 128:(r + 1) * 128]).all()
+            else:
+                assert ok[r * 128:(r + 1) * 128].all()
+
+
 # ---- tests/api/adv_api/tiling/test_tiling.cpp:6540-6712 known answers -----------------------------
 TILING_ANTIQUANT = [
     # srcDims, scaleDims, transpose, outT, (max, min), (live, extra)
