@@ -67,9 +67,13 @@ struct Params {
     const int32_t* biasI32;
     const uint64_t* quantVec;   // low word: fp32 bits, of which the hardware keeps sign, exponent and 10 mantissa bits
     float quantScalar;
+    // kEpiFloat: operand format (0 = half, 1 = bfloat16) and output type (0 = half, 1 = bfloat16, 2 = float)
+    uint32_t abFmt;
+    int outKind;
 };
 constexpr int kEpiDequant = 0;  // bf16(((float(acc) * sB[n]) * sA[m]) + bias[n])
 constexpr int kEpiFixpipe = 1;  // SetQuantScalar / SetQuantVector of the reference's Matmul (DEQF16)
+constexpr int kEpiFloat = 2;    // half / bfloat16 operands (kind::f16), fp32 accumulator cast to the output type
 
 template <int BN, bool PAIR, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -161,7 +165,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (rank == 0 && elect_one()) {
-            constexpr uint32_t idesc = idesc_i8(kTileM, BN);
+            const uint32_t idesc = (EPI == kEpiFloat) ? idesc_f16(kTileM, BN, p.abFmt) : idesc_i8(kTileM, BN);
             uint32_t it = 0, local = 0;
             bool ok = true;
             for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
@@ -181,8 +185,13 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         // advancing K inside the swizzle atom: +32 bytes on the start address (>> 4 = 2)
-                        if constexpr (PAIR) mma_i8_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
-                        else mma_i8(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                        if constexpr (EPI == kEpiFloat) {
+                            if constexpr (PAIR) mma_f16_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                            else mma_f16(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                        } else {
+                            if constexpr (PAIR) mma_i8_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                            else mma_i8(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0);
+                        }
                     }
                     // the stage is free (in both CTAs of a pair) once these MMAs have read it
                     if constexpr (PAIR) tc_commit_pair(&emptyBar[s], 3);
@@ -218,7 +227,9 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 const int t = threadIdx.x - 64;  // index over the epilogue threads
                 for (int j = t; j < BN; j += 32 * kEpiWarps) {
                     const int n = n0 + j;
-                    if constexpr (EPI == kEpiFixpipe) {
+                    if constexpr (EPI == kEpiFloat) {
+                        (void)n;
+                    } else if constexpr (EPI == kEpiFixpipe) {
                         const uint32_t bits = (p.quantVec != nullptr && n < p.N)
                                                   ? static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned long long*>(p.quantVec) + n)) & 0xFFFFE000u
                                                   : 0x3F800000u;
@@ -255,6 +266,20 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             auto convert32 = [&](const uint32_t(&r)[32], int colInTile, uint32_t* packed) {
                 const float4* sb4 = reinterpret_cast<const float4*>(sBs + colInTile);
                 const float4* bi4 = reinterpret_cast<const float4*>(biasS + colInTile);
+                if constexpr (EPI == kEpiFloat) {
+                    // fp32 accumulator -> half or bfloat16 (RINT; half overflows to infinity as IEEE does)
+#pragma unroll
+                    for (int v = 0; v < 16; ++v) {
+                        const float f0 = __uint_as_float(r[2 * v]), f1 = __uint_as_float(r[2 * v + 1]);
+                        if (p.outKind == 1) {
+                            packed[v] = pack_bf16x2_sat(f0, f1);
+                        } else {
+                            const __half2 h = __floats2half2_rn(f0, f1);
+                            packed[v] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                    }
+                    return;
+                }
                 if constexpr (EPI == kEpiFixpipe) {
                     // matmul_quant/scripts/gen_data.py:26-44: (acc + bias) -> half; scalar mode: half * half(scale);
                     // vector mode: float(half) * scale (19 significant bits kept) -> half
@@ -322,6 +347,19 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     }
                 }
                 if (!haveC) continue;
+                if constexpr (EPI == kEpiFloat) {
+                    if (p.outKind == 2) {  // fp32 output: every thread writes its own row
+                        if (m < p.M) {
+                            float* crow = reinterpret_cast<float*>(p.C[0]) + static_cast<size_t>(m) * p.ldc + p.colOffset + n;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (n + j < p.N) crow[j] = __uint_as_float(r0[j]);
+                                if (n + 32 + j < p.N) crow[32 + j] = __uint_as_float(r1[j]);
+                            }
+                        }
+                        continue;
+                    }
+                }
                 uint32_t packed[32];
                 convert32(r0, c2 * 64, packed);
                 convert32(r1, c2 * 64 + 32, packed + 16);
@@ -437,13 +475,17 @@ struct FixpipeArgs {
     const int32_t* biasI32;
     const uint64_t* quantVec;
     float quantScalar;
+    int floatKind;     // 0: int8 operands + fixpipe epilogue; 1: half / bfloat16 operands (kEpiFloat)
+    uint32_t abFmt;    // floatKind: 0 = half, 1 = bfloat16
+    int outKind;       // floatKind: 0 = half, 1 = bfloat16, 2 = float
 };
 
 ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
                      const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc, int32_t* accDump,
                      cudaStream_t st, const FixpipeArgs* fix = nullptr)
 {
-    const int epi = fix ? kEpiFixpipe : kEpiDequant;
+    const int epi = fix ? (fix->floatKind ? kEpiFloat : kEpiFixpipe) : kEpiDequant;
+    const int elemBytes = (epi == kEpiFloat) ? 2 : 1;
     if (!A || !B_nk) return fail(ASCQ_ERR_INVALID_ARG, "A and B must not be NULL");
     if (nBufs < 0 || nBufs > kMaxPeers) return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
     const bool haveC = nBufs > 0 && outBufs != nullptr && outBufs[0] != nullptr;
@@ -452,7 +494,7 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     if (haveC && ldc < colOffset + N) return fail(ASCQ_ERR_INVALID_ARG, "ldc %d is smaller than colOffset + N = %d", ldc, colOffset + N);
     if (M == 0 || N == 0) return ASCQ_OK;
     if (K == 0) return fail(ASCQ_ERR_INVALID_ARG, "K must be positive");
-    if (K % 16 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of 16 (TMA row pitch)", K);
+    if ((K * elemBytes) % 16 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of %d (TMA row pitch of 16 bytes)", K, 16 / elemBytes);
     if (!aligned16(A) || !aligned16(B_nk)) return fail(ASCQ_ERR_ALIGNMENT, "A and B must be 16-byte aligned");
 
     Params p{};
@@ -467,8 +509,10 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     p.sB = sB_n;
     p.bias = static_cast<const __nv_bfloat16*>(bias_bf16);
     p.accDump = accDump;
-    p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+    p.M = M; p.N = N; p.K = K * elemBytes; p.ldc = ldc;  // the kernel counts K in bytes of an operand row
     if (fix) {
+        p.abFmt = fix->abFmt;
+        p.outKind = fix->outKind;
         p.biasI32 = fix->biasI32;
         p.quantVec = fix->quantVec;
         p.quantScalar = fix->quantScalar;
@@ -497,10 +541,14 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         else if (!strcmp(e, "narrow")) mode = 0;
     }
     CUtensorMap ta, tb;
-    ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K), kBM);
+    ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K) * elemBytes, kBM);
     if (rc != ASCQ_OK) return rc;
-    rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), mode == 1 ? 256 : 128);
+    rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
+    if (epi == kEpiFloat) {
+        if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, p, st);
+        return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, p, st) : launch<128, false, kEpiFloat>(ta, tb, p, st);
+    }
     if (epi == kEpiFixpipe) {
         if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, p, st);
         return mode == 1 ? launch<256, false, kEpiFixpipe>(ta, tb, p, st) : launch<128, false, kEpiFixpipe>(ta, tb, p, st);
@@ -553,8 +601,51 @@ extern "C" ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const 
     if (quantVector && (reinterpret_cast<uintptr_t>(quantVector) & 7u))
         return fail(ASCQ_ERR_ALIGNMENT, "quantVector must be 8-byte aligned");
     void* bufs[1] = {C_f16};
-    const FixpipeArgs fix{bias_i32, quantVector, quantScalar};
+    const FixpipeArgs fix{bias_i32, quantVector, quantScalar, 0, 0, 0};
     return run_w8a8(bufs, 1, 0, 0, A, B_nk, nullptr, nullptr, nullptr, M, N, K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fix);
+}
+
+// ---- half / bfloat16 matmul and the weight-only-quantised matmul built on it -------------------------------------
+extern "C" ascq_status ascq_matmul_f16(void* C, ascq_dtype cT, const void* A, const void* B_nk, ascq_dtype abT, int M, int N,
+                                       int K, int ldc, void* stream)
+{
+    if (!C) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
+    if (abT != ASCQ_DT_F16 && abT != ASCQ_DT_BF16) return fail(ASCQ_ERR_UNSUPPORTED, "operands must be half or bfloat16_t");
+    if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)
+        return fail(ASCQ_ERR_UNSUPPORTED, "output must be half, bfloat16_t or float");
+    void* bufs[1] = {C};
+    const FixpipeArgs fa{nullptr, nullptr, 0.f, 1, abT == ASCQ_DT_BF16 ? 1u : 0u, cT == ASCQ_DT_F16 ? 0 : (cT == ASCQ_DT_BF16 ? 1 : 2)};
+    return run_w8a8(bufs, 1, 0, 0, static_cast<const int8_t*>(A), static_cast<const int8_t*>(B_nk), nullptr, nullptr, nullptr, M, N,
+                    K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fa);
+}
+
+extern "C" size_t ascq_matmul_w8a16_workspace_size(int N, int K)
+{
+    return (N <= 0 || K <= 0) ? 0 : static_cast<size_t>(N) * K * 2;
+}
+
+extern "C" ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk,
+                                         const void* offset, const void* scale, float offsetScalar, float scaleScalar,
+                                         int M, int N, int K, int ldc, void* workspace, size_t workspaceBytes, void* stream)
+{
+    if (!B_nk || !workspace) return fail(ASCQ_ERR_INVALID_ARG, "B and workspace must not be NULL");
+    if (N <= 0 || K <= 0) return fail(ASCQ_ERR_INVALID_ARG, "N and K must be positive");
+    if (workspaceBytes < ascq_matmul_w8a16_workspace_size(N, K))
+        return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", ascq_matmul_w8a16_workspace_size(N, K), workspaceBytes);
+    if (aT != ASCQ_DT_F16 && aT != ASCQ_DT_BF16) return fail(ASCQ_ERR_UNSUPPORTED, "A must be half or bfloat16_t");
+    // step 1: the weight tile through AscendAntiQuant<int8_t, aT, isTranspose = true> (src [N, K], one scale / offset per
+    // row n), as antiquant_processor_using_ub.h:86-137 does before the cube unit sees it
+    ascq_antiquant_param ap{static_cast<uint32_t>(N), static_cast<uint32_t>(K), 0, 0, 1, 1, 1};
+    ascq_status rc;
+    if (scale) {
+        ap.hasOffset = offset ? 1 : 0;
+        rc = ascq_antiquant(workspace, aT, B_nk, ASCQ_DT_I8, offset, scale, aT, 0.f, 0.f, ASCQ_PER_CHANNEL, &ap, stream);
+    } else {
+        rc = ascq_antiquant(workspace, aT, B_nk, ASCQ_DT_I8, nullptr, nullptr, aT, offsetScalar, scaleScalar, ASCQ_PER_TENSOR, &ap, stream);
+    }
+    if (rc != ASCQ_OK) return rc;
+    // step 2: half / bfloat16 matmul on the tensor cores
+    return ascq_matmul_f16(C, cT, A, workspace, aT, M, N, K, ldc, stream);
 }
 
 // [K, N] row-major int8 (the reference's ND weight, CubeFormat::ND, not transposed) -> [N, K]: one-off weight preparation.

@@ -137,6 +137,25 @@ __device__ __forceinline__ void mma_mxf4(uint32_t tmemD, uint64_t descA, uint64_
         ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(tmemSfa), "r"(tmemSfb)
         : "memory");
 }
+// half / bfloat16 operands, fp32 accumulator: K = 16 per instruction
+__device__ __forceinline__ void mma_f16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // 8-bit (and 6/4-bit padded) operands with one E8M0 scale per 32 elements: K = 32 per instruction
 __device__ __forceinline__ void mma_mxf8(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate,
                                          uint32_t tmemSfa, uint32_t tmemSfb)
@@ -280,6 +299,11 @@ __device__ __forceinline__ uint64_t smem_desc_noswizzle(uint32_t smemAddr, uint3
 __host__ __device__ constexpr uint32_t idesc_i8(uint32_t M, uint32_t N)
 {
     return (2u << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);  // int8 x int8 -> int32
+}
+// kind::f16: D format 1 = f32; A/B format 0 = half, 1 = bfloat16
+__host__ __device__ constexpr uint32_t idesc_f16(uint32_t M, uint32_t N, uint32_t abFmt)
+{
+    return (1u << 4) | (abFmt << 7) | (abFmt << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 // Block-scaled descriptor for kind::mxf4: A/B format 1 = E2M1, bit 23 scale format (1 = UE8M0),
 // [4,6) B scale-factor id, [29,31) A scale-factor id (which 16-bit half of the 32-bit SF column pair is used).

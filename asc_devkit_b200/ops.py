@@ -251,6 +251,32 @@ def TransposeI8KnToNk(B_nk: torch.Tensor, B_kn: torch.Tensor, stream=None):
     return B_nk
 
 
+def MatmulF16(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, stream=None):
+    """half / bfloat16 matmul with fp32 accumulation (``ascq_matmul_f16``): C [M, N] = A [M, K] . B_nk [N, K]^T."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    L.check(L.lib().ascq_matmul_f16(_ptr(C), dtype_code(C), _ptr(A), _ptr(B_nk), dtype_code(A), M, N, K, C.stride(0),
+                                    _stream(stream)))
+    return C
+
+
+def MatmulW8A16(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, offset, scale, workspace: Optional[torch.Tensor] = None,
+                stream=None):
+    """Weight-only-quantised matmul (``ascq_matmul_w8a16``): B_nk int8 [N, K] goes through AscendAntiQuant (per-channel
+    ``offset`` / ``scale`` tensors of A's dtype, or two Python floats: SetAntiQuantVector / SetAntiQuantScalar) and then
+    through the half / bfloat16 matmul."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    if workspace is None:
+        workspace = torch.empty(N * K * 2, dtype=torch.uint8, device=A.device)
+    st = isinstance(scale, torch.Tensor)
+    L.check(L.lib().ascq_matmul_w8a16(_ptr(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk),
+                                      _ptr(offset) if isinstance(offset, torch.Tensor) else None, _ptr(scale) if st else None,
+                                      0.0 if st else float(offset), 0.0 if st else float(scale), M, N, K, C.stride(0),
+                                      _ptr(workspace), workspace.numel(), _stream(stream)))
+    return C
+
+
 def GroupMatmulMxfp4Workspace(sumM: int, G: int, K: int, N: int) -> int:
     return int(L.lib().ascq_group_matmul_mxfp4_workspace_size(sumM, G, K, N))
 

@@ -320,6 +320,29 @@ ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const int8_t* B_n
 ascq_status ascq_transpose_i8_kn_to_nk(int8_t* B_nk, const int8_t* B_kn, int K, int N, void* stream);
 
 /*
+ * half / bfloat16 matmul, fp32 accumulation (AscendC::Matmul<half, half, half|float>; tcgen05 kind::f16, the same
+ * kernel template and tile shapes as the int8 matmul).  A [M,K], B_nk [N,K] of abT, K-major; C [M, ldc] of cT = half,
+ * bfloat16_t or float; K % 8 == 0.
+ */
+ascq_status ascq_matmul_f16(void* C, ascq_dtype cT, const void* A, const void* B_nk, ascq_dtype abT, int M, int N, int K,
+                            int ldc, void* stream);
+/*
+ * Weight-only-quantised matmul: A half / bfloat16, B int8 dequantised on its way to the tensor cores with
+ * Matmul::SetAntiQuantScalar / SetAntiQuantVector (include/adv_api/matmul/matmul.h:155-168; the reference converts each
+ * weight tile with AscendAntiQuant<int8_t, TransT, isTranspose> before the cube unit reads it,
+ * impl/adv_api/detail/matmul/stage/copy_cube_in/antiquant/antiquant_processor_using_ub.h:86-137).
+ *   W[n, k] = AscendAntiQuant(B_nk[n, k]) = scale[n] * (B + offset[n]) in aT arithmetic (half: half add, half multiply;
+ *   bfloat16: fp32 intermediates) -- offset / scale [N] tensors of aT, or (scale NULL) the two scalars;
+ *   C = A . W^T with fp32 accumulation, cast to cT.
+ * Two launches: the dequantised weight goes through `workspace` (N * K * 2 bytes, 16-byte aligned) and stays in L2 for
+ * the matmul when it fits.  K % 32 == 0.
+ */
+ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk, const void* offset,
+                              const void* scale, float offsetScalar, float scaleScalar, int M, int N, int K, int ldc,
+                              void* workspace, size_t workspaceBytes, void* stream);
+size_t ascq_matmul_w8a16_workspace_size(int N, int K);
+
+/*
  * The grouped MX matmul with 8-bit operands (fp8_e4m3fn / fp8_e5m2 in any combination, one E8M0 scale per 32 elements
  * of K): MatmulWithScalePolicy on fp8 types (impl/adv_api/detail/matmul/mx_matmul_impl.h:29-181, sample
  * examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx, basic-API form .../03_matrix_compute/mmad_mx).

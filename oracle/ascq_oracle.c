@@ -732,6 +732,29 @@ int ascq_oracle_group_matmul_mxfp4(uint16_t* C, float* C_f32, const uint8_t* A, 
     return OR_OK;
 }
 
+/* half / bfloat16 matmul: products exact, sum in double (the samples' goldens use fp64 / fp32 numpy matmuls), one
+ * cast to the output type.  A [M,K], B [N,K] as 16-bit patterns; returns fp32 and, when C16 is given, the cT cast.
+ * The weight-only-quantised matmul of the reference (Matmul::SetAntiQuantVector, antiquant_processor_using_ub.h:86-137)
+ * is this matmul applied to AscendAntiQuant's output. */
+int ascq_oracle_matmul_f16(uint16_t* C16, float* C_f32, int cT, const uint16_t* A, const uint16_t* B, int abT, int M, int N, int K)
+{
+    if (!A || !B || M < 0 || N < 0 || K < 0) return OR_INVALID;
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            double acc = 0.0;
+            for (int k = 0; k < K; ++k) {
+                const uint16_t a = A[(size_t)m * K + k], b = B[(size_t)n * K + k];
+                const double af = abT == DT_BF16 ? (double)orc_bf16_to_f32(a) : (double)orc_f16_to_f32(a);
+                const double bf = abT == DT_BF16 ? (double)orc_bf16_to_f32(b) : (double)orc_f16_to_f32(b);
+                acc += af * bf;
+            }
+            if (C_f32) C_f32[(size_t)m * N + n] = (float)acc;
+            if (C16) C16[(size_t)m * N + n] = cT == DT_BF16 ? orc_f32_to_bf16_sat((float)acc) : f64_to_f16_ieee((double)(float)acc);
+        }
+    return OR_OK;
+}
+
 /* MX matmul with 8-bit operands (fp8_e4m3fn / fp8_e5m2, one E8M0 scale per 32 elements of K), grouped like the fp4
  * one.  Golden formula: examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py:52-66 and
  * examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/mmad_mx/scripts/gen_data.py (mx_decompress, fp64 matmul,

@@ -233,6 +233,30 @@ def group_matmul_mxfp4(A, sA, B, sB, groupList, K, N, want_f32=False):
     return (Cb, Cf) if want_f32 else Cb
 
 
+def matmul_f16(A, B_nk, abT, cT=F32):
+    """A [M, K], B_nk [N, K] as float16 arrays or bf16 bit patterns (uint16); returns (cT cast as uint16 bits or None, fp32)."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    Cf = np.zeros((M, N), np.float32)
+    C16 = np.zeros((M, N), np.uint16) if cT != F32 else None
+    _check(lib().ascq_oracle_matmul_f16(_p(C16), _p(Cf), cT, _p(np.ascontiguousarray(A).view(np.uint16)),
+                                        _p(np.ascontiguousarray(B_nk).view(np.uint16)), abT, M, N, K))
+    return C16, Cf
+
+
+def matmul_w8a16(A, abT, B_nk, offset, scale, cT=F32):
+    """Weight-only-quantised matmul: AscendAntiQuant<int8, abT, isTranspose=true> on B_nk [N, K] (per-channel tensors
+    [N] or two floats), then the half / bfloat16 matmul."""
+    N, K = B_nk.shape
+    if isinstance(scale, np.ndarray):
+        W = ascend_antiquant(B_nk, I8, abT, policy=PER_CHANNEL, m=N, n=K, scale=scale, offset=offset, scaleT=abT,
+                             isTranspose=True)
+    else:
+        W = ascend_antiquant(B_nk, I8, abT, policy=PER_TENSOR, m=N, n=K, scaleScalar=float(scale), offsetScalar=float(offset),
+                             scaleT=abT, isTranspose=True, hasOffset=True)
+    return matmul_f16(A, W, abT, cT), W
+
+
 def group_matmul_mxfp8(A, aFmt, sA, B, bFmt, sB, groupList, K, N):
     """A [sumM, K] u8 (fp8 codes), sA [sumM, K/32] u8, B [G, N, K] u8, sB [G, N, K/32] u8; aFmt/bFmt 0 = e4m3fn, 1 = e5m2.
     Returns (bf16 bits, fp32)."""
