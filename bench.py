@@ -6,7 +6,7 @@
 Prints ONE JSON line (rank 0).  A "step" is one pass of the headline workload over its synthetic input:
 the operator call(s) through the C ABI with inputs resident in HBM (``value``), and the same call with
 pinned-host inputs and a device->host read of the result inside the timed region (``e2e``).  The other
-BASELINE configurations are measured in the same run and reported under ``workloads``.  Timing is by CUDA
+benchmark configurations are measured in the same run and reported under ``workloads``.  Timing is by CUDA
 events on the launching stream; buffers rotate over a set larger than L2 so every step reads DRAM.
 ``--impl reference`` times the CPU restatement of the reference operators (oracle/, all host threads) on a
 bounded sample of the same workload; the reference's own CPU-debug build needs the closed tikicpulib and
@@ -42,7 +42,7 @@ def measured_peaks():
 
 
 # ------------------------------------------------------------------------------------------------
-# Synthetic inputs (numpy, seeded): the five BASELINE configurations.
+# Synthetic inputs (numpy, seeded): the five benchmark configurations.
 # ------------------------------------------------------------------------------------------------
 def f32_to_bf16_bits(x):
     u = np.ascontiguousarray(x, np.float32).view(np.uint32)

@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this directory from the reference's own example generators.
 
-Run in a checkout that has the asc-devkit tree available (default /root/reference):
+Run in a checkout that has the asc-devkit tree available (pass its path with --reference):
 
     python tests/golden/make_golden.py [--reference /path/to/asc-devkit]
 
@@ -62,8 +62,10 @@ CASES = [
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("ASC_DEVKIT_ROOT"), help="root of the asc-devkit tree (or set ASC_DEVKIT_ROOT)")
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("give --reference /path/to/asc-devkit or set ASC_DEVKIT_ROOT")
     for name, script, argv, seed, files in CASES:
         path = os.path.join(args.reference, script)
         with tempfile.TemporaryDirectory() as tmp:

@@ -37,7 +37,7 @@ def both(src, srcT, dstT, what, **kw):
 
 
 def test_cfg2_full_size():
-    # BASELINE config 2: int8 [4096, 11008], bf16 scale ~ U(0.001, 0.02), bf16 offset ~ U(-4, 4) -> bf16
+    # benchmark config 2: int8 [4096, 11008], bf16 scale ~ U(0.001, 0.02), bf16 offset ~ U(-4, 4) -> bf16
     rng = np.random.default_rng(20251125 + 2)
     K, N = 4096, 11008
     w = rng.integers(-127, 128, (K, N)).astype(np.int8)

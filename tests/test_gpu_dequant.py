@@ -36,7 +36,7 @@ def run_dequant(src, srcT, dstT, **kw):
 
 
 def test_cfg3_full_size():
-    # BASELINE config 3: int32 [2048, 4096] in [-2^20, 2^20], per-channel fp32 x per-token fp32 -> bf16
+    # benchmark config 3: int32 [2048, 4096] in [-2^20, 2^20], per-channel fp32 x per-token fp32 -> bf16
     rng = np.random.default_rng(20251125 + 3)
     M, N = 2048, 4096
     acc = rng.integers(-2 ** 20, 2 ** 20 + 1, (M, N)).astype(np.int32)

@@ -150,7 +150,7 @@ def test_invalid_arguments():
 
 
 def test_cfg5_full_size():
-    # BASELINE config 5: G=16, 16384 tokens split by a seeded multinomial, K=7168, N=2048
+    # benchmark config 5: G=16, 16384 tokens split by a seeded multinomial, K=7168, N=2048
     G, K, N, total = 16, 7168, 2048, 16384
     rng = np.random.default_rng(20251125 + 5)
     groups = rng.multinomial(total, np.full(G, 1.0 / G)).astype(np.int64)

@@ -79,7 +79,7 @@ def test_invalid_arguments():
 
 
 def test_cfg4_full_size_exact():
-    # BASELINE config 4 at full size; the integer reference is computed on the GPU in fp64-free exact arithmetic:
+    # benchmark config 4 at full size; the integer reference is computed on the GPU in fp64-free exact arithmetic:
     # int8 products summed in float32 blocks of K=256 stay below 2^24 and are therefore exact.
     M = N = K = 4096
     A, B, sA, sB, bias = make_case(M, N, K, 20251125 + 4)

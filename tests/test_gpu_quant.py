@@ -38,7 +38,7 @@ def run_quant(src, srcT, **kw):
 
 
 def test_cfg1_per_tensor_full_size():
-    # BASELINE config 1: fp16 [256, 4096] ~ N(0,1), scale 64, offset 0
+    # benchmark config 1: fp16 [256, 4096] ~ N(0,1), scale 64, offset 0
     x = np.random.default_rng(20251125 + 1).standard_normal((256, 4096)).astype(np.float16)
     want = O.ascend_quant(x, O.F16, policy=O.PER_TENSOR, scaleScalar=64.0, offsetScalar=0.0)
     got = run_quant(x, O.F16, policy=O.PER_TENSOR, scaleScalar=64.0, offsetScalar=0.0)

@@ -262,7 +262,7 @@ def test_tiling_known_answers_oracle():
                          O.antiquant_tmp_size, O.antiquant_factor)
 
 
-# ---- independent numpy / ml_dtypes restatement of the BASELINE configurations (reduced sizes) ------
+# ---- independent numpy / ml_dtypes restatement of the benchmark configurations (reduced sizes) ------
 def test_cfg1_per_tensor_fp16_formula():
     x = np.random.default_rng(20251126).standard_normal((64, 4096)).astype(np.float16)
     out = O.ascend_quant(x, O.F16, policy=O.PER_TENSOR, scaleScalar=64.0, offsetScalar=0.0)
