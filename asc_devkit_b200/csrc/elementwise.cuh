@@ -197,11 +197,19 @@ __device__ __forceinline__ void apply_op(CT (&x)[VEC], const CT (&s)[SV], const 
 
 // Tuning constants (measured on config 2/3-sized and larger inputs): four resident CTAs per SM (at most 64
 // registers per thread), two row batches in flight per thread, about sixteen CTAs per SM in the grid.
+// Per-operator tuning: row batches in flight per thread and CTAs per SM in the grid.  The dequant operator reads
+// 4-byte elements (two 16-byte loads per vector already) and does best with one batch and a finer grid.
+#define ASCQ_EW_U_DEFAULT 2
+template <int OP> struct EwTune {
+    static constexpr int kRowsInFlight = ASCQ_EW_U_DEFAULT;
+    static constexpr uint32_t kCtasPerSm = 16u;
+};
+template <> struct EwTune<1 /* kOpDequant */> {
+    static constexpr int kRowsInFlight = 1;
+    static constexpr uint32_t kCtasPerSm = 32u;
+};
 #ifndef ASCQ_EW_MINB
 #define ASCQ_EW_MINB 4
-#endif
-#ifndef ASCQ_EW_U
-#define ASCQ_EW_U 2
 #endif
 #ifndef ASCQ_EW_TARGET
 #define ASCQ_EW_TARGET 16u
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
 
     // Rows are taken U at a time: all U source vectors (and the per-row scalars) are requested before
     // the first result is stored, so every thread keeps U vector loads in flight.
-    constexpr int U = (SMODE == kSRowVec) ? 1 : ASCQ_EW_U;
+    constexpr int U = (SMODE == kSRowVec) ? 1 : EwTune<OP>::kRowsInFlight;
     const uint32_t gy = gridDim.y;
     for (uint32_t r0 = blockIdx.y; r0 < a.rows; r0 += gy * U) {
         Pack<Src, VEC> in[U];
@@ -287,7 +295,7 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
 }
 
 // Grid shape: x covers the column vectors, y strides the rows; about ASCQ_EW_TARGET 256-thread CTAs per SM.
-inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* block)
+inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* block, uint32_t ctasPerSm = ASCQ_EW_TARGET)
 {
     const uint32_t nvec = (cols + vec - 1) / vec;
     auto waste = [nvec](uint32_t b) { return (nvec + b - 1) / b * b - nvec; };
@@ -296,7 +304,7 @@ inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* blo
         if (waste(cand) + nvec / 32 < waste(bx)) bx = cand;
     if (nvec < bx) bx = (nvec + 31) / 32 * 32;
     const uint32_t gx = (nvec + bx - 1) / bx;
-    const uint32_t target = 148u * ASCQ_EW_TARGET * 256u / bx;  // CTAs
+    const uint32_t target = 148u * ctasPerSm * 256u / bx;  // CTAs
     uint32_t gy = (target + gx - 1) / gx;
     if (gy > rows) gy = rows;
     if (gy < 1) gy = 1;
@@ -312,7 +320,7 @@ ascq_status launch_ew_rows(const EwArgs& a, int smode, bool hasOff, bool hasTok,
 {
     if (a.rows == 0 || a.cols == 0) return ASCQ_OK;
     dim3 grid, block;
-    ew_grid(a.rows, a.cols, VecOf<Src, Dst>::value, &grid, &block);
+    ew_grid(a.rows, a.cols, VecOf<Src, Dst>::value, &grid, &block, EwTune<OP>::kCtasPerSm);
 #define ASCQ_EW_LAUNCH(SM, OFF, TOK) \
     ew_rows_kernel<OP, Src, Dst, Sc, CT, SM, OFF, TOK><<<grid, block, 0, stream>>>(a)
 #define ASCQ_EW_SMODE(OFF, TOK)                            \

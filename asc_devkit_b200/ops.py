@@ -42,8 +42,11 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream(stream: Optional[torch.cuda.Stream]):
-    s = torch.cuda.current_stream() if stream is None else stream
-    return C.c_void_p(s.cuda_stream)
+    """Raw cudaStream_t of ``stream`` or of torch's current stream (the raw-handle getter skips building a Stream
+    object: a few microseconds per call, which matters next to a 10 us kernel)."""
+    if stream is None:
+        return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
+    return stream.cuda_stream
 
 
 @dataclass
