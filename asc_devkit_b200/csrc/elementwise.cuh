@@ -43,6 +43,7 @@ struct EwArgs {
     SRef scale, offset;
     const float* tok;  // dequant only: optional fp32 per-row multiplier applied after the scale
     int roundMode;
+    int wide32;        // src / dst bases and row pitches are 32-byte aligned: 32-byte vectors move as one 256-bit access
 };
 
 template <int BYTES> struct Chunk;
@@ -64,6 +65,30 @@ template <typename T, int N, bool STREAM> __device__ __forceinline__ Pack<T, N> 
     for (int i = 0; i < BYTES / CB; ++i) o[i] = STREAM ? __ldcs(q + i) : __ldg(q + i);
     return r;
 }
+// 256-bit streaming accesses (sm_100): one instruction per 32-byte vector; the address must be 32-byte aligned.
+__device__ __forceinline__ void ld_cs_256(const void* p, uint32_t (&a)[8])
+{
+    asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_cs_256(void* p, const uint32_t (&a)[8])
+{
+    asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]),
+                 "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7])
+                 : "memory");
+}
+template <typename T, int N> __device__ __forceinline__ Pack<T, N> load_pack_wide(const T* p, bool wide)
+{
+    if constexpr (sizeof(T) * N == 32) {
+        if (wide) {
+            Pack<T, N> r;
+            ld_cs_256(p, *reinterpret_cast<uint32_t(*)[8]>(&r));
+            return r;
+        }
+    }
+    return load_pack<T, N, true>(p);
+}
 template <typename T, int N> __device__ __forceinline__ void store_pack(T* p, const Pack<T, N>& r)
 {
     constexpr int BYTES = sizeof(T) * N;
@@ -73,6 +98,17 @@ template <typename T, int N> __device__ __forceinline__ void store_pack(T* p, co
     const C* o = reinterpret_cast<const C*>(&r);
 #pragma unroll
     for (int i = 0; i < BYTES / CB; ++i) __stcs(q + i, o[i]);
+}
+
+template <typename T, int N> __device__ __forceinline__ void store_pack_wide(T* p, const Pack<T, N>& r, bool wide)
+{
+    if constexpr (sizeof(T) * N == 32) {
+        if (wide) {
+            st_cs_256(p, *reinterpret_cast<const uint32_t(*)[8]>(&r));
+            return;
+        }
+    }
+    store_pack<T, N>(p, r);
 }
 
 template <typename Src, typename Dst> struct VecOf {
@@ -203,10 +239,12 @@ __device__ __forceinline__ void apply_op(CT (&x)[VEC], const CT (&s)[SV], const 
 template <int OP> struct EwTune {
     static constexpr int kRowsInFlight = ASCQ_EW_U_DEFAULT;
     static constexpr uint32_t kCtasPerSm = 16u;
+    static constexpr bool kWide256 = false;  // 256-bit accesses measured no better (antiquant) or worse (quant)
 };
 template <> struct EwTune<1 /* kOpDequant */> {
     static constexpr int kRowsInFlight = 1;
     static constexpr uint32_t kCtasPerSm = 32u;
+    static constexpr bool kWide256 = true;   // its 32-byte source vectors move as one 256-bit load
 };
 #ifndef ASCQ_EW_MINB
 #define ASCQ_EW_MINB 4
@@ -256,7 +294,7 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
         for (int u = 0; u < U; ++u) {
             const uint32_t r = r0 + u * gy;
             if (r < a.rows) {
-                in[u] = load_pack<Src, VEC, true>(static_cast<const Src*>(a.src) + static_cast<size_t>(r) * a.srcStride + c0);
+                in[u] = load_pack_wide<Src, VEC>(static_cast<const Src*>(a.src) + static_cast<size_t>(r) * a.srcStride + c0, a.wide32 != 0);
                 if constexpr (SMODE == kSRowBcast) {
                     const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + sc_col;
                     srow[u] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.scale.p) + idx)));
@@ -289,7 +327,7 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
             apply_op<OP, CT, VEC, SV, HAS_OFF, HAS_TOK>(x, s, o, HAS_TOK ? tok[u] : 1.0f);
             Pack<Dst, VEC> out;
             pack_dst<Dst, CT, VEC>(x, out, a.roundMode);
-            store_pack<Dst, VEC>(static_cast<Dst*>(a.dst) + static_cast<size_t>(r) * a.dstStride + c0, out);
+            store_pack_wide<Dst, VEC>(static_cast<Dst*>(a.dst) + static_cast<size_t>(r) * a.dstStride + c0, out, a.wide32 != 0);
         }
     }
 }
@@ -321,8 +359,11 @@ ascq_status launch_ew_rows(const EwArgs& a, int smode, bool hasOff, bool hasTok,
     if (a.rows == 0 || a.cols == 0) return ASCQ_OK;
     dim3 grid, block;
     ew_grid(a.rows, a.cols, VecOf<Src, Dst>::value, &grid, &block, EwTune<OP>::kCtasPerSm);
+    EwArgs b = a;
+    b.wide32 = EwTune<OP>::kWide256 && ((reinterpret_cast<uintptr_t>(a.src) | reinterpret_cast<uintptr_t>(a.dst)) & 31u) == 0 &&
+               (static_cast<size_t>(a.srcStride) * sizeof(Src)) % 32 == 0 && (static_cast<size_t>(a.dstStride) * sizeof(Dst)) % 32 == 0;
 #define ASCQ_EW_LAUNCH(SM, OFF, TOK) \
-    ew_rows_kernel<OP, Src, Dst, Sc, CT, SM, OFF, TOK><<<grid, block, 0, stream>>>(a)
+    ew_rows_kernel<OP, Src, Dst, Sc, CT, SM, OFF, TOK><<<grid, block, 0, stream>>>(b)
 #define ASCQ_EW_SMODE(OFF, TOK)                            \
     switch (smode) {                                       \
         case kSScalar: ASCQ_EW_LAUNCH(kSScalar, OFF, TOK); break;     \
