@@ -56,6 +56,7 @@ template <int BN, bool PAIR> struct Cfg {
 
 struct Params {
     __nv_bfloat16* C[kMaxPeers];  // output buffers (own first); every one gets this launch's [M, N] block
+    int multicast;  // C[0] is a multicast address: one multimem store reaches every GPU's matrix
     int nPeers, colOffset, firstPeer;  // block goes to columns [colOffset, colOffset + N); stores start at buffer firstPeer
     const float* sA;
     const float* sB;
@@ -384,6 +385,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                             const int gm = m0 + q * 32 + h * 16 + rl;
                             if (gm < p.M) {
                                 const size_t off = static_cast<size_t>(gm) * p.ldc + p.colOffset + n + piece * 8;
+                                if (p.multicast) {
+                                    multimem_st_v4(p.C[0] + off, val);
+                                    continue;
+                                }
                                 for (int pi = 0; pi < p.nPeers; ++pi) {
                                     int b = p.firstPeer + pi;
                                     if (b >= p.nPeers) b -= p.nPeers;
@@ -482,7 +487,7 @@ struct FixpipeArgs {
 
 ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
                      const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc, int32_t* accDump,
-                     cudaStream_t st, const FixpipeArgs* fix = nullptr)
+                     cudaStream_t st, const FixpipeArgs* fix = nullptr, bool multicast = false)
 {
     const int epi = fix ? (fix->floatKind ? kEpiFloat : kEpiFixpipe) : kEpiDequant;
     const int elemBytes = (epi == kEpiFloat) ? 2 : 1;
@@ -503,6 +508,7 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         p.C[i] = haveC ? static_cast<__nv_bfloat16*>(outBufs[i]) : nullptr;
         if (haveC && !p.C[i]) return fail(ASCQ_ERR_INVALID_ARG, "output buffer %d is NULL", i);
     }
+    p.multicast = multicast ? 1 : 0;
     p.firstPeer = (p.nPeers > 0) ? ((firstBuf % p.nPeers) + p.nPeers) % p.nPeers : 0;
     p.colOffset = colOffset;
     p.sA = sA_m;
@@ -590,6 +596,19 @@ extern "C" ascq_status ascq_matmul_status(void* stream)
         return fail(ASCQ_ERR_TIMEOUT, "a bounded wait inside the W8A8 matmul kernel expired (status %d)", v);
     }
     return mxfp4_read_status(st);
+}
+
+extern "C" ascq_status ascq_matmul_w8a8_multicast(void* C_multicast, int colOffset, int ldc, const int8_t* A, const int8_t* B_nk,
+                                                  const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K,
+                                                  void* stream)
+{
+    if (!C_multicast) return fail(ASCQ_ERR_INVALID_ARG, "the multicast address must not be NULL");
+    // only whole 16-byte pieces can be multicast: the ragged-edge path of the epilogue writes single elements
+    if (N % 64 != 0 || ldc % 8 != 0 || colOffset % 8 != 0 || (reinterpret_cast<uintptr_t>(C_multicast) & 15u))
+        return fail(ASCQ_ERR_ALIGNMENT, "multicast output needs N %% 64 == 0, ldc and colOffset multiples of 8, a 16-byte aligned base");
+    void* bufs[1] = {C_multicast};
+    return run_w8a8(bufs, 1, 0, colOffset, A, B_nk, sA_m, sB_n, bias_bf16, M, N, K, ldc, nullptr, static_cast<cudaStream_t>(stream),
+                    nullptr, true);
 }
 
 // ---- int8 matmul with the reference's fixpipe quantisation of the result (fp16 output) ----------------------------

@@ -300,6 +300,14 @@ __host__ __device__ constexpr uint32_t idesc_i8(uint32_t M, uint32_t N)
 {
     return (2u << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);  // int8 x int8 -> int32
 }
+// One 16-byte store to a multicast address: NVSwitch delivers it to the memory of every GPU bound to the multicast
+// object, so an all-gather costs each GPU one copy of its own data on its links instead of one per peer.
+__device__ __forceinline__ void multimem_st_v4(void* mcAddr, uint4 v)
+{
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mcAddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
 // kind::f16: D format 1 = f32; A/B format 0 = half, 1 = bfloat16
 __host__ __device__ constexpr uint32_t idesc_f16(uint32_t M, uint32_t N, uint32_t abFmt)
 {

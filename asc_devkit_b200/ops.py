@@ -353,6 +353,16 @@ def MatmulW8A8Scatter(buffer_ptrs, first_buf: int, col_offset: int, ldc: int, A:
                                              _ptr(scaleA), _ptr(scaleB), _ptr(bias), M, N, K, _stream(stream)))
 
 
+def MatmulW8A8Multicast(multicast_ptr: int, col_offset: int, ldc: int, A: torch.Tensor, B_nk: torch.Tensor, scaleA=None,
+                        scaleB=None, bias=None, stream=None):
+    """W8A8 matmul whose epilogue writes its column block to the multicast address of the [M, ldc] bf16 output: one
+    multimem store per 16 bytes reaches every GPU's matrix (``ascq_matmul_w8a8_multicast``)."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    L.check(L.lib().ascq_matmul_w8a8_multicast(C.c_void_p(int(multicast_ptr)), col_offset, ldc, _ptr(A), _ptr(B_nk), _ptr(scaleA),
+                                               _ptr(scaleB), _ptr(bias), M, N, K, _stream(stream)))
+
+
 def MatmulStatus(stream=None):
     """Synchronise and raise AscqError(ERR_TIMEOUT) if a matmul kernel gave up a bounded wait."""
     L.check(L.lib().ascq_matmul_status(_stream(stream)))

@@ -292,6 +292,7 @@ class W8A8Cfg4(Workload):
         # Fused reassembly: every rank's epilogue stores its column block into every rank's [M, N] matrix over NVLink
         # (peer-mapped symmetric memory); a device-side barrier ends the step.  Falls back to an NCCL all-gather.
         self.fused = None
+        self.mc = None
         if world > 1:
             try:
                 import torch.distributed._symmetric_memory as symm
@@ -301,6 +302,10 @@ class W8A8Cfg4(Workload):
                     self.hdl.append(symm.rendezvous(t, dist.group.WORLD))
                     self.full.append(t)
                 self.fused = True
+                # ASCQ_BENCH_REASSEMBLY=multicast: one multimem store per piece through NVSwitch multicast instead of one
+                # store per peer (measured slower at two ranks, where the local copy then crosses NVLink too)
+                mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in self.hdl]
+                self.mc = mc if all(mc) and os.environ.get("ASCQ_BENCH_REASSEMBLY", "peer") == "multicast" else None
             except Exception as e:  # noqa: BLE001
                 self.fused = False
                 self.fused_error = repr(e)[:200]
@@ -314,8 +319,12 @@ class W8A8Cfg4(Workload):
             self.ops.MatmulW8A8(self.C[s], self.A[s], self.B[s], self.sA, self.sB, self.bias)
         elif self.fused:
             f = i % 2
-            self.ops.MatmulW8A8Scatter(self.hdl[f].buffer_ptrs, self.rank + 1, self.rank * self.nl, self.N, self.A[s], self.B[s],
-                                       self.sA, self.sB, self.bias)
+            if self.mc:
+                self.ops.MatmulW8A8Multicast(self.mc[f], self.rank * self.nl, self.N, self.A[s], self.B[s], self.sA, self.sB,
+                                             self.bias)
+            else:
+                self.ops.MatmulW8A8Scatter(self.hdl[f].buffer_ptrs, self.rank + 1, self.rank * self.nl, self.N, self.A[s],
+                                           self.B[s], self.sA, self.sB, self.bias)
             self.hdl[f].barrier(channel=0)
         else:
             self.nccl_step(i)
@@ -358,9 +367,21 @@ class W8A8Cfg4(Workload):
         want = O.matmul_w8a8(np.ascontiguousarray(self.host["A"][:rows]), np.ascontiguousarray(self.host["B"][n0:n0 + self.nl]),
                              self.host["sA"][:rows].copy(), self.host["sB"][n0:n0 + self.nl].copy(),
                              self.host["bias"][n0:n0 + self.nl].copy())
+        self.gemm_only_step(0)
         got = self.C[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
         self.ops.MatmulStatus()
-        return bool(np.array_equal(got, want))
+        ok = bool(np.array_equal(got, want))
+        if self.world > 1 and self.fused:
+            # the reassembled matrix on this rank: every rank's column block must have arrived with the oracle's bits
+            self.step(0)
+            self.torch.cuda.synchronize()
+            self.hdl[0].barrier(channel=0)
+            self.torch.cuda.synchronize()
+            whole = O.matmul_w8a8(np.ascontiguousarray(self.host["A"][:rows]), self.host["B"], self.host["sA"][:rows].copy(),
+                                  self.host["sB"], self.host["bias"])
+            full = self.full[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
+            ok = ok and bool(np.array_equal(full, whole))
+        return ok
 
 
 class Mxfp4Cfg5(Workload):
@@ -663,7 +684,8 @@ def run_ours(args):
             peak = (2.0 if int8 else 4.0) * peaks["bf16_tflops"]
             extra = {}
             if world > 1:
-                extra["reassembly"] = ("fused epilogue peer stores + symmetric-memory barrier" if wl.fused
+                extra["reassembly"] = (("fused epilogue multimem stores through NVSwitch multicast + symmetric-memory barrier"
+                                        if getattr(wl, "mc", None) else "fused epilogue peer stores + symmetric-memory barrier") if wl.fused
                                        else "NCCL all-gather (symmetric memory unavailable: %s)" % getattr(wl, "fused_error", ""))
                 nsec = time_steps(torch, wl.nccl_step, args.steps, args.warmup, dist)
                 extra["nccl_allgather_variant"] = work / (nsec / args.steps) / 1e12

@@ -377,6 +377,17 @@ ascq_status ascq_group_matmul_mxfp4_scatter(void* const* C_bufs, int nBufs, int 
                                             size_t workspaceBytes, void* stream);
 
 /*
+ * The same fused all-gather through NVSwitch multicast: C_multicast is the multicast address of the [M, ldc] bf16 output
+ * (every GPU's matrix bound to one multicast object, e.g. torch symmetric memory's `multicast_ptr`); each 16-byte piece of
+ * this launch's column block leaves the SM as ONE multimem.st and the switch writes it into every GPU's matrix, this
+ * GPU's included.  Each GPU's links then carry its own block once instead of once per peer.  No reference counterpart.
+ * N % 64 == 0, ldc % 8 == 0, colOffset % 8 == 0.  The caller orders the step with a barrier as for the scatter form.
+ */
+ascq_status ascq_matmul_w8a8_multicast(void* C_multicast, int colOffset, int ldc, const int8_t* A, const int8_t* B_nk,
+                                       const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K,
+                                       void* stream);
+
+/*
  * Synchronises `stream`, then reads and clears the status word the matmul kernels keep on the
  * current device.  ASCQ_ERR_TIMEOUT when a kernel gave up a bounded wait (its output is then
  * undefined); no counterpart in the reference, whose kernels cannot report.
