@@ -756,6 +756,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if "TORCHELASTIC_RUN_ID" in os.environ and os.environ.get("OMP_NUM_THREADS") == "1":
+        del os.environ["OMP_NUM_THREADS"]   # torchrun's default of one thread per rank; this arm runs alone on all host cores
     from oracle import oracle as O
     nm = args.workload if args.workload != "all" else HEADLINE
     unit = "GB/s"
