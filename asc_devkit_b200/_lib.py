@@ -76,6 +76,9 @@ SIGNATURES = {
     "ascq_group_matmul_mxfp4_scatter": (_i, [C.POINTER(_vp), _i, _i, _P64, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp8": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp8_workspace_size": (C.c_size_t, [C.c_int64, _i, _i, _i]),
+    "ascq_group_matmul_mxfp4_packed_scale_b_size": (C.c_size_t, [_i, _i, _i]),
+    "ascq_group_matmul_mxfp4_pack_scale_b": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "ascq_group_matmul_mxfp4_prepacked": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp4_workspace_size": (C.c_size_t, [C.c_int64, _i, _i, _i]),
     "ascq_group_matmul_mxfp4_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp]),
     "ascq_group_matmul_mxfp4_noalloc_max_scratch": (C.c_size_t, []),

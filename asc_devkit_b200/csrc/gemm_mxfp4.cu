@@ -606,16 +606,19 @@ struct Mx8Args {  // 8-bit operands (kind::mxf8f6f4): formats 0 = E4M3, 1 = E5M2
 static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, const int64_t* outRowStart_host,
                              const uint8_t* A_fp4, const uint8_t* sA_e8m0, const uint8_t* B_fp4, const uint8_t* sB_e8m0,
                              const int64_t* groupList_host, int G, int K, int N, void* workspace, size_t workspaceBytes,
-                             void* stream, const Mx8Args* mx8 = nullptr)
+                             void* stream, const Mx8Args* mx8 = nullptr, const uint8_t* sB_packed = nullptr)
 {
+    // sB_packed: the scales of B already in the packed order (weights are static: ascq_group_matmul_mxfp4_pack_scale_b once)
     const int sfc = mx8 ? 1 : 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!outBufs || nBufs < 1 || nBufs > kMaxPeers)
         return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
     for (int i = 0; i < nBufs; ++i)
         if (!outBufs[i]) return fail(ASCQ_ERR_INVALID_ARG, "output buffer %d is NULL", i);
-    if (!A_fp4 || !sA_e8m0 || !B_fp4 || !sB_e8m0 || !groupList_host)
+    if (!A_fp4 || !sA_e8m0 || !B_fp4 || (!sB_e8m0 && !sB_packed) || !groupList_host)
         return fail(ASCQ_ERR_INVALID_ARG, "C, A, sA, B, sB and groupList must not be NULL");
+    if (sB_packed && (reinterpret_cast<uintptr_t>(sB_packed) & 255u))
+        return fail(ASCQ_ERR_ALIGNMENT, "packed scales must be 256-byte aligned");
     if (G <= 0 || N <= 0 || K <= 0) return fail(ASCQ_ERR_INVALID_ARG, "G, N, K must be positive");
     if (K % 128 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of 128", K);
     if (!aligned16(A_fp4) || !aligned16(B_fp4)) return fail(ASCQ_ERR_ALIGNMENT, "A and B must be 16-byte aligned");
@@ -692,7 +695,9 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
     const int kChunks = L.kBlocks * sfc;
     const int sfRowBytes = K / 32;
     {
-        const dim3 grid(static_cast<unsigned>(numTilesM + G * L.nTiles128), static_cast<unsigned>((kChunks + kSlab - 1) / kSlab));
+        // with prepacked scales of B only the A tiles are repacked
+        const dim3 grid(static_cast<unsigned>(numTilesM + (sB_packed ? 0 : G * L.nTiles128)),
+                        static_cast<unsigned>((kChunks + kSlab - 1) / kSlab));
         repack_sf_kernel<<<grid, 256, 0, st>>>(ws + L.sfaOff, ws + L.sfbOff, sA_e8m0, sB_e8m0,
                                                reinterpret_cast<TileInfo*>(ws + L.tileOff), gr, inlineGroups ? G : 0,
                                                static_cast<int>(step), numTilesM, kChunks, K / 128, sfRowBytes, N, L.nTiles128, sumM);
@@ -708,7 +713,7 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
     if (const char* e = getenv("ASCQ_MXFP4_STORE")) p.wideStores = !strcmp(e, "wide") ? 1 : (!strcmp(e, "narrow") && nBufs == 1 ? 0 : p.wideStores);
     p.tiles = reinterpret_cast<const TileInfo*>(ws + L.tileOff);
     p.sfaPacked = ws + L.sfaOff;
-    p.sfbPacked = ws + L.sfbOff;
+    p.sfbPacked = sB_packed ? sB_packed : ws + L.sfbOff;
     p.numTilesM = pair ? numTilesM / 2 : numTilesM;
     p.N = N; p.K = K; p.kBlocks = L.kBlocks; p.nTilesPerGroup128 = L.nTiles128;
 
@@ -723,7 +728,7 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
     // can be counted on the leader's barrier)
     rc = make_tmap_kib_rows(&tsa, ws + L.sfaOff, static_cast<uint64_t>(numTilesM) * L.kBlocks, sfc * kChunkBytes);
     if (rc != ASCQ_OK) return rc;
-    rc = make_tmap_kib_rows(&tsb, ws + L.sfbOff, static_cast<uint64_t>(G) * L.nTiles128 * L.kBlocks, sfc * kChunkBytes);
+    rc = make_tmap_kib_rows(&tsb, p.sfbPacked, static_cast<uint64_t>(G) * L.nTiles128 * L.kBlocks, sfc * kChunkBytes);
     if (rc != ASCQ_OK) return rc;
     if (mx8) {
         if (pair) return launch<256, true, 1>(ta, tb, tsa, tsb, p, st);
@@ -741,6 +746,43 @@ extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp
     void* bufs[1] = {C_bf16};
     return run_mxfp4(bufs, 1, 0, nullptr, A_fp4, sA_e8m0, B_fp4, sB_e8m0, groupList_host, G, K, N, workspace, workspaceBytes,
                      stream);
+}
+
+// ---- static weights: pack the scales of B once --------------------------------------------------------------------
+extern "C" size_t ascq_group_matmul_mxfp4_packed_scale_b_size(int G, int K, int N)
+{
+    if (G <= 0 || K <= 0 || N <= 0) return 0;
+    const Layout L = make_layout(0, G, K, N);
+    return align_up(static_cast<size_t>(G) * L.nTiles128 * L.kBlocks * 2 * kChunkBytes, 256);
+}
+
+extern "C" ascq_status ascq_group_matmul_mxfp4_pack_scale_b(uint8_t* sB_packed, const uint8_t* sB_e8m0, int G, int K, int N,
+                                                            void* stream)
+{
+    if (!sB_packed || !sB_e8m0) return fail(ASCQ_ERR_INVALID_ARG, "sB_packed and sB must not be NULL");
+    if (G <= 0 || N <= 0 || K <= 0) return fail(ASCQ_ERR_INVALID_ARG, "G, N, K must be positive");
+    if (K % 128 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of 128", K);
+    if ((reinterpret_cast<uintptr_t>(sB_packed) & 255u) || (reinterpret_cast<uintptr_t>(sB_e8m0) & 3u))
+        return fail(ASCQ_ERR_ALIGNMENT, "sB_packed must be 256-byte aligned, sB 4-byte aligned");
+    const Layout L = make_layout(0, G, K, N);
+    const int kChunks = L.kBlocks * 2;
+    const dim3 grid(static_cast<unsigned>(G * L.nTiles128), static_cast<unsigned>((kChunks + kSlab - 1) / kSlab));
+    const GroupRows none{};
+    repack_sf_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(nullptr, sB_packed, nullptr, sB_e8m0, nullptr, none, 0, 128, 0,
+                                                                          kChunks, K / 128, K / 32, N, L.nTiles128, 0);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}
+
+extern "C" ascq_status ascq_group_matmul_mxfp4_prepacked(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
+                                                         const uint8_t* B_fp4, const uint8_t* sB_packed,
+                                                         const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                                         size_t workspaceBytes, void* stream)
+{
+    if (!C_bf16 || !sB_packed) return fail(ASCQ_ERR_INVALID_ARG, "C, A, sA, B, sB and groupList must not be NULL");
+    void* bufs[1] = {C_bf16};
+    return run_mxfp4(bufs, 1, 0, nullptr, A_fp4, sA_e8m0, B_fp4, nullptr, groupList_host, G, K, N, workspace, workspaceBytes,
+                     stream, nullptr, sB_packed);
 }
 
 extern "C" ascq_status ascq_group_matmul_mxfp4_scatter(void* const* C_bufs, int nBufs, int firstBuf,

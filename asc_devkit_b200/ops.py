@@ -299,6 +299,27 @@ def GroupMatmulMxfp4(C: torch.Tensor, A: torch.Tensor, scaleA: torch.Tensor, B: 
     return C
 
 
+def GroupMatmulMxfp4PackScaleB(scaleB: torch.Tensor, K: int, N: int, stream=None) -> torch.Tensor:
+    """Packs the scales of static weights once (``ascq_group_matmul_mxfp4_pack_scale_b``); returns the packed buffer."""
+    G = scaleB.shape[0]
+    out = torch.empty(int(L.lib().ascq_group_matmul_mxfp4_packed_scale_b_size(G, K, N)), dtype=torch.uint8, device=scaleB.device)
+    L.check(L.lib().ascq_group_matmul_mxfp4_pack_scale_b(_ptr(out), _ptr(scaleB), G, K, N, _stream(stream)))
+    return out
+
+
+def GroupMatmulMxfp4Prepacked(C: torch.Tensor, A: torch.Tensor, scaleA: torch.Tensor, B: torch.Tensor, scaleB_packed: torch.Tensor,
+                              groupList, K: int, N: int, workspace: Optional[torch.Tensor] = None, stream=None):
+    """``GroupMatmulMxfp4`` with the scales of B already packed by ``GroupMatmulMxfp4PackScaleB``."""
+    gl = (C_int64 * len(groupList))(*[int(v) for v in groupList])
+    G = len(groupList)
+    need = GroupMatmulMxfp4Workspace(int(sum(int(v) for v in groupList)), G, K, N)
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=C.device)
+    L.check(L.lib().ascq_group_matmul_mxfp4_prepacked(_ptr(C), _ptr(A), _ptr(scaleA), _ptr(B), _ptr(scaleB_packed), gl, G, K, N,
+                                                      _ptr(workspace), workspace.numel(), _stream(stream)))
+    return C
+
+
 def GroupMatmulMxfp8(C: torch.Tensor, A: torch.Tensor, a_dtype: int, scaleA: torch.Tensor, B: torch.Tensor, b_dtype: int,
                      scaleB: torch.Tensor, groupList, K: int, N: int, workspace: Optional[torch.Tensor] = None, stream=None):
     """MX matmul with fp8 operands (``ascq_group_matmul_mxfp8``).  A [sumM, K] uint8 (fp8 codes), B [G, N, K] uint8,

@@ -258,6 +258,19 @@ ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp4, const ui
 size_t ascq_group_matmul_mxfp4_workspace_size(int64_t sumM, int G, int K, int N);
 
 /*
+ * Static weights: the scales of B can be brought into the kernel's packed order once instead of on every call.
+ * ascq_group_matmul_mxfp4_pack_scale_b writes ascq_group_matmul_mxfp4_packed_scale_b_size(G, K, N) bytes (256-byte
+ * aligned); ascq_group_matmul_mxfp4_prepacked takes that buffer in place of sB_e8m0 and repacks only the scales of A
+ * (the reference likewise expects its weights in a prepared layout: README_en.md:64-67 of matmul_mxfp4_high_performance).
+ */
+size_t ascq_group_matmul_mxfp4_packed_scale_b_size(int G, int K, int N);
+ascq_status ascq_group_matmul_mxfp4_pack_scale_b(uint8_t* sB_packed, const uint8_t* sB_e8m0, int G, int K, int N, void* stream);
+ascq_status ascq_group_matmul_mxfp4_prepacked(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
+                                              const uint8_t* B_fp4, const uint8_t* sB_packed,
+                                              const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                              size_t workspaceBytes, void* stream);
+
+/*
  * The same grouped matmul for callers that cannot hand over scratch memory.  It has no counterpart in
  * the reference.  Some hosts of this library must not create device allocations of their own: an
  * inference server that has given all of HBM to its own memory pool at start-up (a cudaMalloc from a

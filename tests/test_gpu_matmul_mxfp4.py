@@ -73,6 +73,19 @@ def test_both_tile_shapes_give_the_same_bits(tile, monkeypatch):
     check_close(run(A, sA, B, sB, groups, K, N), want_f32, tile)
 
 
+def test_prepacked_weight_scales_give_the_same_bits():
+    groups, N, K = [300, 0, 129, 64], 512, 1024
+    A, sA, B, sB = make_case(groups, N, K, 41)
+    want = run(A, sA, B, sB, groups, K, N)
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    packed = ops.GroupMatmulMxfp4PackScaleB(t(sB), K, N)
+    C = torch.full((sum(groups), N), -1.0, dtype=torch.bfloat16, device=DEV)
+    for _ in range(2):   # the packed buffer is reused across calls
+        ops.GroupMatmulMxfp4Prepacked(C, t(A), t(sA), t(B), packed, groups, K, N)
+    ops.MatmulStatus()
+    assert_bits_equal(C.view(torch.int16).cpu().numpy().view(np.uint16), want, "prepacked")
+
+
 def test_scatter_writes_every_buffer_at_the_given_rows():
     """The fused reassembly of a group-parallel layout, on one GPU: three output matrices stand for this GPU's and two
     peers'; the groups computed here are placed at their rows of the full output, other rows stay untouched."""
