@@ -531,8 +531,8 @@ WORKLOADS = {"w8a8_cfg4": W8A8Cfg4, "mxfp4_cfg5": Mxfp4Cfg5, "antiquant_cfg2": A
 HEADLINE = "w8a8_cfg4"
 # DRAM bytes read + written by the dominant kernel of one step at full size on one GPU, from the ncu captures
 # summarised in profiles/<workload>_ncu_counters.md (outputs that stay in the 126 MB L2 do not show up as DRAM writes).
-TRAFFIC_BYTES = {"w8a8_cfg4": 36.8e6, "mxfp4_cfg5": 234.5e6, "antiquant_cfg2": 79.4e6, "dequant_cfg3": 33.6e6,
-                 "quant_scaled": 364.1e6}
+TRAFFIC_BYTES = {"w8a8_cfg4": 35.2e6, "mxfp4_cfg5": 234.4e6, "antiquant_cfg2": 78.6e6, "dequant_cfg3": 33.6e6,
+                 "quant_scaled": 365.3e6}
 
 
 # ------------------------------------------------------------------------------------------------
