@@ -21,6 +21,7 @@
 
 #include "ascq_internal.h"
 #include "numerics.cuh"
+#include "elementwise.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.h"
 
@@ -41,12 +42,17 @@ __device__ int g_w8a8_status = 0;  // 0 ok, 1 = a bounded wait expired
 
 // PAIR: two CTAs of a cluster drive one tcgen05.mma.cta_group::2 on a 256 x BN tile; each CTA loads its 128 rows of A
 // and its half (BN/2 rows) of B, so every byte of B is fetched from L2 once per pair instead of once per CTA.
-template <int BN, bool PAIR> struct Cfg {
+// CONV (weight-only-quantised matmul): the stage also holds this CTA's int8 rows of B (64 bytes per row and k-block);
+// four converter warps turn them into the half / bfloat16 tile the MMAs read.
+constexpr int kConvWarps = 4;
+template <int BN, bool PAIR, bool CONV = false> struct Cfg {
     static constexpr int kBRows = PAIR ? BN / 2 : BN;          // rows of B this CTA loads
     static constexpr int kABytes = kBM * kBK;
     static constexpr int kBBytes = kBRows * kBK;
-    static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 x 48 KiB, or 6 x 32 KiB
+    static constexpr int kBqBytes = CONV ? kBRows * (kBK / 2) : 0;
+    static constexpr int kStageBytes = kABytes + kBBytes + kBqBytes;
+    static constexpr int kStages = CONV ? 4 : (192 * 1024) / kStageBytes;  // 4 x 48 KiB, or 6 x 32 KiB; CONV: 4 x 40 KiB
+    static constexpr int kThreadsCta = kThreads + (CONV ? 32 * kConvWarps : 0);
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
     static constexpr int kEpiBytes = 2 * 2 * BN * 4;  // per accumulator: sB[BN] and bias[BN] as fp32
     static constexpr int kOutBytes = kEpiWarps * 16 * kStagePitch;  // per epilogue warp: 16 rows x 64 bf16 columns
@@ -71,16 +77,39 @@ struct Params {
     // kEpiFloat: operand format (0 = half, 1 = bfloat16) and output type (0 = half, 1 = bfloat16, 2 = float)
     uint32_t abFmt;
     int outKind;
+    // CONV: AscendAntiQuant operands of the int8 weight: per-row (of B_nk) tensors of the operand type, or two scalars
+    const void* aqScale;
+    const void* aqOffset;
+    float aqScaleScalar, aqOffsetScalar;
+    int aqHasOffset;
 };
 constexpr int kEpiDequant = 0;  // bf16(((float(acc) * sB[n]) * sA[m]) + bias[n])
 constexpr int kEpiFixpipe = 1;  // SetQuantScalar / SetQuantVector of the reference's Matmul (DEQF16)
 constexpr int kEpiFloat = 2;    // half / bfloat16 operands (kind::f16), fp32 accumulator cast to the output type
 
-template <int BN, bool PAIR, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+// One int8 row segment of 16 weights -> 16 half / bfloat16 values with AscendAntiQuant's arithmetic (the elementwise
+// operator's own code: bfloat16 through fp32, half in half), as two 16-byte chunks.
+template <typename CT, typename Dst, bool HAS_OFF>
+__device__ __forceinline__ void antiquant16(const uint4& raw, CT s, CT o, uint4& lo, uint4& hi)
+{
+    Pack<int8_t, 16> in;
+    *reinterpret_cast<uint4*>(&in) = raw;
+    alignas(4) CT x[16];
+    unpack_src<int8_t, CT, 16>(in, x);
+    const CT sv[1] = {s}, ov[1] = {o};
+    apply_op<kOpAntiQuant, CT, 16, 1, HAS_OFF, false>(x, sv, ov, 1.0f);
+    Pack<Dst, 16> out;
+    pack_dst<Dst, CT, 16>(x, out, kRoundRint);
+    lo = reinterpret_cast<const uint4*>(&out)[0];
+    hi = reinterpret_cast<const uint4*>(&out)[1];
+}
+
+template <int BN, bool PAIR, int EPI, bool CONV = false>
+__global__ void __launch_bounds__(Cfg<BN, PAIR, CONV>::kThreadsCta, 1)
 w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
 {
-    using C = Cfg<BN, PAIR>;
+    using C = Cfg<BN, PAIR, CONV>;
+    static_assert(!CONV || (PAIR && EPI == kEpiFloat), "the converting variant is built for CTA pairs and kind::f16 only");
     extern __shared__ uint8_t smem_raw[];
     // stage buffers need 1024-byte alignment for the 128B swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -91,6 +120,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     uint64_t* tmemEmpty = tmemFull + 2;            // [2] epilogue -> MMA
     uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
+    uint64_t* fullQ = bars + 2 * C::kStages + 5;   // [kStages] CONV: this CTA's int8 rows have landed
+    uint64_t* convDone = fullQ + C::kStages;       // [kStages] CONV: converter warps of both CTAs -> MMA (leader's is used)
     float* epiScale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + 256);  // [2][2][BN]
     uint8_t* outStage = reinterpret_cast<uint8_t*>(epiScale) + C::kEpiBytes;                // [kEpiWarps][16][kStagePitch]
 
@@ -108,6 +139,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(&fullBar[s], 1);
             mbar_init(&emptyBar[s], 1);
+            if constexpr (CONV) {
+                mbar_init(&fullQ[s], 1);
+                mbar_init(&convDone[s], 2 * kConvWarps);
+            }
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmemFull[a], 1);
@@ -149,7 +184,15 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait_bounded(&emptyBar[s], ph ^ 1, abortFlag))) break;
                     uint8_t* sa = smem + s * C::kStageBytes;
-                    if constexpr (PAIR) {
+                    if constexpr (CONV) {
+                        // A of both CTAs on the leader's barrier; this CTA's int8 rows of B on its own barrier, where
+                        // its converter warps wait for them
+                        if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], 2 * C::kABytes);
+                        const uint32_t leaderBar = mapa_u32(smem_u32(&fullBar[s]), 0);
+                        tma_load_2d_pair(sa, &tmapA, leaderBar, kb * kBK, m0);
+                        mbar_arrive_expect_tx(&fullQ[s], C::kBqBytes);
+                        tma_load_2d(sa + C::kABytes + C::kBBytes, &tmapB, &fullQ[s], kb * (kBK / 2), n0);
+                    } else if constexpr (PAIR) {
                         // both CTAs' loads are counted on the leader's barrier; the leader announces the bytes of both
                         if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], 2 * C::kStageBytes);
                         const uint32_t leaderBar = mapa_u32(smem_u32(&fullBar[s]), 0);
@@ -179,6 +222,11 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait_bounded(&fullBar[s], ph, abortFlag))) break;
+                    if constexpr (CONV) {
+                        if (!(ok = mbar_wait_bounded(&convDone[s], ph, abortFlag))) break;
+                        // half of the converted tile was written by the other CTA's warps (released at cluster scope)
+                        asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                    }
                     tc_fence_after();
                     const uint32_t aAddr = smem_u32(smem + s * C::kStageBytes);
                     const uint64_t descA = smem_desc_sw128(aAddr);
@@ -201,6 +249,65 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 if (ok) {
                     if constexpr (PAIR) tc_commit_pair(&tmemFull[acc], 3);
                     else tc_commit(&tmemFull[acc]);
+                }
+            }
+        }
+    } else if (CONV && warp >= 2 + kEpiWarps) {
+        // ---------------- converter warps: int8 rows of B -> the swizzled half / bfloat16 tile of the stage ----------------
+        if constexpr (CONV) {
+            const int t = threadIdx.x - 32 * (2 + kEpiWarps);  // 0..127: row t/4 of each 32-row pass, 16-byte segment t%4
+            const int seg = t & 3;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = unit; tile < numTiles && ok; tile += numUnits) {
+                const int n0 = (tile / p.tilesM) * BN + static_cast<int>(rank) * C::kBRows;
+                float sc[4], of[4];  // this thread's four rows: scale / offset as fp32 (exact widening of the operand type)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int n = n0 + i * 32 + (t >> 2);
+                    sc[i] = p.aqScaleScalar;
+                    of[i] = p.aqOffsetScalar;
+                    if (p.aqScale != nullptr) {
+                        sc[i] = 0.f;
+                        of[i] = 0.f;
+                        if (n < p.N) {
+                            if (p.abFmt == 1) {
+                                sc[i] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.aqScale)[n]);
+                                if (p.aqHasOffset) of[i] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.aqOffset)[n]);
+                            } else {
+                                sc[i] = __half2float(static_cast<const __half*>(p.aqScale)[n]);
+                                if (p.aqHasOffset) of[i] = __half2float(static_cast<const __half*>(p.aqOffset)[n]);
+                            }
+                        }
+                    }
+                }
+                for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!(ok = mbar_wait_bounded(&fullQ[s], ph, abortFlag))) break;
+                    const uint8_t* bq = smem + s * C::kStageBytes + C::kABytes + C::kBBytes;
+                    uint8_t* bc = smem + s * C::kStageBytes + C::kABytes;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = i * 32 + (t >> 2);
+                        const uint4 raw = *reinterpret_cast<const uint4*>(bq + r * (kBK / 2) + seg * 16);
+                        uint4 lo, hi;
+                        if (p.abFmt == 1) {
+                            if (p.aqHasOffset) antiquant16<float, __nv_bfloat16, true>(raw, sc[i], of[i], lo, hi);
+                            else antiquant16<float, __nv_bfloat16, false>(raw, sc[i], of[i], lo, hi);
+                        } else {
+                            if (p.aqHasOffset) antiquant16<__half, __half, true>(raw, __float2half_rn(sc[i]), __float2half_rn(of[i]), lo, hi);
+                            else antiquant16<__half, __half, false>(raw, __float2half_rn(sc[i]), __float2half_rn(of[i]), lo, hi);
+                        }
+                        // 128-byte rows in the 128B swizzle: 16-byte chunk c of row r lives at chunk c ^ (r % 8)
+                        uint8_t* row = bc + r * kBK;
+                        *reinterpret_cast<uint4*>(row + (((2 * seg) ^ (r & 7)) << 4)) = lo;
+                        *reinterpret_cast<uint4*>(row + (((2 * seg + 1) ^ (r & 7)) << 4)) = hi;
+                    }
+                    // the tensor cores read shared memory through the async proxy: order these writes before it
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&convDone[s]), 0));  // the leader's barrier
                 }
             }
         }
@@ -433,13 +540,13 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 }
 
 // ---- host side -------------------------------------------------------------------------------------
-template <int BN, bool PAIR, int EPI = kEpiDequant>
+template <int BN, bool PAIR, int EPI = kEpiDequant, bool CONV = false>
 ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
 {
-    using C = Cfg<BN, PAIR>;
+    using C = Cfg<BN, PAIR, CONV>;
     static bool attrSet = false;
     if (!attrSet) {
-        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN, PAIR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN, PAIR, EPI, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(C::kSmemBytes)));
         attrSet = true;
     }
@@ -450,7 +557,7 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaS
         const int clusters = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
-        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.blockDim = dim3(C::kThreadsCta, 1, 1);
         cfg.dynamicSmemBytes = C::kSmemBytes;
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
@@ -460,10 +567,10 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaS
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI>, ta, tb, p));
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, p));
     } else {
         const int grid = tiles < sm_count() ? tiles : sm_count();
-        w8a8_kernel<BN, PAIR, EPI><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+        w8a8_kernel<BN, PAIR, EPI, CONV><<<grid, C::kThreadsCta, C::kSmemBytes, st>>>(ta, tb, p);
     }
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
@@ -483,6 +590,12 @@ struct FixpipeArgs {
     int floatKind;     // 0: int8 operands + fixpipe epilogue; 1: half / bfloat16 operands (kEpiFloat)
     uint32_t abFmt;    // floatKind: 0 = half, 1 = bfloat16
     int outKind;       // floatKind: 0 = half, 1 = bfloat16, 2 = float
+    // floatKind with B_nk int8: AscendAntiQuant inside the matmul (converter warps)
+    int convert;
+    const void* aqScale;
+    const void* aqOffset;
+    float aqScaleScalar, aqOffsetScalar;
+    int aqHasOffset;
 };
 
 ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
@@ -519,6 +632,11 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     if (fix) {
         p.abFmt = fix->abFmt;
         p.outKind = fix->outKind;
+        p.aqScale = fix->aqScale;
+        p.aqOffset = fix->aqOffset;
+        p.aqScaleScalar = fix->aqScaleScalar;
+        p.aqOffsetScalar = fix->aqOffsetScalar;
+        p.aqHasOffset = fix->aqHasOffset;
         p.biasI32 = fix->biasI32;
         p.quantVec = fix->quantVec;
         p.quantScalar = fix->quantScalar;
@@ -551,6 +669,12 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     if (rc != ASCQ_OK) return rc;
     rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
+    if (epi == kEpiFloat && fix->convert) {
+        // B_nk is the int8 weight: its tile goes through the converter warps (CTA pairs, 256 x 256 tiles only)
+        rc = make_tmap_u8_plain(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kBK / 2, 128);
+        if (rc != ASCQ_OK) return rc;
+        return launch<256, true, kEpiFloat, true>(ta, tb, p, st);
+    }
     if (epi == kEpiFloat) {
         if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, p, st);
         return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, p, st) : launch<128, false, kEpiFloat>(ta, tb, p, st);
@@ -620,7 +744,7 @@ extern "C" ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const 
     if (quantVector && (reinterpret_cast<uintptr_t>(quantVector) & 7u))
         return fail(ASCQ_ERR_ALIGNMENT, "quantVector must be 8-byte aligned");
     void* bufs[1] = {C_f16};
-    const FixpipeArgs fix{bias_i32, quantVector, quantScalar, 0, 0, 0};
+    const FixpipeArgs fix{bias_i32, quantVector, quantScalar, 0, 0, 0, 0, nullptr, nullptr, 0.f, 0.f, 0};
     return run_w8a8(bufs, 1, 0, 0, A, B_nk, nullptr, nullptr, nullptr, M, N, K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fix);
 }
 
@@ -633,7 +757,8 @@ extern "C" ascq_status ascq_matmul_f16(void* C, ascq_dtype cT, const void* A, co
     if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)
         return fail(ASCQ_ERR_UNSUPPORTED, "output must be half, bfloat16_t or float");
     void* bufs[1] = {C};
-    const FixpipeArgs fa{nullptr, nullptr, 0.f, 1, abT == ASCQ_DT_BF16 ? 1u : 0u, cT == ASCQ_DT_F16 ? 0 : (cT == ASCQ_DT_BF16 ? 1 : 2)};
+    const FixpipeArgs fa{nullptr, nullptr, 0.f, 1, abT == ASCQ_DT_BF16 ? 1u : 0u, cT == ASCQ_DT_F16 ? 0 : (cT == ASCQ_DT_BF16 ? 1 : 2),
+                         0, nullptr, nullptr, 0.f, 0.f, 0};
     return run_w8a8(bufs, 1, 0, 0, static_cast<const int8_t*>(A), static_cast<const int8_t*>(B_nk), nullptr, nullptr, nullptr, M, N,
                     K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fa);
 }
@@ -652,6 +777,25 @@ extern "C" ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, 
     if (workspaceBytes < ascq_matmul_w8a16_workspace_size(N, K))
         return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", ascq_matmul_w8a16_workspace_size(N, K), workspaceBytes);
     if (aT != ASCQ_DT_F16 && aT != ASCQ_DT_BF16) return fail(ASCQ_ERR_UNSUPPORTED, "A must be half or bfloat16_t");
+    // Fused form (default): four converter warps per CTA run AscendAntiQuant on each int8 tile between the TMA stage and
+    // the MMA stage, so the dequantised weight never leaves shared memory.  ASCQ_W8A16=twostep takes the two launches.
+    bool fused = (K % 32 == 0) && aligned16(B_nk);
+    if (const char* e = getenv("ASCQ_W8A16")) fused = fused && strcmp(e, "twostep") != 0;
+    if (fused) {
+        if (!C) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
+        if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)
+            return fail(ASCQ_ERR_UNSUPPORTED, "output must be half, bfloat16_t or float");
+        float ss = scaleScalar, os = offsetScalar;
+        if (!scale) {  // the scalars arrive as aT values (include/adv_api/quantization/ascend_antiquant.h:136-205)
+            if (aT == ASCQ_DT_F16) { ss = __half2float(__float2half_rn(ss)); os = __half2float(__float2half_rn(os)); }
+            else { ss = __bfloat162float(__float2bfloat16_rn(ss)); os = __bfloat162float(__float2bfloat16_rn(os)); }
+        }
+        void* bufs[1] = {C};
+        const FixpipeArgs fa{nullptr, nullptr, 0.f, 1, aT == ASCQ_DT_BF16 ? 1u : 0u, cT == ASCQ_DT_F16 ? 0 : (cT == ASCQ_DT_BF16 ? 1 : 2),
+                             1, scale, offset, ss, os, scale ? (offset ? 1 : 0) : 1};
+        return run_w8a8(bufs, 1, 0, 0, static_cast<const int8_t*>(A), B_nk, nullptr, nullptr, nullptr, M, N, K, ldc, nullptr,
+                        static_cast<cudaStream_t>(stream), &fa);
+    }
     // step 1: the weight tile through AscendAntiQuant<int8_t, aT, isTranspose = true> (src [N, K], one scale / offset per
     // row n), as antiquant_processor_using_ub.h:86-137 does before the cube unit sees it
     ascq_antiquant_param ap{static_cast<uint32_t>(N), static_cast<uint32_t>(K), 0, 0, 1, 1, 1};

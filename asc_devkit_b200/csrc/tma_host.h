@@ -44,6 +44,23 @@ inline ascq_status make_tmap_u8(CUtensorMap* out, const void* base, uint64_t row
     return ASCQ_OK;
 }
 
+// uint8 [rows, colsBytes] row-major tensor map with a [boxRows, boxBytes] box and no swizzle (rows land back to back).
+inline ascq_status make_tmap_u8_plain(CUtensorMap* out, const void* base, uint64_t rows, uint64_t colsBytes, uint32_t boxBytes,
+                                      uint32_t boxRows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    const cuuint64_t dims[2] = {colsBytes, rows};
+    const cuuint64_t strides[1] = {colsBytes};
+    const cuuint32_t box[2] = {boxBytes, boxRows};
+    const cuuint32_t elemStrides[2] = {1, 1};
+    const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elemStrides,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled (plain) failed with CUresult %d", static_cast<int>(rc));
+    return ASCQ_OK;
+}
+
 // uint32 [rows, words] tensor map (rows of recordBytes, no swizzle) with a one-row box: one load moves one record.
 inline ascq_status make_tmap_kib_rows(CUtensorMap* out, const void* base, uint64_t rows, uint32_t recordBytes = 1024)
 {

@@ -47,8 +47,44 @@ def test_matmul_f16_exact_on_small_integers():
 
 
 @pytest.mark.parametrize("abT", [O.F16, O.BF16])
+@pytest.mark.parametrize("M,N,K", [(192, 640, 512), (256, 256, 64), (1000, 1030, 2080), (4096, 2048, 1024)])
+@pytest.mark.parametrize("per_channel,with_offset", [(True, True), (True, False), (False, True)])
+def test_w8a16_fused_equals_two_launches(abT, M, N, K, per_channel, with_offset, monkeypatch):
+    """The converter warps inside the matmul run the AscendAntiQuant arithmetic on every weight tile; the two-launch form
+    writes the same weight to a workspace first.  Same tile shape and MMA order on both sides: the outputs must be the
+    same bits (and both within tolerance of the oracle)."""
+    rng = np.random.default_rng(M + N + K + abT)
+    A = rand_float(rng, (M, K), abT, -1, 1)
+    B = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    if per_channel:
+        sc_h = rand_float(rng, (N,), abT, 0.002, 0.02)
+        of_h = rand_float(rng, (N,), abT, -4, 4) if with_offset else None
+        scale, offset = to_dev(sc_h, abT), (to_dev(of_h, abT) if with_offset else None)
+    else:
+        sc_h, of_h = 0.0078125, 1.5
+        scale, offset = sc_h, of_h
+    dA, dB = to_dev(A, abT), torch.from_numpy(B).to(DEV)
+    outs = {}
+    for mode in ("fused", "twostep"):
+        monkeypatch.setenv("ASCQ_W8A16", mode)
+        monkeypatch.setenv("ASCQ_W8A8_TILE", "pair")
+        C = torch.full((M, N), -1.0, dtype=torch.float32, device=DEV)
+        ops.MatmulW8A16(C, dA, dB, offset, scale)
+        ops.MatmulStatus()
+        outs[mode] = C.cpu().numpy()
+    assert np.array_equal(outs["fused"].view(np.uint32), outs["twostep"].view(np.uint32))
+    if per_channel:
+        W = O.ascend_antiquant(B, O.I8, abT, policy=O.PER_CHANNEL, m=N, n=K, scale=sc_h, offset=of_h, scaleT=abT, isTranspose=True)
+        _, want = O.matmul_f16(A, W, abT)
+    else:
+        (_, want), _ = O.matmul_w8a16(A, abT, B, of_h, sc_h)
+    close(outs["fused"], want)
+
+
+@pytest.mark.parametrize("abT", [O.F16, O.BF16])
 @pytest.mark.parametrize("per_channel", [True, False])
-def test_matmul_w8a16(abT, per_channel):
+def test_matmul_w8a16(abT, per_channel, monkeypatch):
+    monkeypatch.setenv("ASCQ_W8A16", "twostep")   # this test reads the dequantised weight back from the workspace
     rng = np.random.default_rng(11 + abT)
     M, N, K = 192, 640, 512
     A = rand_float(rng, (M, K), abT, -1, 1)
