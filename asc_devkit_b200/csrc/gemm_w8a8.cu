@@ -104,6 +104,67 @@ __device__ __forceinline__ void antiquant16(const uint4& raw, CT s, CT o, uint4&
     hi = reinterpret_cast<const uint4*>(&out)[1];
 }
 
+// Converter warps of the weight-only-quantised matmul.  Warp w takes the k-blocks that land in pipeline stage w (there
+// are as many stages as converter warps), so four k-blocks are being converted at any time and the fixed costs of a
+// hand-over (barrier wake-up, proxy fence, arrive) are paid once per 8192 weights.  Per pass of 8 rows, lane l owns row
+// l/4 and the 16-byte segment l%4 of the row's 64 int8 values; the 32 bytes of half / bfloat16 they become go into the
+// 128B-swizzled tile the MMAs read (16-byte chunk c of row r lives at chunk c ^ (r % 8)).
+template <typename C, int BN, typename CT, typename Dst, bool HAS_OFF>
+__device__ __forceinline__ void convert_tiles(const Params& p, uint8_t* smem, float* rowParams, uint64_t* fullQ, uint64_t* convDone,
+                                              volatile int* abortFlag, int w, int lane, uint32_t rank, int unit, int numUnits,
+                                              int numTiles, int kBlocks)
+{
+    static_assert(C::kStages == kConvWarps, "one converter warp per pipeline stage");
+    float* myScale = rowParams + w * 2 * C::kBRows;  // this warp's copy of the tile's 128 row scales, then 128 offsets
+    float* myOffset = myScale + C::kBRows;
+    const int seg = lane & 3;
+    const int s = w;  // the stage this warp serves
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = unit; tile < numTiles && ok; tile += numUnits) {
+        const int n0 = (tile / p.tilesM) * BN + static_cast<int>(rank) * C::kBRows;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < C::kBRows / 32; ++i) {
+            const int r = i * 32 + lane, n = n0 + r;
+            float fs = p.aqScaleScalar, fo = p.aqOffsetScalar;
+            if (p.aqScale != nullptr) {
+                fs = 0.f;
+                fo = 0.f;
+                if (n < p.N) {
+                    fs = to_f32<Dst>(static_cast<const Dst*>(p.aqScale)[n]);
+                    if (HAS_OFF) fo = to_f32<Dst>(static_cast<const Dst*>(p.aqOffset)[n]);
+                }
+            }
+            myScale[r] = fs;
+            myOffset[r] = fo;
+        }
+        __syncwarp();
+        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+            if (static_cast<int>(it % C::kStages) != s) continue;
+            const uint32_t ph = (it / C::kStages) & 1;
+            if (!(ok = mbar_wait_bounded(&fullQ[s], ph, abortFlag))) break;
+            const uint8_t* bq = smem + s * C::kStageBytes + C::kABytes + C::kBBytes;
+            uint8_t* bc = smem + s * C::kStageBytes + C::kABytes;
+#pragma unroll 4
+            for (int pass = 0; pass < C::kBRows / 8; ++pass) {
+                const int r = pass * 8 + (lane >> 2);
+                const uint4 raw = *reinterpret_cast<const uint4*>(bq + r * (kBK / 2) + seg * 16);
+                const CT sc = Ct<CT>::from_f32(myScale[r]), of = Ct<CT>::from_f32(myOffset[r]);
+                uint4 lo, hi;
+                antiquant16<CT, Dst, HAS_OFF>(raw, sc, of, lo, hi);
+                uint8_t* row = bc + r * kBK;
+                *reinterpret_cast<uint4*>(row + (((2 * seg) ^ (r & 7)) << 4)) = lo;
+                *reinterpret_cast<uint4*>(row + (((2 * seg + 1) ^ (r & 7)) << 4)) = hi;
+            }
+            // the tensor cores read shared memory through the async proxy: order these writes before it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&convDone[s]), 0));  // the leader's barrier
+        }
+    }
+}
+
 template <int BN, bool PAIR, int EPI, bool CONV = false>
 __global__ void __launch_bounds__(Cfg<BN, PAIR, CONV>::kThreadsCta, 1)
 w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
@@ -141,7 +202,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             mbar_init(&emptyBar[s], 1);
             if constexpr (CONV) {
                 mbar_init(&fullQ[s], 1);
-                mbar_init(&convDone[s], 2 * kConvWarps);
+                mbar_init(&convDone[s], 2);  // one converter warp of each CTA serves the stage
             }
         }
         for (int a = 0; a < 2; ++a) {
@@ -223,9 +284,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait_bounded(&fullBar[s], ph, abortFlag))) break;
                     if constexpr (CONV) {
-                        if (!(ok = mbar_wait_bounded(&convDone[s], ph, abortFlag))) break;
                         // half of the converted tile was written by the other CTA's warps (released at cluster scope)
-                        asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                        if (!(ok = mbar_wait_bounded_cluster(&convDone[s], ph, abortFlag))) break;
                     }
                     tc_fence_after();
                     const uint32_t aAddr = smem_u32(smem + s * C::kStageBytes);
@@ -255,60 +315,21 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     } else if (CONV && warp >= 2 + kEpiWarps) {
         // ---------------- converter warps: int8 rows of B -> the swizzled half / bfloat16 tile of the stage ----------------
         if constexpr (CONV) {
-            const int t = threadIdx.x - 32 * (2 + kEpiWarps);  // 0..127: row t/4 of each 32-row pass, 16-byte segment t%4
-            const int seg = t & 3;
-            uint32_t it = 0;
-            bool ok = true;
-            for (int tile = unit; tile < numTiles && ok; tile += numUnits) {
-                const int n0 = (tile / p.tilesM) * BN + static_cast<int>(rank) * C::kBRows;
-                float sc[4], of[4];  // this thread's four rows: scale / offset as fp32 (exact widening of the operand type)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int n = n0 + i * 32 + (t >> 2);
-                    sc[i] = p.aqScaleScalar;
-                    of[i] = p.aqOffsetScalar;
-                    if (p.aqScale != nullptr) {
-                        sc[i] = 0.f;
-                        of[i] = 0.f;
-                        if (n < p.N) {
-                            if (p.abFmt == 1) {
-                                sc[i] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.aqScale)[n]);
-                                if (p.aqHasOffset) of[i] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.aqOffset)[n]);
-                            } else {
-                                sc[i] = __half2float(static_cast<const __half*>(p.aqScale)[n]);
-                                if (p.aqHasOffset) of[i] = __half2float(static_cast<const __half*>(p.aqOffset)[n]);
-                            }
-                        }
-                    }
-                }
-                for (int kb = 0; kb < kBlocks; ++kb, ++it) {
-                    const int s = it % C::kStages;
-                    const uint32_t ph = (it / C::kStages) & 1;
-                    if (!(ok = mbar_wait_bounded(&fullQ[s], ph, abortFlag))) break;
-                    const uint8_t* bq = smem + s * C::kStageBytes + C::kABytes + C::kBBytes;
-                    uint8_t* bc = smem + s * C::kStageBytes + C::kABytes;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = i * 32 + (t >> 2);
-                        const uint4 raw = *reinterpret_cast<const uint4*>(bq + r * (kBK / 2) + seg * 16);
-                        uint4 lo, hi;
-                        if (p.abFmt == 1) {
-                            if (p.aqHasOffset) antiquant16<float, __nv_bfloat16, true>(raw, sc[i], of[i], lo, hi);
-                            else antiquant16<float, __nv_bfloat16, false>(raw, sc[i], of[i], lo, hi);
-                        } else {
-                            if (p.aqHasOffset) antiquant16<__half, __half, true>(raw, __float2half_rn(sc[i]), __float2half_rn(of[i]), lo, hi);
-                            else antiquant16<__half, __half, false>(raw, __float2half_rn(sc[i]), __float2half_rn(of[i]), lo, hi);
-                        }
-                        // 128-byte rows in the 128B swizzle: 16-byte chunk c of row r lives at chunk c ^ (r % 8)
-                        uint8_t* row = bc + r * kBK;
-                        *reinterpret_cast<uint4*>(row + (((2 * seg) ^ (r & 7)) << 4)) = lo;
-                        *reinterpret_cast<uint4*>(row + (((2 * seg + 1) ^ (r & 7)) << 4)) = hi;
-                    }
-                    // the tensor cores read shared memory through the async proxy: order these writes before it
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&convDone[s]), 0));  // the leader's barrier
-                }
+            // the operand type and the presence of an offset are fixed for the launch: pick the straight-line loop once
+            const int t = threadIdx.x - 32 * (2 + kEpiWarps);
+            auto run = [&](auto ctTag, auto dstTag, auto offTag) {
+                using CT = decltype(ctTag);
+                using Dst = decltype(dstTag);
+                constexpr bool kOff = decltype(offTag)::value;
+                convert_tiles<C, BN, CT, Dst, kOff>(p, smem, epiScale, fullQ, convDone, abortFlag, t >> 5, lane, rank, unit, numUnits, numTiles,
+                                                    kBlocks);
+            };
+            if (p.abFmt == 1) {
+                if (p.aqHasOffset) run(float{}, __nv_bfloat16{}, std::true_type{});
+                else run(float{}, __nv_bfloat16{}, std::false_type{});
+            } else {
+                if (p.aqHasOffset) run(__half{}, __half{}, std::true_type{});
+                else run(__half{}, __half{}, std::false_type{});
             }
         }
     } else {
@@ -323,7 +344,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             const uint32_t accPh = (local >> 1) & 1;
             const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
             const int n0 = (tile / p.tilesM) * BN;
-            ok = mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
+            ok = CONV ? mbar_wait_bounded_sleepy(&tmemFull[acc], accPh, abortFlag) : mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
             tc_fence_after();
             const int m = m0 + q * 32 + lane;
             const float sa = (p.sA != nullptr && m < p.M) ? __ldg(p.sA + m) : 1.0f;
@@ -777,10 +798,13 @@ extern "C" ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, 
     if (workspaceBytes < ascq_matmul_w8a16_workspace_size(N, K))
         return fail(ASCQ_ERR_INVALID_ARG, "workspace of %zu bytes needed, %zu given", ascq_matmul_w8a16_workspace_size(N, K), workspaceBytes);
     if (aT != ASCQ_DT_F16 && aT != ASCQ_DT_BF16) return fail(ASCQ_ERR_UNSUPPORTED, "A must be half or bfloat16_t");
-    // Fused form (default): four converter warps per CTA run AscendAntiQuant on each int8 tile between the TMA stage and
-    // the MMA stage, so the dequantised weight never leaves shared memory.  ASCQ_W8A16=twostep takes the two launches.
-    bool fused = (K % 32 == 0) && aligned16(B_nk);
-    if (const char* e = getenv("ASCQ_W8A16")) fused = fused && strcmp(e, "twostep") != 0;
+    // Two forms.  Default: two launches (AscendAntiQuant into the workspace, then the half / bfloat16 matmul).
+    // ASCQ_W8A16=fused: four converter warps per CTA run AscendAntiQuant on each int8 tile between the TMA stage and the
+    // MMA stage, so the dequantised weight never leaves shared memory -- same bits, but measured 2 to 4 times slower:
+    // the tile then crosses shared memory three more times (int8 in, 16-bit out, 16-bit into the tensor cores) next to
+    // the operand traffic of the MMAs, and a k-block waits for a whole warp's conversion before its MMAs can start.
+    bool fused = false;
+    if (const char* e = getenv("ASCQ_W8A16")) fused = !strcmp(e, "fused") && (K % 32 == 0) && aligned16(B_nk);
     if (fused) {
         if (!C) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
         if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)

@@ -72,6 +72,57 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return true;
 }
 
+// The same wait for warps that expect to wait long (an epilogue warp waits for a whole tile): between polls the warp
+// sleeps, so that it leaves the issue slots and the barrier unit to warps of the same SM that do arithmetic.
+__device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint64_t* bar, uint32_t parity, volatile int* abortFlag)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(128);
+        if ((++spins & 0x3Fu) == 0) {
+            if (*abortFlag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *abortFlag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// The same wait with acquire semantics at cluster scope: for barriers whose arrivals (from the other CTA of a pair)
+// release ordinary shared-memory writes rather than copy-engine bytes.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity, volatile int* abortFlag)
+{
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 0x3Fu) == 0) {
+            if (*abortFlag) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                *abortFlag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 // ---- TMA ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m)
 {

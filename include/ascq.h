@@ -348,7 +348,9 @@ ascq_status ascq_matmul_f16(void* C, ascq_dtype cT, const void* A, const void* B
  *   bfloat16: fp32 intermediates) -- offset / scale [N] tensors of aT, or (scale NULL) the two scalars;
  *   C = A . W^T with fp32 accumulation, cast to cT.
  * Two launches: the dequantised weight goes through `workspace` (N * K * 2 bytes, 16-byte aligned) and stays in L2 for
- * the matmul when it fits.  K % 32 == 0.
+ * the matmul when it fits.  K % 32 == 0.  (With ASCQ_W8A16=fused in the environment the conversion runs inside the
+ * matmul instead -- converter warps between the copy stage and the MMA stage, same bits, no workspace traffic; it is
+ * slower on B200 and kept as a tested alternative.)
  */
 ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk, const void* offset,
                               const void* scale, float offsetScalar, float scaleScalar, int M, int N, int K, int ldc,
