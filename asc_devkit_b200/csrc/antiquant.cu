@@ -122,8 +122,10 @@ static ascq_status antiquant_common(void* dst, ascq_dtype dstT, const void* src,
         g.scale.p = scale; g.fp4Transposed = p->isTranspose;
         return launch_ew_generic(g, st);
     }
-    if (srcT != ASCQ_DT_I8)
-        return fail(ASCQ_ERR_UNSUPPORTED, "AscendAntiQuant source dtype %d is not built (int8 and fp4x2_e2m1 are)", (int)srcT);
+    if (srcT != ASCQ_DT_I8 && srcT != ASCQ_DT_I4X2)
+        return fail(ASCQ_ERR_UNSUPPORTED, "AscendAntiQuant source dtype %d is not built (int8, int4b_t and fp4x2_e2m1 are)", (int)srcT);
+    if (srcT == ASCQ_DT_I4X2 && (n % 2 != 0))
+        return fail(ASCQ_ERR_INVALID_ARG, "n must be even for a packed int4b_t source");
 
     EwArgs a{};
     a.src = src;
@@ -213,7 +215,7 @@ static ascq_status antiquant_common(void* dst, ascq_dtype dstT, const void* src,
     }
 
     if (unified) ct = ASCQ_DT_F32;
-    if (ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {
+    if (srcT == ASCQ_DT_I8 && ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {
         bool handled = false;
         ascq_status rc = dispatch_fast(a, dstT, scaleT, ct, smode, hasOff, st, &handled);
         if (rc != ASCQ_OK || handled) return rc;

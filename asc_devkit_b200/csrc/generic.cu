@@ -13,6 +13,11 @@ __device__ __forceinline__ float load_any_f32(const void* p, int dt, size_t i)
         case ASCQ_DT_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
         case ASCQ_DT_F32: return static_cast<const float*>(p)[i];
         case ASCQ_DT_I8: return static_cast<float>(static_cast<const int8_t*>(p)[i]);
+        case ASCQ_DT_I4X2: {  // int4b_t: two signed 4-bit values per byte, the even element in the low nibble
+            const uint32_t byte = static_cast<const uint8_t*>(p)[i >> 1];
+            const int32_t nib = static_cast<int32_t>((i & 1) ? (byte >> 4) : (byte & 0xFu));
+            return static_cast<float>((nib ^ 8) - 8);
+        }
         case ASCQ_DT_I32: return __int2float_rn(static_cast<const int32_t*>(p)[i]);
         case ASCQ_DT_U64: return to_f32<uint64_t>(static_cast<const uint64_t*>(p)[i]);
         default: return 0.f;

@@ -51,11 +51,11 @@ typedef enum {
     ASCQ_DT_U64 = 5,        /* AscendDequant scale: low 32 bits hold fp32 bits */
     ASCQ_DT_FP4X2_E2M1 = 6,
     ASCQ_DT_E8M0 = 7,
-    ASCQ_DT_FP8_E4M3 = 8,   /* declared by the reference, not built here: ASCQ_ERR_UNSUPPORTED */
-    ASCQ_DT_FP8_E5M2 = 9,
-    ASCQ_DT_HIF8 = 10,
+    ASCQ_DT_FP8_E4M3 = 8,   /* fp8_e4m3fn_t / fp8_e5m2_t: operands of ascq_group_matmul_mxfp8 only; as quantisation */
+    ASCQ_DT_FP8_E5M2 = 9,   /* targets or antiquant sources they are declared by the reference and not built here  */
+    ASCQ_DT_HIF8 = 10,      /* declared by the reference, not built here: ASCQ_ERR_UNSUPPORTED */
     ASCQ_DT_FP4X2_E1M2 = 11,
-    ASCQ_DT_I4X2 = 12
+    ASCQ_DT_I4X2 = 12       /* int4b_t, two per byte (even element in the low nibble): AscendAntiQuant source only */
 } ascq_dtype;
 
 /* include/adv_api/quantization/ascend_quant_utils.h:73-80 (same order in the

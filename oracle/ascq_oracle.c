@@ -28,7 +28,7 @@
 #endif
 
 /* ---- dtype / policy / round codes: numerically identical to include/ascq.h ---------------- */
-enum { DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2, DT_I8 = 3, DT_I32 = 4, DT_U64 = 5, DT_FP4X2_E2M1 = 6, DT_E8M0 = 7 };
+enum { DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2, DT_I8 = 3, DT_I32 = 4, DT_U64 = 5, DT_FP4X2_E2M1 = 6, DT_E8M0 = 7, DT_I4X2 = 12 };
 enum { PER_TENSOR = 0, PER_CHANNEL = 1, PER_TOKEN = 2, PER_GROUP = 3 };
 enum { CAST_NONE = 0, CAST_RINT = 1, CAST_FLOOR = 2, CAST_CEIL = 3, CAST_ROUND = 4, CAST_TRUNC = 5 };
 enum { OR_OK = 0, OR_INVALID = 1, OR_UNSUPPORTED = 2 };
@@ -535,7 +535,9 @@ static int antiquant_common(void* dst, int dstT, const void* src, int srcT, cons
             }
         return OR_OK;
     }
-    if (srcT != DT_I8) return OR_UNSUPPORTED;
+    /* int4b_t (ascend_antiquant_impl.h:246-247, 512: Cast<half, int4b_t>): two signed nibbles per byte, even element low */
+    if (srcT != DT_I8 && srcT != DT_I4X2) return OR_UNSUPPORTED;
+    if (srcT == DT_I4X2 && (n & 1)) return OR_INVALID;
 
     if (policy == PER_TENSOR || policy == PER_CHANNEL) {
         if (dstT != DT_F16 && dstT != DT_BF16) return OR_UNSUPPORTED;
@@ -581,7 +583,10 @@ static int antiquant_common(void* dst, int dstT, const void* src, int srcT, cons
     for (uint32_t r = 0; r < rows; ++r) {
         for (uint32_t c = 0; c < n; ++c) {
             size_t i = (size_t)r * n + c;
-            cval x = cv_from_f32((float)((const int8_t*)src)[i], ct);
+            float xin;
+            if (srcT == DT_I8) xin = (float)((const int8_t*)src)[i];
+            else { uint8_t byte = ((const uint8_t*)src)[i >> 1]; int nib = (i & 1) ? (byte >> 4) : (byte & 0xF); xin = (float)((nib ^ 8) - 8); }
+            cval x = cv_from_f32(xin, ct);
             if (has_off) x = cv_add(x, cv_from_f32(sref_get(&so, r, c), ct));
             x = cv_mul(x, cv_from_f32(sref_get(&ss, r, c), ct));
             if (ct == DT_F32) store_from_f32(dst, dstT, i, x.f);

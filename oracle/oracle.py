@@ -19,6 +19,7 @@ _SO = os.path.join(_HERE, "libascq_oracle.so")
 
 # dtype / policy / round codes (identical to include/ascq.h)
 F16, BF16, F32, I8, I32, U64, FP4X2_E2M1, E8M0 = range(8)
+I4X2 = 12   # int4b_t, two per byte
 PER_TENSOR, PER_CHANNEL, PER_TOKEN, PER_GROUP, PER_CHANNEL_PER_GROUP, PER_TOKEN_PER_GROUP = range(6)
 CAST_NONE, CAST_RINT, CAST_FLOOR, CAST_CEIL, CAST_ROUND, CAST_TRUNC = range(6)
 

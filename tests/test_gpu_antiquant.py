@@ -154,3 +154,28 @@ def test_quant_of_antiquant_round_trip_at_scale():
     ops.AscendQuant(back, deq, 8.0, 0.0, K * N)
     torch.cuda.synchronize()
     assert torch.equal(back, w)
+
+
+@pytest.mark.parametrize("dstT", [O.F16, O.BF16])
+@pytest.mark.parametrize("isTranspose", [False, True])
+def test_int4_source(dstT, isTranspose):
+    """int4b_t weights (two signed nibbles per byte, even element in the low nibble) through the legacy per-channel
+    operator: ascend_antiquant_impl.h:246-247 casts them to half and runs the same arithmetic."""
+    rng = np.random.default_rng(7 + dstT)
+    rows, cols = (96, 256) if not isTranspose else (256, 128)   # [K, N] or [N, K]; cols even
+    packed = rng.integers(0, 256, (rows, cols // 2), dtype=np.uint8)
+    nper = cols if not isTranspose else rows
+    scale = rand_float(rng, (nper,), dstT, 0.01, 0.5)
+    offset = rand_float(rng, (nper,), dstT, -4, 4)
+    want = O.ascend_antiquant(packed, O.I4X2, dstT, policy=O.PER_CHANNEL, m=rows, n=cols, scale=scale, offset=offset,
+                              scaleT=dstT, isTranspose=isTranspose)
+    d_dst = torch.zeros((rows, cols), dtype=TORCH_OF[dstT], device=DEV)
+    ops.AscendAntiQuant(d_dst, torch.from_numpy(packed).to(DEV), to_dev(offset, dstT), to_dev(scale, dstT),
+                        ops.AscendAntiQuantParam(rows, cols), isTranspose=isTranspose, src_dtype=L.DT_I4X2)
+    assert_bits_equal(to_host(d_dst, dstT), want, "int4 source")
+    # the values themselves: nibble n decodes to ((n ^ 8) - 8)
+    ones = O.ascend_antiquant(np.arange(256, dtype=np.uint8).reshape(1, 256), O.I4X2, O.F16, policy=O.PER_TENSOR, m=1,
+                              n=512, scaleScalar=1.0, offsetScalar=0.0, scaleT=O.F16, hasOffset=True)
+    lo = ((np.arange(256) & 15) ^ 8) - 8
+    hi = ((np.arange(256) >> 4) ^ 8) - 8
+    assert np.array_equal(ones.reshape(256, 2).astype(np.int32), np.stack([lo, hi], 1))
