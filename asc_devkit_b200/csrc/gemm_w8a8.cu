@@ -70,6 +70,9 @@ struct Params {
     int32_t* accDump;
     int M, N, K, ldc;
     int tilesM, tilesN;
+    // Work items: items [0, fullTiles) are whole tiles; from there on two items share one tile, each taking half of
+    // its columns (the tail of a pair-shaped launch, so that the last, partly filled wave lasts half as long).
+    int fullTiles, workItems;
     // fixpipe-style epilogue (EPI == kEpiFixpipe): C is fp16 = half(acc + biasI32[n]) scaled by quantVec[n] or quantScalar
     const int32_t* biasI32;
     const uint64_t* quantVec;   // low word: fp32 bits, of which the hardware keeps sign, exponent and 10 mantissa bits
@@ -83,6 +86,16 @@ struct Params {
     float aqScaleScalar, aqOffsetScalar;
     int aqHasOffset;
 };
+// Work item -> tile, first column inside the tile, columns of the item.
+struct Item {
+    int tile, nOff, nCols;
+};
+template <int BN> __device__ __forceinline__ Item decode_item(const Params& p, int w)
+{
+    if (w < p.fullTiles) return Item{w, 0, BN};
+    const int h = w - p.fullTiles;
+    return Item{p.fullTiles + (h >> 1), (h & 1) * (BN / 2), BN / 2};
+}
 constexpr int kEpiDequant = 0;  // bf16(((float(acc) * sB[n]) * sA[m]) + bias[n])
 constexpr int kEpiFixpipe = 1;  // SetQuantScalar / SetQuantVector of the reference's Matmul (DEQF16)
 constexpr int kEpiFloat = 2;    // half / bfloat16 operands (kind::f16), fp32 accumulator cast to the output type
@@ -188,7 +201,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int numTiles = p.tilesM * p.tilesN;
+    const int numTiles = p.workItems;  // loop bound of every role (work items; whole tiles unless the tail is split)
     const int kBlocks = (p.K + kBK - 1) / kBK;
     // work unit = CTA (single) or cluster of two CTAs (PAIR); rank = position inside the pair, rank 0 issues the MMAs
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
@@ -237,9 +250,13 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         if (elect_one()) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = unit; tile < numTiles && ok; tile += numUnits) {
+            for (int w = unit; w < numTiles && ok; w += numUnits) {
+                const Item item = decode_item<BN>(p, w);
+                const int tile = item.tile;
                 const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
-                const int n0 = (tile / p.tilesM) * BN + (PAIR ? static_cast<int>(rank) * C::kBRows : 0);
+                // rows of B this CTA loads: its half of the item's columns (a half-tile item still moves a whole box of
+                // kBRows rows; the MMAs read the first nCols / 2 of them)
+                const int n0 = (tile / p.tilesM) * BN + item.nOff + (PAIR ? static_cast<int>(rank) * (item.nCols / 2) : 0);
                 for (int kb = 0; kb < kBlocks; ++kb, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
@@ -270,10 +287,12 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (rank == 0 && elect_one()) {
-            const uint32_t idesc = (EPI == kEpiFloat) ? idesc_f16(kTileM, BN, p.abFmt) : idesc_i8(kTileM, BN);
+            const uint32_t idescFull = (EPI == kEpiFloat) ? idesc_f16(kTileM, BN, p.abFmt) : idesc_i8(kTileM, BN);
+            const uint32_t idescHalf = (EPI == kEpiFloat) ? idesc_f16(kTileM, BN / 2, p.abFmt) : idesc_i8(kTileM, BN / 2);
             uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
+            for (int w = unit; w < numTiles && ok; w += numUnits, ++local) {
+                const uint32_t idesc = (w < p.fullTiles) ? idescFull : idescHalf;
                 const int acc = local & 1;
                 const uint32_t accPh = (local >> 1) & 1;
                 if (!(ok = mbar_wait_bounded(&tmemEmpty[acc], accPh ^ 1, abortFlag))) break;
@@ -339,11 +358,13 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         uint8_t* stageW = outStage + (warp - 2) * (16 * kStagePitch);
         uint32_t local = 0;
         bool ok = true;
-        for (int tile = unit; tile < numTiles && ok; tile += numUnits, ++local) {
+        for (int w = unit; w < numTiles && ok; w += numUnits, ++local) {
+            const Item item = decode_item<BN>(p, w);
+            const int tile = item.tile;
             const int acc = local & 1;
             const uint32_t accPh = (local >> 1) & 1;
             const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
-            const int n0 = (tile / p.tilesM) * BN;
+            const int n0 = (tile / p.tilesM) * BN + item.nOff;
             ok = CONV ? mbar_wait_bounded_sleepy(&tmemFull[acc], accPh, abortFlag) : mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
             tc_fence_after();
             const int m = m0 + q * 32 + lane;
@@ -460,7 +481,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 }
             };
 #pragma unroll 1
-            for (int c2 = sub; c2 < BN / 64; c2 += kEpiWarps / 4) {  // 64 columns = 128 bytes of bf16 per row at a time
+            for (int c2 = sub; c2 < item.nCols / 64; c2 += kEpiWarps / 4) {  // 64 columns = 128 bytes of bf16 per row at a time
                 uint32_t r0[32], r1[32];
                 tmem_ld_32x32b_x32(taddr + c2 * 64, r0);
                 tmem_ld_32x32b_x32(taddr + c2 * 64 + 32, r1);
@@ -574,8 +595,17 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaS
     p.tilesM = (p.M + (PAIR ? 2 * kBM : kBM) - 1) / (PAIR ? 2 * kBM : kBM);
     p.tilesN = (p.N + BN - 1) / BN;
     const int tiles = p.tilesM * p.tilesN;
+    p.fullTiles = tiles;
+    p.workItems = tiles;
     if constexpr (PAIR) {
         const int clusters = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+        // Tail split: when the last wave would keep at most half of the pairs busy, its tiles are cut into two column
+        // halves, so that every pair gets at most one half tile and the wave lasts half as long.
+        const int rest = tiles % clusters;
+        if (!CONV && BN == 256 && tiles > clusters && rest > 0 && 2 * rest <= clusters && getenv("ASCQ_W8A8_NOSPLIT") == nullptr) {
+            p.fullTiles = tiles - rest;
+            p.workItems = p.fullTiles + 2 * rest;
+        }
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
         cfg.blockDim = dim3(C::kThreadsCta, 1, 1);

@@ -99,6 +99,23 @@ def test_cfg4_full_size_exact():
     assert_bits_equal(got_C[:64], want_C, "cfg4 rows 0..63 vs oracle")
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 128), (2560, 3840, 192), (2304, 4100, 64)])
+@pytest.mark.parametrize("split", [True, False])
+def test_tail_split_gives_the_same_bits(M, N, K, split, monkeypatch):
+    """Pair-shaped launches whose last wave is at most half full cut its tiles into column halves (two work items per
+    tile); shapes chosen so that this happens, with ragged edges too.  Exact against an integer reference on the GPU."""
+    monkeypatch.setenv("ASCQ_W8A8_TILE", "pair")
+    if not split:
+        monkeypatch.setenv("ASCQ_W8A8_NOSPLIT", "1")
+    A, B, sA, sB, bias = make_case(M, N, K, M + N + K)
+    dA, dB = torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV)
+    acc = (dA.float() @ dB.float().T).to(torch.int32).cpu().numpy()      # K <= 256: every sum is exact in fp32
+    got_C, got_acc = run(A, B, sA, sB, bias)
+    assert np.array_equal(got_acc, acc)
+    f = (acc.astype(np.float32) * sB[None, :]) * sA[:, None] + O.bf16_bits_to_f32(bias)[None, :]
+    assert_bits_equal(got_C, O.f32_to_bf16_bits(f), "tail split")
+
+
 def test_scatter_writes_the_block_into_every_buffer():
     # three [M, ldc] matrices stand in for this GPU's and two peers' output: the block must land at colOffset in each
     M, N, K, ldc, col = 200, 192, 256, 640, 256
