@@ -70,6 +70,7 @@ SIGNATURES = {
     "ascq_matmul_f16": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "ascq_matmul_w8a16": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _f, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_matmul_w8a16_workspace_size": (C.c_size_t, [_i, _i]),
+    "ascq_matmul_w4a16": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _f, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_matmul_w8a8_multicast": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ascq_matmul_status": (_i, [_vp]),
     "ascq_group_matmul_mxfp4": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),

@@ -819,7 +819,7 @@ extern "C" size_t ascq_matmul_w8a16_workspace_size(int N, int K)
     return (N <= 0 || K <= 0) ? 0 : static_cast<size_t>(N) * K * 2;
 }
 
-extern "C" ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk,
+static ascq_status matmul_wq_a16(ascq_dtype bT, void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk,
                                          const void* offset, const void* scale, float offsetScalar, float scaleScalar,
                                          int M, int N, int K, int ldc, void* workspace, size_t workspaceBytes, void* stream)
 {
@@ -834,7 +834,7 @@ extern "C" ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, 
     // the tile then crosses shared memory three more times (int8 in, 16-bit out, 16-bit into the tensor cores) next to
     // the operand traffic of the MMAs, and a k-block waits for a whole warp's conversion before its MMAs can start.
     bool fused = false;
-    if (const char* e = getenv("ASCQ_W8A16")) fused = !strcmp(e, "fused") && (K % 32 == 0) && aligned16(B_nk);
+    if (const char* e = getenv("ASCQ_W8A16")) fused = bT == ASCQ_DT_I8 && !strcmp(e, "fused") && (K % 32 == 0) && aligned16(B_nk);
     if (fused) {
         if (!C) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
         if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)
@@ -856,13 +856,30 @@ extern "C" ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, 
     ascq_status rc;
     if (scale) {
         ap.hasOffset = offset ? 1 : 0;
-        rc = ascq_antiquant(workspace, aT, B_nk, ASCQ_DT_I8, offset, scale, aT, 0.f, 0.f, ASCQ_PER_CHANNEL, &ap, stream);
+        rc = ascq_antiquant(workspace, aT, B_nk, bT, offset, scale, aT, 0.f, 0.f, ASCQ_PER_CHANNEL, &ap, stream);
     } else {
-        rc = ascq_antiquant(workspace, aT, B_nk, ASCQ_DT_I8, nullptr, nullptr, aT, offsetScalar, scaleScalar, ASCQ_PER_TENSOR, &ap, stream);
+        rc = ascq_antiquant(workspace, aT, B_nk, bT, nullptr, nullptr, aT, offsetScalar, scaleScalar, ASCQ_PER_TENSOR, &ap, stream);
     }
     if (rc != ASCQ_OK) return rc;
     // step 2: half / bfloat16 matmul on the tensor cores
     return ascq_matmul_f16(C, cT, A, workspace, aT, M, N, K, ldc, stream);
+}
+
+extern "C" ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk,
+                                         const void* offset, const void* scale, float offsetScalar, float scaleScalar,
+                                         int M, int N, int K, int ldc, void* workspace, size_t workspaceBytes, void* stream)
+{
+    return matmul_wq_a16(ASCQ_DT_I8, C, cT, A, aT, B_nk, offset, scale, offsetScalar, scaleScalar, M, N, K, ldc, workspace,
+                         workspaceBytes, stream);
+}
+
+// int4b_t weights: B_nk holds [N, K/2] bytes, two signed nibbles per byte (even k in the low nibble)
+extern "C" ascq_status ascq_matmul_w4a16(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const uint8_t* B_nk_int4,
+                                         const void* offset, const void* scale, float offsetScalar, float scaleScalar,
+                                         int M, int N, int K, int ldc, void* workspace, size_t workspaceBytes, void* stream)
+{
+    return matmul_wq_a16(ASCQ_DT_I4X2, C, cT, A, aT, reinterpret_cast<const int8_t*>(B_nk_int4), offset, scale, offsetScalar,
+                         scaleScalar, M, N, K, ldc, workspace, workspaceBytes, stream);
 }
 
 // [K, N] row-major int8 (the reference's ND weight, CubeFormat::ND, not transposed) -> [N, K]: one-off weight preparation.

@@ -280,6 +280,21 @@ def MatmulW8A16(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, offset, sc
     return C
 
 
+def MatmulW4A16(C: torch.Tensor, A: torch.Tensor, B_nk_int4: torch.Tensor, offset, scale,
+                workspace: Optional[torch.Tensor] = None, stream=None):
+    """``MatmulW8A16`` with int4b_t weights: ``B_nk_int4`` is a uint8 tensor [N, K/2] (two signed nibbles per byte)."""
+    M, K = A.shape
+    N = B_nk_int4.shape[0]
+    if workspace is None:
+        workspace = torch.empty(N * K * 2, dtype=torch.uint8, device=A.device)
+    st = isinstance(scale, torch.Tensor)
+    L.check(L.lib().ascq_matmul_w4a16(_ptr(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk_int4),
+                                      _ptr(offset) if isinstance(offset, torch.Tensor) else None, _ptr(scale) if st else None,
+                                      0.0 if st else float(offset), 0.0 if st else float(scale), M, N, K, C.stride(0),
+                                      _ptr(workspace), workspace.numel(), _stream(stream)))
+    return C
+
+
 def GroupMatmulMxfp4Workspace(sumM: int, G: int, K: int, N: int) -> int:
     return int(L.lib().ascq_group_matmul_mxfp4_workspace_size(sumM, G, K, N))
 

@@ -103,3 +103,21 @@ def test_matmul_w8a16(abT, per_channel, monkeypatch):
     # the dequantised weight the tensor cores read is AscendAntiQuant's output, bit for bit
     assert np.array_equal(to_host(ws.view(TDT[abT]).view(N, K), abT).view(np.uint16), W.view(np.uint16))
     close(C.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("abT", [O.F16, O.BF16])
+def test_matmul_w4a16(abT):
+    """int4b_t weights: AscendAntiQuant's int4 source, then the same matmul."""
+    rng = np.random.default_rng(21 + abT)
+    M, N, K = 160, 384, 256
+    A = rand_float(rng, (M, K), abT, -1, 1)
+    B4 = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    sc_h, of_h = rand_float(rng, (N,), abT, 0.02, 0.2), rand_float(rng, (N,), abT, -2, 2)
+    W = O.ascend_antiquant(B4, O.I4X2, abT, policy=O.PER_CHANNEL, m=N, n=K, scale=sc_h, offset=of_h, scaleT=abT, isTranspose=True)
+    _, want = O.matmul_f16(A, W, abT)
+    ws = torch.zeros(N * K * 2, dtype=torch.uint8, device=DEV)
+    C = torch.zeros((M, N), dtype=torch.float32, device=DEV)
+    ops.MatmulW4A16(C, to_dev(A, abT), torch.from_numpy(B4).to(DEV), to_dev(of_h, abT), to_dev(sc_h, abT), workspace=ws)
+    ops.MatmulStatus()
+    assert np.array_equal(to_host(ws.view(TDT[abT]).view(N, K), abT).view(np.uint16), W.view(np.uint16))
+    close(C.cpu().numpy(), want)
