@@ -58,6 +58,7 @@ SIGNATURES = {
     "ascq_version": (_i, []),
     "ascq_quant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(QuantParam), _vp]),
     "ascq_dynamic_quant_per_token": (_i, [_vp, _vp, _vp, _vp, _i, _u32, _u32, _vp]),
+    "ascq_dynamic_quant_mxfp4": (_i, [_vp, _vp, _vp, _i, _u32, _u32, _vp]),
     "ascq_dequant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _i, C.POINTER(DequantParam), _vp]),
     "ascq_antiquant": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(AntiQuantParam), _vp]),
    "ascq_quantize": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(QuantizeParam), _vp]),

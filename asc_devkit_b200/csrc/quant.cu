@@ -303,3 +303,99 @@ extern "C" ascq_status ascq_dynamic_quant_per_token(int8_t* dst, float* scaleOut
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
+
+// ---- dynamic MX-FP4 block quantisation ---------------------------------------------------------------
+// One thread per block of 32 consecutive elements of a row: amax -> shared exponent -> E8M0 byte, then every value is
+// scaled by the exact power of two and converted float -> bfloat16 (RINT) -> E2M1 (RINT, saturating), the conversion
+// chain of AscendQuant's fp4 destination.  Consecutive threads take consecutive blocks: 64-byte loads, 16-byte stores and
+// one scale byte per thread, all coalesced.
+namespace ascq {
+namespace {
+template <typename Src>
+__global__ void __launch_bounds__(256) dyn_quant_mxfp4_kernel(uint8_t* __restrict__ dst, uint8_t* __restrict__ scaleOut,
+                                                              const Src* __restrict__ src, uint64_t blocks)
+{
+    const uint64_t b = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
+    if (b >= blocks) return;
+    float v[32];
+    if constexpr (sizeof(Src) == 2) {
+        const uint4* q = reinterpret_cast<const uint4*>(src + b * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 w = __ldcs(q + i);
+            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                Src lo, hi;
+                *reinterpret_cast<unsigned short*>(&lo) = static_cast<unsigned short>(ws[j] & 0xFFFFu);
+                *reinterpret_cast<unsigned short*>(&hi) = static_cast<unsigned short>(ws[j] >> 16);
+                v[i * 8 + j * 2] = to_f32<Src>(lo);
+                v[i * 8 + j * 2 + 1] = to_f32<Src>(hi);
+            }
+        }
+    } else {
+        const float4* q = reinterpret_cast<const float4*>(src + b * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 w = __ldcs(q + i);
+            v[i * 4] = w.x; v[i * 4 + 1] = w.y; v[i * 4 + 2] = w.z; v[i * 4 + 3] = w.w;
+        }
+    }
+    float amax = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float a = fabsf(v[i]);
+        bad = bad || !(a <= 3.4028234663852886e38f);  // NaN or infinity
+        amax = fmaxf(amax, a);
+    }
+    // shared exponent = floor(log2(amax)) - 2 (E2M1's largest exponent), clamped to the E8M0 range; all-zero blocks get 2^0
+    int e = 0;
+    if (amax > 0.f) {
+        const uint32_t bits = __float_as_uint(amax);
+        const int ex = static_cast<int>((bits >> 23) & 0xFF);
+        e = (ex == 0 ? -126 : ex - 127) - 2;   // subnormal amax: floor(log2) is below -126; -126 is close enough to clamp
+        e = max(e, -127);
+        e = min(e, 127);
+    }
+    const uint32_t sbyte = bad ? 0xFFu : static_cast<uint32_t>(e + 127);
+    scaleOut[b] = static_cast<uint8_t>(sbyte);
+    // multiply by 2^-e in two exact steps so that neither factor leaves the normal range
+    const int h1 = (-e) / 2, h2 = (-e) - h1;
+    const float f1 = __uint_as_float(static_cast<uint32_t>(h1 + 127) << 23), f2 = __uint_as_float(static_cast<uint32_t>(h2 + 127) << 23);
+    uint32_t out[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float y = __fmul_rn(__fmul_rn(v[w * 8 + j], f1), f2);
+            const uint32_t code = bad ? 0u : f32_to_e2m1(__bfloat162float(f32_to_bf16_sat(y)), kRoundRint);
+            word |= code << (4 * j);
+        }
+        out[w] = word;
+    }
+    reinterpret_cast<uint4*>(dst)[b] = make_uint4(out[0], out[1], out[2], out[3]);
+}
+}  // namespace
+}  // namespace ascq
+
+extern "C" ascq_status ascq_dynamic_quant_mxfp4(uint8_t* dst_fp4, uint8_t* scale_e8m0, const void* src, ascq_dtype srcT,
+                                                uint32_t m, uint32_t n, void* stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!dst_fp4 || !scale_e8m0 || !src) return fail(ASCQ_ERR_INVALID_ARG, "dst, scale and src must not be NULL");
+    if (!is_float_type(srcT)) return fail(ASCQ_ERR_UNSUPPORTED, "src dtype must be half, bfloat16_t or float");
+    if (n % 32 != 0) return fail(ASCQ_ERR_INVALID_ARG, "n is %u, which must be a multiple of the MX block size 32", n);
+    if (!aligned16(src) || !aligned16(dst_fp4)) return fail(ASCQ_ERR_ALIGNMENT, "src and dst must be 16-byte aligned");
+    const uint64_t blocks = static_cast<uint64_t>(m) * (n / 32);
+    if (blocks == 0) return ASCQ_OK;
+    const unsigned grid = static_cast<unsigned>((blocks + 255) / 256);
+    if (srcT == ASCQ_DT_F16) dyn_quant_mxfp4_kernel<__half><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __half*>(src), blocks);
+    else if (srcT == ASCQ_DT_BF16)
+        dyn_quant_mxfp4_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __nv_bfloat16*>(src), blocks);
+    else dyn_quant_mxfp4_kernel<float><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const float*>(src), blocks);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}
+

@@ -101,6 +101,15 @@ def DynamicQuantPerToken(dstTensor, scaleOut, srcTensor, deqScaleOut=None, strea
     return dstTensor, scaleOut
 
 
+def DynamicQuantMxfp4(dstTensor: torch.Tensor, scaleOut: torch.Tensor, srcTensor: torch.Tensor, stream=None):
+    """Blocks of 32 elements -> E8M0 scale byte + 32 E2M1 codes (``ascq_dynamic_quant_mxfp4``): dst uint8 [m, n/2],
+    scale uint8 [m, n/32]."""
+    m, n = srcTensor.shape
+    L.check(L.lib().ascq_dynamic_quant_mxfp4(_ptr(dstTensor), _ptr(scaleOut), _ptr(srcTensor), dtype_code(srcTensor), m, n,
+                                             _stream(stream)))
+    return dstTensor, scaleOut
+
+
 @dataclass
 class DequantParams:
     """include/adv_api/quantization/ascend_dequant_utils.h:26-30"""

@@ -154,6 +154,18 @@ ascq_status ascq_dynamic_quant_per_token(int8_t* dst, float* scaleOut, float* de
                                          ascq_dtype srcT, uint32_t m, uint32_t n, void* stream);
 
 /*
+ * Dynamic MX-FP4 block quantisation (no counterpart in the reference, which always takes its scales as inputs): turns
+ * activations into the operand format of ascq_group_matmul_mxfp4 on the GPU.  For every block of 32 consecutive
+ * elements of a row: amax = max |x|; shared exponent e = floor(log2(amax)) - 2 clamped to [-127, 127] (0 for an
+ * all-zero block), scale byte = e + 127 (0xFF if the block holds a NaN or an infinity, its codes are then 0);
+ * code = e2m1(bf16(x * 2^-e)), both roundings to nearest even, saturating at +-6 -- the conversion chain of
+ * AscendQuant's fp4 destination (ascend_quant_3510_impl.h:994-1032).  dst [m, n/2] bytes (even element in the low
+ * nibble), scale [m, n/32]; n % 32 == 0.
+ */
+ascq_status ascq_dynamic_quant_mxfp4(uint8_t* dst_fp4, uint8_t* scale_e8m0, const void* src, ascq_dtype srcT, uint32_t m,
+                                     uint32_t n, void* stream);
+
+/*
  * AscendDequant.  dst = cast(float(src) * scale), fp32 arithmetic, final cast RINT + saturate.
  *   PER_TENSOR  scalar deqScale overloads, include/adv_api/quantization/ascend_dequant.h:186-281
  *               (scaleScalar; `scale` NULL).

@@ -416,6 +416,44 @@ int ascq_oracle_dynamic_quant_per_token(int8_t* dst, float* scaleOut, float* deq
     return OR_OK;
 }
 
+/* Build-defined dynamic MX-FP4 block quantisation (no reference counterpart): per 32 elements amax -> shared exponent
+ * floor(log2(amax)) - 2 clamped to [-127, 127] (0 when amax == 0) -> byte e + 127 (0xFF with codes 0 when the block
+ * holds NaN / Inf); code = e2m1(bf16(x * 2^-e)) with RINT twice, saturating (the fp4 chain of AscendQuant above). */
+int ascq_oracle_dynamic_quant_mxfp4(uint8_t* dst, uint8_t* scaleOut, const void* src, int srcT, uint32_t m, uint32_t n)
+{
+    if (!dst || !scaleOut || !src || n % 32 != 0) return OR_INVALID;
+    const uint64_t blocks = (uint64_t)m * (n / 32);
+#pragma omp parallel for schedule(static)
+    for (uint64_t b = 0; b < blocks; ++b) {
+        float v[32], amax = 0.f;
+        int bad = 0;
+        for (int i = 0; i < 32; ++i) {
+            v[i] = load_as_f32(src, srcT, (size_t)b * 32 + i);
+            float a = fabsf(v[i]);
+            if (!(a <= 3.4028234663852886e38f)) bad = 1;
+            if (a > amax) amax = a;
+        }
+        int e = 0;
+        if (amax > 0.f) {
+            uint32_t bits = f32_bits(amax);
+            int ex = (int)((bits >> 23) & 0xFF);
+            e = (ex == 0 ? -126 : ex - 127) - 2;
+            if (e < -127) e = -127;
+            if (e > 127) e = 127;
+        }
+        scaleOut[b] = bad ? 0xFFu : (uint8_t)(e + 127);
+        for (int i = 0; i < 32; ++i) {
+            /* x * 2^-e: exact unless it underflows; two steps keep both factors normal, as the kernel does */
+            int h1 = (-e) / 2, h2 = (-e) - h1;
+            float y = (v[i] * ldexpf(1.0f, h1)) * ldexpf(1.0f, h2);
+            uint8_t code = bad ? 0 : orc_f32_to_e2m1(orc_bf16_to_f32(orc_f32_to_bf16_sat(y)), CAST_RINT);
+            uint8_t* d = dst + ((size_t)b * 32 + i) / 2;
+            if (i & 1) *d = (uint8_t)((*d & 0x0Fu) | (code << 4)); else *d = (uint8_t)((*d & 0xF0u) | code);
+        }
+    }
+    return OR_OK;
+}
+
 /* ------------------------------------------------------------------------------------------
  * AscendDequant
  *   per-channel / scalar  impl/adv_api/detail/quantization/dequant/ascend_dequant_common_impl.h:

@@ -141,6 +141,14 @@ def dynamic_quant_per_token(src, srcT, m, n):
     return dst, sc, dq
 
 
+def dynamic_quant_mxfp4(src, srcT, m, n):
+    """Returns (codes uint8 [m, n/2], scale bytes uint8 [m, n/32])."""
+    dst = np.zeros((m, n // 2), np.uint8)
+    sc = np.zeros((m, n // 32), np.uint8)
+    _check(lib().ascq_oracle_dynamic_quant_mxfp4(_p(dst), _p(sc), _p(src), srcT, C.c_uint32(m), C.c_uint32(n)))
+    return dst, sc
+
+
 def dequant_dst_stride(n, dstT):
     return int(lib().ascq_oracle_dequant_dst_stride(n, dstT))
 

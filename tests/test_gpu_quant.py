@@ -180,3 +180,44 @@ def test_quant_is_monotone_at_scale():
     torch.cuda.synchronize()
     d = q[1:].to(torch.int16) - q[:-1].to(torch.int16)
     assert int(d.min()) >= 0 and int(q.min()) == -128 and int(q.max()) == 127
+
+
+@pytest.mark.parametrize("srcT", [O.F16, O.BF16, O.F32])
+@pytest.mark.parametrize("m,n", [(1, 32), (77, 7168), (512, 4096)])
+def test_dynamic_quant_mxfp4(srcT, m, n):
+    """Activations -> MX-FP4 operands on the GPU, bit for bit against the oracle (codes and scale bytes)."""
+    rng = np.random.default_rng(m + n + srcT)
+    x = rng.standard_normal((m, n)).astype(np.float32) * np.exp2(rng.integers(-6, 7, (m, n // 32)).repeat(32, axis=1)).astype(np.float32)
+    x[0, :32] = 0.0
+    if srcT == O.F16:
+        xs = x.astype(np.float16)
+    elif srcT == O.BF16:
+        xs = O.f32_to_bf16_bits(x)
+    else:
+        xs = x
+    want_codes, want_sc = O.dynamic_quant_mxfp4(xs, srcT, m, n)
+    dst = torch.zeros((m, n // 2), dtype=torch.uint8, device=DEV)
+    sc = torch.zeros((m, n // 32), dtype=torch.uint8, device=DEV)
+    ops.DynamicQuantMxfp4(dst, sc, to_dev(xs, srcT))
+    assert np.array_equal(sc.cpu().numpy(), want_sc)
+    assert np.array_equal(dst.cpu().numpy(), want_codes)
+
+
+def test_dynamic_quant_mxfp4_feeds_the_grouped_matmul():
+    """bf16 activations -> ascq_dynamic_quant_mxfp4 -> ascq_group_matmul_mxfp4 reproduces the oracle run on the same
+    quantised operands, and stays close to the unquantised product."""
+    rng = np.random.default_rng(3)
+    groups, N, K = [96, 160], 256, 512
+    M = sum(groups)
+    x = O.f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    B = rng.integers(0, 256, (2, N, K // 2)).astype(np.uint8)
+    sB = (127 + rng.integers(-2, 3, (2, N, K // 32))).astype(np.uint8)
+    dA = torch.zeros((M, K // 2), dtype=torch.uint8, device=DEV)
+    dsA = torch.zeros((M, K // 32), dtype=torch.uint8, device=DEV)
+    ops.DynamicQuantMxfp4(dA, dsA, to_dev(x, O.BF16))
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+    ops.GroupMatmulMxfp4(C, dA, dsA, torch.from_numpy(B).to(DEV), torch.from_numpy(sB).to(DEV), groups, K, N)
+    ops.MatmulStatus()
+    _, want = O.group_matmul_mxfp4(dA.cpu().numpy(), dsA.cpu().numpy(), B, sB, np.array(groups, np.int64), K, N, want_f32=True)
+    got = C.float().cpu().numpy()
+    assert (np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3 * np.abs(want).max()).all()

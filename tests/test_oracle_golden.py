@@ -233,6 +233,28 @@ def test_fp8_decode_matches_ml_dtypes():
                 assert ok[r * 128:(r + 1) * 128].all()
 
 
+# ---- dynamic MX-FP4 block quantiser (build-defined front end) -----------------------------------------
+def test_dynamic_quant_mxfp4_matches_an_independent_restatement():
+    ml_dtypes = pytest.importorskip("ml_dtypes")
+    rng = np.random.default_rng(17)
+    m, n = 24, 256
+    x = (rng.standard_normal((m, n)) * np.exp2(rng.integers(-12, 12, (m, n // 32)).repeat(32, axis=1))).astype(np.float32)
+    x[3, 32:64] = 0.0                                   # an all-zero block
+    codes, sc = O.dynamic_quant_mxfp4(x, O.F32, m, n)
+    xb = x.reshape(m, n // 32, 32)
+    amax = np.abs(xb).max(axis=2)
+    e = np.where(amax > 0, np.floor(np.log2(np.where(amax > 0, amax, 1.0))) - 2, 0).astype(np.int64)
+    assert np.array_equal(sc.astype(np.int64), e + 127)
+    y = (xb.astype(np.float64) * np.exp2(-e)[:, :, None]).astype(np.float32).astype(ml_dtypes.bfloat16).astype(np.float32)
+    want = y.astype(ml_dtypes.float4_e2m1fn).view(np.uint8).reshape(m, n) & 0xF       # RINT, saturating at +-6
+    got = np.stack([codes & 0xF, codes >> 4], axis=2).reshape(m, n)
+    assert np.array_equal(got, want)
+    # what the block decodes to stays within 2 * 2^e of the input: amax / 2^e lies in [4, 8), values above 6 saturate
+    mags = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6])
+    deq = mags[got].reshape(m, n // 32, 32) * np.exp2(e)[:, :, None]
+    assert (np.abs(deq - xb) <= np.exp2(e)[:, :, None] * 2.0 + 1e-30).all()
+
+
 # ---- tests/api/adv_api/tiling/test_tiling.cpp:6540-6712 known answers -----------------------------
 TILING_ANTIQUANT = [
     # srcDims, scaleDims, transpose, outT, (max, min), (live, extra)
