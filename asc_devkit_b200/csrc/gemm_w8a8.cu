@@ -54,7 +54,7 @@ template <int BN, bool PAIR, bool CONV = false> struct Cfg {
     static constexpr int kStages = CONV ? 4 : (192 * 1024) / kStageBytes;  // 4 x 48 KiB, or 6 x 32 KiB; CONV: 4 x 40 KiB
     static constexpr int kThreadsCta = kThreads + (CONV ? 32 * kConvWarps : 0);
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
-    static constexpr int kEpiBytes = 2 * 2 * BN * 4;  // per accumulator: sB[BN] and bias[BN] as fp32
+    static constexpr int kEpiBytes = 2 * 3 * BN * 4;  // per accumulator: sB[BN], bias[BN] (fp32 or int32 bits), aux[BN]
     static constexpr int kOutBytes = kEpiWarps * 16 * kStagePitch;  // per epilogue warp: 16 rows x 64 bf16 columns
     static constexpr size_t kSmemBytes =
         static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes + kOutBytes;
@@ -77,6 +77,9 @@ struct Params {
     const int32_t* biasI32;
     const uint64_t* quantVec;   // low word: fp32 bits, of which the hardware keeps sign, exponent and 10 mantissa bits
     float quantScalar;
+    // kEpiRequant: C is int8 / uint8; quantVec[n] or quantBits is the whole 64-bit fixpipe parameter (scale bits 31:13,
+    // shift count 35:32, shift enable 36, offset 45:37, signed-result flag 46)
+    unsigned long long quantBits;
     // kEpiFloat: operand format (0 = half, 1 = bfloat16) and output type (0 = half, 1 = bfloat16, 2 = float)
     uint32_t abFmt;
     int outKind;
@@ -99,6 +102,8 @@ template <int BN> __device__ __forceinline__ Item decode_item(const Params& p, i
 constexpr int kEpiDequant = 0;  // bf16(((float(acc) * sB[n]) * sA[m]) + bias[n])
 constexpr int kEpiFixpipe = 1;  // SetQuantScalar / SetQuantVector of the reference's Matmul (DEQF16)
 constexpr int kEpiFloat = 2;    // half / bfloat16 operands (kind::f16), fp32 accumulator cast to the output type
+constexpr int kEpiRequant = 3;  // SetQuantScalar / SetQuantVector with an int8 / uint8 result ((V)REQ8)
+constexpr int kBytePitch = 80;  // bytes per staged row of a byte-typed result: 64 B + 16 B pad
 
 // One int8 row segment of 16 weights -> 16 half / bfloat16 values with AscendAntiQuant's arithmetic (the elementwise
 // operator's own code: bfloat16 through fp32, half in half), as two 16-byte chunks.
@@ -371,14 +376,21 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             const float sa = (p.sA != nullptr && m < p.M) ? __ldg(p.sA + m) : 1.0f;
             // this tile's per-channel scale and bias, once, into shared memory (fp32): every thread needs all BN of
             // them and reads them back as warp-wide broadcasts
-            float* sBs = epiScale + acc * 2 * BN;
+            float* sBs = epiScale + acc * 3 * BN;
             float* biasS = sBs + BN;
+            uint32_t* auxS = reinterpret_cast<uint32_t*>(biasS + BN);
             {
                 const int t = threadIdx.x - 64;  // index over the epilogue threads
                 for (int j = t; j < BN; j += 32 * kEpiWarps) {
                     const int n = n0 + j;
                     if constexpr (EPI == kEpiFloat) {
                         (void)n;
+                    } else if constexpr (EPI == kEpiRequant) {
+                        unsigned long long qp = 0;
+                        if (n < p.N) qp = p.quantVec != nullptr ? __ldg(reinterpret_cast<const unsigned long long*>(p.quantVec) + n) : p.quantBits;
+                        sBs[j] = __uint_as_float(static_cast<uint32_t>(qp) & 0xFFFFE000u);
+                        biasS[j] = __int_as_float((p.biasI32 != nullptr && n < p.N) ? __ldg(p.biasI32 + n) : 0);
+                        auxS[j] = static_cast<uint32_t>(qp >> 32) & 0x7FFFu;
                     } else if constexpr (EPI == kEpiFixpipe) {
                         const uint32_t bits = (p.quantVec != nullptr && n < p.N)
                                                   ? static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned long long*>(p.quantVec) + n)) & 0xFFFFE000u
@@ -469,6 +481,34 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     packed[2 * v + 1] = pack_bf16x2_sat(f2, f3);
                 }
             };
+            // (V)REQ8, fixpipe_l0c2gm/scripts/gen_data_s322s8.py:75-97: optional arithmetic shift with saturation to int16,
+            // float(acc) * scale in fp32, clamp to [-256, 255], RINT, + offset, clamp to the int8 or uint8 range.
+            // 32 accumulator columns of this thread's row -> 8 words of four result bytes
+            auto requant32 = [&](const uint32_t(&r)[32], int colInTile, uint32_t* packed) {
+                const float4* sb4 = reinterpret_cast<const float4*>(sBs + colInTile);
+                const int4* bi4 = reinterpret_cast<const int4*>(biasS + colInTile);
+                const uint4* ax4 = reinterpret_cast<const uint4*>(auxS + colInTile);
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const float4 s4 = sb4[v];
+                    const int4 b4 = bi4[v];
+                    const uint4 a4 = ax4[v];
+                    const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+                    const int bi[4] = {b4.x, b4.y, b4.z, b4.w};
+                    const uint32_t ax[4] = {a4.x, a4.y, a4.z, a4.w};
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        int32_t a = static_cast<int32_t>(r[4 * v + e] + static_cast<uint32_t>(bi[e]));
+                        if (ax[e] & 16u) a = max(-32768, min(32767, a >> (ax[e] & 15u)));
+                        const float f = fminf(fmaxf(__fmul_rn(__int2float_rn(a), sc[e]), -256.0f), 255.0f);
+                        int o = __float2int_rn(f) + static_cast<int>((ax[e] >> 5) & 0x1FFu);
+                        o = (ax[e] & 0x4000u) ? max(-128, min(127, o)) : max(0, min(255, o));
+                        word |= static_cast<uint32_t>(o & 0xFF) << (8 * e);
+                    }
+                    packed[v] = word;
+                }
+            };
             // slow path for ragged edges / unaligned outputs: every thread writes its own row segment
             auto store_direct = [&](const uint32_t* packed, int n) {
                 if (m >= p.M || n >= p.N) return;
@@ -509,6 +549,42 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                         }
                         continue;
                     }
+                }
+                if constexpr (EPI == kEpiRequant) {
+                    uint32_t pk[16];
+                    requant32(r0, c2 * 64, pk);
+                    requant32(r1, c2 * 64 + 32, pk + 8);
+                    uint8_t* Cb = reinterpret_cast<uint8_t*>(p.C[0]);
+                    const bool vecB = (p.ldc % 16 == 0) && (p.colOffset % 16 == 0) && ((reinterpret_cast<uintptr_t>(Cb) & 15u) == 0);
+                    if (vecB && n + 64 <= p.N) {
+                        // as below, with 64-byte row segments: every store instruction writes eight of them
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if ((lane >> 4) == h) {
+#pragma unroll
+                                for (int v = 0; v < 4; ++v)
+                                    *reinterpret_cast<uint4*>(stageW + (lane & 15) * kBytePitch + v * 16) =
+                                        make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+                            }
+                            __syncwarp();
+                            const int piece = lane & 3;
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                const int rl = i * 8 + (lane >> 2);
+                                const uint4 val = *reinterpret_cast<const uint4*>(stageW + rl * kBytePitch + piece * 16);
+                                const int gm = m0 + q * 32 + h * 16 + rl;
+                                if (gm < p.M)
+                                    *reinterpret_cast<uint4*>(Cb + static_cast<size_t>(gm) * p.ldc + p.colOffset + n + piece * 16) = val;
+                            }
+                            __syncwarp();
+                        }
+                    } else if (m < p.M) {
+                        uint8_t* crow = Cb + static_cast<size_t>(m) * p.ldc + p.colOffset + n;
+#pragma unroll
+                        for (int j = 0; j < 64; ++j)
+                            if (n + j < p.N) crow[j] = static_cast<uint8_t>(pk[j >> 2] >> ((j & 3) * 8));
+                    }
+                    continue;
                 }
                 uint32_t packed[32];
                 convert32(r0, c2 * 64, packed);
@@ -647,13 +723,16 @@ struct FixpipeArgs {
     const void* aqOffset;
     float aqScaleScalar, aqOffsetScalar;
     int aqHasOffset;
+    // int8 operands, int8 / uint8 result ((V)REQ8): the whole 64-bit parameter of the scalar form
+    int requant;
+    unsigned long long quantBits;
 };
 
 ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
                      const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc, int32_t* accDump,
                      cudaStream_t st, const FixpipeArgs* fix = nullptr, bool multicast = false)
 {
-    const int epi = fix ? (fix->floatKind ? kEpiFloat : kEpiFixpipe) : kEpiDequant;
+    const int epi = fix ? (fix->floatKind ? kEpiFloat : (fix->requant ? kEpiRequant : kEpiFixpipe)) : kEpiDequant;
     const int elemBytes = (epi == kEpiFloat) ? 2 : 1;
     if (!A || !B_nk) return fail(ASCQ_ERR_INVALID_ARG, "A and B must not be NULL");
     if (nBufs < 0 || nBufs > kMaxPeers) return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
@@ -691,6 +770,7 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         p.biasI32 = fix->biasI32;
         p.quantVec = fix->quantVec;
         p.quantScalar = fix->quantScalar;
+        p.quantBits = fix->quantBits;
     }
 
     // Tile shape: the one with the smallest estimated time = waves x time of one wave.  One wave of CTA pairs on
@@ -729,6 +809,10 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     if (epi == kEpiFloat) {
         if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, p, st);
         return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, p, st) : launch<128, false, kEpiFloat>(ta, tb, p, st);
+    }
+    if (epi == kEpiRequant) {
+        if (mode == 2) return launch<256, true, kEpiRequant>(ta, tb, p, st);
+        return mode == 1 ? launch<256, false, kEpiRequant>(ta, tb, p, st) : launch<128, false, kEpiRequant>(ta, tb, p, st);
     }
     if (epi == kEpiFixpipe) {
         if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, p, st);
@@ -796,6 +880,23 @@ extern "C" ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const 
         return fail(ASCQ_ERR_ALIGNMENT, "quantVector must be 8-byte aligned");
     void* bufs[1] = {C_f16};
     const FixpipeArgs fix{bias_i32, quantVector, quantScalar, 0, 0, 0, 0, nullptr, nullptr, 0.f, 0.f, 0};
+    return run_w8a8(bufs, 1, 0, 0, A, B_nk, nullptr, nullptr, nullptr, M, N, K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fix);
+}
+
+// ---- int8 matmul with the reference's fixpipe requantisation of the result (int8 / uint8 output) -----------------
+extern "C" ascq_status ascq_matmul_i8_requant(void* C_b8, const int8_t* A, const int8_t* B_nk, const int32_t* bias_i32,
+                                              const uint64_t* quantVector, uint64_t quantScalar, int M, int N, int K, int ldc,
+                                              void* stream)
+{
+    if (!C_b8) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
+    if (quantVector && (reinterpret_cast<uintptr_t>(quantVector) & 7u))
+        return fail(ASCQ_ERR_ALIGNMENT, "quantVector must be 8-byte aligned");
+    void* bufs[1] = {C_b8};
+    FixpipeArgs fix{};
+    fix.biasI32 = bias_i32;
+    fix.quantVec = quantVector;
+    fix.requant = 1;
+    fix.quantBits = quantScalar;
     return run_w8a8(bufs, 1, 0, 0, A, B_nk, nullptr, nullptr, nullptr, M, N, K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fix);
 }
 

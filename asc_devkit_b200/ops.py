@@ -257,6 +257,18 @@ def MatmulI8Quant(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, bias: Op
     return C
 
 
+def MatmulI8Requant(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                    quantVector: Optional[torch.Tensor] = None, quantScalar: int = 0, stream=None):
+    """int8 matmul whose result is requantised to int8 / uint8 by the fixpipe rule ((V)REQ8): ``ascq_matmul_i8_requant``.
+    ``C`` is an int8 or uint8 [M, N] tensor, ``quantVector`` an int64 tensor holding the 64-bit parameter words,
+    ``quantScalar`` the same word as a Python int (used when ``quantVector`` is None)."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    L.check(L.lib().ascq_matmul_i8_requant(_ptr(C), _ptr(A), _ptr(B_nk), _ptr(bias), _ptr(quantVector),
+                                           int(quantScalar) & 0xFFFFFFFFFFFFFFFF, M, N, K, C.stride(0), _stream(stream)))
+    return C
+
+
 def TransposeI8KnToNk(B_nk: torch.Tensor, B_kn: torch.Tensor, stream=None):
     K, N = B_kn.shape
     L.check(L.lib().ascq_transpose_i8_kn_to_nk(_ptr(B_nk), _ptr(B_kn), K, N, _stream(stream)))

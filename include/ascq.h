@@ -342,6 +342,24 @@ ascq_status ascq_matmul_w8a8_scatter(void* const* C_bufs, int nBufs, int firstBu
 ascq_status ascq_matmul_i8_quant(void* C_f16, const int8_t* A, const int8_t* B_nk, const int32_t* bias_i32,
                                  const uint64_t* quantVector, float quantScalar, int M, int N, int K, int ldc,
                                  void* stream);
+
+/*
+ * The same matmul with an int8 or uint8 result: the fixpipe's requantisation (quant_processor_fixpipe.h:93-95 and
+ * 201-203, modes REQ8 / VREQ8), with the arithmetic of the reference's own description of it
+ * (examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/fixpipe_l0c2gm/scripts/gen_data_s322s8.py:39-97; field
+ * layout docs/zh/api/SIMD-API/基础API/矩阵计算（ISASI）/矩阵计算的搬出/关键特性说明/随路量化.md:53-58).  Per column n the
+ * 64-bit parameter q = quantVector[n] (or quantScalar when quantVector is NULL) holds
+ *   bits 31:13  scale: fp32 sign, exponent and the top 10 mantissa bits      bit  36     shift enable
+ *   bits 35:32  shift count                                                   bits 45:37  offset (0..511)
+ *   bit  46     1: int8 result, 0: uint8 result
+ * and   a = acc + bias_i32[n];   if shift enabled: a = sat_int16(a >> count);
+ *       t = RINT(clamp(float(a) * scale, -256, 255)) + offset;   C = clamp(t, -128..127 or 0..255).
+ * No ReLU stage (the Matmul object does not expose one), so negative values take the same scale.  C is a byte
+ * matrix [M, ldc]; everything else as in ascq_matmul_i8_quant.
+ */
+ascq_status ascq_matmul_i8_requant(void* C_b8, const int8_t* A, const int8_t* B_nk, const int32_t* bias_i32,
+                                   const uint64_t* quantVector, uint64_t quantScalar, int M, int N, int K, int ldc,
+                                   void* stream);
 ascq_status ascq_transpose_i8_kn_to_nk(int8_t* B_nk, const int8_t* B_kn, int K, int N, void* stream);
 
 /*

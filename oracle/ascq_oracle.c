@@ -722,6 +722,55 @@ int ascq_oracle_matmul_i8_quant(uint16_t* C, const int8_t* A, const int8_t* B, c
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Fixpipe requantisation int32 -> int8 / uint8 ((V)REQ8), following the reference's description of the unit:
+ * examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/fixpipe_l0c2gm/scripts/gen_data_s322s8.py:39-64
+ * (fields of the 64-bit parameter) and :75-97 (arithmetic), without the ReLU branch (negative values take the
+ * same scale).  The scale is read as the fp32 whose low 13 bits are cleared; for a zero exponent field that
+ * differs from the script's (1 + m/1024) * 2^-127, but either product is far below one half and rounds to 0.
+ * Returns the result as an integer in [-128, 255].
+ * ---------------------------------------------------------------------------------------- */
+int ascq_oracle_req8(int32_t data, uint64_t q)
+{
+    uint32_t bits = (uint32_t)(q & 0xFFFFFFFFull) & 0xFFFFE000u;
+    float alpha; memcpy(&alpha, &bits, 4);
+    const unsigned shift = (unsigned)(q >> 32) & 15u, mcb = (unsigned)(q >> 36) & 1u;
+    const int offset = (int)((q >> 37) & 0x1FFu), sign = (int)((q >> 46) & 1u);
+    if (mcb) {
+        data >>= shift; /* arithmetic */
+        if (data < -32768) data = -32768;
+        if (data > 32767) data = 32767;
+    }
+    volatile float f = (float)data * alpha; /* one fp32 rounding, as numpy does for float32 * python float */
+    float c = f;
+    if (!(c >= -256.0f)) c = -256.0f;
+    if (c > 255.0f) c = 255.0f;
+    int t = (int)nearbyintf(c) + offset;
+    if (sign) { if (t < -128) t = -128; if (t > 127) t = 127; }
+    else { if (t < 0) t = 0; if (t > 255) t = 255; }
+    return t;
+}
+
+/* int8 matmul + int32 bias + (V)REQ8 (Matmul<int8, int8, int8> with SetQuantScalar / SetQuantVector,
+ * quant_processor_fixpipe.h:93-95, 201-203).  C is a byte matrix [M, ldc]. */
+int ascq_oracle_matmul_i8_requant(uint8_t* C, const int8_t* A, const int8_t* B, const int32_t* bias,
+                                  const uint64_t* quantVec, uint64_t quantScalar, int M, int N, int K, int ldc)
+{
+    if (!C || !A || !B || M < 0 || N < 0 || K < 0) return OR_INVALID;
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        for (int n = 0; n < N; ++n) {
+            int32_t acc = 0;
+            const int8_t* a = A + (size_t)m * K;
+            const int8_t* b = B + (size_t)n * K;
+            for (int k = 0; k < K; ++k) acc += (int32_t)a[k] * (int32_t)b[k];
+            if (bias) acc = (int32_t)((uint32_t)acc + (uint32_t)bias[n]);
+            C[(size_t)m * ldc + n] = (uint8_t)(ascq_oracle_req8(acc, quantVec ? quantVec[n] : quantScalar) & 0xFF);
+        }
+    }
+    return OR_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
  * MX-FP4 grouped matmul.  Golden semantics of
  * examples/.../matmul_mxfp4_high_performance/scripts/gen_data.py:38-72 and
  * examples/.../03_matrix_compute/mmad_mx/scripts/gen_data.py: operands are dequantised

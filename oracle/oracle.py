@@ -231,6 +231,26 @@ def matmul_i8_quant(A, B_nk, bias=None, quantVector=None, quantScalar=1.0):
     return Cq
 
 
+def req8(data, q):
+    """One value through the fixpipe requantisation: int32 ``data``, 64-bit parameter ``q`` -> int in [-128, 255]."""
+    f = lib().ascq_oracle_req8
+    f.restype = C.c_int
+    f.argtypes = [C.c_int32, C.c_uint64]
+    return int(f(int(data), int(q) & 0xFFFFFFFFFFFFFFFF))
+
+
+def matmul_i8_requant(A, B_nk, bias=None, quantVector=None, quantScalar=0):
+    """int8 matmul + int32 bias, result requantised to bytes as the fixpipe does ((V)REQ8); returns [M, N] uint8."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    Cq = np.zeros((M, N), np.uint8)
+    f = lib().ascq_oracle_matmul_i8_requant
+    f.restype = C.c_int
+    f.argtypes = [C.c_void_p] * 5 + [C.c_uint64] + [C.c_int] * 4
+    _check(f(_p(Cq), _p(A), _p(B_nk), _p(bias), _p(quantVector), int(quantScalar) & 0xFFFFFFFFFFFFFFFF, M, N, K, N))
+    return Cq
+
+
 def group_matmul_mxfp4(A, sA, B, sB, groupList, K, N, want_f32=False):
     """A [sumM, K/2] u8, sA [sumM, K/32] u8, B [G, N, K/2] u8, sB [G, N, K/32] u8, groupList int64 [G]."""
     G = int(len(groupList))

@@ -60,6 +60,50 @@ CASES = [
 ]
 
 
+FIXPIPE = "examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/fixpipe_l0c2gm/scripts/gen_data_s322s8.py"
+
+
+def fixpipe_req8(reference):
+    """The fixpipe sample's int32 -> int8 generator has no command line: its functions are called directly.  Two
+    fixtures: the sample's own matmul case (vector parameters, no ReLU, row-major output), and its scalar routine
+    ``req8_pre`` on single values that exercise rounding, the offset, both result types and the shift mode."""
+    path = os.path.join(reference, FIXPIPE)
+    with tempfile.TemporaryDirectory() as tmp:
+        cwd = os.getcwd()
+        os.chdir(tmp)
+        try:
+            mod = runpy.run_path(path)          # seeds numpy's global generator with 9
+            mod["gen_golden_data"](1, 2, 0)
+            x1 = np.fromfile("input/x1_gm.bin", np.int8).reshape(2, 128, 64).transpose(1, 0, 2).reshape(128, 128)
+            out = {"x1_gm": np.ascontiguousarray(x1),
+                   "x2_gm": np.fromfile("input/x2_gm.bin", np.int8).reshape(128, 256),
+                   "quant_pre": np.fromfile("input/quant_pre.bin", np.uint64),
+                   "golden": np.fromfile("output/golden.bin", np.int8).reshape(128, 256)}
+        finally:
+            os.chdir(cwd)
+    np.savez_compressed(os.path.join(HERE, "fixpipe_req8_matmul.npz"), **out)
+    print("fixpipe_req8_matmul", {k: v.shape for k, v in out.items()})
+
+    rng = np.random.default_rng(109)
+    n = 6000
+    scale = rng.uniform(0.0005, 3.0, n).astype(np.float32) * rng.choice([1.0, 1.0, 1.0, -1.0], n).astype(np.float32)
+    scale[:64] = rng.choice([0.5, 0.25, 1.5, 2.0, 0.125], 64).astype(np.float32)        # products that land on .5 ties
+    bits = scale.view(np.uint32).astype(np.uint64)
+    bits[64:96] = rng.integers(0, 1 << 23, 32).astype(np.uint64)                           # zero exponent field
+    data = np.where(rng.random(n) < 0.5, rng.integers(-600, 600, n), rng.integers(-(1 << 31), 1 << 31, n)).astype(np.int32)
+    data[:64] = rng.integers(-511, 511, 64)
+    offset = np.where(rng.random(n) < 0.4, 0, rng.integers(0, 512, n)).astype(np.uint64)
+    sign = rng.integers(0, 2, n).astype(np.uint64)
+    mcb = (rng.random(n) < 0.3).astype(np.uint64)
+    shift = rng.integers(0, 16, n).astype(np.uint64)
+    q = bits | (shift << np.uint64(32)) | (mcb << np.uint64(36)) | (offset << np.uint64(37)) | (sign << np.uint64(46))
+    req8 = mod["req8_pre"]
+    with np.errstate(all="ignore"):
+        res = np.array([int(req8(np.int32(d), int(w), int(w) & 0xFFFFFFFF)) for d, w in zip(data, q)], np.int16)
+    np.savez_compressed(os.path.join(HERE, "fixpipe_req8_values.npz"), data=data, quant_pre=q, golden=res)
+    print("fixpipe_req8_values", n)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("ASC_DEVKIT_ROOT"), help="root of the asc-devkit tree (or set ASC_DEVKIT_ROOT)")
@@ -88,6 +132,7 @@ def main():
             out["golden"] = out["golden"][:KEEP_ROWS].copy()
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
         print(name, {k: v.shape for k, v in out.items()})
+    fixpipe_req8(args.reference)
 
 
 if __name__ == "__main__":

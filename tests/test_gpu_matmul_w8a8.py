@@ -167,3 +167,68 @@ def test_matmul_quant_matches_oracle(M, N, K, vector, tile, monkeypatch):
                       torch.from_numpy(qv.view(np.int64)).to(DEV) if vector else None, 0.37)
     ops.MatmulStatus()
     assert_bits_equal(C.cpu().numpy().view(np.uint16), want.view(np.uint16), f"{M}x{N}x{K}")
+
+
+# ---- fixpipe requantisation of the result to int8 / uint8 ((V)REQ8) -----------------------------------------------
+def _req8_words(rng, n, scale_lo, scale_hi, signed=None, shift=False):
+    """Random 64-bit fixpipe parameters: fp32 scale bits, offset in bits 45:37, result type in bit 46, optional shift."""
+    s = rng.uniform(scale_lo, scale_hi, n).astype(np.float32) * rng.choice([1.0, 1.0, -1.0], n).astype(np.float32)
+    w = s.view(np.uint32).astype(np.uint64)
+    w |= np.where(rng.random(n) < 0.5, 0, rng.integers(0, 512, n)).astype(np.uint64) << np.uint64(37)
+    sg = rng.integers(0, 2, n) if signed is None else np.full(n, int(signed))
+    w |= sg.astype(np.uint64) << np.uint64(46)
+    if shift:
+        on = (rng.random(n) < 0.5).astype(np.uint64)
+        w |= (on << np.uint64(36)) | (rng.integers(0, 9, n).astype(np.uint64) << np.uint64(32))
+    return w
+
+
+def test_fixpipe_req8_sample_golden_through_the_gpu():
+    """The fixpipe sample's int32 -> int8 case (vector parameters, no ReLU): same bytes as its generator wrote."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fixpipe_req8_matmul.npz"))
+    A = torch.from_numpy(g["x1_gm"]).to(DEV)
+    B_nk = torch.from_numpy(np.ascontiguousarray(g["x2_gm"].T)).to(DEV)
+    qv = torch.from_numpy(g["quant_pre"].view(np.int64)).to(DEV)
+    C = torch.zeros((128, 256), dtype=torch.int8, device=DEV)
+    ops.MatmulI8Requant(C, A, B_nk, None, qv)
+    ops.MatmulStatus()
+    assert np.array_equal(C.cpu().numpy(), g["golden"])
+
+
+@pytest.mark.parametrize("M,N,K,vector", [(128, 128, 128, True), (300, 520, 272, True), (257, 384, 1024, False), (4096, 512, 512, True)])
+@pytest.mark.parametrize("tile", ["pair", "wide", "narrow"])
+def test_matmul_requant_matches_oracle(M, N, K, vector, tile, monkeypatch):
+    monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
+    rng = np.random.default_rng(7 * M + N + K)
+    A = rng.integers(-20, 21, (M, K), dtype=np.int8)
+    B = rng.integers(-20, 21, (N, K), dtype=np.int8)
+    bias = rng.integers(-500, 500, N, dtype=np.int32)
+    spread = 115.0 * np.sqrt(K)  # standard deviation of an accumulator entry
+    qv = _req8_words(rng, N, 20.0 / spread, 200.0 / spread, shift=True) if vector else None
+    qs = int(_req8_words(rng, 1, 60.0 / spread, 61.0 / spread, signed=False)[0])
+    want = O.matmul_i8_requant(A, B, bias, qv, qs)
+    assert len(np.unique(want)) > 100, "the case must not saturate everywhere"
+    C = torch.full((M, N), 77, dtype=torch.uint8, device=DEV)
+    ops.MatmulI8Requant(C, torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV), torch.from_numpy(bias).to(DEV),
+                        torch.from_numpy(qv.view(np.int64)).to(DEV) if vector else None, qs)
+    ops.MatmulStatus()
+    got = C.cpu().numpy()
+    bad = np.argwhere(got != want)
+    assert bad.size == 0, f"{len(bad)} bytes differ, first at {bad[0]}: got {got[tuple(bad[0])]} want {want[tuple(bad[0])]}"
+
+
+def test_matmul_requant_into_a_wider_unaligned_matrix():
+    """ldc that is not a multiple of 16 takes the byte-by-byte store path; columns beyond N stay untouched."""
+    M, N, K, ldc = 150, 200, 128, 213
+    rng = np.random.default_rng(5)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    qv = _req8_words(rng, N, 0.0005, 0.005)
+    want = O.matmul_i8_requant(A, B, None, qv)
+    C = torch.full((M, ldc), 99, dtype=torch.uint8, device=DEV)
+    ops.MatmulI8Requant(C, torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV), None, torch.from_numpy(qv.view(np.int64)).to(DEV))
+    ops.MatmulStatus()
+    got = C.cpu().numpy()
+    assert np.array_equal(got[:, :N], want)
+    assert (got[:, N:] == 99).all()

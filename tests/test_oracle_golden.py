@@ -186,6 +186,25 @@ def test_matmul_quant_sample_golden(golden_dir, name):
     assert np.array_equal(out.view(np.uint16), g["golden"].view(np.uint16))
 
 
+# ---- int8 matmul with the fixpipe requantisation to int8 / uint8 (fixpipe_l0c2gm sample, (V)REQ8) --------
+def test_fixpipe_req8_values_golden(golden_dir):
+    # fixpipe_l0c2gm/scripts/gen_data_s322s8.py:75-97 (req8_pre) called value by value when the fixture was made:
+    # ties, offsets, both result types, the shift mode, scales with a zero exponent field
+    g = _load(golden_dir, "fixpipe_req8_values")
+    got = np.array([O.req8(d, q) for d, q in zip(g["data"], g["quant_pre"])], np.int16)
+    assert np.array_equal(got, g["golden"])
+
+
+def test_fixpipe_req8_matmul_sample_golden(golden_dir):
+    # gen_data_s322s8.py:147-175 with vector parameters, no ReLU, row-major output; B stored [K, N]
+    g = _load(golden_dir, "fixpipe_req8_matmul")
+    out = O.matmul_i8_requant(g["x1_gm"], np.ascontiguousarray(g["x2_gm"].T), None, g["quant_pre"])
+    assert np.array_equal(out.view(np.int8), g["golden"])
+    # the scalar form with the same word gives the same matrix
+    out2 = O.matmul_i8_requant(g["x1_gm"], np.ascontiguousarray(g["x2_gm"].T), None, None, int(g["quant_pre"][0]))
+    assert np.array_equal(out2, out)
+
+
 # ---- MX matmul with fp8 operands (matmul_mx and mmad_mx samples) --------------------------------------
 def test_matmul_mx_sample_golden(golden_dir):
     # matmul_mx/scripts/gen_data.py: e5m2 x e5m2, m=32 n=k=128, B stored [K,N], scaleB stored [sk/2, n, 2]
