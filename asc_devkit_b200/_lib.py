@@ -69,6 +69,7 @@ SIGNATURES = {
     "ascq_matmul_i8_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _vp]),
     "ascq_matmul_i8_requant": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_uint64, _i, _i, _i, _i, _vp]),
     "ascq_transpose_i8_kn_to_nk": (_i, [_vp, _vp, _i, _i, _vp]),
+    "ascq_matmul_f16_quant": (_i, [_vp, _vp, _vp, _i, _vp, C.c_uint64, _i, _i, _i, _i, _vp]),
     "ascq_matmul_f16": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "ascq_matmul_w8a16": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _f, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_matmul_w8a16_workspace_size": (C.c_size_t, [_i, _i]),

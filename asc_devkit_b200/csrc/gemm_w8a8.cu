@@ -383,9 +383,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 const int t = threadIdx.x - 64;  // index over the epilogue threads
                 for (int j = t; j < BN; j += 32 * kEpiWarps) {
                     const int n = n0 + j;
-                    if constexpr (EPI == kEpiFloat) {
-                        (void)n;
-                    } else if constexpr (EPI == kEpiRequant) {
+                    if constexpr (EPI == kEpiFloat || EPI == kEpiRequant) {
+                        if (EPI == kEpiFloat && p.outKind != 3) continue;  // only the quantising form has per-column parameters
                         unsigned long long qp = 0;
                         if (n < p.N) qp = p.quantVec != nullptr ? __ldg(reinterpret_cast<const unsigned long long*>(p.quantVec) + n) : p.quantBits;
                         sBs[j] = __uint_as_float(static_cast<uint32_t>(qp) & 0xFFFFE000u);
@@ -483,6 +482,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             };
             // (V)REQ8, fixpipe_l0c2gm/scripts/gen_data_s322s8.py:75-97: optional arithmetic shift with saturation to int16,
             // float(acc) * scale in fp32, clamp to [-256, 255], RINT, + offset, clamp to the int8 or uint8 range.
+            // (V)QF322B8_PRE (fp32 accumulator of a half / bfloat16 matmul, scripts/gen_data_f322s8.py:75-97): the same
+            // from the multiplication on.
             // 32 accumulator columns of this thread's row -> 8 words of four result bytes
             auto requant32 = [&](const uint32_t(&r)[32], int colInTile, uint32_t* packed) {
                 const float4* sb4 = reinterpret_cast<const float4*>(sBs + colInTile);
@@ -499,9 +500,15 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     uint32_t word = 0;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        int32_t a = static_cast<int32_t>(r[4 * v + e] + static_cast<uint32_t>(bi[e]));
-                        if (ax[e] & 16u) a = max(-32768, min(32767, a >> (ax[e] & 15u)));
-                        const float f = fminf(fmaxf(__fmul_rn(__int2float_rn(a), sc[e]), -256.0f), 255.0f);
+                        float x;
+                        if constexpr (EPI == kEpiFloat) {  // fp32 accumulator: the shift fields do not apply
+                            x = __uint_as_float(r[4 * v + e]);
+                        } else {
+                            int32_t a = static_cast<int32_t>(r[4 * v + e] + static_cast<uint32_t>(bi[e]));
+                            if (ax[e] & 16u) a = max(-32768, min(32767, a >> (ax[e] & 15u)));
+                            x = __int2float_rn(a);
+                        }
+                        const float f = fminf(fmaxf(__fmul_rn(x, sc[e]), -256.0f), 255.0f);
                         int o = __float2int_rn(f) + static_cast<int>((ax[e] >> 5) & 0x1FFu);
                         o = (ax[e] & 0x4000u) ? max(-128, min(127, o)) : max(0, min(255, o));
                         word |= static_cast<uint32_t>(o & 0xFF) << (8 * e);
@@ -550,7 +557,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                         continue;
                     }
                 }
-                if constexpr (EPI == kEpiRequant) {
+                if (EPI == kEpiRequant || (EPI == kEpiFloat && p.outKind == 3)) {
                     uint32_t pk[16];
                     requant32(r0, c2 * 64, pk);
                     requant32(r1, c2 * 64 + 32, pk + 8);
@@ -716,7 +723,7 @@ struct FixpipeArgs {
     float quantScalar;
     int floatKind;     // 0: int8 operands + fixpipe epilogue; 1: half / bfloat16 operands (kEpiFloat)
     uint32_t abFmt;    // floatKind: 0 = half, 1 = bfloat16
-    int outKind;       // floatKind: 0 = half, 1 = bfloat16, 2 = float
+    int outKind;       // floatKind: 0 = half, 1 = bfloat16, 2 = float, 3 = int8 / uint8 through the fixpipe quantisation
     // floatKind with B_nk int8: AscendAntiQuant inside the matmul (converter warps)
     int convert;
     const void* aqScale;
@@ -911,6 +918,24 @@ extern "C" ascq_status ascq_matmul_f16(void* C, ascq_dtype cT, const void* A, co
     void* bufs[1] = {C};
     const FixpipeArgs fa{nullptr, nullptr, 0.f, 1, abT == ASCQ_DT_BF16 ? 1u : 0u, cT == ASCQ_DT_F16 ? 0 : (cT == ASCQ_DT_BF16 ? 1 : 2),
                          0, nullptr, nullptr, 0.f, 0.f, 0};
+    return run_w8a8(bufs, 1, 0, 0, static_cast<const int8_t*>(A), static_cast<const int8_t*>(B_nk), nullptr, nullptr, nullptr, M, N,
+                    K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fa);
+}
+
+extern "C" ascq_status ascq_matmul_f16_quant(void* C_b8, const void* A, const void* B_nk, ascq_dtype abT, const uint64_t* quantVector,
+                                             uint64_t quantScalar, int M, int N, int K, int ldc, void* stream)
+{
+    if (!C_b8) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
+    if (abT != ASCQ_DT_F16 && abT != ASCQ_DT_BF16) return fail(ASCQ_ERR_UNSUPPORTED, "operands must be half or bfloat16_t");
+    if (quantVector && (reinterpret_cast<uintptr_t>(quantVector) & 7u))
+        return fail(ASCQ_ERR_ALIGNMENT, "quantVector must be 8-byte aligned");
+    void* bufs[1] = {C_b8};
+    FixpipeArgs fa{};
+    fa.floatKind = 1;
+    fa.abFmt = abT == ASCQ_DT_BF16 ? 1u : 0u;
+    fa.outKind = 3;
+    fa.quantVec = quantVector;
+    fa.quantBits = quantScalar;
     return run_w8a8(bufs, 1, 0, 0, static_cast<const int8_t*>(A), static_cast<const int8_t*>(B_nk), nullptr, nullptr, nullptr, M, N,
                     K, ldc, nullptr, static_cast<cudaStream_t>(stream), &fa);
 }

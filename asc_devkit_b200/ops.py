@@ -284,6 +284,17 @@ def MatmulF16(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, stream=None)
     return C
 
 
+def MatmulF16Quant(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, quantVector: Optional[torch.Tensor] = None,
+                   quantScalar: int = 0, stream=None):
+    """half / bfloat16 matmul whose fp32 result is quantised to int8 / uint8 by the fixpipe rule ((V)QF322B8_PRE):
+    ``ascq_matmul_f16_quant``.  Parameter words as for ``MatmulI8Requant``."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    L.check(L.lib().ascq_matmul_f16_quant(_ptr(C), _ptr(A), _ptr(B_nk), dtype_code(A), _ptr(quantVector),
+                                          int(quantScalar) & 0xFFFFFFFFFFFFFFFF, M, N, K, C.stride(0), _stream(stream)))
+    return C
+
+
 def MatmulW8A16(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, offset, scale, workspace: Optional[torch.Tensor] = None,
                 stream=None):
     """Weight-only-quantised matmul (``ascq_matmul_w8a16``): B_nk int8 [N, K] goes through AscendAntiQuant (per-channel

@@ -369,6 +369,18 @@ ascq_status ascq_transpose_i8_kn_to_nk(int8_t* B_nk, const int8_t* B_kn, int K, 
  */
 ascq_status ascq_matmul_f16(void* C, ascq_dtype cT, const void* A, const void* B_nk, ascq_dtype abT, int M, int N, int K,
                             int ldc, void* stream);
+
+/*
+ * The same matmul with an int8 or uint8 result: the fixpipe's quantisation of an fp32 accumulator
+ * (Matmul<half, half, int8_t> with SetQuantScalar / SetQuantVector, quant_processor_fixpipe.h:95-97 and 203-205, modes
+ * QF322B8_PRE / VQF322B8_PRE; arithmetic of .../fixpipe_l0c2gm/scripts/gen_data_f322s8.py:75-97).  The 64-bit
+ * parameter has the layout given for ascq_matmul_i8_requant; its shift fields do not apply to this mode:
+ *       t = RINT(clamp(acc * scale, -256, 255)) + offset;   C = clamp(t, -128..127 or 0..255).
+ * The accumulator is the tensor cores' fp32 sum, so a product that lands within rounding distance of a tie can come
+ * out one step away from a result computed with another summation order.
+ */
+ascq_status ascq_matmul_f16_quant(void* C_b8, const void* A, const void* B_nk, ascq_dtype abT, const uint64_t* quantVector,
+                                  uint64_t quantScalar, int M, int N, int K, int ldc, void* stream);
 /*
  * Weight-only-quantised matmul: A half / bfloat16, B int8 dequantised on its way to the tensor cores with
  * Matmul::SetAntiQuantScalar / SetAntiQuantVector (include/adv_api/matmul/matmul.h:155-168; the reference converts each

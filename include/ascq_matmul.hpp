@@ -14,6 +14,7 @@
 //   int8 x int8 -> half                         SetQuantScalar | SetQuantVector ascq_matmul_i8_quant   (DEQF16 / VDEQF16)
 //   int8 x int8 -> int8 | uint8                 SetQuantScalar | SetQuantVector ascq_matmul_i8_requant (REQ8 / VREQ8)
 //   half x half, bf16 x bf16 -> half|bf16|float -                               ascq_matmul_f16
+//   half x half, bf16 x bf16 -> int8 | uint8    SetQuantScalar | SetQuantVector ascq_matmul_f16_quant  (QF322B8_PRE / VQF322B8_PRE)
 //   half|bf16 x int8 -> half|bf16|float         SetAntiQuantScalar | ...Vector  ascq_matmul_w8a16 (needs SetWorkspace)
 //   fp4x2_e2m1 x fp4x2_e2m1 (with scale) -> bf16     SetTensorScaleA / B        ascq_group_matmul_mxfp4 (one group; SetWorkspace)
 //   fp8 x fp8 (with scale) -> bf16 | float           SetTensorScaleA / B        ascq_group_matmul_mxfp8 (one group; SetWorkspace)
@@ -294,6 +295,10 @@ private:
             if (!quantSet_) throw ascq::Error(ASCQ_ERR_INVALID_ARG, "int8 -> int8 needs SetQuantScalar or SetQuantVector");
             check(ascq_matmul_i8_requant(gm.ptr, a_ptr<int8_t>(), static_cast<const int8_t*>(bNk), bias_ptr<int32_t>(), quantVector_,
                                          quantScalar_, m_, n_, k_, ldc, stream_));
+        } else if constexpr (kFloat16 && !kMx && one_of<DstT, int8_t, uint8_t>) {
+            if (bias_) throw ascq::Error(ASCQ_ERR_UNSUPPORTED, "half / bfloat16 matmul: the bias is not mirrored");
+            if (!quantSet_) throw ascq::Error(ASCQ_ERR_INVALID_ARG, "half -> int8 needs SetQuantScalar or SetQuantVector");
+            check(ascq_matmul_f16_quant(gm.ptr, a_, bNk, ascq::DTypeOf<SrcAT>::value, quantVector_, quantScalar_, m_, n_, k_, ldc, stream_));
         } else if constexpr (kFloat16 && !kMx && one_of<DstT, half, bfloat16_t, float>) {
             if (bias_) throw ascq::Error(ASCQ_ERR_UNSUPPORTED, "half / bfloat16 matmul: the bias is not mirrored");
             check(ascq_matmul_f16(gm.ptr, ascq::DTypeOf<DstT>::value, a_, bNk, ascq::DTypeOf<SrcAT>::value, m_, n_, k_, ldc, stream_));

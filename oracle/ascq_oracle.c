@@ -847,6 +847,46 @@ int ascq_oracle_matmul_f16(uint16_t* C16, float* C_f32, int cT, const uint16_t* 
     return OR_OK;
 }
 
+/* Fixpipe quantisation of an fp32 accumulator to int8 / uint8 ((V)QF322B8_PRE), following
+ * examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/fixpipe_l0c2gm/scripts/gen_data_f322s8.py:75-97 without its
+ * ReLU branch: data * scale in fp32, clamp to [-256, 255], RINT, + offset, clamp to the result type.  The shift
+ * fields of the parameter word do not apply to this mode (随路量化.md:54-55) and are ignored. */
+int ascq_oracle_qf322b8(float data, uint64_t q)
+{
+    uint32_t bits = (uint32_t)(q & 0xFFFFFFFFull) & 0xFFFFE000u;
+    float alpha; memcpy(&alpha, &bits, 4);
+    const int offset = (int)((q >> 37) & 0x1FFu), sign = (int)((q >> 46) & 1u);
+    volatile float f = data * alpha;
+    float c = f;
+    if (!(c >= -256.0f)) c = -256.0f;
+    if (c > 255.0f) c = 255.0f;
+    int t = (int)nearbyintf(c) + offset;
+    if (sign) { if (t < -128) t = -128; if (t > 127) t = 127; }
+    else { if (t < 0) t = 0; if (t > 255) t = 255; }
+    return t;
+}
+
+/* half / bfloat16 matmul (products summed in double, rounded once to fp32) + (V)QF322B8_PRE: Matmul<half, half, int8>
+ * with SetQuantScalar / SetQuantVector (quant_processor_fixpipe.h:95-97, 203-205).  C is a byte matrix [M, ldc]. */
+int ascq_oracle_matmul_f16_quant(uint8_t* C, const uint16_t* A, const uint16_t* B, int abT, const uint64_t* quantVec,
+                                 uint64_t quantScalar, int M, int N, int K, int ldc)
+{
+    if (!C || !A || !B || M < 0 || N < 0 || K < 0) return OR_INVALID;
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            double acc = 0.0;
+            for (int k = 0; k < K; ++k) {
+                const uint16_t a = A[(size_t)m * K + k], b = B[(size_t)n * K + k];
+                const double af = abT == DT_BF16 ? (double)orc_bf16_to_f32(a) : (double)orc_f16_to_f32(a);
+                const double bf = abT == DT_BF16 ? (double)orc_bf16_to_f32(b) : (double)orc_f16_to_f32(b);
+                acc += af * bf;
+            }
+            C[(size_t)m * ldc + n] = (uint8_t)(ascq_oracle_qf322b8((float)acc, quantVec ? quantVec[n] : quantScalar) & 0xFF);
+        }
+    return OR_OK;
+}
+
 /* MX matmul with 8-bit operands (fp8_e4m3fn / fp8_e5m2, one E8M0 scale per 32 elements of K), grouped like the fp4
  * one.  Golden formula: examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_mx/scripts/gen_data.py:52-66 and
  * examples/01_simd_cpp_api/03_basic_api/03_matrix_compute/mmad_mx/scripts/gen_data.py (mx_decompress, fp64 matmul,

@@ -286,6 +286,27 @@ def matmul_w8a16(A, abT, B_nk, offset, scale, cT=F32):
     return matmul_f16(A, W, abT, cT), W
 
 
+def qf322b8(data, q):
+    """One fp32 value through the fixpipe quantisation to int8 / uint8: -> int in [-128, 255]."""
+    f = lib().ascq_oracle_qf322b8
+    f.restype = C.c_int
+    f.argtypes = [C.c_float, C.c_uint64]
+    return int(f(float(data), int(q) & 0xFFFFFFFFFFFFFFFF))
+
+
+def matmul_f16_quant(A, B_nk, abT, quantVector=None, quantScalar=0):
+    """half / bfloat16 matmul whose fp32 result is quantised to bytes as the fixpipe does ((V)QF322B8_PRE); [M, N] uint8."""
+    M, K = A.shape
+    N = B_nk.shape[0]
+    Cq = np.zeros((M, N), np.uint8)
+    f = lib().ascq_oracle_matmul_f16_quant
+    f.restype = C.c_int
+    f.argtypes = [C.c_void_p] * 3 + [C.c_int, C.c_void_p, C.c_uint64] + [C.c_int] * 4
+    _check(f(_p(Cq), _p(np.ascontiguousarray(A).view(np.uint16)), _p(np.ascontiguousarray(B_nk).view(np.uint16)), abT,
+             _p(quantVector), int(quantScalar) & 0xFFFFFFFFFFFFFFFF, M, N, K, N))
+    return Cq
+
+
 def group_matmul_mxfp8(A, aFmt, sA, B, bFmt, sB, groupList, K, N):
     """A [sumM, K] u8 (fp8 codes), sA [sumM, K/32] u8, B [G, N, K] u8, sB [G, N, K/32] u8; aFmt/bFmt 0 = e4m3fn, 1 = e5m2.
     Returns (bf16 bits, fp32)."""

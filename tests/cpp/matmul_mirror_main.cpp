@@ -110,6 +110,18 @@ int main(int argc, char** argv)
             mm.End();
             if (blocks != 1) throw std::runtime_error("expected one iteration");
             download(dir + "c.bin", c);
+        } else if (op == "f16_quant") {
+            // half x half -> int8 through the quantising output (fixpipe sample, fp32 accumulator), B stored [K, N] is 16-bit:
+            // the test hands it over K-major
+            Matmul<Gm<half>, Gm<half, true>, Gm<int8_t>> mm;
+            mm.Init(&tiling);
+            auto a = upload<half>(dir + "a.bin"), b = upload<half>(dir + "b_nk.bin");
+            auto c = device_alloc<int8_t>(size_t(M) * N);
+            mm.SetTensorA(a);
+            mm.SetTensorB(b, true);
+            mm.SetQuantVector(upload<uint64_t>(dir + "quant.bin"));
+            mm.IterateAll(c);
+            download(dir + "c.bin", c);
         } else if (op == "acc_i32") {
             Matmul<Gm<int8_t>, Gm<int8_t, true>, Gm<int32_t>, Gm<int32_t>> mm;
             mm.Init(&tiling);

@@ -104,6 +104,43 @@ def fixpipe_req8(reference):
     print("fixpipe_req8_values", n)
 
 
+def fixpipe_qf322b8(reference):
+    """The same for the sample's fp32 -> int8 generator (half operands, fp32 accumulator): its matmul case, and its
+    scalar routine ``qf322b8_pre`` on single values (shift mode off: the field table says it does not apply here)."""
+    path = os.path.join(reference, os.path.dirname(FIXPIPE), "gen_data_f322s8.py")
+    with tempfile.TemporaryDirectory() as tmp:
+        cwd = os.getcwd()
+        os.chdir(tmp)
+        try:
+            mod = runpy.run_path(path)
+            mod["gen_golden_data"](1, 2, 0)
+            x1 = np.fromfile("input/x1_gm.bin", np.float16).reshape(2, 128, 64).transpose(1, 0, 2).reshape(128, 128)
+            out = {"x1_gm": np.ascontiguousarray(x1),
+                   "x2_gm": np.fromfile("input/x2_gm.bin", np.float16).reshape(128, 256),
+                   "quant_pre": np.fromfile("input/quant_pre.bin", np.uint64),
+                   "golden": np.fromfile("output/golden.bin", np.int8).reshape(128, 256)}
+        finally:
+            os.chdir(cwd)
+    np.savez_compressed(os.path.join(HERE, "fixpipe_qf322b8_matmul.npz"), **out)
+    print("fixpipe_qf322b8_matmul", {k: v.shape for k, v in out.items()})
+
+    rng = np.random.default_rng(110)
+    n = 6000
+    scale = rng.uniform(0.0005, 3.0, n).astype(np.float32) * rng.choice([1.0, 1.0, 1.0, -1.0], n).astype(np.float32)
+    scale[:64] = rng.choice([0.5, 0.25, 1.5, 2.0, 0.125], 64).astype(np.float32)
+    bits = scale.view(np.uint32).astype(np.uint64)
+    data = np.where(rng.random(n) < 0.6, rng.uniform(-400, 400, n), rng.normal(0, 1e6, n)).astype(np.float32)
+    data[:64] = rng.integers(-511, 511, 64).astype(np.float32)          # with the scales above: exact .5 ties
+    offset = np.where(rng.random(n) < 0.4, 0, rng.integers(0, 512, n)).astype(np.uint64)
+    sign = rng.integers(0, 2, n).astype(np.uint64)
+    q = bits | (offset << np.uint64(37)) | (sign << np.uint64(46))
+    fn = mod["qf322b8_pre"]
+    with np.errstate(all="ignore"):
+        res = np.array([int(fn(np.float32(d), int(w), int(w) & 0xFFFFFFFF)) for d, w in zip(data, q)], np.int16)
+    np.savez_compressed(os.path.join(HERE, "fixpipe_qf322b8_values.npz"), data=data, quant_pre=q, golden=res)
+    print("fixpipe_qf322b8_values", n)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("ASC_DEVKIT_ROOT"), help="root of the asc-devkit tree (or set ASC_DEVKIT_ROOT)")
@@ -133,6 +170,7 @@ def main():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
         print(name, {k: v.shape for k, v in out.items()})
     fixpipe_req8(args.reference)
+    fixpipe_qf322b8(args.reference)
 
 
 if __name__ == "__main__":

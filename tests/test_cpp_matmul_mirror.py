@@ -74,6 +74,15 @@ def test_requant_through_iterate_and_get_tensor_c(exe, tmp_path):
 
 
 @pytest.mark.gpu
+def test_half_matmul_with_quantised_output(exe, tmp_path):
+    g = np.load(os.path.join(GOLDEN, "fixpipe_qf322b8_matmul.npz"))
+    run(exe, "f16_quant", tmp_path, [128, 256, 128], a=g["x1_gm"], b_nk=g["x2_gm"].T, quant=g["quant_pre"])
+    got = np.fromfile(tmp_path / "c.bin", np.int8).reshape(128, 256).astype(np.int32)
+    diff = np.abs(got - g["golden"].astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 2e-3
+
+
+@pytest.mark.gpu
 def test_int32_accumulator_output(exe, tmp_path):
     rng = np.random.default_rng(21)
     M, N, K = 200, 320, 192

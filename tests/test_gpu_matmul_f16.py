@@ -121,3 +121,51 @@ def test_matmul_w4a16(abT):
     ops.MatmulStatus()
     assert np.array_equal(to_host(ws.view(TDT[abT]).view(N, K), abT).view(np.uint16), W.view(np.uint16))
     close(C.cpu().numpy(), want)
+
+
+# ---- fixpipe quantisation of the fp32 result to int8 / uint8 ((V)QF322B8_PRE) --------------------------------------
+def _quant_words(rng, n, lo, hi, signed=None):
+    s = rng.uniform(lo, hi, n).astype(np.float32) * rng.choice([1.0, 1.0, -1.0], n).astype(np.float32)
+    w = s.view(np.uint32).astype(np.uint64)
+    w |= np.where(rng.random(n) < 0.5, 0, rng.integers(0, 512, n)).astype(np.uint64) << np.uint64(37)
+    sg = rng.integers(0, 2, n) if signed is None else np.full(n, int(signed))
+    return w | (sg.astype(np.uint64) << np.uint64(46))
+
+
+def _one_step_apart(got, want, signed_cols):
+    """Byte results agree, or differ by one step where the fp32 sums of the two sides round differently at a tie."""
+    g = np.where(signed_cols[None, :], got.view(np.int8).astype(np.int32), got.astype(np.int32))
+    w = np.where(signed_cols[None, :], want.view(np.int8).astype(np.int32), want.astype(np.int32))
+    diff = np.abs(g - w)
+    assert diff.max() <= 1 and (diff != 0).mean() < 2e-3, (diff.max(), (diff != 0).mean())
+
+
+def test_fixpipe_qf322b8_sample_golden_through_the_gpu():
+    """The fixpipe sample's fp32 -> int8 case: half operands, vector parameters, no ReLU."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "fixpipe_qf322b8_matmul.npz"))
+    C = torch.zeros((128, 256), dtype=torch.int8, device=DEV)
+    ops.MatmulF16Quant(C, torch.from_numpy(g["x1_gm"]).to(DEV), torch.from_numpy(np.ascontiguousarray(g["x2_gm"].T)).to(DEV),
+                       torch.from_numpy(g["quant_pre"].view(np.int64)).to(DEV))
+    ops.MatmulStatus()
+    _one_step_apart(C.cpu().numpy().view(np.uint8), g["golden"].view(np.uint8), np.ones(256, bool))
+
+
+@pytest.mark.parametrize("M,N,K,abT,vector", [(128, 128, 64, O.F16, True), (300, 520, 264, O.BF16, True), (257, 384, 1024, O.F16, False),
+                                             (2048, 1024, 512, O.BF16, True)])
+@pytest.mark.parametrize("tile", ["pair", "wide", "narrow"])
+def test_matmul_f16_quant_matches_oracle(M, N, K, abT, vector, tile, monkeypatch):
+    monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
+    rng = np.random.default_rng(3 * M + N + K + abT)
+    A = rand_float(rng, (M, K), abT, -1, 1)
+    B = rand_float(rng, (N, K), abT, -1, 1)
+    spread = np.sqrt(K) / 3.0  # standard deviation of a result entry
+    qv = _quant_words(rng, N, 20.0 / spread, 120.0 / spread) if vector else None
+    qs = int(_quant_words(rng, 1, 60.0 / spread, 61.0 / spread, signed=True)[0])
+    want = O.matmul_f16_quant(A, B, abT, qv, qs)
+    assert len(np.unique(want)) > 100
+    C = torch.full((M, N), 77, dtype=torch.uint8, device=DEV)
+    ops.MatmulF16Quant(C, to_dev(A, abT), to_dev(B, abT), torch.from_numpy(qv.view(np.int64)).to(DEV) if vector else None, qs)
+    ops.MatmulStatus()
+    signed = ((qv >> np.uint64(46)) & np.uint64(1)).astype(bool) if vector else np.ones(N, bool)
+    _one_step_apart(C.cpu().numpy(), want, signed)

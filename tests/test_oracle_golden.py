@@ -205,6 +205,23 @@ def test_fixpipe_req8_matmul_sample_golden(golden_dir):
     assert np.array_equal(out2, out)
 
 
+def test_fixpipe_qf322b8_values_golden(golden_dir):
+    # fixpipe_l0c2gm/scripts/gen_data_f322s8.py:75-97 (qf322b8_pre) called value by value when the fixture was made
+    g = _load(golden_dir, "fixpipe_qf322b8_values")
+    got = np.array([O.qf322b8(d, q) for d, q in zip(g["data"], g["quant_pre"])], np.int16)
+    assert np.array_equal(got, g["golden"])
+
+
+def test_fixpipe_qf322b8_matmul_sample_golden(golden_dir):
+    # gen_data_f322s8.py:136-165: half operands, fp32 matmul by numpy, vector parameters (scale 2, int8), no ReLU.
+    # The oracle sums in double and rounds once; numpy sums in fp32, so a value within rounding distance of a tie
+    # may come out one step away: at most 1 apart, and almost never.
+    g = _load(golden_dir, "fixpipe_qf322b8_matmul")
+    out = O.matmul_f16_quant(g["x1_gm"], np.ascontiguousarray(g["x2_gm"].T), O.F16, g["quant_pre"]).view(np.int8)
+    diff = np.abs(out.astype(np.int32) - g["golden"].astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 1e-3, (diff.max(), (diff != 0).mean())
+
+
 # ---- MX matmul with fp8 operands (matmul_mx and mmad_mx samples) --------------------------------------
 def test_matmul_mx_sample_golden(golden_dir):
     # matmul_mx/scripts/gen_data.py: e5m2 x e5m2, m=32 n=k=128, B stored [K,N], scaleB stored [sk/2, n, 2]
