@@ -73,6 +73,7 @@ struct Params {
     // Work items: items [0, fullTiles) are whole tiles; from there on two items share one tile, each taking half of
     // its columns (the tail of a pair-shaped launch, so that the last, partly filled wave lasts half as long).
     int fullTiles, workItems;
+    int tmaStore;  // 16-bit result of one buffer, suitably aligned: the epilogue hands its staged rows to TMA stores
     // fixpipe-style epilogue (EPI == kEpiFixpipe): C is fp16 = half(acc + biasI32[n]) scaled by quantVec[n] or quantScalar
     const int32_t* biasI32;
     const uint64_t* quantVec;   // low word: fp32 bits, of which the hardware keeps sign, exponent and 10 mantissa bits
@@ -185,14 +186,17 @@ __device__ __forceinline__ void convert_tiles(const Params& p, uint8_t* smem, fl
 
 template <int BN, bool PAIR, int EPI, bool CONV = false>
 __global__ void __launch_bounds__(Cfg<BN, PAIR, CONV>::kThreadsCta, 1)
-w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const Params p)
+w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+            const __grid_constant__ CUtensorMap tmapC, const Params p)
 {
     using C = Cfg<BN, PAIR, CONV>;
     static_assert(!CONV || (PAIR && EPI == kEpiFloat), "the converting variant is built for CTA pairs and kind::f16 only");
     extern __shared__ uint8_t smem_raw[];
     // stage buffers need 1024-byte alignment for the 128B swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+    // [stages][output staging, 1024-aligned for swizzled TMA stores][barriers, 256 B][per-column epilogue parameters]
+    uint8_t* outStage = smem + C::kStages * C::kStageBytes;  // [kEpiWarps][16][kStagePitch], or [kEpiWarps][16 x 128 B swizzled]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(outStage + C::kOutBytes);
     uint64_t* fullBar = bars;                      // [kStages] TMA -> MMA
     uint64_t* emptyBar = bars + C::kStages;        // [kStages] MMA -> TMA
     uint64_t* tmemFull = bars + 2 * C::kStages;    // [2] MMA -> epilogue
@@ -201,8 +205,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
     uint64_t* fullQ = bars + 2 * C::kStages + 5;   // [kStages] CONV: this CTA's int8 rows have landed
     uint64_t* convDone = fullQ + C::kStages;       // [kStages] CONV: converter warps of both CTAs -> MMA (leader's is used)
-    float* epiScale = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes + 256);  // [2][2][BN]
-    uint8_t* outStage = reinterpret_cast<uint8_t*>(epiScale) + C::kEpiBytes;                // [kEpiWarps][16][kStagePitch]
+    float* epiScale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [2][3][BN]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -231,6 +234,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         fence_barrier_init();
         prefetch_tensormap(&tmapA);
         prefetch_tensormap(&tmapB);
+        if (p.tmaStore) prefetch_tensormap(&tmapC);
     }
     if (warp == 1) {
         if constexpr (PAIR) {
@@ -370,12 +374,12 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             const uint32_t accPh = (local >> 1) & 1;
             const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
             const int n0 = (tile / p.tilesM) * BN + item.nOff;
-            ok = CONV ? mbar_wait_bounded_sleepy(&tmemFull[acc], accPh, abortFlag) : mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
-            tc_fence_after();
             const int m = m0 + q * 32 + lane;
             const float sa = (p.sA != nullptr && m < p.M) ? __ldg(p.sA + m) : 1.0f;
             // this tile's per-channel scale and bias, once, into shared memory (fp32): every thread needs all BN of
-            // them and reads them back as warp-wide broadcasts
+            // them and reads them back as warp-wide broadcasts.  Fetched before the accumulator is waited for, so that
+            // the latency of these loads is hidden; the buffer of this accumulator was last read two tiles ago, and every
+            // warp has passed the barrier of the tile in between since.
             float* sBs = epiScale + acc * 3 * BN;
             float* biasS = sBs + BN;
             uint32_t* auxS = reinterpret_cast<uint32_t*>(biasS + BN);
@@ -401,6 +405,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                         biasS[j] = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
                     }
                 }
+                ok = CONV ? mbar_wait_bounded_sleepy(&tmemFull[acc], accPh, abortFlag) : mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
+                tc_fence_after();
                 // barrier of the epilogue warps only; it also makes the give-up decision uniform, so that no warp is
                 // left waiting at it for one that stopped
                 uint32_t anyFail;
@@ -596,7 +602,31 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 uint32_t packed[32];
                 convert32(r0, c2 * 64, packed);
                 convert32(r1, c2 * 64 + 32, packed + 16);
-                if (vecStore && n + 64 <= p.N) {
+                if (p.tmaStore) {
+                    // Sixteen rows at a time go into this warp's swizzled staging rows (16-byte piece v of row r at
+                    // v ^ (r & 7), which also keeps the writes free of bank conflicts) and leave as one TMA store; rows
+                    // past M and columns past N are clipped by the tensor map.
+                    uint8_t* stageT = outStage + (warp - 2) * 2048;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (lane == 0) bulk_wait_group_read<0>();  // the previous store has read the staging rows
+                        __syncwarp();
+                        if ((lane >> 4) == h) {
+                            const int row = lane & 15;
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                *reinterpret_cast<uint4*>(stageT + row * 128 + ((v ^ (row & 7)) << 4)) =
+                                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                            fence_proxy_async();
+                        }
+                        __syncwarp();
+                        const int row0 = m0 + q * 32 + h * 16;
+                        if (lane == 0 && row0 < p.M) {
+                            tma_store_2d(&tmapC, stageT, p.colOffset + n, row0);
+                            bulk_commit_group();
+                        }
+                    }
+                } else if (vecStore && n + 64 <= p.N) {
                     // Transpose through this warp's staging rows, sixteen rows at a time, so that every store instruction
                     // writes four complete 128-byte row segments (instead of thirty-two 16-byte pieces): the output leaves
                     // the SM in whole lines, which is what both L2 and NVLink move best.
@@ -642,6 +672,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 else mbar_arrive(&tmemEmpty[acc]);
             }
         }
+        if (lane == 0) bulk_wait_group_all();  // the staging rows stay valid until the last TMA store has read them
     }
 
     // ---------------- teardown ----------------
@@ -666,7 +697,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 
 // ---- host side -------------------------------------------------------------------------------------
 template <int BN, bool PAIR, int EPI = kEpiDequant, bool CONV = false>
-ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaStream_t st)
+ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, Params p, cudaStream_t st)
 {
     using C = Cfg<BN, PAIR, CONV>;
     static bool attrSet = false;
@@ -701,10 +732,10 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, Params p, cudaS
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, p));
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, tc, p));
     } else {
         const int grid = tiles < sm_count() ? tiles : sm_count();
-        w8a8_kernel<BN, PAIR, EPI, CONV><<<grid, C::kThreadsCta, C::kSmemBytes, st>>>(ta, tb, p);
+        w8a8_kernel<BN, PAIR, EPI, CONV><<<grid, C::kThreadsCta, C::kSmemBytes, st>>>(ta, tb, tc, p);
     }
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
@@ -802,31 +833,42 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         else if (!strcmp(e, "wide")) mode = 1;
         else if (!strcmp(e, "narrow")) mode = 0;
     }
-    CUtensorMap ta, tb;
+    // 16-bit result in one suitably aligned buffer: TMA stores (ASCQ_W8A8_STORE=plain keeps the per-thread stores)
+    const bool out16 = epi == kEpiDequant || epi == kEpiFixpipe || (epi == kEpiFloat && fix->outKind <= 1);
+    const char* storeEnv = getenv("ASCQ_W8A8_STORE");
+    p.tmaStore = haveC && out16 && p.nPeers == 1 && !multicast && ldc % 8 == 0 && colOffset % 8 == 0 && aligned16(outBufs[0]) &&
+                 !(storeEnv && !strcmp(storeEnv, "plain"));
+    CUtensorMap ta, tb, tc;
     ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K) * elemBytes, kBM);
     if (rc != ASCQ_OK) return rc;
     rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
+    if (p.tmaStore) {
+        rc = make_tmap_out16(&tc, outBufs[0], static_cast<uint64_t>(M), static_cast<uint64_t>(colOffset) + N, static_cast<uint64_t>(ldc), 16);
+        if (rc != ASCQ_OK) return rc;
+    } else {
+        tc = ta;  // not read by the kernel
+    }
     if (epi == kEpiFloat && fix->convert) {
         // B_nk is the int8 weight: its tile goes through the converter warps (CTA pairs, 256 x 256 tiles only)
         rc = make_tmap_u8_plain(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kBK / 2, 128);
         if (rc != ASCQ_OK) return rc;
-        return launch<256, true, kEpiFloat, true>(ta, tb, p, st);
+        return launch<256, true, kEpiFloat, true>(ta, tb, tc, p, st);
     }
     if (epi == kEpiFloat) {
-        if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, p, st);
-        return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, p, st) : launch<128, false, kEpiFloat>(ta, tb, p, st);
+        if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, tc, p, st);
+        return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, tc, p, st) : launch<128, false, kEpiFloat>(ta, tb, tc, p, st);
     }
     if (epi == kEpiRequant) {
-        if (mode == 2) return launch<256, true, kEpiRequant>(ta, tb, p, st);
-        return mode == 1 ? launch<256, false, kEpiRequant>(ta, tb, p, st) : launch<128, false, kEpiRequant>(ta, tb, p, st);
+        if (mode == 2) return launch<256, true, kEpiRequant>(ta, tb, tc, p, st);
+        return mode == 1 ? launch<256, false, kEpiRequant>(ta, tb, tc, p, st) : launch<128, false, kEpiRequant>(ta, tb, tc, p, st);
     }
     if (epi == kEpiFixpipe) {
-        if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, p, st);
-        return mode == 1 ? launch<256, false, kEpiFixpipe>(ta, tb, p, st) : launch<128, false, kEpiFixpipe>(ta, tb, p, st);
+        if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, tc, p, st);
+        return mode == 1 ? launch<256, false, kEpiFixpipe>(ta, tb, tc, p, st) : launch<128, false, kEpiFixpipe>(ta, tb, tc, p, st);
     }
-    if (mode == 2) return launch<256, true>(ta, tb, p, st);
-    return mode == 1 ? launch<256, false>(ta, tb, p, st) : launch<128, false>(ta, tb, p, st);
+    if (mode == 2) return launch<256, true>(ta, tb, tc, p, st);
+    return mode == 1 ? launch<256, false>(ta, tb, tc, p, st) : launch<128, false>(ta, tb, tc, p, st);
 }
 }  // namespace
 }  // namespace ascq

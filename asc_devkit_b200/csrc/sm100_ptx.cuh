@@ -145,6 +145,20 @@ __device__ __forceinline__ void tma_load_3d(void* smemDst, const CUtensorMap* m,
 }
 
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
+// TMA store of one 2D box from shared memory (bulk async-group completion).  c0 (innermost) times the element size must
+// be a multiple of 16 bytes; boxes that reach past the tensor's extents are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smemSrc, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smemSrc)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest N groups of this thread have finished READING shared memory (the source may be overwritten)
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
+// all groups of this thread have completed (their global writes are done)
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void bulk_load(void* smemDst, const void* gsrc, uint32_t bytes, uint64_t* bar)
 {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

@@ -77,6 +77,23 @@ inline ascq_status make_tmap_kib_rows(CUtensorMap* out, const void* base, uint64
     return ASCQ_OK;
 }
 
+// 16-bit [rows, cols] row-major output matrix with row pitch ldElems: a [boxRows, 64-element] box (128 bytes) with the
+// 128B swizzle, for TMA stores.  base 16-byte aligned, ldElems a multiple of 8.
+inline ascq_status make_tmap_out16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ldElems, uint32_t boxRows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ldElems * 2};
+    const cuuint32_t box[2] = {64, boxRows};
+    const cuuint32_t elemStrides[2] = {1, 1};
+    const CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, elemStrides,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(ASCQ_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(rc));
+    return ASCQ_OK;
+}
+
 inline int sm_count()
 {
     static int n = [] {
