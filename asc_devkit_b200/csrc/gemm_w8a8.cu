@@ -672,7 +672,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 else mbar_arrive(&tmemEmpty[acc]);
             }
         }
-        if (lane == 0) bulk_wait_group_all();  // the staging rows stay valid until the last TMA store has read them
+        if (lane == 0) bulk_wait_group_read<0>();  // the staging rows must stay valid until the last TMA store has read them
     }
 
     // ---------------- teardown ----------------
