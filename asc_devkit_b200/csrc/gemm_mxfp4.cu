@@ -75,6 +75,7 @@ template <int BN, bool PAIR, int SFC> struct Cfg {
     static constexpr int kWarpStageBytes = 32 * kNarrowPitch > 16 * kStagePitch ? 32 * kNarrowPitch : 16 * kStagePitch;
     static constexpr int kOutBytes = kEpiWarps * kWarpStageBytes;  // per epilogue warp: 16 rows x 128 B or 32 rows x 64 B
     static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kOutBytes;
+    static_assert(kWarpStageBytes == 2560, "a 1024-aligned block of 2 KiB must fit into every warp's staging region");
     static_assert(kSmemBytes <= 232448, "shared memory budget");
     static_assert(kAccCols + 2 * (kSfaCols + kSfbCols) <= 512, "tensor memory budget (scale columns are double buffered)");
     static_assert(kStageBytes % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
@@ -91,6 +92,7 @@ struct Params {
     const uint8_t* sfaPacked;
     const uint8_t* sfbPacked;
     int numTilesM, tilesN, N, K, kBlocks, nTilesPerGroup128;  // nTilesPerGroup128 = ceil(N/128)
+    int tmaStore;  // bf16 result in one aligned matrix: whole 128-row tiles leave through TMA stores
 };
 
 // ---- scale repack ----------------------------------------------------------------------------------
@@ -216,19 +218,21 @@ __device__ __forceinline__ void tile_coords(int tile, int numTilesM, int tilesN,
 template <int BN, bool PAIR, int SFC>
 __global__ void __launch_bounds__(kThreads, 1)
 mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-             const __grid_constant__ CUtensorMap tmapSfa, const __grid_constant__ CUtensorMap tmapSfb, const __grid_constant__ Params p)
+             const __grid_constant__ CUtensorMap tmapSfa, const __grid_constant__ CUtensorMap tmapSfb,
+             const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ Params p)
 {
     using C = Cfg<BN, PAIR, SFC>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+    // [stages][output staging, 1024-aligned for swizzled TMA stores][barriers]
+    uint8_t* outStage = smem + C::kStages * C::kStageBytes;  // [kEpiWarps][kWarpStageBytes]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(outStage + C::kOutBytes);
     uint64_t* fullBar = bars;
     uint64_t* emptyBar = bars + C::kStages;
     uint64_t* tmemFull = bars + 2 * C::kStages;
     uint64_t* tmemEmpty = tmemFull + 2;
     uint32_t* tmemBaseSlot = reinterpret_cast<uint32_t*>(tmemEmpty + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemBaseSlot + 1);
-    uint8_t* outStage = reinterpret_cast<uint8_t*>(bars) + 256;  // [kEpiWarps][16][kStagePitch]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -253,6 +257,7 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         fence_barrier_init();
         prefetch_tensormap(&tmapA);
         prefetch_tensormap(&tmapB);
+        if (p.tmaStore) prefetch_tensormap(&tmapC);
     }
     if (warp == 1) {
         if constexpr (PAIR) {
@@ -440,7 +445,32 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                 for (int j = 0; j < 32; ++j)
                     packed[j] = pack_bf16x2_sat(__uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15)]),
                                                 __uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15) + 1]));
-                if (n + 64 <= p.N && vecStore && !p.wideStores) {
+                if (p.tmaStore && ti.rowsValid == kBM) {
+                    // A whole tile of one aligned matrix: sixteen rows at a time go into the warp's swizzled staging rows
+                    // (16-byte piece v of row r at v ^ (r & 7)) and leave as one TMA store; columns past N are clipped
+                    // by the tensor map.  (A tile that ends inside its group's rows must not touch the next group's.)
+                    // 2 KiB at the first 1024-byte boundary inside this warp's own staging region (the region is 2.5 KiB and
+                    // starts at a multiple of 512 bytes), so that warps on different paths never share staging bytes
+                    uint8_t* stageT = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(stageW) + 1023) & ~uintptr_t(1023));
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (lane == 0) bulk_wait_group_read<0>();  // the previous store has read the staging rows
+                        __syncwarp();
+                        if ((lane >> 4) == h) {
+                            const int row = lane & 15;
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                *reinterpret_cast<uint4*>(stageT + row * 128 + ((v ^ (row & 7)) << 4)) =
+                                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                            fence_proxy_async();
+                        }
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmapC, stageT, n, ti.outRow + q * 32 + h * 16);
+                            bulk_commit_group();
+                        }
+                    }
+                } else if (n + 64 <= p.N && vecStore && !p.wideStores) {
                     // One output buffer in this GPU's memory: 64-byte row segments, all thirty-two rows in one pass
                     // (fewer instructions and warp barriers than the 128-byte form below, and L2 merges the halves).
 #pragma unroll
@@ -504,6 +534,7 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                 }
             }
         }
+        if (lane == 0) bulk_wait_group_read<0>();  // the staging rows must stay valid until the last TMA store has read them
     }
 
     __syncthreads();
@@ -545,8 +576,8 @@ Layout make_layout(int64_t sumM, int G, int K, int N, int sfc = 2)
 }
 
 template <int BN, bool PAIR, int SFC = 2>
-ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb, Params p,
-                   cudaStream_t st)
+ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                   const CUtensorMap& tc, Params p, cudaStream_t st)
 {
     using C = Cfg<BN, PAIR, SFC>;
     static bool attrSet = false;
@@ -581,7 +612,7 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mxfp4_kernel<BN, PAIR, SFC>, ta, tb, tsa, tsb, p));
+    ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mxfp4_kernel<BN, PAIR, SFC>, ta, tb, tsa, tsb, tc, p));
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
@@ -730,12 +761,21 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
     if (rc != ASCQ_OK) return rc;
     rc = make_tmap_kib_rows(&tsb, p.sfbPacked, static_cast<uint64_t>(G) * L.nTiles128 * L.kBlocks, sfc * kChunkBytes);
     if (rc != ASCQ_OK) return rc;
-    if (mx8) {
-        if (pair) return launch<256, true, 1>(ta, tb, tsa, tsb, p, st);
-        return wide ? launch<256, false, 1>(ta, tb, tsa, tsb, p, st) : launch<128, false, 1>(ta, tb, tsa, tsb, p, st);
+    // bf16 result in one 16-byte aligned matrix whose rows are whole 16-byte pieces: TMA stores for whole tiles
+    // (ASCQ_MXFP4_STORE=narrow|wide keeps the per-thread stores).  The row extent of the map only bounds the clipping;
+    // tiles that are written this way lie inside the matrix by construction.
+    CUtensorMap tc = ta;
+    p.tmaStore = nBufs == 1 && !p.outF32 && N % 8 == 0 && aligned16(outBufs[0]) && getenv("ASCQ_MXFP4_STORE") == nullptr;
+    if (p.tmaStore) {
+        rc = make_tmap_out16(&tc, outBufs[0], 1ull << 30, static_cast<uint64_t>(N), static_cast<uint64_t>(N), 16);
+        if (rc != ASCQ_OK) return rc;
     }
-    if (pair) return launch<256, true>(ta, tb, tsa, tsb, p, st);
-    return wide ? launch<256, false>(ta, tb, tsa, tsb, p, st) : launch<128, false>(ta, tb, tsa, tsb, p, st);
+    if (mx8) {
+        if (pair) return launch<256, true, 1>(ta, tb, tsa, tsb, tc, p, st);
+        return wide ? launch<256, false, 1>(ta, tb, tsa, tsb, tc, p, st) : launch<128, false, 1>(ta, tb, tsa, tsb, tc, p, st);
+    }
+    if (pair) return launch<256, true>(ta, tb, tsa, tsb, tc, p, st);
+    return wide ? launch<256, false>(ta, tb, tsa, tsb, tc, p, st) : launch<128, false>(ta, tb, tsa, tsb, tc, p, st);
 }
 
 extern "C" ascq_status ascq_group_matmul_mxfp4(void* C_bf16, const uint8_t* A_fp4, const uint8_t* sA_e8m0,
