@@ -253,6 +253,11 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     }
     tc_fence_after();
     const uint32_t tmemBase = *tmemBaseSlot;
+    // Programmatic dependent launch, both ways: the launch after this one may bring its CTAs onto SMs as they become
+    // free and run its own set-up there; and everything above ran while the launch before this one was still
+    // draining -- nothing below may touch global memory before that launch has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -706,6 +711,7 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
                                              static_cast<int>(C::kSmemBytes)));
         attrSet = true;
     }
+    const bool pdl = getenv("ASCQ_W8A8_NOPDL") == nullptr;
     p.tilesM = (p.M + (PAIR ? 2 * kBM : kBM) - 1) / (PAIR ? 2 * kBM : kBM);
     p.tilesN = (p.N + BN - 1) / BN;
     const int tiles = p.tilesM * p.tilesN;
@@ -725,17 +731,29 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
         cfg.blockDim = dim3(C::kThreadsCta, 1, 1);
         cfg.dynamicSmemBytes = C::kSmemBytes;
         cfg.stream = st;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // set-up may overlap the previous launch's tail
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = pdl ? 2 : 1;
         ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, tc, p));
     } else {
         const int grid = tiles < sm_count() ? tiles : sm_count();
-        w8a8_kernel<BN, PAIR, EPI, CONV><<<grid, C::kThreadsCta, C::kSmemBytes, st>>>(ta, tb, tc, p);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+        cfg.blockDim = dim3(C::kThreadsCta, 1, 1);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, tc, p));
     }
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
