@@ -232,3 +232,27 @@ def test_matmul_requant_into_a_wider_unaligned_matrix():
     got = C.cpu().numpy()
     assert np.array_equal(got[:, :N], want)
     assert (got[:, N:] == 99).all()
+
+
+def test_block_into_one_wider_matrix_through_the_tma_store_path(monkeypatch):
+    """One aligned output matrix takes the TMA-store epilogue; with a column offset and ragged M / N the tensor map must
+    clip exactly: the block lands at its columns, everything around it stays untouched, and the per-thread store path
+    gives the same bits."""
+    M, N, K, ldc, col = 333, 200, 256, 640, 128
+    A, B, sA, sB, bias = make_case(M, N, K, 123)
+    want = O.matmul_w8a8(A, B, sA, sB, bias)
+    t = lambda a: torch.from_numpy(a).to(DEV)  # noqa: E731
+    dbias = torch.from_numpy(bias.view(np.int16)).to(DEV).view(torch.bfloat16)
+    outs = {}
+    for mode in ("tma", "plain"):
+        if mode == "plain":
+            monkeypatch.setenv("ASCQ_W8A8_STORE", "plain")
+        buf = torch.full((M + 5, ldc), -1.0, dtype=torch.bfloat16, device=DEV)
+        ops.MatmulW8A8Scatter([buf.data_ptr()], 0, col, ldc, t(A), t(B), t(sA), t(sB), dbias)
+        ops.MatmulStatus()
+        got = buf.view(torch.int16).cpu().numpy().view(np.uint16)
+        assert_bits_equal(np.ascontiguousarray(got[:M, col:col + N]), want, f"block ({mode})")
+        assert (got[:M, :col] == 0xBF80).all() and (got[:M, col + N:] == 0xBF80).all() and (got[M:] == 0xBF80).all(), \
+            f"elements outside the block changed ({mode})"
+        outs[mode] = got
+    assert np.array_equal(outs["tma"], outs["plain"])
