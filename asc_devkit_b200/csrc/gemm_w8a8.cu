@@ -673,7 +673,9 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&tmemEmpty[acc]), 0));  // the leader's barrier
+                // the leader's barrier; relaxed: it guards tensor memory only (reads complete: tcgen05.wait::ld), and a
+                // release would make this thread wait for its stores of the tile to become visible first
+                if constexpr (PAIR) mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&tmemEmpty[acc]), 0));
                 else mbar_arrive(&tmemEmpty[acc]);
             }
         }

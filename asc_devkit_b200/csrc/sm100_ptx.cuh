@@ -279,6 +279,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t clusterAddr)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
 }
+// the same without release semantics: for barriers that order nothing but tensor-memory accesses, which tcgen05.wait / fence
+// instructions order on their own
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t clusterAddr)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
 // TMA tile load whose completion bytes are counted on an mbarrier of either CTA of the pair (no multicast:
 // the data lands only in the issuing CTA's shared memory)
 __device__ __forceinline__ void tma_load_2d_pair(void* smemDst, const CUtensorMap* m, uint32_t barClusterAddr, int c0, int c1)
