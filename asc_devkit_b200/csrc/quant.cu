@@ -305,77 +305,95 @@ extern "C" ascq_status ascq_dynamic_quant_per_token(int8_t* dst, float* scaleOut
 }
 
 // ---- dynamic MX-FP4 block quantisation ---------------------------------------------------------------
-// One thread per block of 32 consecutive elements of a row: amax -> shared exponent -> E8M0 byte, then every value is
-// scaled by the exact power of two and converted float -> bfloat16 (RINT) -> E2M1 (RINT, saturating), the conversion
-// chain of AscendQuant's fp4 destination.  Consecutive threads take consecutive blocks: 64-byte loads, 16-byte stores and
-// one scale byte per thread, all coalesced.
+// Per block of 32 consecutive elements of a row: amax -> shared exponent -> E8M0 byte, then every value is scaled by the
+// exact power of two and converted float -> bfloat16 (RINT) -> E2M1 (RINT, saturating; cvt.rn.satfinite.e2m1x2.f32), the
+// conversion chain of AscendQuant's fp4 destination.
 namespace ascq {
 namespace {
+// Two fp32 values -> one byte of two E2M1 codes (first value in the low nibble), round to nearest even, saturating.
+__device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float first, float second)
+{
+    unsigned short r;
+    asm("{ .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %2, %1;\n mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(first), "f"(second));
+    return r;
+}
+
+// One lane owns one 16-byte vector of the source (8 half / bfloat16 or 4 float elements); the 4 or 8 lanes that share
+// a 32-element block combine their maxima with shuffles.  Every load, code store and scale store of a warp is
+// contiguous.  U vectors per thread are requested before the first is worked on.
 template <typename Src>
 __global__ void __launch_bounds__(256) dyn_quant_mxfp4_kernel(uint8_t* __restrict__ dst, uint8_t* __restrict__ scaleOut,
-                                                              const Src* __restrict__ src, uint64_t blocks)
+                                                              const Src* __restrict__ src, uint64_t vectors)
 {
-    const uint64_t b = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x;
-    if (b >= blocks) return;
-    float v[32];
-    if constexpr (sizeof(Src) == 2) {
-        const uint4* q = reinterpret_cast<const uint4*>(src + b * 32);
+    constexpr int EPL = 16 / static_cast<int>(sizeof(Src));  // elements per lane
+    constexpr int LPB = 32 / EPL;                            // lanes per block
+    constexpr int U = 4;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const uint32_t lane = threadIdx.x & 31u;
+    for (uint64_t g0 = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g0 - lane < vectors; g0 += stride * U) {
+        uint4 raw[U];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 w = __ldcs(q + i);
-            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        for (int u = 0; u < U; ++u) {
+            const uint64_t g = g0 + u * stride;
+            raw[u] = g < vectors ? __ldcs(reinterpret_cast<const uint4*>(src) + g) : make_uint4(0u, 0u, 0u, 0u);
+        }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                Src lo, hi;
-                *reinterpret_cast<unsigned short*>(&lo) = static_cast<unsigned short>(ws[j] & 0xFFFFu);
-                *reinterpret_cast<unsigned short*>(&hi) = static_cast<unsigned short>(ws[j] >> 16);
-                v[i * 8 + j * 2] = to_f32<Src>(lo);
-                v[i * 8 + j * 2 + 1] = to_f32<Src>(hi);
+        for (int u = 0; u < U; ++u) {
+            const uint64_t g = g0 + u * stride;
+            if (g - lane >= vectors) break;  // uniform over the warp
+            const uint32_t ws[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+            float v[EPL];
+            if constexpr (sizeof(Src) == 2) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    Src lo, hi;
+                    *reinterpret_cast<unsigned short*>(&lo) = static_cast<unsigned short>(ws[j] & 0xFFFFu);
+                    *reinterpret_cast<unsigned short*>(&hi) = static_cast<unsigned short>(ws[j] >> 16);
+                    v[2 * j] = to_f32<Src>(lo);
+                    v[2 * j + 1] = to_f32<Src>(hi);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(ws[j]);
+            }
+            float amax = 0.f;
+            uint32_t bad = 0;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                const float a = fabsf(v[i]);
+                bad |= !(a <= 3.4028234663852886e38f);  // NaN or infinity
+                amax = fmaxf(amax, a);
+            }
+#pragma unroll
+            for (int o = 1; o < LPB; o <<= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+                bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+            }
+            // shared exponent = floor(log2(amax)) - 2 (E2M1's largest exponent), clamped to the E8M0 range; all-zero blocks get 2^0
+            int e = 0;
+            if (amax > 0.f) {
+                const int ex = static_cast<int>((__float_as_uint(amax) >> 23) & 0xFF);
+                e = (ex == 0 ? -126 : ex - 127) - 2;  // subnormal amax: floor(log2) is below -126; -126 is close enough to clamp
+                e = min(max(e, -127), 127);
+            }
+            // multiply by 2^-e in two exact steps so that neither factor leaves the normal range
+            const int h1 = (-e) / 2, h2 = (-e) - h1;
+            const float f1 = __uint_as_float(static_cast<uint32_t>(h1 + 127) << 23), f2 = __uint_as_float(static_cast<uint32_t>(h2 + 127) << 23);
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < EPL / 2; ++j) {
+                // scaled value -> bfloat16 (round to nearest even) -> E2M1 (round to nearest even, saturating)
+                const uint32_t b2 = pack_bf16x2_sat(__fmul_rn(__fmul_rn(v[2 * j], f1), f2), __fmul_rn(__fmul_rn(v[2 * j + 1], f1), f2));
+                word |= f32x2_to_e2m1x2(__uint_as_float(b2 << 16), __uint_as_float(b2 & 0xFFFF0000u)) << (8 * j);
+            }
+            if (bad) word = 0;
+            if (g < vectors) {
+                if constexpr (EPL == 8) reinterpret_cast<uint32_t*>(dst)[g] = word;
+                else reinterpret_cast<unsigned short*>(dst)[g] = static_cast<unsigned short>(word);
+                if ((lane & (LPB - 1)) == 0) scaleOut[g / LPB] = static_cast<uint8_t>(bad ? 0xFFu : static_cast<uint32_t>(e + 127));
             }
         }
-    } else {
-        const float4* q = reinterpret_cast<const float4*>(src + b * 32);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float4 w = __ldcs(q + i);
-            v[i * 4] = w.x; v[i * 4 + 1] = w.y; v[i * 4 + 2] = w.z; v[i * 4 + 3] = w.w;
-        }
     }
-    float amax = 0.f;
-    bool bad = false;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const float a = fabsf(v[i]);
-        bad = bad || !(a <= 3.4028234663852886e38f);  // NaN or infinity
-        amax = fmaxf(amax, a);
-    }
-    // shared exponent = floor(log2(amax)) - 2 (E2M1's largest exponent), clamped to the E8M0 range; all-zero blocks get 2^0
-    int e = 0;
-    if (amax > 0.f) {
-        const uint32_t bits = __float_as_uint(amax);
-        const int ex = static_cast<int>((bits >> 23) & 0xFF);
-        e = (ex == 0 ? -126 : ex - 127) - 2;   // subnormal amax: floor(log2) is below -126; -126 is close enough to clamp
-        e = max(e, -127);
-        e = min(e, 127);
-    }
-    const uint32_t sbyte = bad ? 0xFFu : static_cast<uint32_t>(e + 127);
-    scaleOut[b] = static_cast<uint8_t>(sbyte);
-    // multiply by 2^-e in two exact steps so that neither factor leaves the normal range
-    const int h1 = (-e) / 2, h2 = (-e) - h1;
-    const float f1 = __uint_as_float(static_cast<uint32_t>(h1 + 127) << 23), f2 = __uint_as_float(static_cast<uint32_t>(h2 + 127) << 23);
-    uint32_t out[4];
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float y = __fmul_rn(__fmul_rn(v[w * 8 + j], f1), f2);
-            const uint32_t code = bad ? 0u : f32_to_e2m1(__bfloat162float(f32_to_bf16_sat(y)), kRoundRint);
-            word |= code << (4 * j);
-        }
-        out[w] = word;
-    }
-    reinterpret_cast<uint4*>(dst)[b] = make_uint4(out[0], out[1], out[2], out[3]);
 }
 }  // namespace
 }  // namespace ascq
@@ -390,11 +408,14 @@ extern "C" ascq_status ascq_dynamic_quant_mxfp4(uint8_t* dst_fp4, uint8_t* scale
     if (!aligned16(src) || !aligned16(dst_fp4)) return fail(ASCQ_ERR_ALIGNMENT, "src and dst must be 16-byte aligned");
     const uint64_t blocks = static_cast<uint64_t>(m) * (n / 32);
     if (blocks == 0) return ASCQ_OK;
-    const unsigned grid = static_cast<unsigned>((blocks + 255) / 256);
-    if (srcT == ASCQ_DT_F16) dyn_quant_mxfp4_kernel<__half><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __half*>(src), blocks);
+    // one lane per 16-byte source vector, four vectors per thread and pass; at most 16 CTAs of 256 threads per SM
+    const uint64_t vectors = blocks * (srcT == ASCQ_DT_F32 ? 8u : 4u);
+    const uint64_t want = (vectors + 1023) / 1024;
+    const unsigned grid = static_cast<unsigned>(want < 148u * 16u ? want : 148u * 16u);
+    if (srcT == ASCQ_DT_F16) dyn_quant_mxfp4_kernel<__half><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __half*>(src), vectors);
     else if (srcT == ASCQ_DT_BF16)
-        dyn_quant_mxfp4_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __nv_bfloat16*>(src), blocks);
-    else dyn_quant_mxfp4_kernel<float><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const float*>(src), blocks);
+        dyn_quant_mxfp4_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __nv_bfloat16*>(src), vectors);
+    else dyn_quant_mxfp4_kernel<float><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const float*>(src), vectors);
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
