@@ -203,6 +203,48 @@ def test_dynamic_quant_mxfp4(srcT, m, n):
     assert np.array_equal(dst.cpu().numpy(), want_codes)
 
 
+@pytest.mark.parametrize("srcT", [O.F16, O.BF16, O.F32])
+def test_dynamic_quant_mxfp4_edge_blocks(srcT):
+    """Blocks with NaN / infinity (scale 0xFF, codes 0), the largest and smallest magnitudes of the source type
+    (exponent clamps, two-step scaling), signed zeros, and values on the rounding ties of E2M1."""
+    rng = np.random.default_rng(17 + srcT)
+    m, n = 64, 256
+    x = rng.standard_normal((m, n)).astype(np.float32)
+    big = {O.F16: 6.0e4, O.BF16: 3.0e38, O.F32: 3.0e38}[srcT]
+    tiny = {O.F16: 6.0e-8, O.BF16: 1.0e-38, O.F32: 1.0e-38}[srcT]
+    x[0, 5] = np.nan
+    x[1, 40] = np.inf
+    x[2, 70] = -np.inf
+    x[3, :32] = big * rng.uniform(-1, 1, 32)
+    x[4, :32] = tiny * rng.uniform(-1, 1, 32)
+    x[5, :32] = tiny * 1e-3 * rng.uniform(-1, 1, 32)          # subnormal (float, bfloat16) or zero (half)
+    x[6, :32] = -0.0
+    x[7, :32] = 0.0
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, 7.0, 7.99, 0.2499, 0.2501], np.float32)
+    for r, sc in enumerate((1.0, 2.0 ** -20, 2.0 ** 30, 2.0 ** -100 if srcT != O.F16 else 2.0 ** -12)):
+        row = 8 + r
+        x[row, :32] = 0.0
+        x[row, 0] = 7.5 * sc                                   # fixes the block's exponent: 2^e = sc
+        x[row, 1:1 + len(ties)] = ties * sc
+        x[row, 16:16 + len(ties)] = -ties * sc
+    if srcT == O.F16:
+        with np.errstate(over="ignore"):
+            xs = x.astype(np.float16)
+    elif srcT == O.BF16:
+        xs = O.f32_to_bf16_bits(x)
+    else:
+        xs = x
+    want_codes, want_sc = O.dynamic_quant_mxfp4(xs, srcT, m, n)
+    assert want_sc[0, 0] == 0xFF and want_sc[1, 1] == 0xFF and want_sc[2, 2] == 0xFF
+    dst = torch.full((m, n // 2), 0x5A, dtype=torch.uint8, device=DEV)
+    sc = torch.full((m, n // 32), 0x5A, dtype=torch.uint8, device=DEV)
+    ops.DynamicQuantMxfp4(dst, sc, to_dev(xs, srcT))
+    assert np.array_equal(sc.cpu().numpy(), want_sc)
+    got = dst.cpu().numpy()
+    bad = np.argwhere(got != want_codes)
+    assert bad.size == 0, f"first difference at {bad[0]}: got {got[tuple(bad[0])]:#x} want {want_codes[tuple(bad[0])]:#x}"
+
+
 def test_dynamic_quant_mxfp4_feeds_the_grouped_matmul():
     """bf16 activations -> ascq_dynamic_quant_mxfp4 -> ascq_group_matmul_mxfp4 reproduces the oracle run on the same
     quantised operands, and stays close to the unquantised product."""
