@@ -318,6 +318,17 @@ __device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float first, float second)
     return r;
 }
 
+// max that returns NaN when either operand is NaN
+__device__ __forceinline__ float fmax_nan(float a, float b)
+{
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+template <typename T> struct Two;
+template <> struct Two<__half> { using type = __half2; };
+template <> struct Two<__nv_bfloat16> { using type = __nv_bfloat162; };
+
 // One lane owns one 16-byte vector of the source (8 half / bfloat16 or 4 float elements); the 4 or 8 lanes that share
 // a 32-element block combine their maxima with shuffles.  Every load, code store and scale store of a warp is
 // contiguous.  U vectors per thread are requested before the first is worked on.
@@ -342,33 +353,21 @@ __global__ void __launch_bounds__(256) dyn_quant_mxfp4_kernel(uint8_t* __restric
             const uint64_t g = g0 + u * stride;
             if (g - lane >= vectors) break;  // uniform over the warp
             const uint32_t ws[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-            float v[EPL];
+            // largest magnitude of the lane's elements, NaN propagating (so that one test at the end finds NaN and infinity)
+            float amax;
             if constexpr (sizeof(Src) == 2) {
+                using Src2 = typename Two<Src>::type;
+                Src2 mx = __habs2(*reinterpret_cast<const Src2*>(&ws[0]));
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    Src lo, hi;
-                    *reinterpret_cast<unsigned short*>(&lo) = static_cast<unsigned short>(ws[j] & 0xFFFFu);
-                    *reinterpret_cast<unsigned short*>(&hi) = static_cast<unsigned short>(ws[j] >> 16);
-                    v[2 * j] = to_f32<Src>(lo);
-                    v[2 * j + 1] = to_f32<Src>(hi);
-                }
+                for (int j = 1; j < 4; ++j) mx = __hmax2_nan(mx, __habs2(*reinterpret_cast<const Src2*>(&ws[j])));
+                amax = fmax_nan(to_f32<Src>(mx.x), to_f32<Src>(mx.y));
             } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(ws[j]);
-            }
-            float amax = 0.f;
-            uint32_t bad = 0;
-#pragma unroll
-            for (int i = 0; i < EPL; ++i) {
-                const float a = fabsf(v[i]);
-                bad |= !(a <= 3.4028234663852886e38f);  // NaN or infinity
-                amax = fmaxf(amax, a);
+                amax = fmax_nan(fmax_nan(fabsf(__uint_as_float(ws[0])), fabsf(__uint_as_float(ws[1]))),
+                                fmax_nan(fabsf(__uint_as_float(ws[2])), fabsf(__uint_as_float(ws[3]))));
             }
 #pragma unroll
-            for (int o = 1; o < LPB; o <<= 1) {
-                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-                bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
-            }
+            for (int o = 1; o < LPB; o <<= 1) amax = fmax_nan(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            const bool bad = !(amax <= 3.4028234663852886e38f);  // a NaN or an infinity in the block
             // shared exponent = floor(log2(amax)) - 2 (E2M1's largest exponent), clamped to the E8M0 range; all-zero blocks get 2^0
             int e = 0;
             if (amax > 0.f) {
@@ -376,15 +375,39 @@ __global__ void __launch_bounds__(256) dyn_quant_mxfp4_kernel(uint8_t* __restric
                 e = (ex == 0 ? -126 : ex - 127) - 2;  // subnormal amax: floor(log2) is below -126; -126 is close enough to clamp
                 e = min(max(e, -127), 127);
             }
-            // multiply by 2^-e in two exact steps so that neither factor leaves the normal range
-            const int h1 = (-e) / 2, h2 = (-e) - h1;
-            const float f1 = __uint_as_float(static_cast<uint32_t>(h1 + 127) << 23), f2 = __uint_as_float(static_cast<uint32_t>(h2 + 127) << 23);
+            // x * 2^-e is exact; the factor is split in two only when 2^-e itself is not a normal number (|e| > 126)
+            const bool twoSteps = e > 126 || e < -127 + 1;
+            const int h1 = twoSteps ? (-e) / 2 : -e, h2 = (-e) - h1;
+            const uint32_t f1b = static_cast<uint32_t>(h1 + 127) << 23, f2b = static_cast<uint32_t>(h2 + 127) << 23;
             uint32_t word = 0;
+            if constexpr (std::is_same<Src, __nv_bfloat16>::value) {
+                // bfloat16 times a power of two is a bfloat16: the scaled values stay packed, no rounding step is needed
+                const uint32_t s1 = (f1b >> 16) * 0x10001u, s2 = (f2b >> 16) * 0x10001u;
 #pragma unroll
-            for (int j = 0; j < EPL / 2; ++j) {
-                // scaled value -> bfloat16 (round to nearest even) -> E2M1 (round to nearest even, saturating)
-                const uint32_t b2 = pack_bf16x2_sat(__fmul_rn(__fmul_rn(v[2 * j], f1), f2), __fmul_rn(__fmul_rn(v[2 * j + 1], f1), f2));
-                word |= f32x2_to_e2m1x2(__uint_as_float(b2 << 16), __uint_as_float(b2 & 0xFFFF0000u)) << (8 * j);
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 y = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&ws[j]), *reinterpret_cast<const __nv_bfloat162*>(&s1));
+                    if (twoSteps) y = __hmul2(y, *reinterpret_cast<const __nv_bfloat162*>(&s2));
+                    const uint32_t b2 = *reinterpret_cast<const uint32_t*>(&y);
+                    word |= f32x2_to_e2m1x2(__uint_as_float(b2 << 16), __uint_as_float(b2 & 0xFFFF0000u)) << (8 * j);
+                }
+            } else {
+                const float f1 = __uint_as_float(f1b), f2 = __uint_as_float(f2b);
+#pragma unroll
+                for (int j = 0; j < EPL / 2; ++j) {
+                    float y0, y1;
+                    if constexpr (sizeof(Src) == 2) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ws[j]));
+                        y0 = f.x; y1 = f.y;
+                    } else {
+                        y0 = __uint_as_float(ws[2 * j]); y1 = __uint_as_float(ws[2 * j + 1]);
+                    }
+                    y0 = __fmul_rn(y0, f1); y1 = __fmul_rn(y1, f1);
+                    if (twoSteps) { y0 = __fmul_rn(y0, f2); y1 = __fmul_rn(y1, f2); }
+                    // scaled value -> bfloat16 (round to nearest even; |y| < 8, nothing to saturate) -> E2M1
+                    uint32_t b2;
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(b2) : "f"(y1), "f"(y0));
+                    word |= f32x2_to_e2m1x2(__uint_as_float(b2 << 16), __uint_as_float(b2 & 0xFFFF0000u)) << (8 * j);
+                }
             }
             if (bad) word = 0;
             if (g < vectors) {
