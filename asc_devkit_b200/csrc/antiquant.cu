@@ -34,37 +34,72 @@ ascq_status dispatch_fast(const EwArgs& a, ascq_dtype dstT, ascq_dtype scT, ascq
 }
 
 // ---- MX decode: fp4x2 (E2M1) + E8M0 scale -> bf16 / half ------------------------------------------
-// One thread converts 32 elements (16 source bytes -> 64 destination bytes).  With the groups along the
-// columns (transposed layout) the 32 elements share one scale byte; with the groups along the rows the
-// thread reads the 32 scale bytes of its columns.
+// One lane converts 8 elements: one 4-byte load, one 16-byte store, so every access of a warp is contiguous.  The four
+// source bytes go through the hardware conversion (cvt.rn.f16x2.e2m1x2; every E2M1 value is exact in half and in
+// bfloat16), the product with the scale is one packed multiply per two elements.  With the groups along the columns
+// (transposed layout) the 8 elements share one scale byte; with the groups along the rows the lane reads the 8 scale
+// bytes of its columns.  Two rows per thread are requested before the first is worked on.
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t w, uint32_t (&h)[4])
+{
+    asm("{ .reg .b8 b0, b1, b2, b3;\n"
+        " mov.b32 {b0, b1, b2, b3}, %4;\n"
+        " cvt.rn.f16x2.e2m1x2 %0, b0;\n cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        " cvt.rn.f16x2.e2m1x2 %2, b2;\n cvt.rn.f16x2.e2m1x2 %3, b3; }"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(w));
+}
+// the scale as the multiplier of the destination type: bfloat16 bits, or the half that the saturating cast gives
+template <typename Dst> __device__ __forceinline__ uint32_t mx_scale_bits(uint32_t e)
+{
+    const unsigned short b = e8m0_to_bf16_bits(e);
+    if constexpr (std::is_same<Dst, __nv_bfloat16>::value) return b;
+    else return __half_as_ushort(f32_to_f16_sat(__uint_as_float(static_cast<uint32_t>(b) << 16)));
+}
 template <typename Dst, bool TRANSPOSED>
 __global__ void __launch_bounds__(256) mx_decode_kernel(Dst* __restrict__ dst, const uint8_t* __restrict__ src,
                                                         const uint8_t* __restrict__ scale, uint32_t rows, uint32_t cols)
 {
-    const uint32_t c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 32u;
+    const uint32_t c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8u;
     if (c0 >= cols) return;
-    for (uint32_t r = blockIdx.y; r < rows; r += gridDim.y) {
-        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(src + (static_cast<size_t>(r) * cols + c0) / 2));
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        uint32_t sb[8];  // 32 scale bytes (row-grouped) or one broadcast byte
-        if (TRANSPOSED) {
-            sb[0] = scale[static_cast<size_t>(r) * (cols / 32) + c0 / 32];
-        } else {
-            const uint4* sp = reinterpret_cast<const uint4*>(scale + static_cast<size_t>(r / 32) * cols + c0);
-            const uint4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
-            sb[0] = s0.x; sb[1] = s0.y; sb[2] = s0.z; sb[3] = s0.w; sb[4] = s1.x; sb[5] = s1.y; sb[6] = s1.z; sb[7] = s1.w;
-        }
-        Pack<Dst, 32> out;
+    constexpr int U = 2;
+    const uint32_t gy = gridDim.y;
+    for (uint32_t r0 = blockIdx.y; r0 < rows; r0 += gy * U) {
+        uint32_t raw[U];
+        uint2 sraw[U];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const uint32_t code = (w[i >> 3] >> ((i & 7) * 4)) & 0xFu;
-            const uint32_t e = TRANSPOSED ? sb[0] : ((sb[i >> 2] >> ((i & 3) * 8)) & 0xFFu);
-            const __nv_bfloat16 s = __ushort_as_bfloat16(e8m0_to_bf16_bits(e));
-            const __nv_bfloat16 v = __float2bfloat16_rn(e2m1_to_f32(code));
-            if constexpr (std::is_same<Dst, __nv_bfloat16>::value) out.v[i] = Ct<__nv_bfloat16>::mul(s, v);
-            else out.v[i] = __hmul_rn(f32_to_f16_sat(__bfloat162float(s)), f32_to_f16_sat(__bfloat162float(v)));
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gy;
+            if (r >= rows) break;
+            raw[u] = __ldcs(reinterpret_cast<const uint32_t*>(src + (static_cast<size_t>(r) * cols + c0) / 2));
+            if (TRANSPOSED) sraw[u].x = scale[static_cast<size_t>(r) * (cols / 32) + c0 / 32];
+            else sraw[u] = __ldg(reinterpret_cast<const uint2*>(scale + static_cast<size_t>(r / 32) * cols + c0));
         }
-        store_pack<Dst, 32>(dst + static_cast<size_t>(r) * cols + c0, out);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gy;
+            if (r >= rows) break;
+            uint32_t h[4], out[4];
+            e2m1x8_to_f16x2(raw[u], h);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t s2;
+                if (TRANSPOSED) {
+                    s2 = mx_scale_bits<Dst>(sraw[u].x) * 0x10001u;
+                } else {
+                    const uint32_t word = (j < 2) ? sraw[u].x : sraw[u].y;
+                    s2 = mx_scale_bits<Dst>((word >> ((j & 1) * 16)) & 0xFFu) | (mx_scale_bits<Dst>((word >> ((j & 1) * 16 + 8)) & 0xFFu) << 16);
+                }
+                if constexpr (std::is_same<Dst, __nv_bfloat16>::value) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[j]));
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(f.x, f.y);  // exact
+                    const __nv_bfloat162 y = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&s2), v);
+                    out[j] = *reinterpret_cast<const uint32_t*>(&y);
+                } else {
+                    const __half2 y = __hmul2(*reinterpret_cast<const __half2*>(&s2), *reinterpret_cast<const __half2*>(&h[j]));
+                    out[j] = *reinterpret_cast<const uint32_t*>(&y);
+                }
+            }
+            __stcs(reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * cols + c0), make_uint4(out[0], out[1], out[2], out[3]));
+        }
     }
 }
 }  // namespace
@@ -103,7 +138,7 @@ static ascq_status antiquant_common(void* dst, ascq_dtype dstT, const void* src,
         if (n % 2) return fail(ASCQ_ERR_INVALID_ARG, "n must be even for packed fp4");
         if (n % 32 == 0 && aligned16(src) && aligned16(dst) && (p->isTranspose || aligned16(scale))) {
             dim3 grid, block;
-            ew_grid(rows, n, 32, &grid, &block);
+            ew_grid(rows, n, 8, &grid, &block);
             uint8_t const* s8 = static_cast<const uint8_t*>(src);
             uint8_t const* sc = static_cast<const uint8_t*>(scale);
             if (dstT == ASCQ_DT_BF16) {
