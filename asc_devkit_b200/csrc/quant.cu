@@ -78,6 +78,111 @@ using namespace ascq;
 // (impl/adv_api/detail/quantization/quantize/quantize_impl.h:832-975): every policy computes in fp32 (source and
 // scale/offset widened to fp32, one rounded multiply, one rounded add), honours hasOffset and roundMode, and takes
 // the tensor as m rows of n (calCount = m * n).
+// ---- AscendQuant PER_GROUP to fp4x2_e2m1, round to nearest even -------------------------------------------------
+// (impl/adv_api/detail/quantization/quant/ascend_quant_per_group_3510_impl.h:346-379, ascend_quant_3510_impl.h:994-1032:
+// the product in the scale's type, then -> bfloat16 -> E2M1.)  One lane per 8 elements: contiguous loads, one 4-byte
+// store; the scale is one value per lane (groups along the columns) or 8 consecutive values (groups along the rows).
+// The last conversion is the hardware's (a NaN becomes +6: the multiply before it has already dropped a NaN's sign).
+namespace ascq {
+namespace {
+template <typename T> struct Two;
+template <> struct Two<__half> { using type = __half2; };
+template <> struct Two<__nv_bfloat16> { using type = __nv_bfloat162; };
+__device__ __forceinline__ uint32_t bf16x2_to_e2m1x2(uint32_t b2)
+{
+    unsigned short r;
+    asm("{ .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %2, %1;\n mov.b16 %0, {t, 0}; }"
+        : "=h"(r) : "f"(__uint_as_float(b2 << 16)), "f"(__uint_as_float(b2 & 0xFFFF0000u)));
+    return r;
+}
+template <typename CT, typename T> __device__ __forceinline__ CT to_ct(T v)
+{
+    if constexpr (std::is_same<CT, T>::value) return v;
+    else return Ct<CT>::from_f32(to_f32<T>(v));
+}
+template <typename Src, typename Sc, typename CT>
+__global__ void __launch_bounds__(256) quant_fp4_kernel(uint8_t* __restrict__ dst, const Src* __restrict__ src, const SRef scale,
+                                                        uint32_t rows, uint32_t cols)
+{
+    const uint32_t c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8u;
+    if (c0 >= cols) return;
+    constexpr int U = 2;
+    const bool perLane = scale.cdiv != 1;  // groups along the columns: the lane's 8 elements share one scale
+    const uint32_t scol = perLane ? c0 / scale.cdiv : c0;
+    const uint32_t gy = gridDim.y;
+    for (uint32_t r0 = blockIdx.y; r0 < rows; r0 += gy * U) {
+        Pack<Src, 8> in[U];
+        Pack<Sc, 8> sv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gy;
+            if (r >= rows) break;
+            in[u] = load_pack<Src, 8, true>(src + static_cast<size_t>(r) * cols + c0);
+            const Sc* sp = static_cast<const Sc*>(scale.p) + static_cast<size_t>(r / scale.rdiv) * scale.stride + scol;
+            if (perLane) sv[u].v[0] = __ldg(sp);
+            else sv[u] = load_pack<Sc, 8, false>(sp);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gy;
+            if (r >= rows) break;
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t b2;  // the two products as bfloat16
+                if constexpr (std::is_same<CT, Src>::value && std::is_same<CT, Sc>::value && sizeof(CT) == 2) {
+                    // half or bfloat16 throughout: one packed multiply (each lane rounded on its own)
+                    using CT2 = typename Two<CT>::type;
+                    CT2 x2, s2;
+                    x2.x = in[u].v[2 * j]; x2.y = in[u].v[2 * j + 1];
+                    s2.x = sv[u].v[perLane ? 0 : 2 * j]; s2.y = sv[u].v[perLane ? 0 : 2 * j + 1];
+                    const CT2 y2 = __hmul2(x2, s2);
+                    if constexpr (std::is_same<CT, __nv_bfloat16>::value) {
+                        b2 = *reinterpret_cast<const uint32_t*>(&y2);
+                    } else {
+                        const float2 f = __half22float2(y2);
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(b2) : "f"(f.y), "f"(f.x));
+                    }
+                } else {
+                    const CT s0 = to_ct<CT>(sv[u].v[perLane ? 0 : 2 * j]), s1 = to_ct<CT>(sv[u].v[perLane ? 0 : 2 * j + 1]);
+                    const float y0 = Ct<CT>::to_f32(Ct<CT>::mul(to_ct<CT>(in[u].v[2 * j]), s0));
+                    const float y1 = Ct<CT>::to_f32(Ct<CT>::mul(to_ct<CT>(in[u].v[2 * j + 1]), s1));
+                    // a product beyond bfloat16's range becomes an infinity here and +-6 in the next step, as it would
+                    // after saturating to the largest bfloat16 first
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(b2) : "f"(y1), "f"(y0));
+                }
+                word |= bf16x2_to_e2m1x2(b2) << (8 * j);
+            }
+            *reinterpret_cast<uint32_t*>(dst + (static_cast<size_t>(r) * cols + c0) / 2) = word;
+        }
+    }
+}
+template <typename Src, typename Sc, typename CT>
+ascq_status launch_quant_fp4(const EwArgs& a, cudaStream_t st)
+{
+    dim3 grid, block;
+    ew_grid(a.rows, a.cols, 8, &grid, &block);
+    quant_fp4_kernel<Src, Sc, CT><<<grid, block, 0, st>>>(static_cast<uint8_t*>(a.dst), static_cast<const Src*>(a.src), a.scale, a.rows, a.cols);
+    ASCQ_CUDA_CHECK(cudaGetLastError());
+    return ASCQ_OK;
+}
+// (src, scale, compute) type triples of the PER_GROUP overloads: compute = scale type (legacy) or float (unified)
+ascq_status dispatch_quant_fp4(const EwArgs& a, ascq_dtype srcT, ascq_dtype scT, ascq_dtype ct, cudaStream_t st, bool* handled)
+{
+    *handled = true;
+    if (srcT == ASCQ_DT_F16 && scT == ASCQ_DT_F16 && ct == ASCQ_DT_F16) return launch_quant_fp4<__half, __half, __half>(a, st);
+    if (srcT == ASCQ_DT_BF16 && scT == ASCQ_DT_BF16 && ct == ASCQ_DT_BF16) return launch_quant_fp4<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(a, st);
+    if (srcT == ASCQ_DT_F16 && scT == ASCQ_DT_F16 && ct == ASCQ_DT_F32) return launch_quant_fp4<__half, __half, float>(a, st);
+    if (srcT == ASCQ_DT_BF16 && scT == ASCQ_DT_BF16 && ct == ASCQ_DT_F32) return launch_quant_fp4<__nv_bfloat16, __nv_bfloat16, float>(a, st);
+    if (srcT == ASCQ_DT_F16 && scT == ASCQ_DT_F32 && ct == ASCQ_DT_F32) return launch_quant_fp4<__half, float, float>(a, st);
+    if (srcT == ASCQ_DT_BF16 && scT == ASCQ_DT_F32 && ct == ASCQ_DT_F32) return launch_quant_fp4<__nv_bfloat16, float, float>(a, st);
+    if (srcT == ASCQ_DT_F32 && scT == ASCQ_DT_F32 && ct == ASCQ_DT_F32) return launch_quant_fp4<float, float, float>(a, st);
+    *handled = false;
+    return ASCQ_OK;
+}
+}  // namespace
+}  // namespace ascq
+
 static ascq_status quant_common(void* dst, ascq_dtype dstT, const void* src, ascq_dtype srcT, const void* scale,
                                 const void* offset, ascq_dtype scaleT, float scaleScalar, float offsetScalar,
                                 ascq_policy policy, const ascq_quant_param* p, void* stream, bool unified)
@@ -189,6 +294,13 @@ static ascq_status quant_common(void* dst, ascq_dtype dstT, const void* src, asc
             ascq_status rc = dispatch_fast(a, srcT, scaleT, ct, smode, hasOff, st, &handled);
             if (rc != ASCQ_OK || handled) return rc;
         }
+    }
+    if (dstT == ASCQ_DT_FP4X2_E2M1 && (a.roundMode == kRoundRint || a.roundMode == kRoundNone) && a.cols % 8 == 0 && aligned16(src) &&
+        (reinterpret_cast<uintptr_t>(dst) & 3u) == 0 && a.scale.rdiv != 0 &&
+        (a.scale.cdiv % 8 == 0 ? a.scale.cdiv != 0 : (a.scale.cdiv == 1 && aligned16(scale) && (a.cols * dtype_size(scaleT)) % 16 == 0))) {
+        bool handled = false;
+        ascq_status rc = dispatch_quant_fp4(a, srcT, scaleT, ct, st, &handled);
+        if (rc != ASCQ_OK || handled) return rc;
     }
     GenericArgs g{};
     g.op = kOpQuant; g.srcT = srcT; g.dstT = dstT; g.scT = scaleT; g.ct = ct;
@@ -325,9 +437,6 @@ __device__ __forceinline__ float fmax_nan(float a, float b)
     asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
     return r;
 }
-template <typename T> struct Two;
-template <> struct Two<__half> { using type = __half2; };
-template <> struct Two<__nv_bfloat16> { using type = __nv_bfloat162; };
 
 // One lane owns one 16-byte vector of the source (8 half / bfloat16 or 4 float elements); the 4 or 8 lanes that share
 // a 32-element block combine their maxima with shuffles.  Every load, code store and scale store of a warp is

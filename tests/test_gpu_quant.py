@@ -153,6 +153,30 @@ def test_per_group_to_fp4(srcT, scaleT):
     assert_bits_equal(run_quant(x, srcT, **kw), O.ascend_quant(x, srcT, **kw), "fp4 quant")
 
 
+@pytest.mark.parametrize("srcT,scaleT", [(O.F16, O.F16), (O.BF16, O.BF16), (O.F16, O.F32), (O.BF16, O.F32), (O.F32, O.F32)])
+@pytest.mark.parametrize("kDim", [0, 1])
+@pytest.mark.parametrize("m,n", [(64, 256), (96, 1000), (32, 36)])
+def test_per_group_to_fp4_shapes_and_specials(srcT, scaleT, kDim, m, n):
+    """The vector kernel (n a multiple of 8) and the scalar one (n = 36) against the oracle: groups along either
+    axis, values beyond +-6, infinities, a NaN (positive: the sign of a NaN does not survive a multiply on the GPU and is
+    not part of the contract), signed zeros."""
+    gs = 32
+    rng = np.random.default_rng(7 * m + n + 3 * srcT + scaleT + kDim)
+    x = rng.uniform(-9, 9, (m, n)).astype(np.float32)
+    x[1, 3] = np.inf; x[2, 5] = -np.inf; x[3, 6] = np.nan; x[5, 8] = -0.0; x[6, 9] = 1e30; x[7, 10] = -1e-30
+    x[8, :12] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -0.75, -2.5, -5.0, 6.5]
+    with np.errstate(over="ignore", invalid="ignore"):
+        xs = x.astype(np.float16) if srcT == O.F16 else (O.f32_to_bf16_bits(x) if srcT == O.BF16 else x)
+    shape = (m, (n + gs - 1) // gs) if kDim == 1 else ((m + gs - 1) // gs, n)
+    scale = rand_float(rng, shape, scaleT, 0.5, 2.0)
+    if kDim == 1:
+        scale.reshape(-1)[0] = scale.reshape(-1)[0] * 0 + 1  # keeps row 8's ties on the ties (first group of row 0 only)
+    kw = dict(policy=O.PER_GROUP, m=m, n=n, calCount=m * n, scale=scale, scaleT=scaleT, groupSize=gs, kDim=kDim, dstT=O.FP4X2_E2M1)
+    got, want = run_quant(xs, srcT, **kw), O.ascend_quant(xs, srcT, **kw)
+    bad = np.argwhere(got.reshape(-1) != want.reshape(-1))
+    assert bad.size == 0, f"{len(bad)} bytes differ, first at {bad[0]}: got {got.reshape(-1)[bad[0][0]]:#x} want {want.reshape(-1)[bad[0][0]]:#x}"
+
+
 def test_dynamic_per_token_quant():
     rng = np.random.default_rng(1234)
     for m, n, dt in [(64, 4096, O.F16), (5, 1000, O.F32), (17, 8192, O.BF16), (3, 7, O.F16)]:
