@@ -9,6 +9,21 @@ ascq_status run_fast(const EwArgs& a, int smode, bool hasOff, cudaStream_t st)
 {
     return launch_ew_rows<kOpAntiQuant, int8_t, Dst, Sc, CT>(a, smode, hasOff, false, st);
 }
+// int4b_t sources: the type triples of the legacy overloads (what the weight-only-quantised matmul uses) and of the
+// unified interface on half; everything else from int4 goes to the scalar kernel
+ascq_status dispatch_fast_i4(const EwArgs& a, ascq_dtype dstT, ascq_dtype scT, ascq_dtype ct, int smode, bool hasOff, cudaStream_t st,
+                             bool* handled)
+{
+    *handled = true;
+    if (ct == ASCQ_DT_F16 && dstT == ASCQ_DT_F16 && (scT == ASCQ_DT_F16 || smode == kSScalar))
+        return launch_ew_rows<kOpAntiQuant, int4x2_t, __half, __half, __half>(a, smode, hasOff, false, st);
+    if (ct == ASCQ_DT_F32 && dstT == ASCQ_DT_BF16 && (scT == ASCQ_DT_BF16 || smode == kSScalar))
+        return launch_ew_rows<kOpAntiQuant, int4x2_t, __nv_bfloat16, __nv_bfloat16, float>(a, smode, hasOff, false, st);
+    if (ct == ASCQ_DT_F32 && dstT == ASCQ_DT_F16 && (scT == ASCQ_DT_F16 || smode == kSScalar))
+        return launch_ew_rows<kOpAntiQuant, int4x2_t, __half, __half, float>(a, smode, hasOff, false, st);
+    *handled = false;
+    return ASCQ_OK;
+}
 
 ascq_status dispatch_fast(const EwArgs& a, ascq_dtype dstT, ascq_dtype scT, ascq_dtype ct, int smode, bool hasOff,
                           cudaStream_t st, bool* handled)
@@ -253,6 +268,11 @@ static ascq_status antiquant_common(void* dst, ascq_dtype dstT, const void* src,
     if (srcT == ASCQ_DT_I8 && ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {
         bool handled = false;
         ascq_status rc = dispatch_fast(a, dstT, scaleT, ct, smode, hasOff, st, &handled);
+        if (rc != ASCQ_OK || handled) return rc;
+    }
+    if (srcT == ASCQ_DT_I4X2 && ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {
+        bool handled = false;
+        ascq_status rc = dispatch_fast_i4(a, dstT, scaleT, ct, smode, hasOff, st, &handled);
         if (rc != ASCQ_OK || handled) return rc;
     }
     GenericArgs g{};

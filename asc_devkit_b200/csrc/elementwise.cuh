@@ -111,6 +111,31 @@ template <typename T, int N> __device__ __forceinline__ void store_pack_wide(T* 
     store_pack<T, N>(p, r);
 }
 
+// int4b_t source: two signed 4-bit values per byte, the even element in the low nibble.  The tag stands for one byte;
+// a thread's 16 elements are 8 source bytes, widened to sixteen int8 in registers right after the load, so that the
+// rest of the kernel is the int8 one.
+struct int4x2_t { uint8_t bits; };
+template <typename Src> struct SrcValue { using type = Src; };
+template <> struct SrcValue<int4x2_t> { using type = int8_t; };
+// four nibbles (16 bits) -> four sign-extended bytes
+__device__ __forceinline__ uint32_t widen_i4x4(uint32_t x)
+{
+    const uint32_t w = __byte_perm(x & 0x0F0Fu, (x >> 4) & 0x0F0Fu, 0x5140);  // bytes n0, n1, n2, n3
+    return w | ((w & 0x08080808u) * 0x1Eu);                                   // bit 3 of each byte copied into bits 4..7
+}
+template <int VEC> __device__ __forceinline__ Pack<int8_t, VEC> load_i4_as_i8(const void* base, size_t elemIndex)
+{
+    static_assert(VEC == 16, "sixteen int4 elements = one 8-byte load");
+    const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(base) + (elemIndex >> 1)));
+    Pack<int8_t, VEC> r;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&r);
+    w[0] = widen_i4x4(raw.x & 0xFFFFu);
+    w[1] = widen_i4x4(raw.x >> 16);
+    w[2] = widen_i4x4(raw.y & 0xFFFFu);
+    w[3] = widen_i4x4(raw.y >> 16);
+    return r;
+}
+
 template <typename Src, typename Dst> struct VecOf {
     static constexpr int kMin = sizeof(Src) < sizeof(Dst) ? sizeof(Src) : sizeof(Dst);
     static constexpr int value = 16 / kMin;
@@ -287,14 +312,18 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
     constexpr int U = (SMODE == kSRowVec) ? 1 : EwTune<OP>::kRowsInFlight;
     const uint32_t gy = gridDim.y;
     for (uint32_t r0 = blockIdx.y; r0 < a.rows; r0 += gy * U) {
-        Pack<Src, VEC> in[U];
+        using SrcV = typename SrcValue<Src>::type;
+        Pack<SrcV, VEC> in[U];
         CT srow[U], orow[U];
         float tok[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const uint32_t r = r0 + u * gy;
             if (r < a.rows) {
-                in[u] = load_pack_wide<Src, VEC>(static_cast<const Src*>(a.src) + static_cast<size_t>(r) * a.srcStride + c0, a.wide32 != 0);
+                if constexpr (std::is_same<Src, int4x2_t>::value)
+                    in[u] = load_i4_as_i8<VEC>(a.src, static_cast<size_t>(r) * a.srcStride + c0);
+                else
+                    in[u] = load_pack_wide<Src, VEC>(static_cast<const Src*>(a.src) + static_cast<size_t>(r) * a.srcStride + c0, a.wide32 != 0);
                 if constexpr (SMODE == kSRowBcast) {
                     const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + sc_col;
                     srow[u] = Ct<CT>::from_f32(to_f32<Sc>(__ldg(static_cast<const Sc*>(a.scale.p) + idx)));
@@ -323,7 +352,7 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
                 }
             }
             alignas(4) CT x[VEC];
-            unpack_src<Src, CT, VEC>(in[u], x);
+            unpack_src<SrcV, CT, VEC>(in[u], x);
             apply_op<OP, CT, VEC, SV, HAS_OFF, HAS_TOK>(x, s, o, HAS_TOK ? tok[u] : 1.0f);
             Pack<Dst, VEC> out;
             pack_dst<Dst, CT, VEC>(x, out, a.roundMode);
