@@ -346,9 +346,10 @@ template <typename Src> __device__ __forceinline__ float absmax8(const Pack<Src,
 }
 
 // One CTA per row.  Pass 1 streams the row (8 elements per thread per step) and reduces |x| with
-// warp shuffles, then across the CTA's warps through shared memory; pass 2 re-reads the row
-// (it is L2 resident: a row is at most a few hundred KB) and writes int8.
-template <typename Src> __global__ void __launch_bounds__(256) dyn_quant_kernel(int8_t* __restrict__ dst,
+// warp shuffles, then across the CTA's warps through shared memory; pass 2 writes int8.  RES > 0: the row has at
+// most RES * 2048 elements and stays in the threads' registers between the passes (one read of the source);
+// otherwise pass 2 re-reads it (it is L2 resident: a row is at most a few hundred KB).
+template <typename Src, int RES> __global__ void __launch_bounds__(256) dyn_quant_kernel(int8_t* __restrict__ dst,
                                                                                 float* __restrict__ scaleOut,
                                                                                 float* __restrict__ deqOut,
                                                                                 const Src* __restrict__ src,
@@ -360,7 +361,17 @@ template <typename Src> __global__ void __launch_bounds__(256) dyn_quant_kernel(
     const Src* row = src + static_cast<size_t>(r) * n;
     int8_t* out = dst + static_cast<size_t>(r) * n;
     float m = 0.f;
-    if (vecOk) {
+    Pack<Src, 8> held[RES > 0 ? RES : 1];
+    if constexpr (RES > 0) {
+#pragma unroll
+        for (int i = 0; i < RES; ++i) {
+            const uint32_t c = (i * 256 + threadIdx.x) * 8;
+            if (c < n) {
+                held[i] = load_pack<Src, 8, true>(row + c);
+                m = fmaxf(m, absmax8<Src>(held[i]));
+            }
+        }
+    } else if (vecOk) {
         for (uint32_t c = threadIdx.x * 8; c < n; c += blockDim.x * 8) m = fmaxf(m, absmax8<Src>(load_pack<Src, 8, false>(row + c)));
     } else {
         for (uint32_t c = threadIdx.x; c < n; c += blockDim.x) m = fmaxf(m, fabsf(to_f32<Src>(row[c])));
@@ -382,14 +393,22 @@ template <typename Src> __global__ void __launch_bounds__(256) dyn_quant_kernel(
     }
     __syncthreads();
     const float s = rowScale;
-    if (vecOk) {
-        for (uint32_t c = threadIdx.x * 8; c < n; c += blockDim.x * 8) {
-            const Pack<Src, 8> v = load_pack<Src, 8, true>(row + c);
-            Pack<int8_t, 8> q;
+    auto quant8 = [&](const Pack<Src, 8>& v, uint32_t c) {
+        uint2 q;
+        q.x = pack_i8x4_rni(__fmul_rn(to_f32<Src>(v.v[0]), s), __fmul_rn(to_f32<Src>(v.v[1]), s), __fmul_rn(to_f32<Src>(v.v[2]), s),
+                            __fmul_rn(to_f32<Src>(v.v[3]), s));
+        q.y = pack_i8x4_rni(__fmul_rn(to_f32<Src>(v.v[4]), s), __fmul_rn(to_f32<Src>(v.v[5]), s), __fmul_rn(to_f32<Src>(v.v[6]), s),
+                            __fmul_rn(to_f32<Src>(v.v[7]), s));
+        __stcs(reinterpret_cast<uint2*>(out + c), q);
+    };
+    if constexpr (RES > 0) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) q.v[i] = static_cast<int8_t>(f32_to_i8_sat(__fmul_rn(to_f32<Src>(v.v[i]), s), kRoundRint));
-            store_pack<int8_t, 8>(out + c, q);
+        for (int i = 0; i < RES; ++i) {
+            const uint32_t c = (i * 256 + threadIdx.x) * 8;
+            if (c < n) quant8(held[i], c);
         }
+    } else if (vecOk) {
+        for (uint32_t c = threadIdx.x * 8; c < n; c += blockDim.x * 8) quant8(load_pack<Src, 8, true>(row + c), c);
     } else {
         for (uint32_t c = threadIdx.x; c < n; c += blockDim.x)
             out[c] = static_cast<int8_t>(f32_to_i8_sat(__fmul_rn(to_f32<Src>(row[c]), s), kRoundRint));
@@ -406,12 +425,16 @@ extern "C" ascq_status ascq_dynamic_quant_per_token(int8_t* dst, float* scaleOut
     if (!is_float_type(srcT)) return fail(ASCQ_ERR_UNSUPPORTED, "src dtype must be half, bfloat16_t or float");
     if (m == 0 || n == 0) return ASCQ_OK;
     const int vecOk = (n % 8 == 0) && aligned16(src) && ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0);
-    if (srcT == ASCQ_DT_F16)
-        dyn_quant_kernel<__half><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, static_cast<const __half*>(src), n, vecOk);
-    else if (srcT == ASCQ_DT_BF16)
-        dyn_quant_kernel<__nv_bfloat16><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, static_cast<const __nv_bfloat16*>(src), n, vecOk);
-    else
-        dyn_quant_kernel<float><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, static_cast<const float*>(src), n, vecOk);
+    auto run = [&](auto tag) {
+        using Src = decltype(tag);
+        const Src* sp = static_cast<const Src*>(src);
+        if (vecOk && n <= 2048u) dyn_quant_kernel<Src, 1><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, sp, n, vecOk);
+        else if (vecOk && n <= 8192u) dyn_quant_kernel<Src, 4><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, sp, n, vecOk);
+        else dyn_quant_kernel<Src, 0><<<m, 256, 0, st>>>(dst, scaleOut, deqScaleOut, sp, n, vecOk);
+    };
+    if (srcT == ASCQ_DT_F16) run(__half{});
+    else if (srcT == ASCQ_DT_BF16) run(__nv_bfloat16{});
+    else run(float{});
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
 }
