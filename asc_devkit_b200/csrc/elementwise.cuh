@@ -154,6 +154,29 @@ __device__ __forceinline__ void unpack_src(const Pack<Src, VEC>& in, CT (&x)[VEC
 #pragma unroll
             for (int j = 0; j < 4; ++j) x[q * 4 + j] = f[j];
         }
+    } else if constexpr (std::is_same<Src, int8_t>::value && std::is_same<CT, __half>::value && (VEC % 4 == 0)) {
+        // byte ^ 0x80 in the low byte of the half 1024.0 (0x6400) is 1024 + (v + 128); subtracting 1152 is exact
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&in);
+        __half2* x2 = reinterpret_cast<__half2*>(x);
+        const uint32_t bias = 0x64806480u;  // 1152.0 twice
+#pragma unroll
+        for (int q = 0; q < VEC / 4; ++q) {
+            const uint32_t b = w[q] ^ 0x80808080u;
+            const uint32_t lo = __byte_perm(b, 0x64646464u, 0x4140), hi = __byte_perm(b, 0x64646464u, 0x4342);
+            x2[2 * q] = __hsub2(*reinterpret_cast<const __half2*>(&lo), *reinterpret_cast<const __half2*>(&bias));
+            x2[2 * q + 1] = __hsub2(*reinterpret_cast<const __half2*>(&hi), *reinterpret_cast<const __half2*>(&bias));
+        }
+    } else if constexpr (std::is_same<Src, int8_t>::value && std::is_same<CT, __nv_bfloat16>::value && (VEC % 4 == 0)) {
+        // through fp32 (no conversion pipe), then two exact narrowing conversions per instruction
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&in);
+        __nv_bfloat162* x2 = reinterpret_cast<__nv_bfloat162*>(x);
+#pragma unroll
+        for (int q = 0; q < VEC / 4; ++q) {
+            float f[4];
+            unpack_i8x4_f32(w[q], f);
+            x2[2 * q] = __floats2bfloat162_rn(f[0], f[1]);
+            x2[2 * q + 1] = __floats2bfloat162_rn(f[2], f[3]);
+        }
     } else if constexpr (std::is_same<Src, CT>::value) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) x[i] = in.v[i];
@@ -175,8 +198,18 @@ __device__ __forceinline__ void pack_dst(const CT (&x)[VEC], Pack<Dst, VEC>& out
                 w[q] = pack_i8x4_rni(Ct<CT>::to_f32(x[q * 4]), Ct<CT>::to_f32(x[q * 4 + 1]), Ct<CT>::to_f32(x[q * 4 + 2]),
                                      Ct<CT>::to_f32(x[q * 4 + 3]));
         } else {
+            // the other modes: round to an integral float first (one instruction for floor / ceil / trunc), then the
+            // same saturating pack (NaN -> 0, out-of-range values clamp)
+            auto packRounded = [&](auto rnd) {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) out.v[i] = static_cast<int8_t>(f32_to_i8_sat(Ct<CT>::to_f32(x[i]), roundMode));
+                for (int q = 0; q < VEC / 4; ++q)
+                    w[q] = pack_i8x4_rni(rnd(Ct<CT>::to_f32(x[q * 4])), rnd(Ct<CT>::to_f32(x[q * 4 + 1])), rnd(Ct<CT>::to_f32(x[q * 4 + 2])),
+                                         rnd(Ct<CT>::to_f32(x[q * 4 + 3])));
+            };
+            if (roundMode == kRoundFloor) packRounded([](float v) { return floorf(v); });
+            else if (roundMode == kRoundCeil) packRounded([](float v) { return ceilf(v); });
+            else if (roundMode == kRoundTrunc) packRounded([](float v) { return truncf(v); });
+            else packRounded([](float v) { return round_by_mode(v, kRoundRound); });
         }
     } else if constexpr (std::is_same<Dst, CT>::value) {
 #pragma unroll
@@ -213,6 +246,27 @@ __device__ __forceinline__ void apply_op(CT (&x)[VEC], const CT (&s)[SV], const 
                 if constexpr (HAS_OFF) v = __hadd2_rn(v, o2);
             } else if constexpr (OP == kOpDequant) {
                 v = __hmul2_rn(v, s2);
+            } else {
+                if constexpr (HAS_OFF) v = __hadd2_rn(v, o2);
+                v = __hmul2_rn(v, s2);
+            }
+            x2[q] = v;
+        }
+    } else if constexpr (std::is_same<CT, __nv_bfloat16>::value && (VEC % 2 == 0)) {
+        // bfloat16 likewise (mul.rn.bf16x2 / add.rn.bf16x2: each lane is the exact result rounded once, which is what the
+        // scalar form computes through fp32)
+        __nv_bfloat162* x2 = reinterpret_cast<__nv_bfloat162*>(x);
+#pragma unroll
+        for (int q = 0; q < VEC / 2; ++q) {
+            const __nv_bfloat162 s2 = kVecScale ? __halves2bfloat162(s[2 * q], s[2 * q + 1]) : __bfloat162bfloat162(s[0]);
+            const __nv_bfloat162 o2 = kVecScale ? __halves2bfloat162(o[2 * q], o[2 * q + 1]) : __bfloat162bfloat162(o[0]);
+            __nv_bfloat162 v = x2[q];
+            if constexpr (OP == kOpQuant) {
+                v = __hmul2_rn(v, s2);
+                if constexpr (HAS_OFF) v = __hadd2_rn(v, o2);
+            } else if constexpr (OP == kOpDequant) {
+                v = __hmul2_rn(v, s2);
+                if constexpr (HAS_TOK) v = __hmul2_rn(v, __bfloat162bfloat162(Ct<CT>::from_f32(tok)));
             } else {
                 if constexpr (HAS_OFF) v = __hadd2_rn(v, o2);
                 v = __hmul2_rn(v, s2);
@@ -309,17 +363,29 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
 
     // Rows are taken U at a time: all U source vectors (and the per-row scalars) are requested before
     // the first result is stored, so every thread keeps U vector loads in flight.
-    constexpr int U = (SMODE == kSRowVec) ? 1 : EwTune<OP>::kRowsInFlight;
+    // Which rows: blockIdx.y + k * gridDim.y in general.  With a scale vector per group of rows (kSRowVec) a block takes a
+    // run of consecutive rows instead, so that the vector (and its conversion to the compute type) is fetched once per
+    // group and not once per row.
+    // one row at a time where two vectors of fp32 parameters are held in registers
+    constexpr int U = (SMODE == kSRowVec && HAS_OFF && sizeof(CT) == 4) ? 1 : EwTune<OP>::kRowsInFlight;
     const uint32_t gy = gridDim.y;
-    for (uint32_t r0 = blockIdx.y; r0 < a.rows; r0 += gy * U) {
+    uint32_t rStart = blockIdx.y, rStep = gy, rEnd = a.rows;
+    if constexpr (SMODE == kSRowVec) {
+        const uint32_t per = (a.rows + gy - 1) / gy;
+        rStart = blockIdx.y * per;
+        rStep = 1;
+        rEnd = min(a.rows, rStart + per);
+    }
+    uint32_t heldGroup = 0xFFFFFFFFu;
+    for (uint32_t r0 = rStart; r0 < rEnd; r0 += rStep * U) {
         using SrcV = typename SrcValue<Src>::type;
         Pack<SrcV, VEC> in[U];
         CT srow[U], orow[U];
         float tok[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const uint32_t r = r0 + u * gy;
-            if (r < a.rows) {
+            const uint32_t r = r0 + u * rStep;
+            if (r < rEnd) {
                 if constexpr (std::is_same<Src, int4x2_t>::value)
                     in[u] = load_i4_as_i8<VEC>(a.src, static_cast<size_t>(r) * a.srcStride + c0);
                 else
@@ -335,13 +401,16 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const uint32_t r = r0 + u * gy;
-            if (r >= a.rows) break;
+            const uint32_t r = r0 + u * rStep;
+            if (r >= rEnd) break;
             if constexpr (SMODE == kSRowBcast) {
                 s[0] = srow[u];
                 if constexpr (HAS_OFF) o[0] = orow[u];
             } else if constexpr (SMODE == kSRowVec) {
-                const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + c0;
+                const uint32_t group = a.scale.rdiv ? r / a.scale.rdiv : 0u;
+                if (group != heldGroup) {
+                heldGroup = group;
+                const size_t idx = static_cast<size_t>(group) * a.scale.stride + c0;
                 const Pack<Sc, VEC> sp = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.scale.p) + idx);
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) s[i] = Ct<CT>::from_f32(to_f32<Sc>(sp.v[i]));
@@ -349,6 +418,7 @@ __global__ void __launch_bounds__(256, ASCQ_EW_MINB) ew_rows_kernel(const EwArgs
                     const Pack<Sc, VEC> op = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.offset.p) + idx);
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(to_f32<Sc>(op.v[i]));
+                }
                 }
             }
             alignas(4) CT x[VEC];
