@@ -332,12 +332,13 @@ template <> struct EwTune<1 /* kOpDequant */> {
 #define ASCQ_EW_TARGET 16u
 #endif
 // Resident CTAs per SM the register budget is set for: four (64 registers), or three (80) where a thread holds a vector
-// of fp32 scales and one of fp32 offsets next to its data -- those spilled at 64.
-template <typename CT, int SMODE, bool HAS_OFF> struct EwMinBlocks {
-    static constexpr int value = ((SMODE == kSColVec || SMODE == kSRowVec) && HAS_OFF && sizeof(CT) == 4) ? 3 : ASCQ_EW_MINB;
+// of fp32 scales and one of fp32 offsets next to its data (quant: 32- or 64-byte source vectors) -- those spilled at 64.
+template <int OP, typename CT, int SMODE, bool HAS_OFF> struct EwMinBlocks {
+    static constexpr int value =
+        (OP == kOpQuant && (SMODE == kSColVec || SMODE == kSRowVec) && HAS_OFF && sizeof(CT) == 4) ? 3 : ASCQ_EW_MINB;
 };
 template <int OP, typename Src, typename Dst, typename Sc, typename CT, int SMODE, bool HAS_OFF, bool HAS_TOK>
-__global__ void __launch_bounds__(256, EwMinBlocks<CT, SMODE, HAS_OFF>::value) ew_rows_kernel(const EwArgs a)
+__global__ void __launch_bounds__(256, EwMinBlocks<OP, CT, SMODE, HAS_OFF>::value) ew_rows_kernel(const EwArgs a)
 {
     constexpr int VEC = VecOf<Src, Dst>::value;
     constexpr bool kVecScale = (SMODE == kSColVec || SMODE == kSRowVec);
