@@ -765,6 +765,108 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_extras(args):
+    """`--workload extras`: the operators of the path that are not among the five benchmark configurations, each timed
+    the same way (K steps replayed from one CUDA graph, CUDA events, inputs rotated over more than the L2 size where
+    one set is smaller) and reported in one JSON line.  Single GPU."""
+    import ctypes as C
+    import numpy as np
+    import torch
+    from asc_devkit_b200 import _lib as L, ops
+    L.lib()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    steps, warm = min(args.steps, 40), max(args.warmup, 3)
+    out = {}
+
+    def add(name, fn, work, unit):
+        sec = time_graph(torch, fn, steps, warm)
+        if sec is None:
+            sec = time_steps(torch, fn, steps, warm)
+        us = sec / steps * 1e6
+        out[name] = {"us": round(us, 1), "rate": round(work / us / 1e6, 2), "unit": unit}  # work per us -> T(unit)/s
+        print(f"extras: {name}: {us:.1f} us, {work / us / 1e6:.2f} {unit}", file=sys.stderr)
+
+    # ---- matmuls at 4096^3 (six operand sets: 200 MB of operands) ----
+    M = N = K = 4096
+    ns = 6
+    flop = 2.0 * M * N * K
+    A8 = [torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev) for _ in range(ns)]
+    B8 = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(ns)]
+    bias = torch.randint(-100, 100, (N,), dtype=torch.int32, device=dev)
+    qv = torch.from_numpy((np.random.default_rng(0).uniform(1e-4, 1e-3, N).astype(np.float32).view(np.uint32).astype(np.uint64)
+                           | np.uint64(1 << 46)).view(np.int64)).to(dev)
+    Ch = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(ns)]
+    Cb = [torch.empty((M, N), dtype=torch.int8, device=dev) for _ in range(ns)]
+    add("int8 matmul + fixpipe quantisation -> fp16 (VDEQF16)", lambda i: ops.MatmulI8Quant(Ch[i % ns], A8[i % ns], B8[i % ns], bias, qv, 1.0), flop, "TOPS")
+    add("int8 matmul + requantisation -> int8 (VREQ8)", lambda i: ops.MatmulI8Requant(Cb[i % ns], A8[i % ns], B8[i % ns], bias, qv), flop, "TOPS")
+    del A8, Ch
+    for dt, nm in ((torch.bfloat16, "bfloat16"), (torch.float16, "half")):
+        A = [torch.randn((M, K), device=dev).to(dt) for _ in range(ns)]
+        B = [torch.randn((N, K), device=dev).to(dt) for _ in range(ns)]
+        Cc = [torch.empty((M, N), dtype=dt, device=dev) for _ in range(ns)]
+        add(f"{nm} matmul", lambda i: ops.MatmulF16(Cc[i % ns], A[i % ns], B[i % ns]), flop, "TFLOPS")
+        add(f"{nm} matmul, cuBLAS through torch (for comparison)", lambda i: torch.matmul(A[i % ns], B[i % ns].t(), out=Cc[i % ns]), flop, "TFLOPS")
+        add(f"{nm} matmul + fixpipe quantisation -> int8 (QF322B8_PRE)",
+            lambda i: ops.MatmulF16Quant(Cb[i % ns], A[i % ns], B[i % ns], None, int(np.float32(0.05).view(np.uint32)) | (1 << 46)), flop, "TFLOPS")
+        sc = (torch.rand(N, device=dev) * 0.02).to(dt)
+        of = torch.randn(N, device=dev).to(dt)
+        ws = torch.empty(N * K * 2, dtype=torch.uint8, device=dev)
+        B4 = [b[:, : K // 2].contiguous().view(torch.uint8) for b in B8]
+        add(f"weight-only-quantised matmul, int8 weights, {nm} activations", lambda i: ops.MatmulW8A16(Cc[i % ns], A[i % ns], B8[i % ns], of, sc, workspace=ws), flop, "TFLOPS")
+        add(f"weight-only-quantised matmul, int4 weights, {nm} activations", lambda i: ops.MatmulW4A16(Cc[i % ns], A[i % ns], B4[i % ns], of, sc, workspace=ws), flop, "TFLOPS")
+        del A, B, Cc
+    del B8, Cb
+    # ---- MX matmul with fp8 operands at config 5's shape (uniform groups) ----
+    G, K5, N5, sumM = 16, 7168, 2048, 16384
+    groups = [sumM // G] * G
+    A5 = torch.randint(0, 120, (sumM, K5), dtype=torch.uint8, device=dev)
+    B5 = torch.randint(0, 120, (G, N5, K5), dtype=torch.uint8, device=dev)
+    sA5 = torch.randint(123, 131, (sumM, K5 // 32), dtype=torch.uint8, device=dev)
+    sB5 = torch.randint(123, 131, (G, N5, K5 // 32), dtype=torch.uint8, device=dev)
+    C5 = torch.empty((sumM, N5), dtype=torch.bfloat16, device=dev)
+    ws5 = torch.empty(int(L.lib().ascq_group_matmul_mxfp8_workspace_size(sumM, G, K5, N5)) + 256, dtype=torch.uint8, device=dev)
+    add("MX matmul, fp8 e4m3 operands, config 5's shape", lambda i: ops.GroupMatmulMxfp8(C5, A5, L.DT_FP8_E4M3, sA5, B5, L.DT_FP8_E4M3, sB5, groups, K5, N5, workspace=ws5),
+        2.0 * sumM * K5 * N5, "TFLOPS")
+    del A5, B5, C5
+    # ---- producers and decoders of the MX operands, [16384, 7168] activations / [4096, 11008] weights ----
+    m, n = 16384, 7168
+    x = torch.randn((m, n), device=dev).bfloat16()
+    d4 = torch.empty((m, n // 2), dtype=torch.uint8, device=dev)
+    s4 = torch.empty((m, n // 32), dtype=torch.uint8, device=dev)
+    add("dynamic MX-FP4 quantiser, bf16 [16384, 7168]", lambda i: ops.DynamicQuantMxfp4(d4, s4, x), x.numel() * 2 + d4.numel() + s4.numel(), "TB/s")
+    scb = (torch.rand((m, n // 32), device=dev) + 0.5).bfloat16()
+    qp = L.QuantParam(m, n, m * n, 32, 0, 1, 1)
+    add("AscendQuant PER_GROUP -> fp4x2, bf16 [16384, 7168]",
+        lambda i: L.check(L.lib().ascq_quant(ops._ptr(d4), L.DT_FP4X2_E2M1, ops._ptr(x), L.DT_BF16, ops._ptr(scb), None, L.DT_BF16, 0.0, 0.0,
+                                             L.PER_GROUP, C.byref(qp), ops._stream(None))), x.numel() * 2 + scb.numel() * 2 + d4.numel(), "TB/s")
+    d8 = torch.empty((m, n), dtype=torch.int8, device=dev)
+    so = torch.empty(m, dtype=torch.float32, device=dev)
+    add("dynamic per-token quantiser, bf16 [16384, 7168] -> int8", lambda i: ops.DynamicQuantPerToken(d8, so, x), x.numel() * 3, "TB/s")
+    rows, cols = 4096, 11008
+    src4 = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=dev)
+    sc4 = torch.randint(120, 135, (rows * (cols // 32),), dtype=torch.uint8, device=dev)
+    dst4 = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev)
+    add("MX decode fp4x2 [4096, 11008] -> bf16 (groups along the columns)",
+        lambda i: ops.AscendAntiQuant(dst4, src4, None, sc4, ops.AscendAntiQuantParam(rows, cols), isTranspose=True, policy=L.PER_GROUP,
+                                      hasOffset=False, src_dtype=L.DT_FP4X2_E2M1, scale_dtype=L.DT_E8M0), src4.numel() + sc4.numel() + dst4.numel() * 2, "TB/s")
+    # ---- the three elementwise operators under the other policies, [16384, 7168], group size 128 ----
+    gs = 128
+    for pol, nm, shape, kd in ((L.PER_TOKEN, "PER_TOKEN", (m,), 1), (L.PER_GROUP, "PER_GROUP kDim=1", (m, n // gs), 1), (L.PER_GROUP, "PER_GROUP kDim=0", (m // gs, n), 0)):
+        sc = (torch.rand(shape, device=dev) + 0.5).bfloat16()
+        of = torch.randn(shape, device=dev).bfloat16()
+        p1 = L.QuantParam(m, n, m * n, gs if pol == L.PER_GROUP else 0, 1, kd, 1)
+        add(f"AscendQuant bf16 -> int8 {nm}", lambda i: L.check(L.lib().ascq_quant(ops._ptr(d8), L.DT_I8, ops._ptr(x), L.DT_BF16, ops._ptr(sc), ops._ptr(of),
+            L.DT_BF16, 0.0, 0.0, pol, C.byref(p1), ops._stream(None))), x.numel() * 3, "TB/s")
+        p2 = L.AntiQuantParam(m, n, m * n, gs if pol == L.PER_GROUP else 0, 1, 0, kd)
+        yb = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        add(f"AscendAntiQuant int8 -> bf16 {nm}", lambda i: L.check(L.lib().ascq_antiquant(ops._ptr(yb), L.DT_BF16, ops._ptr(d8), L.DT_I8, ops._ptr(of), ops._ptr(sc),
+            L.DT_BF16, 0.0, 0.0, pol, C.byref(p2), ops._stream(None))), x.numel() * 3, "TB/s")
+    ops.MatmulStatus()
+    print(json.dumps({"metric": "operators of the path beside the five benchmark configurations", "n_gpus": 1, "steps": steps, "warmup": warm,
+                      "data": "synthetic", "launch": "the K steps replayed from one CUDA graph", "extras": out}))
+
+
 def run_reference(args):
     """The reference arm: the CPU restatement of the reference operators on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -833,7 +935,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all"] + list(WORKLOADS))
+    ap.add_argument("--workload", default="all", choices=["all", "extras"] + list(WORKLOADS))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     # Libraries (NCCL's version banner, for one) write to file descriptor 1; the JSON line must be the only thing on
@@ -843,7 +945,11 @@ def main():
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w")
     if args.impl == "reference":
+        if args.workload == "extras":
+            args.workload = "all"
         run_reference(args)
+    elif args.workload == "extras":
+        run_extras(args)
     else:
         run_ours(args)
     sys.stdout.flush()
