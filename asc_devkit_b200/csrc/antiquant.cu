@@ -265,9 +265,11 @@ static ascq_status antiquant_common(void* dst, ascq_dtype dstT, const void* src,
     }
 
     if (unified) ct = ASCQ_DT_F32;
-    if (srcT == ASCQ_DT_I8 && ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {
+    if (srcT == ASCQ_DT_I8) {
+        EwArgs b = a;
+        b.scalarPath = ew_fast_ok(a, 16, smode, dtype_size(scaleT)) ? 0 : 1;  // ragged / unaligned: one element per thread
         bool handled = false;
-        ascq_status rc = dispatch_fast(a, dstT, scaleT, ct, smode, hasOff, st, &handled);
+        ascq_status rc = dispatch_fast(b, dstT, scaleT, ct, smode, hasOff, st, &handled);
         if (rc != ASCQ_OK || handled) return rc;
     }
     if (srcT == ASCQ_DT_I4X2 && ew_fast_ok(a, 16, smode, dtype_size(scaleT))) {

@@ -124,9 +124,11 @@ extern "C" ascq_status ascq_dequant(void* dst, ascq_dtype dstT, const void* src,
     if (a.rows == 0 || a.cols == 0) return ASCQ_OK;
 
     const int vec = 16 / (dtype_size(dstT) < 4 ? dtype_size(dstT) : 4);
-    if (ew_fast_ok(a, vec, smode, dtype_size(scaleT))) {
+    {
+        EwArgs b = a;
+        b.scalarPath = ew_fast_ok(a, vec, smode, dtype_size(scaleT)) ? 0 : 1;  // ragged / unaligned: one element per thread
         bool handled = false;
-        ascq_status rc = dispatch_fast(a, srcT, dstT, scaleT, smode, tokScale != nullptr, st, &handled);
+        ascq_status rc = dispatch_fast(b, srcT, dstT, scaleT, smode, tokScale != nullptr, st, &handled);
         if (rc != ASCQ_OK || handled) return rc;
     }
     GenericArgs g{};

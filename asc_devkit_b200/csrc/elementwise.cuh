@@ -44,6 +44,7 @@ struct EwArgs {
     const float* tok;  // dequant only: optional fp32 per-row multiplier applied after the scale
     int roundMode;
     int wide32;        // src / dst bases and row pitches are 32-byte aligned: 32-byte vectors move as one 256-bit access
+    int scalarPath;    // ragged widths / unaligned tensors: one element per thread, same types and arithmetic
 };
 
 template <int BYTES> struct Chunk;
@@ -456,6 +457,65 @@ inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* blo
     *block = dim3(bx, 1, 1);
 }
 
+// The same operators, one element per thread: for widths that are not a multiple of the vector, row pitches or
+// pointers that are not 16-byte aligned.  Types are compile-time (the arithmetic is the vector kernel's, element by
+// element).  SCALAR_PARAMS (one scale / offset for the whole tensor, passed by value) is a compile-time choice, so that
+// the variant without parameter tensors contains no load from them at all; how the tensors are indexed otherwise is
+// decided at run time, uniformly over the launch.
+template <int OP, typename Src, typename Dst, typename Sc, typename CT, bool SCALAR_PARAMS, bool HAS_TOK>
+__global__ void __launch_bounds__(256) ew_scalar_kernel(const EwArgs a, int hasOff)
+{
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.cols) return;
+    const Sc* sp = static_cast<const Sc*>(a.scale.p);
+    const Sc* op = static_cast<const Sc*>(a.offset.p);
+    const uint32_t sc_col = a.scale.cdiv ? c / a.scale.cdiv : 0u;
+    constexpr int U = 4;
+    for (uint32_t r0 = blockIdx.y; r0 < a.rows; r0 += gridDim.y * U) {
+        Src in[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gridDim.y;
+            if (r < a.rows) in[u] = static_cast<const Src*>(a.src)[static_cast<size_t>(r) * a.srcStride + c];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t r = r0 + u * gridDim.y;
+            if (r >= a.rows) break;
+            CT s, o = Ct<CT>::from_f32(0.f);
+            if constexpr (SCALAR_PARAMS) {
+                s = Ct<CT>::from_f32(a.scale.scalar);
+                if (hasOff & 1) o = Ct<CT>::from_f32(a.offset.scalar);
+            } else {
+                const size_t idx = static_cast<size_t>(a.scale.rdiv ? r / a.scale.rdiv : 0u) * a.scale.stride + sc_col;
+                s = Ct<CT>::from_f32(to_f32<Sc>(__ldg(sp + idx)));
+                // `op` always points at readable memory here (the launcher passes the scale tensor when the offset is a
+                // scalar): the compiler is free to issue this load before it knows which of the two is wanted
+                if (hasOff & 1) o = (hasOff & 2) ? Ct<CT>::from_f32(a.offset.scalar) : Ct<CT>::from_f32(to_f32<Sc>(__ldg(op + idx)));
+            }
+            CT x;
+            if constexpr (std::is_same<Src, CT>::value) x = in[u];
+            else x = Ct<CT>::from_f32(to_f32<Src>(in[u]));
+            if constexpr (OP == kOpQuant) {
+                x = Ct<CT>::mul(x, s);
+                if (hasOff & 1) x = Ct<CT>::add(x, o);
+            } else if constexpr (OP == kOpDequant) {
+                x = Ct<CT>::mul(x, s);
+                if constexpr (HAS_TOK) x = Ct<CT>::mul(x, Ct<CT>::from_f32(__ldg(a.tok + r)));
+            } else {
+                if (hasOff & 1) x = Ct<CT>::add(x, o);
+                x = Ct<CT>::mul(x, s);
+            }
+            const float y = Ct<CT>::to_f32(x);
+            Dst* d = static_cast<Dst*>(a.dst) + static_cast<size_t>(r) * a.dstStride + c;
+            if constexpr (std::is_same<Dst, int8_t>::value) *d = static_cast<int8_t>(f32_to_i8_sat(y, a.roundMode));
+            else if constexpr (std::is_same<Dst, __nv_bfloat16>::value) *d = f32_to_bf16_sat(y);
+            else if constexpr (std::is_same<Dst, __half>::value) *d = f32_to_f16_sat(y);
+            else *d = y;
+        }
+    }
+}
+
 // Launches the instantiation selected by (smode, hasOff, hasTok).  Offsets exist for quant and
 // antiquant, the per-row multiplier for dequant.
 template <int OP, typename Src, typename Dst, typename Sc, typename CT>
@@ -463,6 +523,32 @@ ascq_status launch_ew_rows(const EwArgs& a, int smode, bool hasOff, bool hasTok,
 {
     if (a.rows == 0 || a.cols == 0) return ASCQ_OK;
     dim3 grid, block;
+    if (a.scalarPath) {
+        if constexpr (std::is_same<Src, int4x2_t>::value) {
+            return fail(ASCQ_ERR_UNSUPPORTED, "packed sources have no element-per-thread form");
+        } else {
+            ew_grid(a.rows, a.cols, 1, &grid, &block, 16u);
+            EwArgs b = a;
+            if (!hasTok) b.tok = nullptr;
+            int off = hasOff ? 1 : 0;  // bit 0: there is an offset; bit 1: it is the scalar
+            if (smode != kSScalar && hasOff && b.offset.p == nullptr) {
+                off |= 2;
+                b.offset.p = b.scale.p;
+            }
+            if constexpr (OP == kOpDequant) {
+                if (hasTok) {
+                    if (smode == kSScalar) ew_scalar_kernel<OP, Src, Dst, Sc, CT, true, true><<<grid, block, 0, stream>>>(b, off);
+                    else ew_scalar_kernel<OP, Src, Dst, Sc, CT, false, true><<<grid, block, 0, stream>>>(b, off);
+                    ASCQ_CUDA_CHECK(cudaGetLastError());
+                    return ASCQ_OK;
+                }
+            }
+            if (smode == kSScalar) ew_scalar_kernel<OP, Src, Dst, Sc, CT, true, false><<<grid, block, 0, stream>>>(b, off);
+            else ew_scalar_kernel<OP, Src, Dst, Sc, CT, false, false><<<grid, block, 0, stream>>>(b, off);
+            ASCQ_CUDA_CHECK(cudaGetLastError());
+            return ASCQ_OK;
+        }
+    }
     ew_grid(a.rows, a.cols, VecOf<Src, Dst>::value, &grid, &block, EwTune<OP>::kCtasPerSm);
     EwArgs b = a;
     b.wide32 = EwTune<OP>::kWide256 && ((reinterpret_cast<uintptr_t>(a.src) | reinterpret_cast<uintptr_t>(a.dst)) & 31u) == 0 &&

@@ -293,6 +293,12 @@ static ascq_status quant_common(void* dst, ascq_dtype dstT, const void* src, asc
             bool handled = false;
             ascq_status rc = dispatch_fast(a, srcT, scaleT, ct, smode, hasOff, st, &handled);
             if (rc != ASCQ_OK || handled) return rc;
+        } else {  // ragged width or unaligned tensors: the same types, one element per thread
+            EwArgs b = a;
+            b.scalarPath = 1;
+            bool handled = false;
+            ascq_status rc = dispatch_fast(b, srcT, scaleT, ct, smode, hasOff, st, &handled);
+            if (rc != ASCQ_OK || handled) return rc;
         }
     }
     if (dstT == ASCQ_DT_FP4X2_E2M1 && (a.roundMode == kRoundRint || a.roundMode == kRoundNone) && a.cols % 8 == 0 && aligned16(src) &&
