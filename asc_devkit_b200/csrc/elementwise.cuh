@@ -45,6 +45,7 @@ struct EwArgs {
     int roundMode;
     int wide32;        // src / dst bases and row pitches are 32-byte aligned: 32-byte vectors move as one 256-bit access
     int scalarPath;    // ragged widths / unaligned tensors: one element per thread, same types and arithmetic
+    int offsetIsScalar;  // set by the launcher: a scale tensor with a scalar offset (offset.p then aliases scale.p)
 };
 
 template <int BYTES> struct Chunk;
@@ -356,11 +357,13 @@ __global__ void __launch_bounds__(256, EwMinBlocks<OP, CT, SMODE, HAS_OFF>::valu
 #pragma unroll
         for (int i = 0; i < VEC; ++i) s[i] = Ct<CT>::from_f32(to_f32<Sc>(sp.v[i]));
         if constexpr (HAS_OFF) {
-            if (a.offset.p != nullptr) {
+            // offsetIsScalar: per-channel scale with a scalar offset; offset.p then holds the scale tensor's address, so
+            // that the load below has a valid address even if it is scheduled ahead of the test
+            if (!a.offsetIsScalar) {
                 const Pack<Sc, VEC> op = load_pack<Sc, VEC, false>(static_cast<const Sc*>(a.offset.p) + c0);
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(to_f32<Sc>(op.v[i]));
-            } else {  // per-channel scale with a scalar offset
+            } else {
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) o[i] = Ct<CT>::from_f32(a.offset.scalar);
             }
@@ -551,6 +554,10 @@ ascq_status launch_ew_rows(const EwArgs& a, int smode, bool hasOff, bool hasTok,
     }
     ew_grid(a.rows, a.cols, VecOf<Src, Dst>::value, &grid, &block, EwTune<OP>::kCtasPerSm);
     EwArgs b = a;
+    if (smode == kSColVec && hasOff && b.offset.p == nullptr) {
+        b.offsetIsScalar = 1;
+        b.offset.p = b.scale.p;
+    }
     b.wide32 = EwTune<OP>::kWide256 && ((reinterpret_cast<uintptr_t>(a.src) | reinterpret_cast<uintptr_t>(a.dst)) & 31u) == 0 &&
                (static_cast<size_t>(a.srcStride) * sizeof(Src)) % 32 == 0 && (static_cast<size_t>(a.dstStride) * sizeof(Dst)) % 32 == 0;
 #define ASCQ_EW_LAUNCH(SM, OFF, TOK) \
