@@ -76,6 +76,21 @@ SIGNATURES = {
     "ascq_matmul_w4a16": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _f, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_matmul_w8a8_multicast": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ascq_matmul_status": (_i, [_vp]),
+    "ascq_comm_flag_bytes": (C.c_size_t, []),
+    "ascq_comm_create": (_i, [C.POINTER(_vp), _i, _i, C.POINTER(_vp)]),
+    "ascq_comm_destroy": (_i, [_vp]),
+    "ascq_comm_rank": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),
+    "ascq_comm_ipc_handle_bytes": (C.c_size_t, []),
+    "ascq_comm_ipc_export": (_i, [_vp, _vp]),
+    "ascq_comm_ipc_open": (_i, [C.POINTER(_vp), _vp]),
+    "ascq_comm_ipc_close": (_i, [_vp]),
+    "ascq_comm_barrier": (_i, [_vp, _vp]),
+    "ascq_shard_columns": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "ascq_shard_groups_lpt": (_i, [_P64, _i, _i, C.POINTER(_i)]),
+    "ascq_matmul_w8a8_sharded": (_i, [_vp, C.POINTER(_vp), _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ascq_group_matmul_mxfp4_sharded": (_i, [_vp, C.POINTER(_vp), _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
+    "ascq_set_wait_limit_cycles": (_i, [C.c_longlong]),
+    "ascq_test_withhold_after": (_i, [_i]),
     "ascq_group_matmul_mxfp4": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp4_scatter": (_i, [C.POINTER(_vp), _i, _i, _P64, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp8": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),

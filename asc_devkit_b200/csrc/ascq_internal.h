@@ -7,6 +7,7 @@
 #include <cstdio>
 
 #include "../../include/ascq.h"
+#include "comm.cuh"
 
 struct CUstream_st;
 
@@ -32,6 +33,22 @@ ascq_status mxfp4_read_status(::CUstream_st* stream);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Sets the wait limit (SM cycles) of the bounded waits in each matmul translation unit on the current device.
+ascq_status w8a8_set_wait_cycles(long long cycles);
+ascq_status mxfp4_set_wait_cycles(long long cycles);
+
+}  // namespace ascq
+
+// The communicator behind ascq_comm_create: this rank's place among the ranks of the box and every rank's flag block
+// as mapped into this process.
+struct ascq_comm {
+    int rank, nranks;
+    ascq::CommFlags* flags[ascq::kCommMaxRanks];
+};
+
+namespace ascq {
+CommArgs comm_args(const ascq_comm* comm);              // kernel argument form (nranks == 0 for NULL)
+ascq_status comm_read_status(::CUstream_st* stream);    // comm.cu: status word of the stand-alone exchange kernel
 }  // namespace ascq
 
 #define ASCQ_CUDA_CHECK(expr)                                                                      \

@@ -18,6 +18,7 @@
 
 #include "ascq_internal.h"
 #include "numerics.cuh"
+#include "tma_host.h"
 
 namespace ascq {
 
@@ -451,7 +452,7 @@ inline void ew_grid(uint32_t rows, uint32_t cols, int vec, dim3* grid, dim3* blo
         if (waste(cand) + nvec / 32 < waste(bx)) bx = cand;
     if (nvec < bx) bx = (nvec + 31) / 32 * 32;
     const uint32_t gx = (nvec + bx - 1) / bx;
-    const uint32_t target = 148u * ctasPerSm * 256u / bx;  // CTAs
+    const uint32_t target = static_cast<uint32_t>(sm_count()) * ctasPerSm * 256u / bx;  // CTAs
     uint32_t gy = (target + gx - 1) / gx;
     if (gy > rows) gy = rows;
     if (gy < 1) gy = 1;

@@ -29,6 +29,7 @@
 #include "ascq_internal.h"
 #include "numerics.cuh"
 #include "sm100_ptx.cuh"
+#include "comm.cuh"
 #include "tma_host.h"
 
 namespace ascq {
@@ -92,7 +93,12 @@ struct Params {
     const uint8_t* sfaPacked;
     const uint8_t* sfbPacked;
     int numTilesM, tilesN, N, K, kBlocks, nTilesPerGroup128;  // nTilesPerGroup128 = ceil(N/128)
-    int tmaStore;  // bf16 result in one aligned matrix: whole 128-row tiles leave through TMA stores
+    int tmaStore;  // bf16 result in aligned matrices: whole 128-row tiles leave through TMA stores (one per matrix)
+    CommArgs comm;  // sharded form: end-of-step exchange with the other ranks (nranks == 0: none)
+};
+// Tensor maps of the output matrices (TMA stores): one per buffer, this GPU's and its peers'.
+struct OutMaps {
+    CUtensorMap m[kMaxPeers];
 };
 
 // ---- scale repack ----------------------------------------------------------------------------------
@@ -219,7 +225,7 @@ template <int BN, bool PAIR, int SFC>
 __global__ void __launch_bounds__(kThreads, 1)
 mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
              const __grid_constant__ CUtensorMap tmapSfa, const __grid_constant__ CUtensorMap tmapSfb,
-             const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ Params p)
+             const __grid_constant__ OutMaps tmapC, const __grid_constant__ Params p)
 {
     using C = Cfg<BN, PAIR, SFC>;
     extern __shared__ uint8_t smem_raw[];
@@ -257,7 +263,8 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         fence_barrier_init();
         prefetch_tensormap(&tmapA);
         prefetch_tensormap(&tmapB);
-        if (p.tmaStore) prefetch_tensormap(&tmapC);
+        if (p.tmaStore)
+            for (int b = 0; b < p.nPeers; ++b) prefetch_tensormap(&tmapC.m[b]);
     }
     if (warp == 1) {
         if constexpr (PAIR) {
@@ -429,6 +436,12 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             bool vecStore = (p.N % 8 == 0);
             for (int pi = 0; pi < p.nPeers; ++pi) vecStore = vecStore && ((reinterpret_cast<uintptr_t>(p.C[pi]) & 15u) == 0);
             uint8_t* stageW = outStage + (warp - 2) * C::kWarpStageBytes;
+            if (p.tmaStore && ti.rowsValid != kBM) {
+                // this tile takes a per-thread path through the same staging bytes: the TMA stores of the previous tile
+                // must have read them
+                if (lane == 0) bulk_wait_group_read<0>();
+                __syncwarp();
+            }
 #pragma unroll
             for (int cp = 0; cp < kChunks / 2; ++cp) {  // two 32-column chunks = 64 columns = 128 bytes of bf16 per row
                 const int n = n0 + cp * 64;
@@ -470,7 +483,12 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                         }
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&tmapC, stageT, n, ti.outRow + q * 32 + h * 16);
+                            // one store per output matrix (this GPU's and the peers'), all reading the same staged rows
+                            for (int pi = 0; pi < p.nPeers; ++pi) {
+                                int b = p.firstPeer + pi;
+                                if (b >= p.nPeers) b -= p.nPeers;
+                                tma_store_2d(&tmapC.m[b], stageT, n, ti.outRow + q * 32 + h * 16);
+                            }
                             bulk_commit_group();
                         }
                     }
@@ -538,10 +556,18 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                 }
             }
         }
-        if (lane == 0) bulk_wait_group_read<0>();  // the staging rows must stay valid until the last TMA store has read them
+        if (lane == 0) {
+            // the staging rows must stay valid until the last TMA store has read them; with an exchange at the end of
+            // the step the stores must also have been performed before this CTA reports itself done
+            if (p.comm.nranks > 1) bulk_wait_group_all();
+            else bulk_wait_group_read<0>();
+        }
     }
 
     __syncthreads();
+    if (p.comm.nranks > 1 && threadIdx.x == 0) {
+        if (!comm_finish(p.comm, gridDim.x, c_waitCycles)) atomicExch(&g_mxfp4_status, 2);
+    }
     if constexpr (PAIR) {  // neither CTA may leave (or free tensor memory) while its partner can still touch it
         cluster_arrive();
         cluster_wait();
@@ -581,14 +607,15 @@ Layout make_layout(int64_t sumM, int G, int K, int N, int sfc = 2)
 
 template <int BN, bool PAIR, int SFC = 2>
 ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
-                   const CUtensorMap& tc, Params p, cudaStream_t st)
+                   const OutMaps& tc, Params p, cudaStream_t st)
 {
     using C = Cfg<BN, PAIR, SFC>;
-    static bool attrSet = false;
-    if (!attrSet) {
+    static PerDeviceOnce attrSet;  // the attribute is per device: a process may drive several GPUs
+    const int dev = current_device();
+    if (!attrSet.done(dev)) {
         ASCQ_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_kernel<BN, PAIR, SFC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(C::kSmemBytes)));
-        attrSet = true;
+        attrSet.mark(dev);
     }
     p.tilesN = (p.N + BN - 1) / BN;
     const int tiles = p.numTilesM * p.tilesN;
@@ -641,7 +668,8 @@ struct Mx8Args {  // 8-bit operands (kind::mxf8f6f4): formats 0 = E4M3, 1 = E5M2
 static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, const int64_t* outRowStart_host,
                              const uint8_t* A_fp4, const uint8_t* sA_e8m0, const uint8_t* B_fp4, const uint8_t* sB_e8m0,
                              const int64_t* groupList_host, int G, int K, int N, void* workspace, size_t workspaceBytes,
-                             void* stream, const Mx8Args* mx8 = nullptr, const uint8_t* sB_packed = nullptr)
+                             void* stream, const Mx8Args* mx8 = nullptr, const uint8_t* sB_packed = nullptr,
+                             const ascq_comm* comm = nullptr)
 {
     // sB_packed: the scales of B already in the packed order (weights are static: ascq_group_matmul_mxfp4_pack_scale_b once)
     const int sfc = mx8 ? 1 : 2;
@@ -664,7 +692,7 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
         if (groupList_host[g] < 0) return fail(ASCQ_ERR_INVALID_ARG, "groupList[%d] is negative", g);
         sumM += groupList_host[g];
     }
-    if (sumM == 0) return ASCQ_OK;
+    if (sumM == 0) return comm ? ascq_comm_barrier(const_cast<ascq_comm*>(comm), stream) : ASCQ_OK;
     if (sumM > 0x7FFFFFFF - 256 || static_cast<int64_t>(G) * N > 0x7FFFFFFF)
         return fail(ASCQ_ERR_INVALID_ARG, "problem too large for 32-bit row indices");
     if (outRowStart_host)
@@ -744,6 +772,7 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
     for (int i = 0; i < nBufs; ++i) p.C[i] = static_cast<__nv_bfloat16*>(outBufs[i]);
     p.firstPeer = ((firstBuf % nBufs) + nBufs) % nBufs;
     p.wideStores = nBufs > 1;
+    p.comm = comm_args(comm);
     if (mx8) { p.aFmt = mx8->aFmt; p.bFmt = mx8->bFmt; p.outF32 = mx8->outF32; }
     if (const char* e = getenv("ASCQ_MXFP4_STORE")) p.wideStores = !strcmp(e, "wide") ? 1 : (!strcmp(e, "narrow") && nBufs == 1 ? 0 : p.wideStores);
     p.tiles = reinterpret_cast<const TileInfo*>(ws + L.tileOff);
@@ -768,11 +797,16 @@ static ascq_status run_mxfp4(void* const* outBufs, int nBufs, int firstBuf, cons
     // bf16 result in one 16-byte aligned matrix whose rows are whole 16-byte pieces: TMA stores for whole tiles
     // (ASCQ_MXFP4_STORE=narrow|wide keeps the per-thread stores).  The row extent of the map only bounds the clipping;
     // tiles that are written this way lie inside the matrix by construction.
-    CUtensorMap tc = ta;
-    p.tmaStore = nBufs == 1 && !p.outF32 && N % 8 == 0 && aligned16(outBufs[0]) && getenv("ASCQ_MXFP4_STORE") == nullptr;
+    OutMaps tc;
+    for (int i = 0; i < kMaxPeers; ++i) tc.m[i] = ta;  // placeholders; the kernel reads maps [0, nPeers) and only for TMA stores
+    p.tmaStore = !p.outF32 && N % 8 == 0 && getenv("ASCQ_MXFP4_STORE") == nullptr;
+    for (int i = 0; i < nBufs && p.tmaStore; ++i) p.tmaStore = aligned16(outBufs[i]);
     if (p.tmaStore) {
-        rc = make_tmap_out16(&tc, outBufs[0], 1ull << 30, static_cast<uint64_t>(N), static_cast<uint64_t>(N), 16);
-        if (rc != ASCQ_OK) return rc;
+        // one map per output matrix (this GPU's and the peer-mapped ones): the store path only
+        for (int i = 0; i < nBufs; ++i) {
+            rc = make_tmap_out16(&tc.m[i], outBufs[i], 1ull << 30, static_cast<uint64_t>(N), static_cast<uint64_t>(N), 16);
+            if (rc != ASCQ_OK) return rc;
+        }
     }
     if (mx8) {
         if (pair) return launch<256, true, 1>(ta, tb, tsa, tsb, tc, p, st);
@@ -858,6 +892,38 @@ extern "C" ascq_status ascq_group_matmul_mxfp8(void* C, ascq_dtype cT, const uin
     const Mx8Args mx8{aT == ASCQ_DT_FP8_E5M2 ? 1u : 0u, bT == ASCQ_DT_FP8_E5M2 ? 1u : 0u, cT == ASCQ_DT_F32 ? 1 : 0};
     return run_mxfp4(bufs, 1, 0, nullptr, A_fp8, sA_e8m0, B_fp8, sB_e8m0, groupList_host, G, K, N, workspace, workspaceBytes,
                      stream, &mx8);
+}
+
+// ---- group-parallel form: one rank's share, reassembly and end-of-step exchange inside the launch ----------------
+extern "C" ascq_status ascq_group_matmul_mxfp4_sharded(ascq_comm* comm, void* const* C_bufs, const uint8_t* A_local,
+                                                       const uint8_t* sA_local, const uint8_t* B_local, const uint8_t* sB_local,
+                                                       const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                                       size_t workspaceBytes, void* stream)
+{
+    if (!comm) return fail(ASCQ_ERR_INVALID_ARG, "the communicator must not be NULL");
+    if (!C_bufs || !groupList_host || G <= 0) return fail(ASCQ_ERR_INVALID_ARG, "C_bufs and groupList must not be NULL and G positive");
+    // this rank's groups in ascending order, as its A / B hold them; their output rows are the groups' global row offsets
+    std::vector<int> owner(static_cast<size_t>(G));
+    const ascq_status rc = ascq_shard_groups_lpt(groupList_host, G, comm->nranks, owner.data());
+    if (rc != ASCQ_OK) return rc;
+    std::vector<int64_t> mine, outStart;
+    int64_t start = 0;
+    for (int g = 0; g < G; ++g) {
+        if (owner[g] == comm->rank) {
+            mine.push_back(groupList_host[g]);
+            outStart.push_back(start);
+        }
+        start += groupList_host[g];
+    }
+    if (mine.empty()) return ascq_comm_barrier(comm, stream);  // no work here, but the other ranks wait for this one
+    return run_mxfp4(C_bufs, comm->nranks, comm->rank + 1, outStart.data(), A_local, sA_local, B_local, sB_local, mine.data(),
+                     static_cast<int>(mine.size()), K, N, workspace, workspaceBytes, stream, nullptr, nullptr, comm);
+}
+
+ascq_status ascq::mxfp4_set_wait_cycles(long long cycles)
+{
+    ASCQ_CUDA_CHECK(cudaMemcpyToSymbol(ptx::c_waitCycles, &cycles, sizeof(cycles)));
+    return ASCQ_OK;
 }
 
 // ---- entry point for callers that may not allocate device memory ------------------------------------

@@ -16,6 +16,7 @@
 // TMEM allocation is released and a device status word reports the timeout.
 #include <cuda_bf16.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -23,6 +24,7 @@
 #include "numerics.cuh"
 #include "elementwise.cuh"
 #include "sm100_ptx.cuh"
+#include "comm.cuh"
 #include "tma_host.h"
 
 namespace ascq {
@@ -73,7 +75,9 @@ struct Params {
     // Work items: items [0, fullTiles) are whole tiles; from there on two items share one tile, each taking half of
     // its columns (the tail of a pair-shaped launch, so that the last, partly filled wave lasts half as long).
     int fullTiles, workItems;
-    int tmaStore;  // 16-bit result of one buffer, suitably aligned: the epilogue hands its staged rows to TMA stores
+    int tmaStore;  // 16-bit result, suitably aligned buffers: the epilogue hands its staged rows to TMA stores (one per buffer)
+    CommArgs comm;      // sharded form: end-of-step exchange with the other ranks (nranks == 0: none)
+    int stopAfter;      // test hook: the producer stops after this many k-blocks (< 0: never), so that a bounded wait runs out
     // fixpipe-style epilogue (EPI == kEpiFixpipe): C is fp16 = half(acc + biasI32[n]) scaled by quantVec[n] or quantScalar
     const int32_t* biasI32;
     const uint64_t* quantVec;   // low word: fp32 bits, of which the hardware keeps sign, exponent and 10 mantissa bits
@@ -184,10 +188,15 @@ __device__ __forceinline__ void convert_tiles(const Params& p, uint8_t* smem, fl
     }
 }
 
+// Tensor maps of the output matrices (TMA stores): one per buffer, this GPU's and its peers'.
+struct OutMaps {
+    CUtensorMap m[kMaxPeers];
+};
+
 template <int BN, bool PAIR, int EPI, bool CONV = false>
 __global__ void __launch_bounds__(Cfg<BN, PAIR, CONV>::kThreadsCta, 1)
 w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-            const __grid_constant__ CUtensorMap tmapC, const Params p)
+            const __grid_constant__ OutMaps tmapC, const Params p)
 {
     using C = Cfg<BN, PAIR, CONV>;
     static_assert(!CONV || (PAIR && EPI == kEpiFloat), "the converting variant is built for CTA pairs and kind::f16 only");
@@ -234,7 +243,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         fence_barrier_init();
         prefetch_tensormap(&tmapA);
         prefetch_tensormap(&tmapB);
-        if (p.tmaStore) prefetch_tensormap(&tmapC);
+        if (p.tmaStore)
+            for (int b = 0; b < p.nPeers; ++b) prefetch_tensormap(&tmapC.m[b]);
     }
     if (warp == 1) {
         if constexpr (PAIR) {
@@ -274,6 +284,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 for (int kb = 0; kb < kBlocks; ++kb, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
+                    if (p.stopAfter >= 0 && it >= static_cast<uint32_t>(p.stopAfter)) {  // test hook: the consumers' waits run out
+                        ok = false;
+                        break;
+                    }
                     if (!(ok = mbar_wait_bounded(&emptyBar[s], ph ^ 1, abortFlag))) break;
                     uint8_t* sa = smem + s * C::kStageBytes;
                     if constexpr (CONV) {
@@ -627,7 +641,12 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                         __syncwarp();
                         const int row0 = m0 + q * 32 + h * 16;
                         if (lane == 0 && row0 < p.M) {
-                            tma_store_2d(&tmapC, stageT, p.colOffset + n, row0);
+                            // one store per output matrix (this GPU's and the peers'), all reading the same staged rows
+                            for (int pi = 0; pi < p.nPeers; ++pi) {
+                                int b = p.firstPeer + pi;
+                                if (b >= p.nPeers) b -= p.nPeers;
+                                tma_store_2d(&tmapC.m[b], stageT, p.colOffset + n, row0);
+                            }
                             bulk_commit_group();
                         }
                     }
@@ -679,11 +698,19 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 else mbar_arrive(&tmemEmpty[acc]);
             }
         }
-        if (lane == 0) bulk_wait_group_read<0>();  // the staging rows must stay valid until the last TMA store has read them
+        if (lane == 0) {
+            // the staging rows must stay valid until the last TMA store has read them; with an exchange at the end of
+            // the step the stores must also have been performed before this CTA reports itself done
+            if (p.comm.nranks > 1) bulk_wait_group_all();
+            else bulk_wait_group_read<0>();
+        }
     }
 
     // ---------------- teardown ----------------
     __syncthreads();
+    if (p.comm.nranks > 1 && threadIdx.x == 0) {
+        if (!comm_finish(p.comm, gridDim.x, c_waitCycles)) atomicExch(&g_w8a8_status, 2);
+    }
     if constexpr (PAIR) {  // neither CTA may leave (or free tensor memory) while its partner can still touch it
         cluster_arrive();
         cluster_wait();
@@ -704,14 +731,15 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 
 // ---- host side -------------------------------------------------------------------------------------
 template <int BN, bool PAIR, int EPI = kEpiDequant, bool CONV = false>
-ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, Params p, cudaStream_t st)
+ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, Params p, cudaStream_t st)
 {
     using C = Cfg<BN, PAIR, CONV>;
-    static bool attrSet = false;
-    if (!attrSet) {
+    static PerDeviceOnce attrSet;  // the attribute is per device: a process may drive several GPUs
+    const int dev = current_device();
+    if (!attrSet.done(dev)) {
         ASCQ_CUDA_CHECK(cudaFuncSetAttribute(w8a8_kernel<BN, PAIR, EPI, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(C::kSmemBytes)));
-        attrSet = true;
+        attrSet.mark(dev);
     }
     const bool pdl = getenv("ASCQ_W8A8_NOPDL") == nullptr;
     p.tilesM = (p.M + (PAIR ? 2 * kBM : kBM) - 1) / (PAIR ? 2 * kBM : kBM);
@@ -786,9 +814,12 @@ struct FixpipeArgs {
     unsigned long long quantBits;
 };
 
+// Test hook (ascq_test_withhold_after): the next W8A8 launch's producers stop after this many k-blocks.
+std::atomic<int> g_stopAfterNext{-1};
+
 ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
                      const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc, int32_t* accDump,
-                     cudaStream_t st, const FixpipeArgs* fix = nullptr, bool multicast = false)
+                     cudaStream_t st, const FixpipeArgs* fix = nullptr, bool multicast = false, const ascq_comm* comm = nullptr)
 {
     const int epi = fix ? (fix->floatKind ? kEpiFloat : (fix->requant ? kEpiRequant : kEpiFixpipe)) : kEpiDequant;
     const int elemBytes = (epi == kEpiFloat) ? 2 : 1;
@@ -817,6 +848,8 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     p.bias = static_cast<const __nv_bfloat16*>(bias_bf16);
     p.accDump = accDump;
     p.M = M; p.N = N; p.K = K * elemBytes; p.ldc = ldc;  // the kernel counts K in bytes of an operand row
+    p.stopAfter = g_stopAfterNext.exchange(-1);
+    p.comm = comm_args(comm);
     if (fix) {
         p.abFmt = fix->abFmt;
         p.outKind = fix->outKind;
@@ -856,18 +889,22 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     // 16-bit result in one suitably aligned buffer: TMA stores (ASCQ_W8A8_STORE=plain keeps the per-thread stores)
     const bool out16 = epi == kEpiDequant || epi == kEpiFixpipe || (epi == kEpiFloat && fix->outKind <= 1);
     const char* storeEnv = getenv("ASCQ_W8A8_STORE");
-    p.tmaStore = haveC && out16 && p.nPeers == 1 && !multicast && ldc % 8 == 0 && colOffset % 8 == 0 && aligned16(outBufs[0]) &&
-                 !(storeEnv && !strcmp(storeEnv, "plain"));
-    CUtensorMap ta, tb, tc;
+    p.tmaStore = haveC && out16 && !multicast && ldc % 8 == 0 && colOffset % 8 == 0 && !(storeEnv && !strcmp(storeEnv, "plain"));
+    for (int i = 0; i < p.nPeers && p.tmaStore; ++i) p.tmaStore = aligned16(outBufs[i]);
+    CUtensorMap ta, tb;
+    OutMaps tc;
     ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K) * elemBytes, kBM);
     if (rc != ASCQ_OK) return rc;
     rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
+    for (int i = 0; i < kMaxPeers; ++i) tc.m[i] = ta;  // placeholders; the kernel reads maps [0, nPeers) and only for TMA stores
     if (p.tmaStore) {
-        rc = make_tmap_out16(&tc, outBufs[0], static_cast<uint64_t>(M), static_cast<uint64_t>(colOffset) + N, static_cast<uint64_t>(ldc), 16);
-        if (rc != ASCQ_OK) return rc;
-    } else {
-        tc = ta;  // not read by the kernel
+        // one map per output matrix (this GPU's and the peer-mapped ones): the store path only, nothing is loaded through them
+        for (int i = 0; i < p.nPeers; ++i) {
+            rc = make_tmap_out16(&tc.m[i], outBufs[i], static_cast<uint64_t>(M), static_cast<uint64_t>(colOffset) + N,
+                                 static_cast<uint64_t>(ldc), 16);
+            if (rc != ASCQ_OK) return rc;
+        }
     }
     if (epi == kEpiFloat && fix->convert) {
         // B_nk is the int8 weight: its tile goes through the converter warps (CTA pairs, 256 x 256 tiles only)
@@ -923,7 +960,47 @@ extern "C" ascq_status ascq_matmul_status(void* stream)
         ASCQ_CUDA_CHECK(cudaMemcpyToSymbolAsync(g_w8a8_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
         return fail(ASCQ_ERR_TIMEOUT, "a bounded wait inside the W8A8 matmul kernel expired (status %d)", v);
     }
-    return mxfp4_read_status(st);
+    const ascq_status rc = mxfp4_read_status(st);
+    if (rc != ASCQ_OK) return rc;
+    return comm_read_status(st);
+}
+
+ascq_status ascq::w8a8_set_wait_cycles(long long cycles)
+{
+    ASCQ_CUDA_CHECK(cudaMemcpyToSymbol(ptx::c_waitCycles, &cycles, sizeof(cycles)));
+    return ASCQ_OK;
+}
+
+// Test hook: the producers of the next W8A8-family launch on this process stop after `kBlocks` k-blocks, so that the
+// bounded waits of the other roles run out and the kernel leaves through its abort path.
+extern "C" ascq_status ascq_test_withhold_after(int kBlocks)
+{
+    g_stopAfterNext.store(kBlocks < 0 ? -1 : kBlocks);
+    return ASCQ_OK;
+}
+
+// Column-parallel W8A8 matmul of one rank with the all-gather and the end-of-step exchange inside the launch.
+extern "C" ascq_status ascq_matmul_w8a8_sharded(ascq_comm* comm, void* const* C_bufs, void* C_multicast, const int8_t* A,
+                                                const int8_t* B_local, const float* sA_m, const float* sB_local,
+                                                const void* bias_local, int M, int N, int K, void* stream)
+{
+    if (!comm) return fail(ASCQ_ERR_INVALID_ARG, "the communicator must not be NULL");
+    if (!C_bufs) return fail(ASCQ_ERR_INVALID_ARG, "the table of output matrices must not be NULL");
+    int c0 = 0, nl = 0;
+    const ascq_status rc = ascq_shard_columns(N, comm->nranks, comm->rank, &c0, &nl);
+    if (rc != ASCQ_OK) return rc;
+    if (nl % 8 != 0) return fail(ASCQ_ERR_ALIGNMENT, "N / nranks = %d must be a multiple of 8", nl);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (M == 0 || nl == 0) return ascq_comm_barrier(comm, stream);  // nothing to compute, but the other ranks wait for this one
+    if (C_multicast) {
+        if (nl % 64 != 0 || (reinterpret_cast<uintptr_t>(C_multicast) & 15u))
+            return fail(ASCQ_ERR_ALIGNMENT, "multicast output needs N / nranks %% 64 == 0 and a 16-byte aligned base");
+        void* bufs[1] = {C_multicast};
+        return run_w8a8(bufs, 1, 0, c0, A, B_local, sA_m, sB_local, bias_local, M, nl, K, N, nullptr, st, nullptr, true, comm);
+    }
+    // stores start at the next rank's matrix and go round, so that the ranks do not all write to the same GPU at once
+    return run_w8a8(C_bufs, comm->nranks, comm->rank + 1, c0, A, B_local, sA_m, sB_local, bias_local, M, nl, K, N, nullptr, st,
+                    nullptr, false, comm);
 }
 
 extern "C" ascq_status ascq_matmul_w8a8_multicast(void* C_multicast, int colOffset, int ldc, const int8_t* A, const int8_t* B_nk,

@@ -109,7 +109,7 @@ ascq_status launch_ew_generic(const GenericArgs& g, cudaStream_t stream)
     const size_t units = static_cast<size_t>(g.rows) * (g.cols / step);
     if (units == 0) return ASCQ_OK;
     size_t blocks = (units + 255) / 256;
-    if (blocks > 148u * 16u) blocks = 148u * 16u;
+    if (blocks > static_cast<unsigned>(ascq::sm_count()) * 16u) blocks = static_cast<unsigned>(ascq::sm_count()) * 16u;
     ew_generic_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(g);
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;

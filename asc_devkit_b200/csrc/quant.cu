@@ -572,7 +572,7 @@ extern "C" ascq_status ascq_dynamic_quant_mxfp4(uint8_t* dst_fp4, uint8_t* scale
     // one lane per 16-byte source vector, four vectors per thread and pass; at most 16 CTAs of 256 threads per SM
     const uint64_t vectors = blocks * (srcT == ASCQ_DT_F32 ? 8u : 4u);
     const uint64_t want = (vectors + 1023) / 1024;
-    const unsigned grid = static_cast<unsigned>(want < 148u * 16u ? want : 148u * 16u);
+    const unsigned grid = static_cast<unsigned>(want < static_cast<unsigned>(ascq::sm_count()) * 16u ? want : static_cast<unsigned>(ascq::sm_count()) * 16u);
     if (srcT == ASCQ_DT_F16) dyn_quant_mxfp4_kernel<__half><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __half*>(src), vectors);
     else if (srcT == ASCQ_DT_BF16)
         dyn_quant_mxfp4_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dst_fp4, scale_e8m0, static_cast<const __nv_bfloat16*>(src), vectors);

@@ -51,10 +51,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity.  Gives up after `kWaitCycles` SM cycles or as soon as
-// *abortFlag (shared memory) is non-zero; on give-up it raises *abortFlag and returns false so that
-// every role of the CTA leaves its loop instead of spinning for ever.
+// Waits for the phase with the given parity.  Gives up after the wait limit (SM cycles; about two seconds unless the
+// host changed it with ascq_set_wait_limit_cycles) or as soon as *abortFlag (shared memory) is non-zero; on give-up it
+// raises *abortFlag -- in both CTAs when the kernel runs as CTA pairs -- and returns false so that every role of the
+// CTA leaves its loop instead of spinning for ever.
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
+// One copy per translation unit that includes this header; the host keeps them equal (wait_limit_set in each unit).
+static __constant__ long long c_waitCycles = kWaitCycles;
+
+// Raises the abort flag of this CTA and, in a cluster of two, of its partner.  The partner is still resident: no CTA
+// of a pair passes the cluster barrier of the teardown before both have left their loops.
+__device__ __forceinline__ void raise_abort(volatile int* abortFlag)
+{
+    *abortFlag = 1;
+    uint32_t n, r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+    if (n == 2) {
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(const_cast<int*>(abortFlag))), "r"(r ^ 1u));
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(1u) : "memory");
+    }
+}
+
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abortFlag)
 {
     if (mbar_try_wait(bar, parity)) return true;
@@ -63,8 +82,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3Fu) == 0) {
             if (*abortFlag) return false;
-            if (clock64() - t0 > kWaitCycles) {
-                *abortFlag = 1;
+            if (clock64() - t0 > c_waitCycles) {
+                raise_abort(abortFlag);
                 return false;
             }
         }
@@ -83,8 +102,8 @@ __device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint64_t* bar, uint32_t
         __nanosleep(128);
         if ((++spins & 0x3Fu) == 0) {
             if (*abortFlag) return false;
-            if (clock64() - t0 > kWaitCycles) {
-                *abortFlag = 1;
+            if (clock64() - t0 > c_waitCycles) {
+                raise_abort(abortFlag);
                 return false;
             }
         }
@@ -114,8 +133,8 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_
     while (!mbar_try_wait_cluster(bar, parity)) {
         if ((++spins & 0x3Fu) == 0) {
             if (*abortFlag) return false;
-            if (clock64() - t0 > kWaitCycles) {
-                *abortFlag = 1;
+            if (clock64() - t0 > c_waitCycles) {
+                raise_abort(abortFlag);
                 return false;
             }
         }

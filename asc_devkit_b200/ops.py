@@ -41,6 +41,15 @@ def _ptr(t: Optional[torch.Tensor]):
     return C.c_void_p(t.data_ptr())
 
 
+def _workspace(need: int, device, stream: Optional[torch.cuda.Stream]) -> torch.Tensor:
+    """A temporary workspace for a call that returns while its kernels still run.  The caching allocator hands a freed
+    block back to torch's current stream; when the kernels run on another stream the block is tied to that one too."""
+    ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=device)
+    if stream is not None and stream != torch.cuda.current_stream(ws.device):
+        ws.record_stream(stream)
+    return ws
+
+
 def _stream(stream: Optional[torch.cuda.Stream]):
     """Raw cudaStream_t of ``stream`` or of torch's current stream (the raw-handle getter skips building a Stream
     object: a few microseconds per call, which matters next to a 10 us kernel)."""
@@ -303,7 +312,7 @@ def MatmulW8A16(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, offset, sc
     M, K = A.shape
     N = B_nk.shape[0]
     if workspace is None:
-        workspace = torch.empty(N * K * 2, dtype=torch.uint8, device=A.device)
+        workspace = _workspace(N * K * 2, A.device, stream)
     st = isinstance(scale, torch.Tensor)
     L.check(L.lib().ascq_matmul_w8a16(_ptr(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk),
                                       _ptr(offset) if isinstance(offset, torch.Tensor) else None, _ptr(scale) if st else None,
@@ -318,7 +327,7 @@ def MatmulW4A16(C: torch.Tensor, A: torch.Tensor, B_nk_int4: torch.Tensor, offse
     M, K = A.shape
     N = B_nk_int4.shape[0]
     if workspace is None:
-        workspace = torch.empty(N * K * 2, dtype=torch.uint8, device=A.device)
+        workspace = _workspace(N * K * 2, A.device, stream)
     st = isinstance(scale, torch.Tensor)
     L.check(L.lib().ascq_matmul_w4a16(_ptr(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk_int4),
                                       _ptr(offset) if isinstance(offset, torch.Tensor) else None, _ptr(scale) if st else None,
@@ -340,7 +349,7 @@ def GroupMatmulMxfp4(C: torch.Tensor, A: torch.Tensor, scaleA: torch.Tensor, B: 
     G = len(groupList)
     need = GroupMatmulMxfp4Workspace(int(sum(int(v) for v in groupList)), G, K, N)
     if workspace is None:
-        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=C.device)
+        workspace = _workspace(need, C.device, stream)
     L.check(L.lib().ascq_group_matmul_mxfp4(_ptr(C), _ptr(A), _ptr(scaleA), _ptr(B), _ptr(scaleB), gl, G, K, N,
                                             _ptr(workspace), workspace.numel(), _stream(stream)))
     return C
@@ -361,7 +370,7 @@ def GroupMatmulMxfp4Prepacked(C: torch.Tensor, A: torch.Tensor, scaleA: torch.Te
     G = len(groupList)
     need = GroupMatmulMxfp4Workspace(int(sum(int(v) for v in groupList)), G, K, N)
     if workspace is None:
-        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=C.device)
+        workspace = _workspace(need, C.device, stream)
     L.check(L.lib().ascq_group_matmul_mxfp4_prepacked(_ptr(C), _ptr(A), _ptr(scaleA), _ptr(B), _ptr(scaleB_packed), gl, G, K, N,
                                                       _ptr(workspace), workspace.numel(), _stream(stream)))
     return C
@@ -375,7 +384,7 @@ def GroupMatmulMxfp8(C: torch.Tensor, A: torch.Tensor, a_dtype: int, scaleA: tor
     gl = (C_int64 * G)(*[int(v) for v in groupList])
     need = int(L.lib().ascq_group_matmul_mxfp8_workspace_size(int(sum(int(v) for v in groupList)), G, K, N))
     if workspace is None:
-        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=C.device)
+        workspace = _workspace(need, C.device, stream)
     L.check(L.lib().ascq_group_matmul_mxfp8(_ptr(C), dtype_code(C), _ptr(A), a_dtype, _ptr(scaleA), _ptr(B), b_dtype,
                                             _ptr(scaleB), gl, G, K, N, _ptr(workspace), workspace.numel(), _stream(stream)))
     return C
@@ -392,7 +401,7 @@ def GroupMatmulMxfp4Scatter(buffer_ptrs, first_buf: int, out_row_start, A: torch
     rs = (C_int64 * G)(*[int(v) for v in out_row_start]) if out_row_start is not None else None
     need = GroupMatmulMxfp4Workspace(int(sum(int(v) for v in groupList)), G, K, N)
     if workspace is None:
-        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=A.device)
+        workspace = _workspace(need, A.device, stream)
     arr = (C.c_void_p * len(buffer_ptrs))(*[C.c_void_p(int(v)) for v in buffer_ptrs])
     L.check(L.lib().ascq_group_matmul_mxfp4_scatter(arr, len(buffer_ptrs), first_buf, rs, _ptr(A), _ptr(scaleA), _ptr(B),
                                                     _ptr(scaleB), gl, G, K, N, _ptr(workspace), workspace.numel(),
@@ -429,6 +438,94 @@ def MatmulW8A8Multicast(multicast_ptr: int, col_offset: int, ldc: int, A: torch.
     N = B_nk.shape[0]
     L.check(L.lib().ascq_matmul_w8a8_multicast(C.c_void_p(int(multicast_ptr)), col_offset, ldc, _ptr(A), _ptr(B_nk), _ptr(scaleA),
                                                _ptr(scaleB), _ptr(bias), M, N, K, _stream(stream)))
+
+
+class Comm:
+    """The communicator of the sharded matmuls (``ascq_comm_create``): this rank's position among the GPUs of one box and
+    every rank's flag block as mapped into this process.  ``flag_block_ptrs[r]`` is the device address of rank r's block
+    (``Comm.flag_bytes()`` bytes, zeroed, 128-byte aligned; ``flag_block_ptrs[rank]`` the local one).  The caller maps
+    the blocks (CUDA IPC through ``IpcExport`` / ``IpcOpen``, or a symmetric-memory allocator) and makes sure every rank
+    has zeroed its block before any rank launches."""
+
+    def __init__(self, rank: int, nranks: int, flag_block_ptrs):
+        if len(flag_block_ptrs) != nranks:
+            raise ValueError("one flag block per rank is needed")
+        arr = (C.c_void_p * nranks)(*[C.c_void_p(int(v)) for v in flag_block_ptrs])
+        h = C.c_void_p()
+        L.check(L.lib().ascq_comm_create(C.byref(h), rank, nranks, arr))
+        self.handle, self.rank, self.nranks = h, rank, nranks
+
+    @staticmethod
+    def flag_bytes() -> int:
+        return int(L.lib().ascq_comm_flag_bytes())
+
+    def barrier(self, stream=None):
+        """The end-of-step exchange as a launch of its own (``ascq_comm_barrier``)."""
+        L.check(L.lib().ascq_comm_barrier(self.handle, _stream(stream)))
+
+    def destroy(self):
+        if self.handle:
+            L.check(L.lib().ascq_comm_destroy(self.handle))
+            self.handle = C.c_void_p()
+
+
+def IpcExport(t: torch.Tensor) -> bytes:
+    """CUDA IPC handle of a cudaMalloc'ed buffer of this process (``ascq_comm_ipc_export``)."""
+    buf = C.create_string_buffer(int(L.lib().ascq_comm_ipc_handle_bytes()))
+    L.check(L.lib().ascq_comm_ipc_export(buf, C.c_void_p(t.data_ptr())))
+    return buf.raw
+
+
+def IpcOpen(handle: bytes) -> int:
+    """Maps a peer's buffer into this process; returns its device address (``ascq_comm_ipc_open``)."""
+    p = C.c_void_p()
+    L.check(L.lib().ascq_comm_ipc_open(C.byref(p), C.create_string_buffer(handle, len(handle))))
+    return int(p.value)
+
+
+def ShardColumns(N: int, nranks: int, rank: int):
+    a, b = C.c_int(), C.c_int()
+    L.check(L.lib().ascq_shard_columns(N, nranks, rank, C.byref(a), C.byref(b)))
+    return a.value, b.value
+
+
+def ShardGroupsLpt(groupList, nranks: int):
+    """owner[g] = rank of group g (``ascq_shard_groups_lpt``)."""
+    G = len(groupList)
+    gl = (C_int64 * G)(*[int(v) for v in groupList])
+    own = (C.c_int * G)()
+    L.check(L.lib().ascq_shard_groups_lpt(gl, G, nranks, own))
+    return list(own)
+
+
+def MatmulW8A8Sharded(comm: Comm, C_buf_ptrs, A: torch.Tensor, B_local: torch.Tensor, scaleA=None, scaleB_local=None,
+                      bias_local=None, N: Optional[int] = None, multicast_ptr: int = 0, stream=None):
+    """Column-parallel W8A8 matmul of one rank (``ascq_matmul_w8a8_sharded``): ``C_buf_ptrs[r]`` = device address of rank
+    r's bf16 [M, N] matrix; ``B_local`` [N / nranks, K].  The all-gather and the end-of-step exchange are part of the
+    launch."""
+    M, K = A.shape
+    N = int(N if N is not None else B_local.shape[0] * comm.nranks)
+    arr = (C.c_void_p * len(C_buf_ptrs))(*[C.c_void_p(int(v)) for v in C_buf_ptrs])
+    L.check(L.lib().ascq_matmul_w8a8_sharded(comm.handle, arr, C.c_void_p(int(multicast_ptr)) if multicast_ptr else None,
+                                             _ptr(A), _ptr(B_local), _ptr(scaleA), _ptr(scaleB_local), _ptr(bias_local), M, N, K,
+                                             _stream(stream)))
+
+
+def GroupMatmulMxfp4Sharded(comm: Comm, C_buf_ptrs, A_local: torch.Tensor, scaleA_local: torch.Tensor, B_local: torch.Tensor,
+                            scaleB_local: torch.Tensor, groupList, K: int, N: int, workspace: torch.Tensor, stream=None):
+    """Group-parallel MX-FP4 matmul of one rank (``ascq_group_matmul_mxfp4_sharded``): ``groupList`` holds all groups,
+    the ``*_local`` tensors this rank's groups (``ShardGroupsLpt``) back to back in ascending group order."""
+    G = len(groupList)
+    gl = (C_int64 * G)(*[int(v) for v in groupList])
+    arr = (C.c_void_p * len(C_buf_ptrs))(*[C.c_void_p(int(v)) for v in C_buf_ptrs])
+    L.check(L.lib().ascq_group_matmul_mxfp4_sharded(comm.handle, arr, _ptr(A_local), _ptr(scaleA_local), _ptr(B_local),
+                                                    _ptr(scaleB_local), gl, G, K, N, _ptr(workspace), workspace.numel(),
+                                                    _stream(stream)))
+
+
+def SetWaitLimitCycles(cycles: int):
+    """Limit of the bounded device-side waits in SM cycles on the current device; <= 0 restores the default."""
+    L.check(L.lib().ascq_set_wait_limit_cycles(int(cycles)))
 
 
 def MatmulStatus(stream=None):

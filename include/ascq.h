@@ -35,7 +35,7 @@ typedef enum {
     ASCQ_ERR_UNSUPPORTED = 2,  /* dtype / policy combination the reference static_asserts away         */
     ASCQ_ERR_ALIGNMENT = 3,    /* pointer or extent not aligned for the vectorised path                */
     ASCQ_ERR_CUDA = 4,         /* a CUDA runtime / driver call failed                                  */
-    ASCQ_ERR_NCCL = 5,
+    ASCQ_ERR_NCCL = 5,         /* multi-GPU set-up failed: invalid communicator, peer memory could not be mapped   */
     ASCQ_ERR_TIMEOUT = 6       /* a bounded device-side wait expired (kernel left cleanly)             */
 } ascq_status;
 
@@ -448,6 +448,81 @@ ascq_status ascq_group_matmul_mxfp4_scatter(void* const* C_bufs, int nBufs, int 
 ascq_status ascq_matmul_w8a8_multicast(void* C_multicast, int colOffset, int ldc, const int8_t* A, const int8_t* B_nk,
                                        const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K,
                                        void* stream);
+
+/*
+ * ---- Multi-GPU: one process per GPU, the GPUs of one box --------------------------------------------------------
+ * The two matmuls shard the way the reference's samples would (column blocks of the W8A8 weight; whole groups of the
+ * grouped matmul, one core group per group in examples/.../quant_group_matmul_custom.asc:257-289), and reassemble with
+ * the exchange the reference's kernels would use: HCCL's kernel-side AllGather followed by Commit / Wait
+ * (include/adv_api/hccl/hccl.h:82-100, 304-326).  Here both are part of the matmul launch: the epilogue stores each
+ * finished tile into EVERY rank's output matrix over NVLink (TMA stores into peer-mapped memory; nothing is loaded
+ * from a peer), and when the last CTA of a launch has finished, the rank writes an arrival flag into every peer's flag
+ * block and waits -- bounded -- for theirs.  When a *_sharded kernel has completed on a rank, that rank's output
+ * matrix holds every rank's part.  A wait that runs out makes ascq_matmul_status return ASCQ_ERR_TIMEOUT.
+ *
+ * Set-up (once):  every rank allocates a flag block of ascq_comm_flag_bytes() bytes (128-byte aligned, ZEROED) and
+ * its output matrices in memory the other ranks can map -- CUDA IPC (ascq_comm_ipc_export / _open wrap
+ * cudaIpcGetMemHandle / cudaIpcOpenMemHandle for cudaMalloc'ed memory; the handle bytes travel over whatever channel
+ * the host program has) or a symmetric-memory allocator.  After a host-side barrier (every block zeroed and mapped),
+ * ascq_comm_create(rank, nranks, flagBlocks) with flagBlocks[r] = rank r's block as mapped in THIS process
+ * (flagBlocks[rank] = the local one).  All ranks must issue the same sequence of *_sharded / ascq_comm_barrier calls
+ * on a communicator, stream-ordered; the calls may be captured into a CUDA graph (the step counter lives on the
+ * device).  Failures of the set-up calls return ASCQ_ERR_NCCL.
+ */
+typedef struct ascq_comm ascq_comm;
+size_t ascq_comm_flag_bytes(void);
+ascq_status ascq_comm_create(ascq_comm** comm, int rank, int nranks, void* const* flagBlocks);
+ascq_status ascq_comm_destroy(ascq_comm* comm);
+ascq_status ascq_comm_rank(const ascq_comm* comm, int* rank, int* nranks);
+size_t ascq_comm_ipc_handle_bytes(void);
+ascq_status ascq_comm_ipc_export(void* handleOut, const void* devPtr);   /* handle of a cudaMalloc'ed buffer of this process  */
+ascq_status ascq_comm_ipc_open(void** devPtrOut, const void* handle);    /* maps a peer's buffer; enables peer access lazily  */
+ascq_status ascq_comm_ipc_close(void* devPtr);
+/* The end-of-step exchange as a launch of its own (hccl.h:304-326 Commit + Wait): returns at once; when the kernel has
+ * completed, every rank has reached this point of its stream. */
+ascq_status ascq_comm_barrier(ascq_comm* comm, void* stream);
+
+/* The partition.  Columns: rank r owns columns [r * N / nranks, (r + 1) * N / nranks); N % nranks == 0.
+ * Groups: longest group first onto the rank with the fewest rows so far (ties: lower group index, lower rank);
+ * owner[g] = rank of group g.  A rank stores its groups back to back in ascending group order. */
+ascq_status ascq_shard_columns(int N, int nranks, int rank, int* firstColumn, int* columns);
+ascq_status ascq_shard_groups_lpt(const int64_t* groupList_host, int G, int nranks, int* owner);
+
+/*
+ * ascq_matmul_w8a8, column-parallel.  C_bufs[r] = rank r's bf16 [M, N] output matrix (row stride N) as mapped in this
+ * process; B_local [N / nranks, K], sB_local, bias_local = this rank's column block; A, sA_m whole (replicated in each
+ * GPU's own memory).  N / nranks % 8 == 0.  C_multicast (optional, may be NULL): the multicast address of the output
+ * matrix (all ranks' matrices bound to one NVSwitch multicast object); when given, every 16-byte piece leaves as one
+ * multimem.st and the switch replicates it, instead of one TMA store per rank (needs N / nranks % 64 == 0).
+ */
+ascq_status ascq_matmul_w8a8_sharded(ascq_comm* comm, void* const* C_bufs, void* C_multicast, const int8_t* A,
+                                     const int8_t* B_local, const float* sA_m, const float* sB_local,
+                                     const void* bias_local, int M, int N, int K, void* stream);
+/*
+ * ascq_group_matmul_mxfp4, group-parallel.  groupList_host holds ALL G groups; A_local / sA_local / B_local /
+ * sB_local hold the rows and weights of this rank's groups (ascq_shard_groups_lpt) back to back in ascending group
+ * order; C_bufs[r] = rank r's bf16 [sum(groupList), N] matrix.  Workspace sized for this rank's share
+ * (ascq_group_matmul_mxfp4_workspace_size(local rows, local groups, K, N)).  A rank without groups only takes part in
+ * the exchange.
+ */
+ascq_status ascq_group_matmul_mxfp4_sharded(ascq_comm* comm, void* const* C_bufs, const uint8_t* A_local,
+                                            const uint8_t* sA_local, const uint8_t* B_local, const uint8_t* sB_local,
+                                            const int64_t* groupList_host, int G, int K, int N, void* workspace,
+                                            size_t workspaceBytes, void* stream);
+
+/*
+ * Limit of every bounded device-side wait (mbarrier waits inside the matmul kernels, the wait for the other ranks), in
+ * SM cycles, on the current device; the default is about two seconds, cycles <= 0 restores it.  No reference counterpart.
+ */
+ascq_status ascq_set_wait_limit_cycles(long long cycles);
+/*
+ * Test hook, no reference counterpart: the copy-engine producers of the NEXT int8 / half matmul launch of this process
+ * stop after `kBlocks` k-blocks (< 0 cancels).  The kernel's other roles then run into their wait limit, leave through
+ * the abort path (tensor memory released, status word set) and ascq_matmul_status reports ASCQ_ERR_TIMEOUT; the output
+ * of that launch is undefined.  It exists so that the abort path can be exercised without faulting or hanging a GPU;
+ * lower the wait limit first.
+ */
+ascq_status ascq_test_withhold_after(int kBlocks);
 
 /*
  * Synchronises `stream`, then reads and clears the status word the matmul kernels keep on the
