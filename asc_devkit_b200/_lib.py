@@ -74,7 +74,6 @@ SIGNATURES = {
     "ascq_matmul_w8a16": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _f, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_matmul_w8a16_workspace_size": (C.c_size_t, [_i, _i]),
     "ascq_matmul_w4a16": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _f, _f, _i, _i, _i, _i, _vp, C.c_size_t, _vp]),
-    "ascq_matmul_w8a8_multicast": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ascq_matmul_status": (_i, [_vp]),
     "ascq_comm_flag_bytes": (C.c_size_t, []),
     "ascq_comm_create": (_i, [C.POINTER(_vp), _i, _i, C.POINTER(_vp)]),

@@ -74,9 +74,14 @@ struct Params {
     int tilesM, tilesN;
     // Work items: items [0, fullTiles) are whole tiles; from there on two items share one tile, each taking half of
     // its columns (the tail of a pair-shaped launch, so that the last, partly filled wave lasts half as long).
+    // (Half items at the head of a launch that ships its tiles to other GPUs were tried and lost: the first results of
+    // a launch are late because its operands come from HBM cold, not because the tile is large.)
     int fullTiles, workItems;
     int tmaStore;  // 16-bit result, suitably aligned buffers: the epilogue hands its staged rows to TMA stores (one per buffer)
     CommArgs comm;      // sharded form: end-of-step exchange with the other ranks (nranks == 0: none)
+#ifdef ASCQ_TRACE
+    unsigned long long* trace;  // diagnostic builds: 16 time stamps (ns) per CTA, see trace_stamp
+#endif
     int stopAfter;      // test hook: the producer stops after this many k-blocks (< 0: never), so that a bounded wait runs out
     // fixpipe-style epilogue (EPI == kEpiFixpipe): C is fp16 = half(acc + biasI32[n]) scaled by quantVec[n] or quantScalar
     const int32_t* biasI32;
@@ -94,6 +99,22 @@ struct Params {
     float aqScaleScalar, aqOffsetScalar;
     int aqHasOffset;
 };
+// Diagnostic builds (-DASCQ_TRACE) record where the time of a launch goes: slot 0 set-up done, 1 + 2i accumulator of
+// the CTA's i-th item ready, 2 + 2i its stores issued (i < 5), 12 all stores performed, 13 CTA done (after the exchange).
+#ifdef ASCQ_TRACE
+__device__ __forceinline__ void trace_stamp(const Params& p, int slot)
+{
+    if (p.trace != nullptr && slot < 16) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[blockIdx.x * 16 + slot] = t;
+    }
+}
+#define ASCQ_STAMP(p, slot) trace_stamp(p, slot)
+#else
+#define ASCQ_STAMP(p, slot) ((void)0)
+#endif
+
 // Work item -> tile, first column inside the tile, columns of the item.
 struct Item {
     int tile, nOff, nCols;
@@ -191,6 +212,7 @@ __device__ __forceinline__ void convert_tiles(const Params& p, uint8_t* smem, fl
 // Tensor maps of the output matrices (TMA stores): one per buffer, this GPU's and its peers'.
 struct OutMaps {
     CUtensorMap m[kMaxPeers];
+    CUtensorMap bHalf;  // B with a box of half the rows: what a CTA loads for a half-tile work item (pair shape)
 };
 
 template <int BN, bool PAIR, int EPI, bool CONV = false>
@@ -268,6 +290,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     // draining -- nothing below may touch global memory before that launch has completed.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 64) ASCQ_STAMP(p, 0);
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -278,8 +301,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 const Item item = decode_item<BN>(p, w);
                 const int tile = item.tile;
                 const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
-                // rows of B this CTA loads: its half of the item's columns (a half-tile item still moves a whole box of
-                // kBRows rows; the MMAs read the first nCols / 2 of them)
+                // rows of B this CTA loads: its half of the item's columns
                 const int n0 = (tile / p.tilesM) * BN + item.nOff + (PAIR ? static_cast<int>(rank) * (item.nCols / 2) : 0);
                 for (int kb = 0; kb < kBlocks; ++kb, ++it) {
                     const int s = it % C::kStages;
@@ -300,10 +322,12 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                         tma_load_2d(sa + C::kABytes + C::kBBytes, &tmapB, &fullQ[s], kb * (kBK / 2), n0);
                     } else if constexpr (PAIR) {
                         // both CTAs' loads are counted on the leader's barrier; the leader announces the bytes of both
-                        if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], 2 * C::kStageBytes);
+                        // (a half-tile item needs, and loads, only half of this CTA's rows of B)
+                        const bool half = item.nCols != BN;
+                        if (rank == 0) mbar_arrive_expect_tx(&fullBar[s], half ? 2 * (C::kABytes + C::kBBytes / 2) : 2 * C::kStageBytes);
                         const uint32_t leaderBar = mapa_u32(smem_u32(&fullBar[s]), 0);
                         tma_load_2d_pair(sa, &tmapA, leaderBar, kb * kBK, m0);
-                        tma_load_2d_pair(sa + C::kABytes, &tmapB, leaderBar, kb * kBK, n0);
+                        tma_load_2d_pair(sa + C::kABytes, half ? &tmapC.bHalf : &tmapB, leaderBar, kb * kBK, n0);
                     } else {
                         mbar_arrive_expect_tx(&fullBar[s], C::kStageBytes);
                         tma_load_2d(sa, &tmapA, &fullBar[s], kb * kBK, m0);
@@ -441,6 +465,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     ok = false;
                     break;
                 }
+                if (threadIdx.x == 64 && local < 5) ASCQ_STAMP(p, 1 + 2 * static_cast<int>(local));
             }
             const bool hasBias = p.bias != nullptr;
             const uint32_t taddr = tmemBase + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -689,6 +714,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     store_direct(packed + 16, n + 32);
                 }
             }
+            if (threadIdx.x == 64 && local < 5) ASCQ_STAMP(p, 2 + 2 * static_cast<int>(local));
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -704,12 +730,14 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             if (p.comm.nranks > 1) bulk_wait_group_all();
             else bulk_wait_group_read<0>();
         }
+        if (threadIdx.x == 64) ASCQ_STAMP(p, 12);
     }
 
     // ---------------- teardown ----------------
     __syncthreads();
     if (p.comm.nranks > 1 && threadIdx.x == 0) {
         if (!comm_finish(p.comm, gridDim.x, c_waitCycles)) atomicExch(&g_w8a8_status, 2);
+        ASCQ_STAMP(p, 13);
     }
     if constexpr (PAIR) {  // neither CTA may leave (or free tensor memory) while its partner can still touch it
         cluster_arrive();
@@ -748,14 +776,16 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& 
     p.fullTiles = tiles;
     p.workItems = tiles;
     if constexpr (PAIR) {
-        const int clusters = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-        // Tail split: when the last wave would keep at most half of the pairs busy, its tiles are cut into two column
-        // halves, so that every pair gets at most one half tile and the wave lasts half as long.
-        const int rest = tiles % clusters;
-        if (!CONV && BN == 256 && tiles > clusters && rest > 0 && 2 * rest <= clusters && getenv("ASCQ_W8A8_NOSPLIT") == nullptr) {
-            p.fullTiles = tiles - rest;
-            p.workItems = p.fullTiles + 2 * rest;
+        const int maxClusters = sm_count() / 2;
+        const bool canSplit = !CONV && BN == 256;
+        // Tail split: when the last wave of whole tiles would keep at most half of the pairs busy, its tiles are cut
+        // into two column halves, so that every pair gets at most one half tile and the wave lasts half as long.
+        const int rest = p.fullTiles % maxClusters;
+        if (canSplit && p.fullTiles > maxClusters && rest > 0 && 2 * rest <= maxClusters && getenv("ASCQ_W8A8_NOSPLIT") == nullptr) {
+            p.fullTiles -= rest;
+            p.workItems += rest;
         }
+        const int clusters = p.workItems < maxClusters ? p.workItems : maxClusters;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
         cfg.blockDim = dim3(C::kThreadsCta, 1, 1);
@@ -814,6 +844,9 @@ struct FixpipeArgs {
     unsigned long long quantBits;
 };
 
+#ifdef ASCQ_TRACE
+unsigned long long* g_trace = nullptr;  // device buffer of 16 x (number of CTAs) stamps, set by ascq_debug_trace
+#endif
 // Test hook (ascq_test_withhold_after): the next W8A8 launch's producers stop after this many k-blocks.
 std::atomic<int> g_stopAfterNext{-1};
 
@@ -849,6 +882,9 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     p.accDump = accDump;
     p.M = M; p.N = N; p.K = K * elemBytes; p.ldc = ldc;  // the kernel counts K in bytes of an operand row
     p.stopAfter = g_stopAfterNext.exchange(-1);
+#ifdef ASCQ_TRACE
+    p.trace = g_trace;
+#endif
     p.comm = comm_args(comm);
     if (fix) {
         p.abFmt = fix->abFmt;
@@ -889,7 +925,9 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     // 16-bit result in one suitably aligned buffer: TMA stores (ASCQ_W8A8_STORE=plain keeps the per-thread stores)
     const bool out16 = epi == kEpiDequant || epi == kEpiFixpipe || (epi == kEpiFloat && fix->outKind <= 1);
     const char* storeEnv = getenv("ASCQ_W8A8_STORE");
-    p.tmaStore = haveC && out16 && !multicast && ldc % 8 == 0 && colOffset % 8 == 0 && !(storeEnv && !strcmp(storeEnv, "plain"));
+    // (the copy engine clips a box at the matrix edge in whole 16-byte pieces, so the block must end on one)
+    p.tmaStore = haveC && out16 && !multicast && ldc % 8 == 0 && colOffset % 8 == 0 && N % 8 == 0 &&
+                 !(storeEnv && !strcmp(storeEnv, "plain"));
     for (int i = 0; i < p.nPeers && p.tmaStore; ++i) p.tmaStore = aligned16(outBufs[i]);
     CUtensorMap ta, tb;
     OutMaps tc;
@@ -898,6 +936,11 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
     for (int i = 0; i < kMaxPeers; ++i) tc.m[i] = ta;  // placeholders; the kernel reads maps [0, nPeers) and only for TMA stores
+    tc.bHalf = tb;
+    if (mode == 2) {  // pair shape: half-tile work items load 64 rows of B per CTA instead of 128
+        rc = make_tmap_u8(&tc.bHalf, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, 64);
+        if (rc != ASCQ_OK) return rc;
+    }
     if (p.tmaStore) {
         // one map per output matrix (this GPU's and the peer-mapped ones): the store path only, nothing is loaded through them
         for (int i = 0; i < p.nPeers; ++i) {
@@ -979,6 +1022,14 @@ extern "C" ascq_status ascq_test_withhold_after(int kBlocks)
     return ASCQ_OK;
 }
 
+#ifdef ASCQ_TRACE
+extern "C" ascq_status ascq_debug_trace(void* deviceBuffer)
+{
+    g_trace = static_cast<unsigned long long*>(deviceBuffer);
+    return ASCQ_OK;
+}
+#endif
+
 // Column-parallel W8A8 matmul of one rank with the all-gather and the end-of-step exchange inside the launch.
 extern "C" ascq_status ascq_matmul_w8a8_sharded(ascq_comm* comm, void* const* C_bufs, void* C_multicast, const int8_t* A,
                                                 const int8_t* B_local, const float* sA_m, const float* sB_local,
@@ -1001,19 +1052,6 @@ extern "C" ascq_status ascq_matmul_w8a8_sharded(ascq_comm* comm, void* const* C_
     // stores start at the next rank's matrix and go round, so that the ranks do not all write to the same GPU at once
     return run_w8a8(C_bufs, comm->nranks, comm->rank + 1, c0, A, B_local, sA_m, sB_local, bias_local, M, nl, K, N, nullptr, st,
                     nullptr, false, comm);
-}
-
-extern "C" ascq_status ascq_matmul_w8a8_multicast(void* C_multicast, int colOffset, int ldc, const int8_t* A, const int8_t* B_nk,
-                                                  const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K,
-                                                  void* stream)
-{
-    if (!C_multicast) return fail(ASCQ_ERR_INVALID_ARG, "the multicast address must not be NULL");
-    // only whole 16-byte pieces can be multicast: the ragged-edge path of the epilogue writes single elements
-    if (N % 64 != 0 || ldc % 8 != 0 || colOffset % 8 != 0 || (reinterpret_cast<uintptr_t>(C_multicast) & 15u))
-        return fail(ASCQ_ERR_ALIGNMENT, "multicast output needs N %% 64 == 0, ldc and colOffset multiples of 8, a 16-byte aligned base");
-    void* bufs[1] = {C_multicast};
-    return run_w8a8(bufs, 1, 0, colOffset, A, B_nk, sA_m, sB_n, bias_bf16, M, N, K, ldc, nullptr, static_cast<cudaStream_t>(stream),
-                    nullptr, true);
 }
 
 // ---- int8 matmul with the reference's fixpipe quantisation of the result (fp16 output) ----------------------------

@@ -430,16 +430,6 @@ def MatmulW8A8Scatter(buffer_ptrs, first_buf: int, col_offset: int, ldc: int, A:
                                              _ptr(scaleA), _ptr(scaleB), _ptr(bias), M, N, K, _stream(stream)))
 
 
-def MatmulW8A8Multicast(multicast_ptr: int, col_offset: int, ldc: int, A: torch.Tensor, B_nk: torch.Tensor, scaleA=None,
-                        scaleB=None, bias=None, stream=None):
-    """W8A8 matmul whose epilogue writes its column block to the multicast address of the [M, ldc] bf16 output: one
-    multimem store per 16 bytes reaches every GPU's matrix (``ascq_matmul_w8a8_multicast``)."""
-    M, K = A.shape
-    N = B_nk.shape[0]
-    L.check(L.lib().ascq_matmul_w8a8_multicast(C.c_void_p(int(multicast_ptr)), col_offset, ldc, _ptr(A), _ptr(B_nk), _ptr(scaleA),
-                                               _ptr(scaleB), _ptr(bias), M, N, K, _stream(stream)))
-
-
 class Comm:
     """The communicator of the sharded matmuls (``ascq_comm_create``): this rank's position among the GPUs of one box and
     every rank's flag block as mapped into this process.  ``flag_block_ptrs[r]`` is the device address of rank r's block

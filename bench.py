@@ -258,9 +258,32 @@ class QuantScaled(Workload):
         return bool(np.array_equal(self.out[0][:rows].cpu().numpy(), want))
 
 
+class ShardedBuffers:
+    """Device memory every rank of the box can write: the [rows, cols] bf16 output matrices (two, used alternately) and
+    this rank's flag block.  torch's symmetric-memory allocator is used for the allocation and the address exchange
+    only; everything that happens per step goes through the library's communicator (ascq_comm)."""
+
+    def __init__(self, torch, ops, dist, dev, rank, world, rows, cols):
+        import torch.distributed._symmetric_memory as symm
+        self.full, self.hdl = [], []
+        for _ in range(2):
+            t = symm.empty((rows, cols), dtype=torch.bfloat16, device=dev)
+            self.hdl.append(symm.rendezvous(t, dist.group.WORLD))
+            self.full.append(t)
+        self.flags = symm.empty(ops.Comm.flag_bytes(), dtype=torch.uint8, device=dev)
+        self.flags.zero_()
+        fh = symm.rendezvous(self.flags, dist.group.WORLD)
+        torch.cuda.synchronize()
+        dist.barrier()                      # every block is zeroed and mapped before anyone signals
+        torch.cuda.synchronize()
+        self.comm = ops.Comm(rank, world, [int(p) for p in fh.buffer_ptrs])
+        self.ptrs = [[int(p) for p in h.buffer_ptrs] for h in self.hdl]
+        self.mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in self.hdl]
+
+
 class W8A8Cfg4(Workload):
     """Config 4.  With `world` > 1 the weight matrix B (and sB, bias) is column-sharded over the ranks: each rank
-    computes C[:, shard] and an NCCL all-gather reassembles the output on every rank (strong scaling)."""
+    computes C[:, shard] and its epilogue writes the block into every rank's [M, N] matrix (strong scaling)."""
     name = "W8A8 int8 matmul M=N=K=4096 + per-token x per-channel dequant + bias -> bf16 (config 4)"
     sharding_note = "B column-sharded over N"
     dtype = "int8"
@@ -287,28 +310,18 @@ class W8A8Cfg4(Workload):
         self.gathered = torch.empty((world * self.M, self.nl), dtype=torch.bfloat16, device=dev) if world > 1 else None
         self.h_A = torch.from_numpy(h["A"]).pin_memory()
         self.h_sA = torch.from_numpy(h["sA"]).pin_memory()
-        self.h_C = torch.empty((self.M, self.N), dtype=torch.bfloat16).pin_memory()
+        self.h_C = torch.empty((self.M, self.nl), dtype=torch.bfloat16).pin_memory()   # this rank's block of the result
         self.launches_per_step = 1
-        # Fused reassembly: every rank's epilogue stores its column block into every rank's [M, N] matrix over NVLink
-        # (peer-mapped symmetric memory); a device-side barrier ends the step.  Falls back to an NCCL all-gather.
-        self.fused = None
-        self.mc = None
-        if world > 1:
-            try:
-                import torch.distributed._symmetric_memory as symm
-                self.full, self.hdl = [], []
-                for _ in range(2):
-                    t = symm.empty((self.M, self.N), dtype=torch.bfloat16, device=dev)
-                    self.hdl.append(symm.rendezvous(t, dist.group.WORLD))
-                    self.full.append(t)
-                self.fused = True
-                # ASCQ_BENCH_REASSEMBLY=multicast: one multimem store per piece through NVSwitch multicast instead of one
-                # store per peer (measured slower at two ranks, where the local copy then crosses NVLink too)
-                mc = [int(getattr(h, "multicast_ptr", 0) or 0) for h in self.hdl]
-                self.mc = mc if all(mc) and os.environ.get("ASCQ_BENCH_REASSEMBLY", "peer") == "multicast" else None
-            except Exception as e:  # noqa: BLE001
-                self.fused = False
-                self.fused_error = repr(e)[:200]
+        self.variant = "peer"     # "peer": one TMA store per rank; "multicast": multimem stores through NVSwitch
+        self.sh = ShardedBuffers(torch, ops, dist, dev, rank, world, self.M, self.N) if world > 1 else None
+        if world > 1:   # the whole job on this GPU alone, for the matmul-phase efficiency T1 / (N * T_N)
+            self.B_all = torch.from_numpy(h["B"]).to(dev)
+            self.sB_all = torch.from_numpy(h["sB"]).to(dev)
+            self.bias_all = bf(h["bias"])
+            self.C_all = torch.empty((self.M, self.N), dtype=torch.bfloat16, device=dev)
+
+    def variants(self):
+        return ["peer"] + (["multicast"] if self.sh is not None and all(self.sh.mc) and self.nl % 64 == 0 else [])
 
     def work_per_step(self):
         return 2 * self.M * self.N * self.K  # whole job (all ranks together)
@@ -317,17 +330,10 @@ class W8A8Cfg4(Workload):
         s = i % self.nsets
         if self.world == 1:
             self.ops.MatmulW8A8(self.C[s], self.A[s], self.B[s], self.sA, self.sB, self.bias)
-        elif self.fused:
-            f = i % 2
-            if self.mc:
-                self.ops.MatmulW8A8Multicast(self.mc[f], self.rank * self.nl, self.N, self.A[s], self.B[s], self.sA, self.sB,
-                                             self.bias)
-            else:
-                self.ops.MatmulW8A8Scatter(self.hdl[f].buffer_ptrs, self.rank + 1, self.rank * self.nl, self.N, self.A[s],
-                                           self.B[s], self.sA, self.sB, self.bias)
-            self.hdl[f].barrier(channel=0)
         else:
-            self.nccl_step(i)
+            f = i % 2
+            self.ops.MatmulW8A8Sharded(self.sh.comm, self.sh.ptrs[f], self.A[s], self.B[s], self.sA, self.sB, self.bias, N=self.N,
+                                       multicast_ptr=self.sh.mc[f] if self.variant == "multicast" else 0)
 
     def nccl_step(self, i):
         s = i % self.nsets
@@ -338,6 +344,9 @@ class W8A8Cfg4(Workload):
         s = i % self.nsets
         self.ops.MatmulW8A8(self.C[s], self.A[s], self.B[s], self.sA, self.sB, self.bias)
 
+    def single_gpu_step(self, i):
+        self.ops.MatmulW8A8(self.C_all, self.A[i % self.nsets], self.B_all, self.sA, self.sB_all, self.bias_all)
+
     def e2e_step(self, i):
         s = i % self.nsets
         self.A[s].copy_(self.h_A, non_blocking=True)     # this step's activations and their scales
@@ -345,13 +354,12 @@ class W8A8Cfg4(Workload):
         self.step(i)
         if self.world == 1:
             self.h_C.copy_(self.C[s], non_blocking=True)
-        elif self.fused:
-            self.h_C.copy_(self.full[i % 2], non_blocking=True)
-        else:
-            self.h_C.view(self.world * self.M, self.nl).copy_(self.gathered, non_blocking=True)
+        else:   # every rank reads back its own column block of the assembled matrix
+            n0 = self.rank * self.nl
+            self.h_C.copy_(self.sh.full[i % 2][:, n0:n0 + self.nl], non_blocking=True)
 
     def e2e_bytes(self):
-        return self.M * self.K + self.M * 4, self.M * self.N * 2
+        return self.M * self.K + self.M * 4, self.M * self.nl * 2
 
     def cpu_sample(self, O):
         rows = 64
@@ -362,25 +370,30 @@ class W8A8Cfg4(Workload):
         return 2 * rows * self.N * self.K / dt / 1e12, f"{rows} of {self.M} rows of A"
 
     def check(self, O):
-        rows = 16
+        """One full tile row (256 rows) of the result against the oracle; with several ranks also the assembled matrix
+        on every rank, under every reassembly variant."""
+        rows = 256
         n0 = self.rank * self.nl
-        want = O.matmul_w8a8(np.ascontiguousarray(self.host["A"][:rows]), np.ascontiguousarray(self.host["B"][n0:n0 + self.nl]),
-                             self.host["sA"][:rows].copy(), self.host["sB"][n0:n0 + self.nl].copy(),
-                             self.host["bias"][n0:n0 + self.nl].copy())
+        A = np.ascontiguousarray(self.host["A"][:rows])
+        sA = self.host["sA"][:rows].copy()
+        whole = O.matmul_w8a8(A, self.host["B"], sA, self.host["sB"], self.host["bias"])
         self.gemm_only_step(0)
         got = self.C[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
         self.ops.MatmulStatus()
-        ok = bool(np.array_equal(got, want))
-        if self.world > 1 and self.fused:
-            # the reassembled matrix on this rank: every rank's column block must have arrived with the oracle's bits
-            self.step(0)
-            self.torch.cuda.synchronize()
-            self.hdl[0].barrier(channel=0)
-            self.torch.cuda.synchronize()
-            whole = O.matmul_w8a8(np.ascontiguousarray(self.host["A"][:rows]), self.host["B"], self.host["sA"][:rows].copy(),
-                                  self.host["sB"], self.host["bias"])
-            full = self.full[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
-            ok = ok and bool(np.array_equal(full, whole))
+        ok = bool(np.array_equal(got, whole[:, n0:n0 + self.nl]))
+        if self.world > 1:
+            keep = self.variant
+            for v in self.variants():
+                self.variant = v
+                self.sh.full[0].zero_()
+                self.torch.cuda.synchronize()
+                self.dist.barrier()
+                self.step(0)
+                self.ops.MatmulStatus()      # synchronises; raises if the wait for the other ranks ran out
+                full = self.sh.full[0][:rows].view(self.torch.int16).cpu().numpy().view(np.uint16)
+                ok = ok and bool(np.array_equal(full, whole))
+                self.dist.barrier()
+            self.variant = keep
         return ok
 
 
@@ -422,25 +435,21 @@ class Mxfp4Cfg5(Workload):
         self.C = [torch.empty((max(self.local_rows, 1), self.N), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
         self.ws = torch.empty(max(256, ops.GroupMatmulMxfp4Workspace(self.local_rows, max(len(mine), 1), self.K, self.N)),
                               dtype=torch.uint8, device=dev)
-        self.fused = None
+        self.sh = None
         if world > 1:
             self.padded = torch.zeros((self.plan.max_rows, self.N), dtype=torch.bfloat16, device=dev)
             self.gathered = torch.empty((world * self.plan.max_rows, self.N), dtype=torch.bfloat16, device=dev)
-            try:
-                import torch.distributed._symmetric_memory as symm
-                self.full, self.hdl = [], []
-                for _ in range(2):
-                    tt = symm.empty((self.total, self.N), dtype=torch.bfloat16, device=dev)
-                    self.hdl.append(symm.rendezvous(tt, dist.group.WORLD))
-                    self.full.append(tt)
-                self.fused = True
-            except Exception as e:  # noqa: BLE001
-                self.fused = False
-                self.fused_error = repr(e)[:200]
+            self.sh = ShardedBuffers(torch, ops, dist, dev, rank, world, self.total, self.N)
+            owner = ops.ShardGroupsLpt(self.all_groups, world)     # the library's partition is the one the data follows
+            assert owner == self.plan.owner, "library and host partition differ"
         self.h_A = torch.from_numpy(h["A"]).pin_memory()
         self.h_sA = torch.from_numpy(h["sA"]).pin_memory()
-        self.h_C = torch.empty((self.total, self.N), dtype=torch.bfloat16).pin_memory()
+        self.h_C = torch.empty((max(self.local_rows, 1), self.N), dtype=torch.bfloat16).pin_memory()  # this rank's rows
         self.launches_per_step = 2  # one scale-repack launch + the matmul
+        self.variant = "peer"
+
+    def variants(self):
+        return ["peer"]
 
     def work_per_step(self):
         return 2 * self.total * self.N * self.K   # whole job (all ranks together)
@@ -450,14 +459,9 @@ class Mxfp4Cfg5(Workload):
         if self.world == 1:
             self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
                                       workspace=self.ws)
-        elif self.fused:
-            f = i % 2
-            if self.groups:
-                self.ops.GroupMatmulMxfp4Scatter(self.hdl[f].buffer_ptrs, self.rank + 1, self.out_row_start, self.A[s], self.sA[s],
-                                                 self.B[s], self.sB[s], self.groups, self.K, self.N, workspace=self.ws)
-            self.hdl[f].barrier(channel=0)
         else:
-            self.nccl_step(i)
+            self.ops.GroupMatmulMxfp4Sharded(self.sh.comm, self.sh.ptrs[i % 2], self.A[s], self.sA[s], self.B[s], self.sB[s],
+                                             self.all_groups, self.K, self.N, self.ws)
 
     def gemm_only_step(self, i):
         s = i % self.nsets
@@ -488,15 +492,14 @@ class Mxfp4Cfg5(Workload):
         self.step(i)
         if self.world == 1:
             self.h_C.copy_(self.C[s], non_blocking=True)
-        elif self.fused:
-            self.h_C.copy_(self.full[i % 2], non_blocking=True)
-        else:
-            if not hasattr(self, "h_gathered"):
-                self.h_gathered = self.torch.empty(self.gathered.shape, dtype=self.torch.bfloat16).pin_memory()
-            self.h_gathered.copy_(self.gathered, non_blocking=True)
+        else:   # every rank reads back the rows of its own groups from the assembled matrix
+            at = 0
+            for r0, n in zip(self.out_row_start, self.groups):
+                self.h_C[at:at + n].copy_(self.sh.full[i % 2][r0:r0 + n], non_blocking=True)
+                at += n
 
     def e2e_bytes(self):
-        return self.host["A"].nbytes + self.host["sA"].nbytes, self.total * self.N * 2
+        return self.host["A"].nbytes + self.host["sA"].nbytes, self.local_rows * self.N * 2
 
     def cpu_sample(self, O):
         rows = 16
@@ -509,30 +512,52 @@ class Mxfp4Cfg5(Workload):
         return 2 * rows * self.N * self.K / dt / 1e12, f"{rows} of {self.total} rows (group 0)"
 
     def check(self, O):
-        rows = 8
+        """128 rows (one tile row) of this rank's first group against the oracle, element by element: |got - want| <=
+        1e-2 |want| + K 2^-24 sum |a_k b_k| (rtol of the target plus the worst case of an fp32 accumulation).  With several
+        ranks the assembled matrix must hold the same bits at those rows, and every rank's matrix must be complete."""
+        rows = min(128, self.groups[0]) if self.groups else 0
         h = self.host
-        _, want = O.group_matmul_mxfp4(np.ascontiguousarray(h["A"][:rows]), np.ascontiguousarray(h["sA"][:rows]),
-                                       np.ascontiguousarray(h["B"][:1]), np.ascontiguousarray(h["sB"][:1]),
-                                       np.array([rows], np.int64), self.K, self.N, want_f32=True)
-        self.gemm_only_step(0)
-        got = self.C[0][:rows].float().cpu().numpy()
-        self.ops.MatmulStatus()
-        ok = bool(np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + 1e-3 * np.abs(want).max()))
-        if self.world > 1 and self.fused:   # the reassembled matrix holds the same bits at this group's rows, on every rank
-            self.step(0)
+        ok = True
+        if rows:
+            A, sA = np.ascontiguousarray(h["A"][:rows]), np.ascontiguousarray(h["sA"][:rows])
+            B, sB = np.ascontiguousarray(h["B"][:1]), np.ascontiguousarray(h["sB"][:1])
+            _, want = O.group_matmul_mxfp4(A, sA, B, sB, np.array([rows], np.int64), self.K, self.N, want_f32=True)
+            bound = mx_abs_product_sum(O, A, sA, B[0], sB[0], self.K) * (self.K * 2.0 ** -24)
+            self.gemm_only_step(0)
+            got = self.C[0][:rows].float().cpu().numpy()
+            self.ops.MatmulStatus()
+            ok = bool(np.all(np.abs(got - want) <= 1e-2 * np.abs(want) + bound))
+        if self.world > 1:
+            self.sh.full[0].zero_()
             self.torch.cuda.synchronize()
-            r0 = self.out_row_start[0]
-            ok = ok and bool(self.torch.equal(self.full[0][r0:r0 + rows], self.C[0][:rows]))
+            self.dist.barrier()
+            self.step(0)
+            self.ops.MatmulStatus()
+            if rows:
+                r0 = self.out_row_start[0]
+                ok = ok and bool(self.torch.equal(self.sh.full[0][r0:r0 + rows], self.C[0][:rows]))
+            # every row of the assembled matrix was written by somebody (random operands: a zero row is a missing row)
+            ok = ok and bool((self.sh.full[0] != 0).any(dim=1).all().item())
+            self.dist.barrier()
         return ok
+
+
+def mx_abs_product_sum(O, A, sA, Bg, sBg, K):
+    """sum_k |a_k b_k| of dequantised MX-FP4 operands, [rows, N] in float64: the scale of the rounding error of an fp32
+    accumulation."""
+    lut = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6], np.float64)
+
+    def dq(codes, sc):
+        lo, hi = codes & 0x7, (codes >> 4) & 0x7
+        v = np.empty((codes.shape[0], K), np.float64)
+        v[:, 0::2], v[:, 1::2] = lut[lo], lut[hi]
+        return v * np.repeat(np.exp2(sc.astype(np.float64) - 127.0), 32, axis=1)
+    return dq(A, sA) @ dq(Bg, sBg).T
 
 
 WORKLOADS = {"w8a8_cfg4": W8A8Cfg4, "mxfp4_cfg5": Mxfp4Cfg5, "antiquant_cfg2": AntiQuantCfg2, "dequant_cfg3": DequantCfg3,
              "quant_scaled": QuantScaled}
 HEADLINE = "w8a8_cfg4"
-# DRAM bytes read + written by the dominant kernel of one step at full size on one GPU, from the ncu captures
-# summarised in profiles/<workload>_ncu_counters.md (outputs that stay in the 126 MB L2 do not show up as DRAM writes).
-TRAFFIC_BYTES = {"w8a8_cfg4": 35.2e6, "mxfp4_cfg5": 234.4e6, "antiquant_cfg2": 78.6e6, "dequant_cfg3": 33.6e6,
-                 "quant_scaled": 365.3e6}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -593,54 +618,122 @@ class ClockSampler:
         return out
 
 
-def time_steps(torch, fn, steps, warmup, dist=None):
-    """W untimed + K timed calls of fn(i); CUDA events on the current stream; returns seconds (max over ranks)."""
-    for i in range(warmup):
-        fn(i)
+def _sync_ranks(torch, dist):
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
+
+
+def _regions(torch, dist, run_region, first_sec):
+    """Repeats a timed region (K steps) R times back to back, R >= 10 and enough for about 50 ms under load, each
+    bracketed by CUDA events on the launching stream; returns the R durations in seconds, max over ranks."""
+    R = int(min(200, max(10, np.ceil(0.05 / max(first_sec, 1e-6)))))
+    if dist is not None:    # every rank must repeat the same number of times
+        t = torch.tensor([R], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        R = int(t.item())
+    _sync_ranks(torch, dist)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(R + 1)]
+    ev[0].record()
+    for r in range(R):
+        run_region()
+        ev[r + 1].record()
+    _sync_ranks(torch, dist)
+    secs = torch.tensor([ev[r].elapsed_time(ev[r + 1]) / 1e3 for r in range(R)], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(secs, op=dist.ReduceOp.MAX)
+    return [float(v) for v in secs.cpu()]
+
+
+def time_steps(torch, fn, steps, warmup, dist=None, repeats=True):
+    """W untimed calls of fn(i), then regions of K host-launched calls each (see _regions).  Returns the list of region
+    durations in seconds (one region when repeats is False)."""
+    _sync_ranks(torch, dist)
+    for i in range(warmup):
+        fn(i)
+    _sync_ranks(torch, dist)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
         fn(warmup + i)
     e1.record()
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-        torch.cuda.synchronize()
-    sec = e0.elapsed_time(e1) / 1e3
-    if dist is not None:
-        t = torch.tensor([sec], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec = float(t.item())
-    return sec
+    _sync_ranks(torch, dist)
+    first = e0.elapsed_time(e1) / 1e3
+    if not repeats:
+        t = torch.tensor([first], device="cuda", dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(t.item())]
+
+    def region():
+        for i in range(steps):
+            fn(warmup + i)
+    return _regions(torch, dist, region, first)
 
 
-def time_graph(torch, fn, steps, warmup):
-    """The same W + K calls, with the K timed ones captured once into a CUDA graph and replayed: the host's launch
-    cost (Python, ctypes) is then outside the timed region.  Returns seconds for K steps, or None if capture fails."""
+def time_graph(torch, fn, steps, warmup, dist=None):
+    """The same, with the K timed calls captured once into a CUDA graph and each region one replay: the host's launch
+    cost (Python, ctypes) is then outside the timed region.  Every rank captures and replays its own graph; the sharded
+    kernels keep their step counter on the device, so replays stay in step across the ranks.  Returns the list of region
+    durations, or None if capture fails on any rank."""
+    ok = 1
+    g = None
     try:
+        _sync_ranks(torch, dist)
         for i in range(warmup):
             fn(i)
-        torch.cuda.synchronize()
+        _sync_ranks(torch, dist)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             for i in range(steps):
                 fn(warmup + i)
-        g.replay()                      # untimed: uploads the graph
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        g.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / 1e3
     except Exception as e:  # noqa: BLE001
-        print(f"bench: CUDA graph capture unavailable ({e!r}); timing eager launches", file=sys.stderr)
-        torch.cuda.synchronize()
+        print(f"bench: CUDA graph capture unavailable ({e!r}); timing host launches", file=sys.stderr)
+        ok = 0
+    torch.cuda.synchronize()
+    if dist is not None:
+        t = torch.tensor([ok], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = int(t.item())
+    if not ok:
         return None
+    _sync_ranks(torch, dist)
+    g.replay()                      # untimed: uploads the graph
+    _sync_ranks(torch, dist)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    _sync_ranks(torch, dist)
+    return _regions(torch, dist, g.replay, e0.elapsed_time(e1) / 1e3)
+
+
+def best_of(torch, fn, steps, warmup, dist):
+    """Region durations of fn, host-launched and graph-replayed; returns (median seconds per region, stats, how)."""
+    host = time_steps(torch, fn, steps, warmup, dist)
+    graph = time_graph(torch, fn, steps, warmup, dist)
+    pick, how = host, "one host call per step"
+    if graph is not None and np.median(graph) < np.median(host):
+        pick, how = graph, "the K steps replayed from one CUDA graph"
+    stats = {"regions": len(pick), "median_ms_per_step": float(np.median(pick)) / steps * 1e3,
+             "min_ms_per_step": float(np.min(pick)) / steps * 1e3, "max_ms_per_step": float(np.max(pick)) / steps * 1e3,
+             "host_launched_median_ms_per_step": float(np.median(host)) / steps * 1e3}
+    return float(np.median(pick)), stats, how
+
+
+def profile_traffic(key):
+    """DRAM bytes read + written by the dominant kernel of one step, from the ncu summary kept under profiles/ (a line
+    `traffic_bytes_per_launch: N`); None when there is no summary for the workload."""
+    path = os.path.join(ROOT, "profiles", f"{key}_ncu_counters.md")
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.startswith("traffic_bytes_per_launch:"):
+                    return float(line.split(":", 1)[1].split()[0])
+    except OSError:
+        pass
+    return None
 
 
 def run_ours(args):
@@ -666,41 +759,51 @@ def run_ours(args):
         names = [HEADLINE] + names if args.workload == "all" else names
     results = {}
     head = None
+    steps = args.steps
     sampler = ClockSampler(local) if rank == 0 else None   # runs across every timed region of this process
     for nm in names:
         sharded = nm in ("w8a8_cfg4", "mxfp4_cfg5")
         wl = WORKLOADS[nm](torch, ops, dev, dist, world, rank) if sharded else WORKLOADS[nm](torch, ops, dev)
         is_head = nm == (args.workload if args.workload != "all" else HEADLINE)
-        sec = time_steps(torch, wl.step, args.steps, args.warmup, dist)
-        eager_per = sec / args.steps
-        launch = "one host call per step"
-        if world == 1:
-            gsec_graph = time_graph(torch, wl.step, args.steps, args.warmup)
-            if gsec_graph is not None and gsec_graph < sec:
-                sec, launch = gsec_graph, "the K steps replayed from one CUDA graph"
-        per = sec / args.steps
+        variants = wl.variants() if sharded and world > 1 else [None]
+        tried = {}
+        for v in variants:
+            if v is not None:
+                wl.variant = v
+            tried[v] = best_of(torch, wl.step, steps, args.warmup, dist)
+        best = min(tried, key=lambda k: tried[k][0])
+        if best is not None:
+            wl.variant = best
+        sec, stats, launch = tried[best]
+        per = sec / steps
         work = wl.work_per_step()
         if sharded:
             achieved = work / per / 1e12          # T(FL)OPS of the whole job (strong scaling: work is split over ranks)
             total_value = achieved
-            gsec = time_steps(torch, wl.gemm_only_step, args.steps, args.warmup, dist)
+            gsec, gstats, _ = best_of(torch, wl.gemm_only_step, steps, args.warmup, dist)
             if world == 1:
                 gsec = min(gsec, sec)
             # the slowest rank's matmul alone, as a rate per GPU (group shares are not exactly equal)
-            kern = work / world / (gsec / args.steps) / 1e12
+            kern = work / world / (gsec / steps) / 1e12
             int8 = nm == "w8a8_cfg4"
             peak = (2.0 if int8 else 4.0) * peaks["bf16_tflops"]
             extra = {}
             if world > 1:
-                extra["reassembly"] = (("fused epilogue multimem stores through NVSwitch multicast + symmetric-memory barrier"
-                                        if getattr(wl, "mc", None) else "fused epilogue peer stores + symmetric-memory barrier") if wl.fused
-                                       else "NCCL all-gather (symmetric memory unavailable: %s)" % getattr(wl, "fused_error", ""))
-                nsec = time_steps(torch, wl.nccl_step, args.steps, args.warmup, dist)
-                extra["nccl_allgather_variant"] = work / (nsec / args.steps) / 1e12
+                extra["reassembly"] = {"peer": "epilogue TMA stores into every rank's matrix + arrival flags inside the launch",
+                                       "multicast": "epilogue multimem stores through NVSwitch multicast + arrival flags inside the launch"}[best]
+                extra["reassembly_variants_ms_per_step"] = {k: tried[k][0] / steps * 1e3 for k in tried}
+                nsec = float(np.median(time_steps(torch, wl.nccl_step, steps, args.warmup, dist)))
+                extra["nccl_allgather_variant"] = work / (nsec / steps) / 1e12
+                out_bytes = (wl.M * wl.nl if int8 else wl.local_rows * wl.N) * 2 * (world - 1)
+                extra["nvlink_egress_gbs_per_gpu"] = out_bytes / per / 1e9   # this rank's block to every peer, over the whole step
+                if hasattr(wl, "single_gpu_step"):
+                    t1, _, _ = best_of(torch, wl.single_gpu_step, steps, args.warmup, None)
+                    extra["matmul_phase_efficiency"] = t1 / (world * gsec)   # T1 / (N * T_N), matmul kernels only
+                    extra["single_gpu_ms_per_step_on_this_box"] = t1 / steps * 1e3
             roof = {"bound": "tensor", "achieved": kern, "peak": peak, "unit": wl.unit, "frac": kern / peak, "traffic": None,
                     "peak_source": ("2 x %s dense bf16 cuBLAS burst (int8 runs at twice the bf16 rate; nominal 4500)" if int8 else
                                     "4 x %s dense bf16 cuBLAS burst (FP4 runs at four times the bf16 rate; nominal 9000)")
-                                   % peaks["source"], "kernel_ms": gsec / args.steps * 1e3}
+                                   % peaks["source"], "kernel_ms": gsec / steps * 1e3}
         elif wl.bound == "tensor":
             raise AssertionError("every tensor-bound workload shards")
         else:
@@ -709,31 +812,39 @@ def run_ours(args):
             roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
         if world == 1:
-            roof["traffic"] = TRAFFIC_BYTES.get(nm)
-        e2e_sec = time_steps(torch, wl.e2e_step, max(2, args.steps // 4), 2, dist)
-        e2e_per = e2e_sec / max(2, args.steps // 4)
+            roof["traffic"] = profile_traffic(nm)
+            roof["traffic_source"] = f"profiles/{nm}_ncu_counters.md" if roof["traffic"] is not None else None
+        e2e_steps = max(2, steps // 4)
+        e2e_sec = float(np.median(time_steps(torch, wl.e2e_step, e2e_steps, 2, dist)))
+        e2e_per = e2e_sec / e2e_steps
         h2d, d2h = wl.e2e_bytes()
         e2e_value = (work / e2e_per / 1e12 if sharded else
                      work / e2e_per / 1e12 * world if wl.bound == "tensor" else work / e2e_per / 1e9 * world)
         rec = {"name": wl.name, "value": total_value, "unit": wl.unit, "ms_per_step": per * 1e3,
-               "roofline": roof,
+               "roofline": roof, "timing": stats,
                "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                "scaling": "strong" if sharded else "weak",
                "nsets": wl.nsets, "launches_per_step": wl.launches_per_step, "launch": launch,
-               "ms_per_step_host_launched": eager_per * 1e3}
+               "ms_per_step_host_launched": stats["host_launched_median_ms_per_step"]}
         if sharded and world > 1:
             rec.update(extra)
         if world == 1 and hasattr(wl, "prepacked_step"):
-            psec = time_steps(torch, wl.prepacked_step, args.steps, args.warmup, None)
-            gp = time_graph(torch, wl.prepacked_step, args.steps, args.warmup)
-            psec = min(psec, gp) if gp is not None else psec
-            rec["with_prepacked_weight_scales"] = {"value": work / (psec / args.steps) / 1e12, "unit": wl.unit,
-                                                   "ms_per_step": psec / args.steps * 1e3}
+            psec, _, _ = best_of(torch, wl.prepacked_step, steps, args.warmup, None)
+            rec["with_prepacked_weight_scales"] = {"value": work / (psec / steps) / 1e12, "unit": wl.unit,
+                                                   "ms_per_step": psec / steps * 1e3}
         if rank == 0 or (sharded and world > 1):
             from oracle import oracle as O
-            ok = wl.check(O)      # every rank takes part when the check runs a sharded step
+            try:
+                ok = wl.check(O)      # every rank takes part when the check runs a sharded step
+            except ops.AscqError as e:
+                ok = False
+                rec["check_error"] = str(e)[:200]
             if rank == 0:
                 rec["parity_vs_oracle"] = ok
+        try:
+            ops.MatmulStatus()
+        except ops.AscqError as e:
+            rec["device_status"] = str(e)[:200]
         if rank == 0:
             if world == 1:
                 v, sample = wl.cpu_sample(O)
@@ -751,13 +862,16 @@ def run_ours(args):
                 "value": rec["value"], "unit": rec["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": rec["scaling"], "vs_baseline": None,
                 "dtype": wl.dtype, "data": "synthetic",
-                "config": {"workload": rec["name"], "timing": "buffers rotate over a set larger than L2 (126 MB)",
+                "config": {"workload": rec["name"], "timing": "buffers rotate over a set larger than L2 (126 MB); median of "
+                           "%d regions of K steps each" % rec["timing"]["regions"],
                            "launch": rec["launch"],
                            "sharding": ((wl.sharding_note + "; C reassembled inside the step: ") + rec.get("reassembly", "single GPU")
                                         if rec["scaling"] == "strong"
                                         else "replicas only (elementwise operators do not shard)")},
                 "roofline": rec["roofline"], "e2e": rec["e2e"], "gpu_launches": args.steps * rec["launches_per_step"],
                 "clocks": clocks, "workloads": results}
+        if clocks and clocks.get("sm_mhz"):
+            line["ms_per_step_x_sm_mhz"] = rec["ms_per_step"] * clocks["sm_mhz"]
         if "cpu_baseline" in rec:
             line["cpu_baseline"] = rec["cpu_baseline"]
         print(json.dumps(line))
@@ -780,10 +894,10 @@ def run_extras(args):
     out = {}
 
     def add(name, fn, work, unit):
-        sec = time_graph(torch, fn, steps, warm)
-        if sec is None:
-            sec = time_steps(torch, fn, steps, warm)
-        us = sec / steps * 1e6
+        secs = time_graph(torch, fn, steps, warm)
+        if secs is None:
+            secs = time_steps(torch, fn, steps, warm)
+        us = float(np.median(secs)) / steps * 1e6
         out[name] = {"us": round(us, 1), "rate": round(work / us / 1e6, 2), "unit": unit}  # work per us -> T(unit)/s
         print(f"extras: {name}: {us:.1f} us, {work / us / 1e6:.2f} {unit}", file=sys.stderr)
 

@@ -439,17 +439,6 @@ ascq_status ascq_group_matmul_mxfp4_scatter(void* const* C_bufs, int nBufs, int 
                                             size_t workspaceBytes, void* stream);
 
 /*
- * The same fused all-gather through NVSwitch multicast: C_multicast is the multicast address of the [M, ldc] bf16 output
- * (every GPU's matrix bound to one multicast object, e.g. torch symmetric memory's `multicast_ptr`); each 16-byte piece of
- * this launch's column block leaves the SM as ONE multimem.st and the switch writes it into every GPU's matrix, this
- * GPU's included.  Each GPU's links then carry its own block once instead of once per peer.  No reference counterpart.
- * N % 64 == 0, ldc % 8 == 0, colOffset % 8 == 0.  The caller orders the step with a barrier as for the scatter form.
- */
-ascq_status ascq_matmul_w8a8_multicast(void* C_multicast, int colOffset, int ldc, const int8_t* A, const int8_t* B_nk,
-                                       const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K,
-                                       void* stream);
-
-/*
  * ---- Multi-GPU: one process per GPU, the GPUs of one box --------------------------------------------------------
  * The two matmuls shard the way the reference's samples would (column blocks of the W8A8 weight; whole groups of the
  * grouped matmul, one core group per group in examples/.../quant_group_matmul_custom.asc:257-289), and reassemble with

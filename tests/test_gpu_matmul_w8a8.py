@@ -134,6 +134,27 @@ def test_scatter_writes_the_block_into_every_buffer():
         ops.MatmulW8A8Scatter([bufs[0].data_ptr()] * 9, 0, 0, ldc, t(A), t(B))
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 512, 128), (4096, 1280, 64), (4000, 2300, 64)])
+def test_pair_tiles_into_two_buffers(M, N, K, monkeypatch):
+    """A pair-shaped launch that writes two matrices (one TMA store per matrix from the same staged rows): 16 tiles,
+    80 tiles and 144 ragged tiles whose last wave is cut into half-tile items and whose width is not a multiple of 8
+    (per-thread stores).  Exact against an integer reference on the GPU."""
+    monkeypatch.setenv("ASCQ_W8A8_TILE", "pair")
+    A, B, sA, sB, bias = make_case(M, N, K, M + N)
+    dA, dB = torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV)
+    acc = (dA.float() @ dB.float().T).cpu().numpy()      # K <= 256: every sum is exact in fp32
+    want = O.f32_to_bf16_bits((acc * sB[None, :]) * sA[:, None] + O.bf16_bits_to_f32(bias)[None, :])
+    ldc = (N + 7) // 8 * 8 + 64
+    bufs = [torch.full((M, ldc), -1.0, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    dbias = torch.from_numpy(bias.view(np.int16)).to(DEV).view(torch.bfloat16)
+    ops.MatmulW8A8Scatter([b.data_ptr() for b in bufs], 1, 64, ldc, dA, dB, torch.from_numpy(sA).to(DEV), torch.from_numpy(sB).to(DEV), dbias)
+    ops.MatmulStatus()
+    for b in bufs:
+        got = b.view(torch.int16).cpu().numpy().view(np.uint16)
+        assert_bits_equal(np.ascontiguousarray(got[:, 64:64 + N]), want, "block")
+        assert (got[:, :64] == 0xBF80).all() and (got[:, 64 + N:] == 0xBF80).all()
+
+
 # ---- fixpipe quantisation of the result (SetQuantScalar / SetQuantVector, fp16 output) ----------------------------
 @pytest.mark.parametrize("name", ["matmul_quant_scalar", "matmul_quant_vector"])
 def test_matmul_quant_sample_golden_through_the_gpu(name):
