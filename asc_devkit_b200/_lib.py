@@ -65,6 +65,7 @@ SIGNATURES = {
     "ascq_dequantize": (_i, [_vp, _i, _vp, _i, _vp, _i, _f, _i, C.POINTER(QuantizeParam), _vp]),
     "ascq_antiquantize": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _f, _f, _i, C.POINTER(QuantizeParam), _vp]),
     "ascq_matmul_w8a8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "ascq_group_matmul_w8a8": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _i, _vp]),
     "ascq_matmul_w8a8_scatter": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ascq_matmul_i8_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _vp]),
     "ascq_matmul_i8_requant": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_uint64, _i, _i, _i, _i, _vp]),
@@ -90,6 +91,7 @@ SIGNATURES = {
     "ascq_group_matmul_mxfp4_sharded": (_i, [_vp, C.POINTER(_vp), _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_set_wait_limit_cycles": (_i, [C.c_longlong]),
     "ascq_test_withhold_after": (_i, [_i]),
+    "ascq_measure_tensor_rate": (_i, [_i, _i, C.POINTER(C.c_double), _vp]),
     "ascq_group_matmul_mxfp4": (_i, [_vp, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp4_scatter": (_i, [C.POINTER(_vp), _i, _i, _P64, _vp, _vp, _vp, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),
     "ascq_group_matmul_mxfp8": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _P64, _i, _i, _i, _vp, C.c_size_t, _vp]),

@@ -39,6 +39,10 @@ constexpr int kEpiWarps = 8;    // two warps per TMEM lane quarter, alternating 
 constexpr int kMaxPeers = 8;    // output buffers one launch can write (this GPU's and its peers')
 constexpr int kStagePitch = 144;  // bytes per staged row: 128 B of bf16 + 16 B pad (conflict-free both ways)
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
+// Staging bytes of one epilogue warp: 16 padded rows for the per-thread stores (16 x 144), or a 1024-byte aligned block of
+// 2 KiB for TMA stores -- a region of 2.5 KiB that starts at a multiple of 512 bytes holds either, so a warp never
+// touches another warp's staging bytes whichever path the tile it works on takes.
+constexpr int kWarpStageBytes = 2560;
 
 __device__ int g_w8a8_status = 0;  // 0 ok, 1 = a bounded wait expired
 
@@ -57,7 +61,7 @@ template <int BN, bool PAIR, bool CONV = false> struct Cfg {
     static constexpr int kThreadsCta = kThreads + (CONV ? 32 * kConvWarps : 0);
     static constexpr int kTmemCols = 2 * BN;  // two accumulators
     static constexpr int kEpiBytes = 2 * 3 * BN * 4;  // per accumulator: sB[BN], bias[BN] (fp32 or int32 bits), aux[BN]
-    static constexpr int kOutBytes = kEpiWarps * 16 * kStagePitch;  // per epilogue warp: 16 rows x 64 bf16 columns
+    static constexpr int kOutBytes = kEpiWarps * kWarpStageBytes;  // per epilogue warp: 16 rows x 64 16-bit columns
     static constexpr size_t kSmemBytes =
         static_cast<size_t>(kStages) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes + kOutBytes;
 };
@@ -91,8 +95,10 @@ struct Params {
     // shift count 35:32, shift enable 36, offset 45:37, signed-result flag 46)
     unsigned long long quantBits;
     // kEpiFloat: operand format (0 = half, 1 = bfloat16) and output type (0 = half, 1 = bfloat16, 2 = float)
+    // kEpiDequant: outKind 0 = bfloat16 (ascq_matmul_w8a8), 1 = half; act 1 = FasterGelu before the cast
     uint32_t abFmt;
     int outKind;
+    int act;
     // CONV: AscendAntiQuant operands of the int8 weight: per-row (of B_nk) tensors of the operand type, or two scalars
     const void* aqScale;
     const void* aqOffset;
@@ -115,6 +121,37 @@ __device__ __forceinline__ void trace_stamp(const Params& p, int slot)
 #define ASCQ_STAMP(p, slot) ((void)0)
 #endif
 
+// Grouped launch (ascq_group_matmul_w8a8): rows of A per group; row tiles never straddle two groups.  G == 0: plain matmul.
+constexpr int kMaxGroupsInline = 128;
+struct GroupTable {
+    int G;
+    int rows[kMaxGroupsInline];
+};
+// Where a row tile lives: first row in A / C, first row that no longer belongs to it, row offset of its group's weights
+// in B (and index offset into the per-channel parameters).
+struct RowTile {
+    int m0, rowEnd, nBase;
+};
+// 128-row entry `idx` of the row-tile list: groups in order, ceil(rows / stepRows) * (stepRows / 128) entries per group
+// (stepRows = 256 when CTA pairs work on 256-row tiles; the second half of a pair's tile may be empty).
+__device__ __forceinline__ RowTile group_row_tile(const GroupTable& gt, int N, int stepRows, int idx)
+{
+    int start = 0;
+    const int per = stepRows / 128;
+    for (int g = 0; g < gt.G; ++g) {
+        const int mg = gt.rows[g];
+        const int n = (mg + stepRows - 1) / stepRows * per;
+        if (idx < n) {
+            const int first = start + idx * 128;
+            const int left = mg - idx * 128;
+            return RowTile{first, first + (left <= 0 ? 0 : (left < 128 ? left : 128)), g * N};
+        }
+        idx -= n;
+        start += mg;
+    }
+    return RowTile{start, start, 0};
+}
+
 // Work item -> tile, first column inside the tile, columns of the item.
 struct Item {
     int tile, nOff, nCols;
@@ -125,7 +162,17 @@ template <int BN> __device__ __forceinline__ Item decode_item(const Params& p, i
     const int h = w - p.fullTiles;
     return Item{p.fullTiles + (h >> 1), (h & 1) * (BN / 2), BN / 2};
 }
+// FasterGelu in the reference's operation order (impl/adv_api/detail/activation/gelu/gelu_impl.h:134-166): x * -1.702, exp,
+// + 1, x / that, in fp32.  The exponential and the division are the special-function unit's (ex2.approx, rcp.approx: a few
+// units in the last place of fp32, far below one step of the 16-bit result); the reference's own Exp is a hardware
+// approximation that nothing in its tree specifies bit for bit.
+__device__ __forceinline__ float faster_gelu(float x)
+{
+    const float e = __expf(__fmul_rn(x, -1.702f));
+    return __fdividef(x, __fadd_rn(e, 1.0f));
+}
 constexpr int kEpiDequant = 0;  // bf16(((float(acc) * sB[n]) * sA[m]) + bias[n])
+constexpr int kEpiDequantAct = 4;  // the same with an optional FasterGelu and a half or bfloat16 result (grouped matmul)
 constexpr int kEpiFixpipe = 1;  // SetQuantScalar / SetQuantVector of the reference's Matmul (DEQF16)
 constexpr int kEpiFloat = 2;    // half / bfloat16 operands (kind::f16), fp32 accumulator cast to the output type
 constexpr int kEpiRequant = 3;  // SetQuantScalar / SetQuantVector with an int8 / uint8 result ((V)REQ8)
@@ -218,7 +265,7 @@ struct OutMaps {
 template <int BN, bool PAIR, int EPI, bool CONV = false>
 __global__ void __launch_bounds__(Cfg<BN, PAIR, CONV>::kThreadsCta, 1)
 w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-            const __grid_constant__ OutMaps tmapC, const Params p)
+            const __grid_constant__ OutMaps tmapC, const Params p, const __grid_constant__ GroupTable gt)
 {
     using C = Cfg<BN, PAIR, CONV>;
     static_assert(!CONV || (PAIR && EPI == kEpiFloat), "the converting variant is built for CTA pairs and kind::f16 only");
@@ -226,7 +273,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     // stage buffers need 1024-byte alignment for the 128B swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // [stages][output staging, 1024-aligned for swizzled TMA stores][barriers, 256 B][per-column epilogue parameters]
-    uint8_t* outStage = smem + C::kStages * C::kStageBytes;  // [kEpiWarps][16][kStagePitch], or [kEpiWarps][16 x 128 B swizzled]
+    uint8_t* outStage = smem + C::kStages * C::kStageBytes;  // [kEpiWarps][kWarpStageBytes]
     uint64_t* bars = reinterpret_cast<uint64_t*>(outStage + C::kOutBytes);
     uint64_t* fullBar = bars;                      // [kStages] TMA -> MMA
     uint64_t* emptyBar = bars + C::kStages;        // [kStages] MMA -> TMA
@@ -247,6 +294,11 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
     const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int numUnits = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     constexpr int kTileM = PAIR ? 2 * kBM : kBM;
+    // this CTA's 128 rows of row tile `mt`: a regular grid over M, or the group-aligned list of a grouped launch
+    auto row_tile = [&](int mt) -> RowTile {
+        if (gt.G == 0) return RowTile{mt * kTileM + static_cast<int>(rank) * kBM, p.M, 0};
+        return group_row_tile(gt, p.N, kTileM, mt * (kTileM / kBM) + static_cast<int>(rank));
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -300,9 +352,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             for (int w = unit; w < numTiles && ok; w += numUnits) {
                 const Item item = decode_item<BN>(p, w);
                 const int tile = item.tile;
-                const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
-                // rows of B this CTA loads: its half of the item's columns
-                const int n0 = (tile / p.tilesM) * BN + item.nOff + (PAIR ? static_cast<int>(rank) * (item.nCols / 2) : 0);
+                const RowTile rt = row_tile(tile % p.tilesM);
+                const int m0 = rt.m0;
+                // rows of B this CTA loads: its half of the item's columns (of its group's weights)
+                const int n0 = rt.nBase + (tile / p.tilesM) * BN + item.nOff + (PAIR ? static_cast<int>(rank) * (item.nCols / 2) : 0);
                 for (int kb = 0; kb < kBlocks; ++kb, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
@@ -407,7 +460,9 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
         // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).. (its 32 rows of the tile) ----------------
         const int q = warp & 3;
         const int sub = (warp - 2) >> 2;
-        uint8_t* stageW = outStage + (warp - 2) * (16 * kStagePitch);
+        uint8_t* stageW = outStage + (warp - 2) * kWarpStageBytes;
+        // the 1024-byte aligned 2 KiB inside the same region: staging rows of the TMA stores (128B-swizzled)
+        uint8_t* stageT = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(stageW) + 1023) & ~uintptr_t(1023));
         uint32_t local = 0;
         bool ok = true;
         for (int w = unit; w < numTiles && ok; w += numUnits, ++local) {
@@ -415,10 +470,11 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             const int tile = item.tile;
             const int acc = local & 1;
             const uint32_t accPh = (local >> 1) & 1;
-            const int m0 = (tile % p.tilesM) * kTileM + static_cast<int>(rank) * kBM;
+            const RowTile rt = row_tile(tile % p.tilesM);
+            const int m0 = rt.m0, rowEnd = rt.rowEnd;   // rows [m0, rowEnd) of C are this CTA's to write
             const int n0 = (tile / p.tilesM) * BN + item.nOff;
             const int m = m0 + q * 32 + lane;
-            const float sa = (p.sA != nullptr && m < p.M) ? __ldg(p.sA + m) : 1.0f;
+            const float sa = (p.sA != nullptr && m < rowEnd) ? __ldg(p.sA + m) : 1.0f;
             // this tile's per-channel scale and bias, once, into shared memory (fp32): every thread needs all BN of
             // them and reads them back as warp-wide broadcasts.  Fetched before the accumulator is waited for, so that
             // the latency of these loads is hidden; the buffer of this accumulator was last read two tiles ago, and every
@@ -444,8 +500,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                         sBs[j] = __uint_as_float(bits);
                         biasS[j] = __int_as_float((p.biasI32 != nullptr && n < p.N) ? __ldg(p.biasI32 + n) : 0);
                     } else {
-                        sBs[j] = (p.sB != nullptr && n < p.N) ? __ldg(p.sB + n) : 1.0f;
-                        biasS[j] = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+                        sBs[j] = (p.sB != nullptr && n < p.N) ? __ldg(p.sB + rt.nBase + n) : 1.0f;
+                        biasS[j] = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[rt.nBase + n]) : 0.0f;
                     }
                 }
                 ok = CONV ? mbar_wait_bounded_sleepy(&tmemFull[acc], accPh, abortFlag) : mbar_wait_bounded(&tmemFull[acc], accPh, abortFlag);
@@ -468,6 +524,14 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 if (threadIdx.x == 64 && local < 5) ASCQ_STAMP(p, 1 + 2 * static_cast<int>(local));
             }
             const bool hasBias = p.bias != nullptr;
+            // A row tile of a grouped launch that ends inside its 128 rows must not touch the next group's rows, which a
+            // 16-row box would: such tiles take the per-thread stores.  They stage through the same bytes, so the TMA
+            // stores of the tile before must have read them.
+            const bool tileTma = p.tmaStore && (gt.G == 0 || rowEnd - m0 >= kBM);
+            if (p.tmaStore && !tileTma) {
+                if (lane == 0) bulk_wait_group_read<0>();
+                __syncwarp();
+            }
             const uint32_t taddr = tmemBase + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
             const bool haveC = p.C[0] != nullptr;
             bool vecStore = (p.ldc % 8 == 0) && (p.colOffset % 8 == 0);
@@ -526,6 +590,16 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     if (hasBias) {
                         f0 = __fadd_rn(f0, b4.x); f1 = __fadd_rn(f1, b4.y); f2 = __fadd_rn(f2, b4.z); f3 = __fadd_rn(f3, b4.w);
                     }
+                    if constexpr (EPI == kEpiDequantAct) {
+                        if (p.act) {
+                            f0 = faster_gelu(f0); f1 = faster_gelu(f1); f2 = faster_gelu(f2); f3 = faster_gelu(f3);
+                        }
+                        if (p.outKind == 1) {   // half: finite overflow saturates, as the reference's Cast does
+                            packed[2 * v] = pack_f16x2_sat(f0, f1);
+                            packed[2 * v + 1] = pack_f16x2_sat(f2, f3);
+                            continue;
+                        }
+                    }
                     packed[2 * v] = pack_bf16x2_sat(f0, f1);
                     packed[2 * v + 1] = pack_bf16x2_sat(f2, f3);
                 }
@@ -568,7 +642,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
             };
             // slow path for ragged edges / unaligned outputs: every thread writes its own row segment
             auto store_direct = [&](const uint32_t* packed, int n) {
-                if (m >= p.M || n >= p.N) return;
+                if (m >= rowEnd || n >= p.N) return;
                 for (int pi = 0; pi < p.nPeers; ++pi) {
                     __nv_bfloat16* crow = p.C[pi] + static_cast<size_t>(m) * p.ldc + p.colOffset + n;
 #pragma unroll
@@ -585,7 +659,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 tmem_ld_wait();
                 const int n = n0 + c2 * 64;
                 if (n >= p.N) continue;  // uniform over the warp
-                if (p.accDump != nullptr && m < p.M) {
+                if (p.accDump != nullptr && m < rowEnd) {
                     int32_t* d = p.accDump + static_cast<size_t>(m) * p.N + n;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -596,7 +670,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 if (!haveC) continue;
                 if constexpr (EPI == kEpiFloat) {
                     if (p.outKind == 2) {  // fp32 output: every thread writes its own row
-                        if (m < p.M) {
+                        if (m < rowEnd) {
                             float* crow = reinterpret_cast<float*>(p.C[0]) + static_cast<size_t>(m) * p.ldc + p.colOffset + n;
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
@@ -630,12 +704,12 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                                 const int rl = i * 8 + (lane >> 2);
                                 const uint4 val = *reinterpret_cast<const uint4*>(stageW + rl * kBytePitch + piece * 16);
                                 const int gm = m0 + q * 32 + h * 16 + rl;
-                                if (gm < p.M)
+                                if (gm < rowEnd)
                                     *reinterpret_cast<uint4*>(Cb + static_cast<size_t>(gm) * p.ldc + p.colOffset + n + piece * 16) = val;
                             }
                             __syncwarp();
                         }
-                    } else if (m < p.M) {
+                    } else if (m < rowEnd) {
                         uint8_t* crow = Cb + static_cast<size_t>(m) * p.ldc + p.colOffset + n;
 #pragma unroll
                         for (int j = 0; j < 64; ++j)
@@ -646,11 +720,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 uint32_t packed[32];
                 convert32(r0, c2 * 64, packed);
                 convert32(r1, c2 * 64 + 32, packed + 16);
-                if (p.tmaStore) {
+                if (tileTma) {
                     // Sixteen rows at a time go into this warp's swizzled staging rows (16-byte piece v of row r at
                     // v ^ (r & 7), which also keeps the writes free of bank conflicts) and leave as one TMA store; rows
                     // past M and columns past N are clipped by the tensor map.
-                    uint8_t* stageT = outStage + (warp - 2) * 2048;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         if (lane == 0) bulk_wait_group_read<0>();  // the previous store has read the staging rows
@@ -665,7 +738,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                         }
                         __syncwarp();
                         const int row0 = m0 + q * 32 + h * 16;
-                        if (lane == 0 && row0 < p.M) {
+                        if (lane == 0 && row0 < rowEnd) {
                             // one store per output matrix (this GPU's and the peers'), all reading the same staged rows
                             for (int pi = 0; pi < p.nPeers; ++pi) {
                                 int b = p.firstPeer + pi;
@@ -694,7 +767,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                             const int rl = i * 4 + (lane >> 3);
                             const uint4 val = *reinterpret_cast<const uint4*>(stageW + rl * kStagePitch + piece * 16);
                             const int gm = m0 + q * 32 + h * 16 + rl;
-                            if (gm < p.M) {
+                            if (gm < rowEnd) {
                                 const size_t off = static_cast<size_t>(gm) * p.ldc + p.colOffset + n + piece * 8;
                                 if (p.multicast) {
                                     multimem_st_v4(p.C[0] + off, val);
@@ -759,7 +832,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
 
 // ---- host side -------------------------------------------------------------------------------------
 template <int BN, bool PAIR, int EPI = kEpiDequant, bool CONV = false>
-ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, Params p, cudaStream_t st)
+ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, Params p, cudaStream_t st, const GroupTable& gt)
 {
     using C = Cfg<BN, PAIR, CONV>;
     static PerDeviceOnce attrSet;  // the attribute is per device: a process may drive several GPUs
@@ -770,7 +843,12 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& 
         attrSet.mark(dev);
     }
     const bool pdl = getenv("ASCQ_W8A8_NOPDL") == nullptr;
-    p.tilesM = (p.M + (PAIR ? 2 * kBM : kBM) - 1) / (PAIR ? 2 * kBM : kBM);
+    constexpr int kRowsPerTile = PAIR ? 2 * kBM : kBM;
+    p.tilesM = (p.M + kRowsPerTile - 1) / kRowsPerTile;
+    if (gt.G > 0) {  // grouped: every group starts a new row tile
+        p.tilesM = 0;
+        for (int g = 0; g < gt.G; ++g) p.tilesM += (gt.rows[g] + kRowsPerTile - 1) / kRowsPerTile;
+    }
     p.tilesN = (p.N + BN - 1) / BN;
     const int tiles = p.tilesM * p.tilesN;
     p.fullTiles = tiles;
@@ -800,7 +878,7 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& 
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl ? 2 : 1;
-        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, tc, p));
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, tc, p, gt));
     } else {
         const int grid = tiles < sm_count() ? tiles : sm_count();
         cudaLaunchConfig_t cfg{};
@@ -813,7 +891,7 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& 
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl ? 1 : 0;
-        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, tc, p));
+        ASCQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w8a8_kernel<BN, PAIR, EPI, CONV>, ta, tb, tc, p, gt));
     }
     ASCQ_CUDA_CHECK(cudaGetLastError());
     return ASCQ_OK;
@@ -852,9 +930,12 @@ std::atomic<int> g_stopAfterNext{-1};
 
 ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffset, const int8_t* A, const int8_t* B_nk,
                      const float* sA_m, const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc, int32_t* accDump,
-                     cudaStream_t st, const FixpipeArgs* fix = nullptr, bool multicast = false, const ascq_comm* comm = nullptr)
+                     cudaStream_t st, const FixpipeArgs* fix = nullptr, bool multicast = false, const ascq_comm* comm = nullptr,
+                     const GroupTable* groups = nullptr, int outKind = 0, int act = 0)
 {
-    const int epi = fix ? (fix->floatKind ? kEpiFloat : (fix->requant ? kEpiRequant : kEpiFixpipe)) : kEpiDequant;
+    // groups: M is the total number of rows, B_nk holds groups->G matrices [N, K] one after the other, sB_n / bias [G, N]
+    const int epi = fix ? (fix->floatKind ? kEpiFloat : (fix->requant ? kEpiRequant : kEpiFixpipe))
+                        : ((outKind != 0 || act != 0) ? kEpiDequantAct : kEpiDequant);
     const int elemBytes = (epi == kEpiFloat) ? 2 : 1;
     if (!A || !B_nk) return fail(ASCQ_ERR_INVALID_ARG, "A and B must not be NULL");
     if (nBufs < 0 || nBufs > kMaxPeers) return fail(ASCQ_ERR_INVALID_ARG, "between 1 and %d output buffers are supported", kMaxPeers);
@@ -886,6 +967,10 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     p.trace = g_trace;
 #endif
     p.comm = comm_args(comm);
+    p.outKind = outKind;
+    p.act = act;
+    const GroupTable noGroups{};
+    const GroupTable& gt = groups ? *groups : noGroups;
     if (fix) {
         p.abFmt = fix->abFmt;
         p.outKind = fix->outKind;
@@ -906,8 +991,15 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     // wave at about four fifths of the rate.  Small problems (a column shard on eight GPUs) so end up on 128 x 128
     // tiles that occupy every SM.  ASCQ_W8A8_TILE=pair|wide|narrow overrides the choice.
     const int units = sm_count();
-    const int tilesM = (M + kBM - 1) / kBM;
-    const long long tilesPair = static_cast<long long>((tilesM + 1) / 2) * ((N + 255) / 256);
+    int tilesM = (M + kBM - 1) / kBM, tilesM2 = (tilesM + 1) / 2;   // row tiles of 128 and of 256 rows
+    if (gt.G > 0) {
+        tilesM = tilesM2 = 0;
+        for (int g = 0; g < gt.G; ++g) {
+            tilesM += (gt.rows[g] + kBM - 1) / kBM;
+            tilesM2 += (gt.rows[g] + 2 * kBM - 1) / (2 * kBM);
+        }
+    }
+    const long long tilesPair = static_cast<long long>(tilesM2) * ((N + 255) / 256);
     const long long tiles256 = static_cast<long long>(tilesM) * ((N + 255) / 256);
     const long long tiles128 = static_cast<long long>(tilesM) * ((N + 127) / 128);
     auto waves = [](long long tiles, int n) { return static_cast<double>((tiles + n - 1) / n); };
@@ -923,7 +1015,7 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         else if (!strcmp(e, "narrow")) mode = 0;
     }
     // 16-bit result in one suitably aligned buffer: TMA stores (ASCQ_W8A8_STORE=plain keeps the per-thread stores)
-    const bool out16 = epi == kEpiDequant || epi == kEpiFixpipe || (epi == kEpiFloat && fix->outKind <= 1);
+    const bool out16 = epi == kEpiDequant || epi == kEpiDequantAct || epi == kEpiFixpipe || (epi == kEpiFloat && fix->outKind <= 1);
     const char* storeEnv = getenv("ASCQ_W8A8_STORE");
     // (the copy engine clips a box at the matrix edge in whole 16-byte pieces, so the block must end on one)
     p.tmaStore = haveC && out16 && !multicast && ldc % 8 == 0 && colOffset % 8 == 0 && N % 8 == 0 &&
@@ -933,12 +1025,13 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     OutMaps tc;
     ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K) * elemBytes, kBM);
     if (rc != ASCQ_OK) return rc;
-    rc = make_tmap_u8(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
+    const uint64_t rowsB = static_cast<uint64_t>(N) * (gt.G > 0 ? gt.G : 1);
+    rc = make_tmap_u8(&tb, B_nk, rowsB, static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
     if (rc != ASCQ_OK) return rc;
     for (int i = 0; i < kMaxPeers; ++i) tc.m[i] = ta;  // placeholders; the kernel reads maps [0, nPeers) and only for TMA stores
     tc.bHalf = tb;
     if (mode == 2) {  // pair shape: half-tile work items load 64 rows of B per CTA instead of 128
-        rc = make_tmap_u8(&tc.bHalf, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K) * elemBytes, 64);
+        rc = make_tmap_u8(&tc.bHalf, B_nk, rowsB, static_cast<uint64_t>(K) * elemBytes, 64);
         if (rc != ASCQ_OK) return rc;
     }
     if (p.tmaStore) {
@@ -953,22 +1046,26 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         // B_nk is the int8 weight: its tile goes through the converter warps (CTA pairs, 256 x 256 tiles only)
         rc = make_tmap_u8_plain(&tb, B_nk, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kBK / 2, 128);
         if (rc != ASCQ_OK) return rc;
-        return launch<256, true, kEpiFloat, true>(ta, tb, tc, p, st);
+        return launch<256, true, kEpiFloat, true>(ta, tb, tc, p, st, gt);
     }
     if (epi == kEpiFloat) {
-        if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, tc, p, st);
-        return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, tc, p, st) : launch<128, false, kEpiFloat>(ta, tb, tc, p, st);
+        if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, tc, p, st, gt);
+        return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiFloat>(ta, tb, tc, p, st, gt);
     }
     if (epi == kEpiRequant) {
-        if (mode == 2) return launch<256, true, kEpiRequant>(ta, tb, tc, p, st);
-        return mode == 1 ? launch<256, false, kEpiRequant>(ta, tb, tc, p, st) : launch<128, false, kEpiRequant>(ta, tb, tc, p, st);
+        if (mode == 2) return launch<256, true, kEpiRequant>(ta, tb, tc, p, st, gt);
+        return mode == 1 ? launch<256, false, kEpiRequant>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiRequant>(ta, tb, tc, p, st, gt);
     }
     if (epi == kEpiFixpipe) {
-        if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, tc, p, st);
-        return mode == 1 ? launch<256, false, kEpiFixpipe>(ta, tb, tc, p, st) : launch<128, false, kEpiFixpipe>(ta, tb, tc, p, st);
+        if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, tc, p, st, gt);
+        return mode == 1 ? launch<256, false, kEpiFixpipe>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiFixpipe>(ta, tb, tc, p, st, gt);
     }
-    if (mode == 2) return launch<256, true>(ta, tb, tc, p, st);
-    return mode == 1 ? launch<256, false>(ta, tb, tc, p, st) : launch<128, false>(ta, tb, tc, p, st);
+    if (epi == kEpiDequantAct) {
+        if (mode == 2) return launch<256, true, kEpiDequantAct>(ta, tb, tc, p, st, gt);
+        return mode == 1 ? launch<256, false, kEpiDequantAct>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiDequantAct>(ta, tb, tc, p, st, gt);
+    }
+    if (mode == 2) return launch<256, true>(ta, tb, tc, p, st, gt);
+    return mode == 1 ? launch<256, false>(ta, tb, tc, p, st, gt) : launch<128, false>(ta, tb, tc, p, st, gt);
 }
 }  // namespace
 }  // namespace ascq
@@ -981,6 +1078,31 @@ extern "C" ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int
 {
     void* bufs[1] = {C_bf16};
     return run_w8a8(bufs, 1, 0, 0, A, B_nk, sA_m, sB_n, bias_bf16, M, N, K, ldc, accDump, static_cast<cudaStream_t>(stream));
+}
+
+// Grouped W8A8 matmul: rows of A belong to groups (experts), every group has its own weight matrix and channel scales.
+extern "C" ascq_status ascq_group_matmul_w8a8(void* C, ascq_dtype cT, const int8_t* A, const int8_t* B_gnk, const float* sA_m,
+                                              const float* sB_gn, const void* bias_bf16_gn, const int64_t* groupList_host,
+                                              int G, int N, int K, int activation, void* stream)
+{
+    if (!C || !groupList_host) return fail(ASCQ_ERR_INVALID_ARG, "C and groupList must not be NULL");
+    if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16) return fail(ASCQ_ERR_UNSUPPORTED, "output must be half or bfloat16_t");
+    if (activation != 0 && activation != 1) return fail(ASCQ_ERR_INVALID_ARG, "activation must be 0 (none) or 1 (FasterGelu)");
+    if (G <= 0) return fail(ASCQ_ERR_INVALID_ARG, "G must be positive");
+    if (G > kMaxGroupsInline) return fail(ASCQ_ERR_UNSUPPORTED, "at most %d groups per call are supported", kMaxGroupsInline);
+    GroupTable gt{};
+    gt.G = G;
+    int64_t sumM = 0;
+    for (int g = 0; g < G; ++g) {
+        if (groupList_host[g] < 0) return fail(ASCQ_ERR_INVALID_ARG, "groupList[%d] is negative", g);
+        sumM += groupList_host[g];
+        if (sumM > 0x7FFFFFFF - 512) return fail(ASCQ_ERR_INVALID_ARG, "too many rows for 32-bit row indices");
+        gt.rows[g] = static_cast<int>(groupList_host[g]);
+    }
+    if (static_cast<int64_t>(G) * N > 0x7FFFFFFF) return fail(ASCQ_ERR_INVALID_ARG, "G * N exceeds 32-bit row indices");
+    void* bufs[1] = {C};
+    return run_w8a8(bufs, 1, 0, 0, A, B_gnk, sA_m, sB_gn, bias_bf16_gn, static_cast<int>(sumM), N, K, N, nullptr,
+                    static_cast<cudaStream_t>(stream), nullptr, false, nullptr, &gt, cT == ASCQ_DT_F16 ? 1 : 0, activation);
 }
 
 extern "C" ascq_status ascq_matmul_w8a8_scatter(void* const* C_bufs, int nBufs, int firstBuf, int colOffset, int ldc,

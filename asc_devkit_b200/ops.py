@@ -418,6 +418,17 @@ def MxRepackScaleB(sB_nk: torch.Tensor, sB_ref: torch.Tensor, sK: int, N: int, s
     return sB_nk
 
 
+def GroupMatmulW8A8(C: torch.Tensor, A: torch.Tensor, B_gnk: torch.Tensor, scaleA, scaleB_gn, groupList, bias_gn=None,
+                    activation: int = 0, stream=None):
+    """Grouped W8A8 matmul (``ascq_group_matmul_w8a8``): A int8 [sumM, K], B int8 [G, N, K], scaleA fp32 [sumM], scaleB fp32
+    [G, N], groupList = rows per group (host sequence), C half or bf16 [sumM, N]; ``activation=1`` applies FasterGelu."""
+    G, N, K = B_gnk.shape
+    gl = (C_int64 * len(groupList))(*[int(v) for v in groupList])
+    L.check(L.lib().ascq_group_matmul_w8a8(_ptr(C), dtype_code(C), _ptr(A), _ptr(B_gnk), _ptr(scaleA), _ptr(scaleB_gn),
+                                           _ptr(bias_gn), gl, len(groupList), N, K, int(activation), _stream(stream)))
+    return C
+
+
 def MatmulW8A8Scatter(buffer_ptrs, first_buf: int, col_offset: int, ldc: int, A: torch.Tensor, B_nk: torch.Tensor,
                       scaleA=None, scaleB=None, bias=None, stream=None):
     """W8A8 matmul whose epilogue writes the [M, N_local] block into columns [col_offset, col_offset + N_local) of every
@@ -511,6 +522,14 @@ def GroupMatmulMxfp4Sharded(comm: Comm, C_buf_ptrs, A_local: torch.Tensor, scale
     L.check(L.lib().ascq_group_matmul_mxfp4_sharded(comm.handle, arr, _ptr(A_local), _ptr(scaleA_local), _ptr(B_local),
                                                     _ptr(scaleB_local), gl, G, K, N, _ptr(workspace), workspace.numel(),
                                                     _stream(stream)))
+
+
+def MeasureTensorRate(operand_dtype: int, k_blocks: int, stream=None) -> float:
+    """Enqueues the MMA-only kernel (``ascq_measure_tensor_rate``) and returns the operations it performs; time the call
+    with CUDA events to get the tensor cores' rate for int8 (``DT_I8``) or MX-FP4 (``DT_FP4X2_E2M1``) operands."""
+    n = C.c_double()
+    L.check(L.lib().ascq_measure_tensor_rate(operand_dtype, k_blocks, C.byref(n), _stream(stream)))
+    return float(n.value)
 
 
 def SetWaitLimitCycles(cycles: int):

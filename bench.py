@@ -139,6 +139,12 @@ class AntiQuantCfg2(Workload):
     def e2e_bytes(self):
         return self.K * self.N, self.K * self.N * 2
 
+    def probe_step(self, i):
+        """The same bytes in and out through torch's own type-conversion kernel (int8 -> bfloat16, no arithmetic): an
+        independent reading of what a 1-byte-in, 2-bytes-out stream of this size reaches on this GPU."""
+        s = i % self.nsets
+        self.out[s].copy_(self.w[s])
+
     def cpu_sample(self, O):
         rows = 512
         w = np.ascontiguousarray(self.host["w"][:rows])
@@ -190,6 +196,11 @@ class DequantCfg3(Workload):
 
     def e2e_bytes(self):
         return self.M * self.N * 4, self.M * self.N * 2
+
+    def probe_step(self, i):
+        """The same bytes through torch's type-conversion kernel (int32 -> bfloat16): see AntiQuantCfg2.probe_step."""
+        s = i % self.nsets
+        self.out[s].copy_(self.acc[s])
 
     def cpu_sample(self, O):
         rows = 512
@@ -435,6 +446,8 @@ class Mxfp4Cfg5(Workload):
         self.C = [torch.empty((max(self.local_rows, 1), self.N), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
         self.ws = torch.empty(max(256, ops.GroupMatmulMxfp4Workspace(self.local_rows, max(len(mine), 1), self.K, self.N)),
                               dtype=torch.uint8, device=dev)
+        if world == 1:   # static weights: scales packed once, as at model-load time
+            self.sB_packed = [ops.GroupMatmulMxfp4PackScaleB(self.sB[j], self.K, self.N) for j in range(self.nsets)]
         self.sh = None
         if world > 1:
             self.padded = torch.zeros((self.plan.max_rows, self.N), dtype=torch.bfloat16, device=dev)
@@ -457,23 +470,30 @@ class Mxfp4Cfg5(Workload):
     def step(self, i):
         s = i % self.nsets
         if self.world == 1:
-            self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
-                                      workspace=self.ws)
+            # expert weights are static: their scales were brought into the kernel's order once, when the weights were
+            # loaded (ascq_group_matmul_mxfp4_pack_scale_b); the step repacks the activations' scales only
+            self.prepacked_step(i)
         else:
             self.ops.GroupMatmulMxfp4Sharded(self.sh.comm, self.sh.ptrs[i % 2], self.A[s], self.sA[s], self.B[s], self.sB[s],
                                              self.all_groups, self.K, self.N, self.ws)
 
     def gemm_only_step(self, i):
         s = i % self.nsets
-        if self.groups:
+        if self.world == 1:
+            self.prepacked_step(i)
+        elif self.groups:
             self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
                                       workspace=self.ws)
+
+    def raw_scales_step(self, i):
+        """Weight scales in the reference's [G, N, K/32] order: repacked inside every step."""
+        s = i % self.nsets
+        self.ops.GroupMatmulMxfp4(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB[s], self.groups, self.K, self.N,
+                                  workspace=self.ws)
 
     def prepacked_step(self, i):
         """Static weights: their scales were brought into the kernel's order once, outside the step."""
         s = i % self.nsets
-        if not hasattr(self, "sB_packed"):
-            self.sB_packed = [self.ops.GroupMatmulMxfp4PackScaleB(self.sB[j], self.K, self.N) for j in range(self.nsets)]
         self.ops.GroupMatmulMxfp4Prepacked(self.C[s], self.A[s], self.sA[s], self.B[s], self.sB_packed[s], self.groups, self.K,
                                            self.N, workspace=self.ws)
 
@@ -800,10 +820,15 @@ def run_ours(args):
                     t1, _, _ = best_of(torch, wl.single_gpu_step, steps, args.warmup, None)
                     extra["matmul_phase_efficiency"] = t1 / (world * gsec)   # T1 / (N * T_N), matmul kernels only
                     extra["single_gpu_ms_per_step_on_this_box"] = t1 / steps * 1e3
+            ceiling = measured_tensor_ceiling(torch, ops, _lib.DT_I8 if int8 else _lib.DT_FP4X2_E2M1)
             roof = {"bound": "tensor", "achieved": kern, "peak": peak, "unit": wl.unit, "frac": kern / peak, "traffic": None,
                     "peak_source": ("2 x %s dense bf16 cuBLAS burst (int8 runs at twice the bf16 rate; nominal 4500)" if int8 else
                                     "4 x %s dense bf16 cuBLAS burst (FP4 runs at four times the bf16 rate; nominal 9000)")
-                                   % peaks["source"], "kernel_ms": gsec / steps * 1e3}
+                                   % peaks["source"], "kernel_ms": gsec / steps * 1e3,
+                    # the tensor cores' own rate on this GPU for this operand type, measured in this run: the kernel's MMA
+                    # instructions alone, operands in shared memory (ascq_measure_tensor_rate)
+                    "measured_mma_only_ceiling": ceiling, "frac_of_measured_ceiling": kern / ceiling if ceiling else None,
+                    "frac_of_nominal": kern / (4500.0 if int8 else 9000.0)}
         elif wl.bound == "tensor":
             raise AssertionError("every tensor-bound workload shards")
         else:
@@ -811,6 +836,9 @@ def run_ours(args):
             total_value = achieved * world
             roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}
+        if world == 1 and hasattr(wl, "probe_step"):
+            psec, _, _ = best_of(torch, wl.probe_step, steps, args.warmup, None)
+            roof["same_bytes_through_torch_cast_gbs"] = work / (psec / steps) / 1e9
         if world == 1:
             roof["traffic"] = profile_traffic(nm)
             roof["traffic_source"] = f"profiles/{nm}_ncu_counters.md" if roof["traffic"] is not None else None
@@ -828,10 +856,11 @@ def run_ours(args):
                "ms_per_step_host_launched": stats["host_launched_median_ms_per_step"]}
         if sharded and world > 1:
             rec.update(extra)
-        if world == 1 and hasattr(wl, "prepacked_step"):
-            psec, _, _ = best_of(torch, wl.prepacked_step, steps, args.warmup, None)
-            rec["with_prepacked_weight_scales"] = {"value": work / (psec / steps) / 1e12, "unit": wl.unit,
-                                                   "ms_per_step": psec / steps * 1e3}
+        if world == 1 and hasattr(wl, "raw_scales_step"):
+            psec, _, _ = best_of(torch, wl.raw_scales_step, steps, args.warmup, None)
+            rec["weight_scales"] = "packed once at load time (ascq_group_matmul_mxfp4_pack_scale_b)"
+            rec["with_weight_scales_repacked_every_step"] = {"value": work / (psec / steps) / 1e12, "unit": wl.unit,
+                                                             "ms_per_step": psec / steps * 1e3}
         if rank == 0 or (sharded and world > 1):
             from oracle import oracle as O
             try:
@@ -855,6 +884,9 @@ def run_ours(args):
             head = (wl, rec)
         del wl
         torch.cuda.empty_cache()
+    published = None
+    if world == 1 and args.workload == "all":
+        published = run_published_shapes(torch, ops, dev, steps, args.warmup)
     clocks = sampler.stop() if sampler else None
     if rank == 0:
         wl, rec = head
@@ -874,9 +906,90 @@ def run_ours(args):
             line["ms_per_step_x_sm_mhz"] = rec["ms_per_step"] * clocks["sm_mhz"]
         if "cpu_baseline" in rec:
             line["cpu_baseline"] = rec["cpu_baseline"]
+        if published is not None:
+            line["published_shapes"] = published
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def measured_tensor_ceiling(torch, ops, dtype_code, k_blocks=2048, reps=10):
+    """T(FL)OPS of the MMA-only kernel (operands in shared memory, no copies, no epilogue): the measured ceiling of the
+    matmul with that operand type on this GPU, at the clock a burst of that length runs at.  Best of `reps`."""
+    best = 0.0
+    for _ in range(3):
+        ops.MeasureTensorRate(dtype_code, k_blocks)
+    torch.cuda.synchronize()
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        n = ops.MeasureTensorRate(dtype_code, k_blocks)
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, n / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
+def run_published_shapes(torch, ops, dev, steps, warmup):
+    """The two shapes the reference publishes a timing for (on Ascend 950PR, in its sample READMEs), timed here the same
+    way as the benchmark configurations; and config 1 at its own size (3 MiB: a latency, not a bandwidth)."""
+    out = {}
+    # grouped W8A8 + per-channel x per-token dequant + FasterGelu -> fp16, G = 8, M = N = 8192, K = 1024
+    G, M, N, K = 8, 8192, 8192, 1024
+    groups = [M // G] * G
+    ns = 2
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    A = [torch.randint(-10, 10, (M, K), dtype=torch.int8, device=dev, generator=gen) for _ in range(ns)]
+    B = [torch.randint(-10, 10, (G, N, K), dtype=torch.int8, device=dev, generator=gen) for _ in range(ns)]
+    sA = torch.randn(M, device=dev, generator=gen) * 0.01
+    sB = torch.randn((G, N), device=dev, generator=gen) * 0.01
+    C = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(ns)]
+    for act, nm in ((1, "quant_group_matmul G=8 M=N=8192 K=1024, dequant + FasterGelu -> fp16"),
+                    (0, "the same without the activation")):
+        sec, stats, how = best_of(torch, lambda i: ops.GroupMatmulW8A8(C[i % ns], A[i % ns], B[i % ns], sA, sB, groups, None, act),
+                                  steps, warmup, None)
+        us = sec / steps * 1e6
+        out[nm] = {"us": round(us, 1), "TOPS": round(2.0 * M * N * K / us / 1e6, 1), "launch": how,
+                   "reference_published": {"us": 204.129, "TOPS": 673, "hardware": "Ascend 950PR, 32 cores",
+                                           "source": "quant_group_matmul_high_performance/README_en.md:394-396"} if act else None}
+    r = slice(0, 64)   # parity of the timed call: 64 rows of group 0 against an exact fp32 product
+    acc = A[0][r].float() @ B[0][0].float().T
+    want = ((acc * sB[0][None, :]) * sA[r][:, None]).half()
+    ops.GroupMatmulW8A8(C[0], A[0], B[0], sA, sB, groups, None, 0)
+    torch.cuda.synchronize()
+    out["quant_group_matmul parity (no activation, 64 rows, bit-exact)"] = bool(torch.equal(C[0][r], want))
+    del A, B, C
+    torch.cuda.empty_cache()
+    # MX-FP4 matmul 8192^3 -> bf16 (one group)
+    M = N = K = 8192
+    A4 = [torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev, generator=gen) for _ in range(ns)]
+    B4 = [torch.randint(0, 256, (1, N, K // 2), dtype=torch.uint8, device=dev, generator=gen) for _ in range(ns)]
+    sA4 = [torch.randint(123, 132, (M, K // 32), dtype=torch.uint8, device=dev, generator=gen) for _ in range(ns)]
+    sB4 = [torch.randint(123, 132, (1, N, K // 32), dtype=torch.uint8, device=dev, generator=gen) for _ in range(ns)]
+    C4 = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(ns)]
+    ws = torch.empty(max(256, ops.GroupMatmulMxfp4Workspace(M, 1, K, N)), dtype=torch.uint8, device=dev)
+    sec, stats, how = best_of(torch, lambda i: ops.GroupMatmulMxfp4(C4[i % ns], A4[i % ns], sA4[i % ns], B4[i % ns], sB4[i % ns], [M], K, N,
+                                                                   workspace=ws), steps, warmup, None)
+    us = sec / steps * 1e6
+    out["matmul_mxfp4 M=N=K=8192 -> bf16"] = {"us": round(us, 1), "TFLOPS": round(2.0 * M * N * K / us / 1e6, 1), "launch": how,
+                                             "reference_published": {"us": [693.283, 681.056], "TFLOPS": [1586, 1614],
+                                                                     "hardware": "Ascend 950PR, 32 cores",
+                                                                     "source": "matmul_mxfp4_high_performance/README_en.md:176-177, "
+                                                                               "matmul_mxfp4_basic_api_high_performance/README_en.md:405-407"}}
+    del A4, B4, C4, sA4, sB4
+    torch.cuda.empty_cache()
+    # config 1 at its own size: fp16 [256, 4096] -> int8, 3 MiB in all
+    rows, cols = 256, 4096
+    h = gen_quant_cfg1(rows, cols)
+    ns1 = 96   # 96 x 3 MiB = 288 MiB of distinct buffers: every call reads DRAM
+    x = [torch.from_numpy(h["x"]).to(dev) for _ in range(ns1)]
+    y = [torch.empty((rows, cols), dtype=torch.int8, device=dev) for _ in range(ns1)]
+    sec, stats, how = best_of(torch, lambda i: ops.AscendQuant(y[i % ns1], x[i % ns1], 64.0, 0.0, rows * cols), max(steps, 96), warmup, None)
+    us = sec / max(steps, 96) * 1e6
+    out["AscendQuant per-tensor fp16 [256, 4096] -> int8 (config 1 at its own size)"] = {
+        "latency_us": round(us, 2), "GB/s": round(rows * cols * 3 / us / 1e3, 1), "launch": how,
+        "note": "3 MiB per call: launch- and latency-bound; the DRAM-sized run of the same operator is quant_scaled"}
+    return out
 
 
 def run_extras(args):

@@ -252,6 +252,27 @@ ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int8_t* B_nk, 
                              int32_t* accDump, void* stream);
 
 /*
+ * Grouped W8A8 matmul with per-group channel scales and per-token scales: the reference's fused sample
+ * examples/01_simd_cpp_api/05_best_practices/03_fusion_compute/quant_group_matmul_high_performance
+ * (quant_group_matmul_custom.asc:257-289 group loop, :425-454 vector side; golden scripts/gen_data.py:26-69).
+ *   for each group g with rows [s_g, s_g + groupList[g]):
+ *     acc[r, n] = sum_k A[r, k] * B[g, n, k]                                    (int32, exact)
+ *     f = (float(acc) * sB[g, n]) * sA[r]   (+ float(bias[g, n]))               (separately rounded fp32 operations)
+ *     activation 1:  f = f / (1 + exp(-1.702 f))   (FasterGelu, impl/adv_api/detail/activation/gelu/gelu_impl.h:134-166)
+ *     C[r, n] = half(f) or bfloat16(f)
+ * A int8 [sumM, K]; B int8 [G, N, K] K-major (the sample's [G, K, N] weight is turned once per group with
+ * ascq_transpose_i8_kn_to_nk); sA fp32 [sumM] or NULL; sB fp32 [G, N] or NULL; bias bf16 [G, N] or NULL (this library's
+ * addition, as in ascq_matmul_w8a8); groupList int64 [G] on the HOST = rows per group, zero-row groups are skipped;
+ * C [sumM, N] of cT = ASCQ_DT_F16 (the sample's type) or ASCQ_DT_BF16.  K % 16 == 0, G <= 128.
+ * Without the activation the result is bit-exact; the exponential of FasterGelu is the CUDA library's expf (the
+ * reference's Exp instruction is not pinned by anything in its tree), so results can differ from a correctly rounded
+ * evaluation by one step of the output type.
+ */
+ascq_status ascq_group_matmul_w8a8(void* C, ascq_dtype cT, const int8_t* A, const int8_t* B_gnk, const float* sA_m,
+                                   const float* sB_gn, const void* bias_bf16_gn, const int64_t* groupList_host,
+                                   int G, int N, int K, int activation, void* stream);
+
+/*
  * MX-FP4 grouped matmul (MatmulWithScalePolicy, impl/adv_api/detail/matmul/mx_matmul_impl.h:29-181;
  * grouping examples/.../quant_group_matmul_custom.asc:257-289):
  *   for each group g with rows [s_g, s_g + groupList[g]):
@@ -504,6 +525,15 @@ ascq_status ascq_group_matmul_mxfp4_sharded(ascq_comm* comm, void* const* C_bufs
  * SM cycles, on the current device; the default is about two seconds, cycles <= 0 restores it.  No reference counterpart.
  */
 ascq_status ascq_set_wait_limit_cycles(long long cycles);
+/*
+ * Measured ceiling of the tensor-core matmuls, no reference counterpart: enqueues a kernel that issues nothing but the
+ * matmul kernels' own MMA instructions (tcgen05.mma.cta_group::2 on 256 x 256 tiles, kind::i8 for ASCQ_DT_I8, kind::mxf4
+ * with unit block scales for ASCQ_DT_FP4X2_E2M1), `kBlocks` k-blocks of four instructions per SM pair, operands resident
+ * in shared memory.  *opsPerLaunch receives the operation count (2 x multiply-accumulates); the caller times the launch
+ * (CUDA events) and divides.  What the result leaves out is everything a real matmul adds: copies, barriers, epilogue.
+ */
+ascq_status ascq_measure_tensor_rate(ascq_dtype operandT, int kBlocks, double* opsPerLaunch, void* stream);
+
 /*
  * Test hook, no reference counterpart: the copy-engine producers of the NEXT int8 / half matmul launch of this process
  * stop after `kBlocks` k-blocks (< 0 cancels).  The kernel's other roles then run into their wait limit, leave through

@@ -682,6 +682,54 @@ int ascq_oracle_matmul_w8a8(uint16_t* C, const int8_t* A, const int8_t* B, const
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Grouped W8A8 matmul with per-group channel scales, per-token scales and an optional FasterGelu:
+ * examples/01_simd_cpp_api/05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/
+ * quant_group_matmul_custom.asc:257-289 (group loop: groupList = rows per group, zero-row groups skipped),
+ * :425-454 (vector side: AscendDequant x scale[g][n] -> Mul x perTokenScale[m] -> FasterGelu -> Cast to half).
+ *   acc = sum_k A[m,k] * B[g,n,k]  (int32, exact);   f = (float(acc) * sB[g,n]) * sA[m]  (+ float(bias[g,n]));
+ *   act: f = f / (1 + exp(-1.702 f))  -- impl/adv_api/detail/activation/gelu/gelu_impl.h:134-166, each step one fp32
+ *        operation, the exponential correctly rounded here (the hardware's Exp is not pinned by anything in the tree);
+ *   C = half(f) or bf16(f), round to nearest even.
+ * A [sumM,K], B [G,N,K] (K-major), sA [sumM], sB [G,N], bias bf16 bits [G,N] or NULL (this library's addition).
+ * outKind: 0 = half, 1 = bfloat16.
+ * ---------------------------------------------------------------------------------------- */
+int ascq_oracle_group_matmul_w8a8(uint16_t* C, const int8_t* A, const int8_t* B, const float* sA, const float* sB,
+                                  const uint16_t* bias, const int64_t* groupList, int G, int N, int K, int outKind,
+                                  int act, int32_t* accDump)
+{
+    if (!C || !A || !B || !groupList || G < 0 || N < 0 || K < 0) return OR_INVALID;
+    int64_t start = 0;
+    for (int g = 0; g < G; ++g) {
+        const int64_t mg = groupList[g];
+        if (mg < 0) return OR_INVALID;
+#pragma omp parallel for schedule(dynamic, 8)
+        for (int64_t r = 0; r < mg; ++r) {
+            const int64_t m = start + r;
+            const int8_t* a = A + (size_t)m * K;
+            for (int n = 0; n < N; ++n) {
+                const int8_t* b = B + ((size_t)g * N + n) * K;
+                int32_t acc = 0;
+                for (int k = 0; k < K; ++k) acc += (int32_t)a[k] * (int32_t)b[k];
+                if (accDump) accDump[(size_t)m * N + n] = acc;
+                float f = orc_i32_to_f32(acc);
+                if (sB) f = f * sB[(size_t)g * N + n];
+                if (sA) f = f * sA[m];
+                if (bias) f = f + orc_bf16_to_f32(bias[(size_t)g * N + n]);
+                if (act) {
+                    const float t = f * -1.702f;
+                    const float e = (float)exp((double)t);
+                    const float d = e + 1.0f;
+                    f = f / d;
+                }
+                C[(size_t)m * N + n] = outKind == 1 ? orc_f32_to_bf16_sat(f) : orc_f32_to_f16_sat(f);
+            }
+        }
+        start += mg;
+    }
+    return OR_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
  * int8 matmul leaving through the fixpipe quantisation (Matmul::SetQuantScalar / SetQuantVector, mode DEQF16:
  * impl/adv_api/detail/matmul/stage/copy_cube_out/quant/quant_processor_fixpipe.h:80-119), with the arithmetic of
  * the sample's golden, examples/01_simd_cpp_api/04_advanced_api/00_matmul/matmul_quant/scripts/gen_data.py:26-44:

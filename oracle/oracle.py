@@ -221,6 +221,20 @@ def matmul_w8a8(A, B_nk, sA=None, sB=None, bias_bf16=None, want_acc=False, ldc=N
     return (Cb, acc) if want_acc else Cb
 
 
+def group_matmul_w8a8(A, B_gnk, sA, sB_gn, groupList, bias_bf16=None, out=F16, act=False, want_acc=False):
+    """Grouped W8A8 matmul with per-group channel scales and per-token scales (quant_group_matmul_custom.asc);
+    returns [sumM, N] float16, or bf16 bit patterns (uint16) with ``out=BF16``."""
+    sumM, K = A.shape
+    G, N = B_gnk.shape[0], B_gnk.shape[1]
+    gl = np.ascontiguousarray(groupList, np.int64)
+    Cq = np.zeros((sumM, N), np.uint16)
+    acc = np.zeros((sumM, N), np.int32) if want_acc else None
+    _check(lib().ascq_oracle_group_matmul_w8a8(_p(Cq), _p(A), _p(B_gnk), _p(sA), _p(sB_gn), _p(bias_bf16), _p(gl), G, N, K,
+                                               1 if out == BF16 else 0, 1 if act else 0, _p(acc)))
+    res = Cq if out == BF16 else Cq.view(np.float16)
+    return (res, acc) if want_acc else res
+
+
 def matmul_i8_quant(A, B_nk, bias=None, quantVector=None, quantScalar=1.0):
     """int8 matmul + int32 bias, result quantised as the fixpipe does (fp16); returns [M, N] float16."""
     M, K = A.shape

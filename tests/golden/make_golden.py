@@ -141,13 +141,53 @@ def fixpipe_qf322b8(reference):
     print("fixpipe_qf322b8_values", n)
 
 
+QGMM = "examples/01_simd_cpp_api/05_best_practices/03_fusion_compute/quant_group_matmul_high_performance/scripts/gen_data.py"
+
+
+def quant_group_matmul(reference, only=None):
+    """The grouped W8A8 sample (G = 8, M = N = 8192, K = 1024, FastGelu, fp16 out): its generator runs unmodified with
+    numpy's global seed fixed; the fixture keeps 16 rows of every group and the first 128 columns (an output element
+    depends on its own row of x, its own column of its group's weight and the two scales only).  The weight file is
+    written in the NZ layout [G, N/32, K/16, 16, 32]; it is brought back to [G, K, N] here."""
+    path = os.path.join(reference, QGMM)
+    G, M, K, N, rows_kept, cols_kept = 8, 8192, 1024, 8192, 16, 128
+    with tempfile.TemporaryDirectory() as tmp:
+        cwd = os.getcwd()
+        os.chdir(tmp)
+        try:
+            np.random.seed(111)
+            runpy.run_path(path, run_name="__main__")
+            x = np.fromfile("input/x.bin", np.int8).reshape(M, K)
+            w_nz = np.fromfile("input/weight.bin", np.int8).reshape(G, N // 32, K // 16, 16, 32)
+            w = w_nz.transpose(0, 2, 3, 1, 4).reshape(G, K, N)
+            groups = np.fromfile("input/groupList.bin", np.int64)
+            scale = np.fromfile("input/scale.bin", np.float32).reshape(G, N)
+            tok = np.fromfile("input/perTokenScale.bin", np.float32).reshape(M)
+            golden = np.fromfile("output/golden.bin", np.float16).reshape(M, N)
+        finally:
+            os.chdir(cwd)
+    starts = np.concatenate([[0], np.cumsum(groups)])
+    rows = np.concatenate([np.arange(starts[g], starts[g] + rows_kept) for g in range(G)])
+    out = {"x": np.ascontiguousarray(x[rows]), "weight_gkn": np.ascontiguousarray(w[:, :, :cols_kept]),
+           "groupList": np.full(G, rows_kept, np.int64), "scale": np.ascontiguousarray(scale[:, :cols_kept]),
+           "perTokenScale": np.ascontiguousarray(tok[rows]), "golden": np.ascontiguousarray(golden[rows][:, :cols_kept])}
+    np.savez_compressed(os.path.join(HERE, "quant_group_matmul.npz"), **out)
+    print("quant_group_matmul", {k: v.shape for k, v in out.items()})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("ASC_DEVKIT_ROOT"), help="root of the asc-devkit tree (or set ASC_DEVKIT_ROOT)")
+    ap.add_argument("--only", default=None, help="regenerate one fixture only (its name)")
     args = ap.parse_args()
     if not args.reference:
         ap.error("give --reference /path/to/asc-devkit or set ASC_DEVKIT_ROOT")
+    if args.only == "quant_group_matmul":
+        quant_group_matmul(args.reference)
+        return
     for name, script, argv, seed, files in CASES:
+        if args.only and args.only != name:
+            continue
         path = os.path.join(args.reference, script)
         with tempfile.TemporaryDirectory() as tmp:
             cwd, old_argv = os.getcwd(), sys.argv
@@ -169,8 +209,11 @@ def main():
             out["golden"] = out["golden"][:KEEP_ROWS].copy()
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
         print(name, {k: v.shape for k, v in out.items()})
+    if args.only:
+        return
     fixpipe_req8(args.reference)
     fixpipe_qf322b8(args.reference)
+    quant_group_matmul(args.reference)
 
 
 if __name__ == "__main__":

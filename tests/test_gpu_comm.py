@@ -15,7 +15,7 @@ import torch
 from asc_devkit_b200 import _lib as L, ops
 from oracle import oracle as O
 from tests.gpu_util import DEV, assert_bits_equal
-from tests.test_gpu_matmul_mxfp4 import check_close, make_case as make_mx_case
+from tests.test_gpu_matmul_mxfp4 import abs_product_sums, check_close, make_case as make_mx_case
 from tests.test_gpu_matmul_w8a8 import make_case
 
 pytestmark = pytest.mark.gpu
@@ -127,7 +127,7 @@ def test_mxfp4_ranks_one_after_the_other_assemble_every_matrix():
         comm.destroy()
     ops.MatmulStatus()
     first = outs[0].view(torch.int16).cpu().numpy().view(np.uint16)
-    check_close(first, want, "assembled matrix")
+    check_close(first, want, "assembled matrix", abs_product_sums(A, sA, B, sB, groups, K), K)
     for o in outs[1:]:
         assert torch.equal(o, outs[0])
     assert (words(mem)[:, EPOCH_WORD] == 1).all()

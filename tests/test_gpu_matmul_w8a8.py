@@ -1,5 +1,7 @@
 """GPU parity of the W8A8 matmul: int32 accumulators bit-exact, bf16 epilogue bit-exact (same fp32 operation
 order as the oracle), against the CPU oracle and, at full size, against an exact integer reference on the GPU."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -9,6 +11,7 @@ from oracle import oracle as O
 from tests.gpu_util import DEV, assert_bits_equal
 
 pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
 def make_case(M, N, K, seed):
@@ -277,3 +280,101 @@ def test_block_into_one_wider_matrix_through_the_tma_store_path(monkeypatch):
             f"elements outside the block changed ({mode})"
         outs[mode] = got
     assert np.array_equal(outs["tma"], outs["plain"])
+
+
+# ---- grouped W8A8 (per-group weights and channel scales, per-token scales, optional FasterGelu) --------------------
+def make_group_case(groups, N, K, seed):
+    rng = np.random.default_rng(seed)
+    sumM, G = int(sum(groups)), len(groups)
+    A = rng.integers(-10, 10, (sumM, K)).astype(np.int8)
+    B = rng.integers(-10, 10, (G, N, K)).astype(np.int8)
+    sA = rng.normal(0, 0.01, sumM).astype(np.float32)
+    sB = rng.normal(0, 0.01, (G, N)).astype(np.float32)
+    return A, B, sA, sB
+
+
+def run_group(A, B, sA, sB, groups, out=torch.float16, act=0, bias=None):
+    t = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(DEV)  # noqa: E731
+    C = torch.full((max(int(sum(groups)), 1), B.shape[1]), -1.0, dtype=out, device=DEV)
+    dbias = None if bias is None else torch.from_numpy(bias.view(np.int16).copy()).to(DEV).view(torch.bfloat16)
+    ops.GroupMatmulW8A8(C, t(A), t(B), t(sA), t(sB), groups, dbias, act)
+    ops.MatmulStatus()
+    return C[:int(sum(groups))].view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("groups,N,K", [([128, 256], 256, 128), ([100, 0, 300, 129, 1], 384, 272), ([1, 1, 1], 8, 16),
+                                        ([700, 52], 520, 1024), ([257] * 5, 640, 64)])
+@pytest.mark.parametrize("tile", ["narrow", "wide", "pair"])
+@pytest.mark.parametrize("out", [torch.float16, torch.bfloat16])
+def test_group_matmul_is_bit_exact_without_activation(groups, N, K, tile, out, monkeypatch):
+    monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
+    A, B, sA, sB = make_group_case(groups, N, K, sum(groups) + N + K)
+    bias = O.f32_to_bf16_bits(np.random.default_rng(1).normal(0, 0.1, (len(groups), N)).astype(np.float32)) if K == 272 else None
+    want = O.group_matmul_w8a8(A, B, sA, sB, groups, bias_bf16=bias, out=O.F16 if out == torch.float16 else O.BF16)
+    got = run_group(A, B, sA, sB, groups, out, 0, bias)
+    assert_bits_equal(got, want.view(np.uint16), f"groups {groups} {tile}")
+
+
+@pytest.mark.parametrize("tile", ["narrow", "pair"])
+def test_group_matmul_with_faster_gelu(tile, monkeypatch):
+    """The exponential is the CUDA library's, the oracle's is correctly rounded: at most one half-precision step apart,
+    on a small fraction of the elements."""
+    monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
+    groups, N, K = [300, 0, 129, 64], 512, 512
+    A, B, sA, sB = make_group_case(groups, N, K, 5)
+    sA, sB = sA * 30, sB * 30          # arguments of the activation of order one
+    want = O.group_matmul_w8a8(A, B, sA, sB, groups, act=True)
+    got = run_group(A, B, sA, sB, groups, torch.float16, 1)
+    steps = np.abs(got.view(np.int16).astype(np.int32) - want.view(np.int16).astype(np.int32))
+    assert steps.max() <= 1 and (steps != 0).mean() < 0.01, (steps.max(), (steps != 0).mean())
+
+
+def test_group_matmul_reference_sample_golden_through_the_gpu():
+    """The sample's own vectors (its gen_data.py; 16 rows of each of the 8 groups, 128 columns): within one half-precision
+    step of the golden and inside the sample's acceptance rule (rtol = atol = 1e-3, at most 1e-4 of the elements outside)."""
+    d = np.load(os.path.join(GOLDEN, "quant_group_matmul.npz"))
+    G, K, N = d["weight_gkn"].shape
+    Bnk = torch.empty((G, N, K), dtype=torch.int8, device=DEV)
+    for g in range(G):   # the sample's weight is [K, N] per group: turned once
+        ops.TransposeI8KnToNk(Bnk[g], torch.from_numpy(np.ascontiguousarray(d["weight_gkn"][g])).to(DEV))
+    groups = [int(v) for v in d["groupList"]]
+    C = torch.empty((sum(groups), N), dtype=torch.float16, device=DEV)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)  # noqa: E731
+    ops.GroupMatmulW8A8(C, t(d["x"]), Bnk, t(d["perTokenScale"]), t(d["scale"]), groups, None, 1)
+    ops.MatmulStatus()
+    got, gold = C.cpu().numpy(), d["golden"]
+    outside = ~np.isclose(got.astype(np.float32), gold.astype(np.float32), rtol=1e-3, atol=1e-3)
+    assert outside.mean() <= 1e-4
+    steps = np.abs(got.view(np.int16).astype(np.int32) - gold.view(np.int16).astype(np.int32))
+    assert steps.max() <= 1 and (steps != 0).mean() < 2e-3
+
+
+def test_group_matmul_published_shape_property():
+    """G = 8, M = N = 8192, K = 1024 (the shape of the reference's published timing): int32-exact inputs, compared with
+    an fp32 torch matmul per group (every sum < 2^24, so that product is exact) -- all 67 M elements, bit for bit."""
+    G, M, N, K = 8, 8192, 8192, 1024
+    groups = [M // G] * G
+    g = torch.Generator(device=DEV).manual_seed(3)
+    A = torch.randint(-10, 10, (M, K), dtype=torch.int8, device=DEV, generator=g)
+    B = torch.randint(-10, 10, (G, N, K), dtype=torch.int8, device=DEV, generator=g)
+    sA = torch.randn(M, device=DEV, generator=g) * 0.01
+    sB = torch.randn((G, N), device=DEV, generator=g) * 0.01
+    C = torch.empty((M, N), dtype=torch.float16, device=DEV)
+    ops.GroupMatmulW8A8(C, A, B, sA, sB, groups)
+    ops.MatmulStatus()
+    for i in range(G):
+        r = slice(i * (M // G), (i + 1) * (M // G))
+        acc = A[r].float() @ B[i].float().T
+        want = ((acc * sB[i][None, :]) * sA[r][:, None]).half()
+        assert torch.equal(C[r], want), f"group {i}"
+
+
+def test_group_matmul_argument_checks():
+    z = torch.zeros((256, 64), dtype=torch.int8, device=DEV)
+    c = torch.zeros((256, 64), dtype=torch.float16, device=DEV)
+    with pytest.raises(ops.AscqError):
+        ops.GroupMatmulW8A8(c, z, z.view(1, 256, 64), None, None, [-1])
+    with pytest.raises(ops.AscqError):
+        ops.GroupMatmulW8A8(c, z, z.view(1, 256, 64), None, None, [1] * 129)
+    with pytest.raises(ops.AscqError):
+        ops.GroupMatmulW8A8(c.float(), z, z.view(1, 256, 64), None, None, [256])

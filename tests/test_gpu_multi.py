@@ -1,6 +1,7 @@
-"""Two real GPUs, two processes: the sharded W8A8 matmul over CUDA IPC (the route of a C / C++ host).  Skipped on a
-box with one GPU; the single-GPU emulation of the same protocol is tests/test_gpu_comm.py, the host-side partition is
-covered by the gloo test."""
+"""Two real GPUs, one process per GPU: the sharded W8A8 matmul over CUDA IPC, from Python (tests/multi_gpu_ipc_worker.py)
+and from a plain C++ host that sees nothing but include/ascq.h (tests/cpp/sharded_main.cpp).  The GPU tests are skipped
+on a box with one GPU; the single-GPU emulation of the same protocol is tests/test_gpu_comm.py, the host-side partition
+is covered by the gloo test.  The C++ program is compiled in the CPU suite too, so the header stays consistent."""
 import os
 import subprocess
 import sys
@@ -9,23 +10,52 @@ import tempfile
 import pytest
 import torch
 
-pytestmark = pytest.mark.gpu
+from asc_devkit_b200 import _lib as L
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+two_gpus = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_processes_over_cuda_ipc():
-    world = 2
+def run_ranks(argv_of_rank, world):
+    procs = [subprocess.Popen(argv_of_rank(r), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()          # this exact child
+            o, _ = p.communicate()
+        outs.append(o)
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed (exit code {p.returncode}):\n{o[-2000:]}"
+
+
+@pytest.fixture(scope="module")
+def sharded_exe(tmp_path_factory):
+    out = tmp_path_factory.mktemp("sharded") / "sharded_main"
+    libdir = os.path.dirname(L.LIB_PATH)
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA_HOME, "include"),
+           os.path.join(ROOT, "tests", "cpp", "sharded_main.cpp"), "-o", str(out), "-L", libdir, "-lascq",
+           "-L", os.path.join(CUDA_HOME, "lib64"), "-lcudart", "-lpthread", f"-Wl,-rpath,{libdir}", f"-Wl,-rpath,{CUDA_HOME}/lib64"]
+    subprocess.run(cmd, check=True)
+    return str(out)
+
+
+def test_cpp_host_compiles_against_the_header(sharded_exe):
+    """No GPU needed: wrong arguments end with the usage exit code before any CUDA call."""
+    assert subprocess.run([sharded_exe]).returncode == 64
+
+
+@pytest.mark.gpu
+@two_gpus
+def test_two_python_processes_over_cuda_ipc():
     with tempfile.TemporaryDirectory() as d:
-        procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multi_gpu_ipc_worker.py"), str(r), str(world), d],
-                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
-        outs = []
-        for p in procs:
-            try:
-                o, _ = p.communicate(timeout=240)
-            except subprocess.TimeoutExpired:
-                p.kill()          # this exact child
-                o, _ = p.communicate()
-            outs.append(o)
-        for r, (p, o) in enumerate(zip(procs, outs)):
-            assert p.returncode == 0, f"rank {r} failed:\n{o[-2000:]}"
+        run_ranks(lambda r: [sys.executable, os.path.join(ROOT, "tests", "multi_gpu_ipc_worker.py"), str(r), "2", d], 2)
+
+
+@pytest.mark.gpu
+@two_gpus
+def test_two_cpp_processes_over_cuda_ipc(sharded_exe):
+    with tempfile.TemporaryDirectory() as d:
+        run_ranks(lambda r: [sharded_exe, str(r), "2", d], 2)

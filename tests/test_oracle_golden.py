@@ -387,3 +387,30 @@ def test_mxfp4_matches_reference_golden_formula():
     pack = lambda c: (c[:, 0::2] | (c[:, 1::2] << 4)).astype(np.uint8)  # noqa: E731  element 2i in the low nibble
     out = O.group_matmul_mxfp4(pack(a_codes), sA, pack(b_codes)[None], sB[None], np.array([M], np.int64), K, N)
     assert np.array_equal(out, golden.view(np.uint16))
+
+
+def test_group_matmul_w8a8_vs_reference_sample_golden(golden_dir):
+    """The grouped W8A8 sample's own golden (quant_group_matmul_high_performance/scripts/gen_data.py run unmodified; 16
+    rows of each of the 8 groups, 128 columns kept).  The sample multiplies the two scales with each other first and
+    uses the overflow-safe form of FastGelu, the operator multiplies one after the other (quant_group_matmul_custom.asc:
+    433-441) and divides by 1 + exp(-1.702 x): the results agree within one half-precision step, and far inside the
+    sample's own acceptance rule (rtol = atol = 1e-3, at most 1e-4 of the elements outside: scripts/verify_result.py)."""
+    d = np.load(os.path.join(golden_dir, "quant_group_matmul.npz"))
+    B = np.ascontiguousarray(d["weight_gkn"].transpose(0, 2, 1))      # [G, K, N] as the sample draws it -> [G, N, K]
+    got, acc = O.group_matmul_w8a8(d["x"], B, d["perTokenScale"], d["scale"], d["groupList"], act=True, want_acc=True)
+    gold = d["golden"]
+    starts = np.concatenate([[0], np.cumsum(d["groupList"])])
+    for g in range(len(d["groupList"])):   # int32 accumulators: exact
+        r = slice(int(starts[g]), int(starts[g + 1]))
+        assert np.array_equal(acc[r], d["x"][r].astype(np.int32) @ d["weight_gkn"][g].astype(np.int32))
+    outside = ~np.isclose(got.astype(np.float32), gold.astype(np.float32), rtol=1e-3, atol=1e-3)
+    assert outside.mean() <= 1e-4
+    steps = np.abs(got.view(np.int16).astype(np.int32) - gold.view(np.int16).astype(np.int32))
+    assert steps.max() <= 1 and (steps != 0).mean() < 1e-3
+    # without the activation and with the scales multiplied in the operator's order the result is exact
+    plain = O.group_matmul_w8a8(d["x"], B, d["perTokenScale"], d["scale"], d["groupList"], act=False)
+    want = np.empty_like(plain)
+    for g in range(len(d["groupList"])):
+        r = slice(int(starts[g]), int(starts[g + 1]))
+        want[r] = ((acc[r].astype(np.float32) * d["scale"][g][None, :]) * d["perTokenScale"][r][:, None]).astype(np.float16)
+    assert np.array_equal(plain.view(np.uint16), want.view(np.uint16))
