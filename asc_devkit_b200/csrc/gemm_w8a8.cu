@@ -117,8 +117,12 @@ __device__ __forceinline__ void trace_stamp(const Params& p, int slot)
     }
 }
 #define ASCQ_STAMP(p, slot) trace_stamp(p, slot)
+// slots 8..11 (first item of the CTA, first 64-column chunk of warp 2), SM cycles since the accumulator was ready:
+// 8 tensor-memory loads done, 9 arithmetic done, 10 staged and handed to the copy engine, 11 end of the item's epilogue
+#define ASCQ_CYCLES(p, slot, t0) do { if ((p).trace != nullptr) (p).trace[blockIdx.x * 16 + (slot)] = static_cast<unsigned long long>(clock64() - (t0)); } while (0)
 #else
 #define ASCQ_STAMP(p, slot) ((void)0)
+#define ASCQ_CYCLES(p, slot, t0) ((void)0)
 #endif
 
 // Grouped launch (ascq_group_matmul_w8a8): rows of A per group; row tiles never straddle two groups.  G == 0: plain matmul.
@@ -521,8 +525,10 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     ok = false;
                     break;
                 }
-                if (threadIdx.x == 64 && local < 5) ASCQ_STAMP(p, 1 + 2 * static_cast<int>(local));
+                if (threadIdx.x == 64 && local < 4) ASCQ_STAMP(p, 1 + 2 * static_cast<int>(local));
             }
+            [[maybe_unused]] const long long tAcc = clock64();
+            [[maybe_unused]] const bool stamp = threadIdx.x == 64 && local == 0;
             const bool hasBias = p.bias != nullptr;
             // A row tile of a grouped launch that ends inside its 128 rows must not touch the next group's rows, which a
             // 16-row box would: such tiles take the per-thread stores.  They stage through the same bytes, so the TMA
@@ -657,6 +663,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 tmem_ld_32x32b_x32(taddr + c2 * 64, r0);
                 tmem_ld_32x32b_x32(taddr + c2 * 64 + 32, r1);
                 tmem_ld_wait();
+                if (stamp && c2 == sub) ASCQ_CYCLES(p, 8, tAcc);
                 const int n = n0 + c2 * 64;
                 if (n >= p.N) continue;  // uniform over the warp
                 if (p.accDump != nullptr && m < rowEnd) {
@@ -720,6 +727,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                 uint32_t packed[32];
                 convert32(r0, c2 * 64, packed);
                 convert32(r1, c2 * 64 + 32, packed + 16);
+                if (stamp && c2 == sub) ASCQ_CYCLES(p, 9, tAcc);
                 if (tileTma) {
                     // Sixteen rows at a time go into this warp's swizzled staging rows (16-byte piece v of row r at
                     // v ^ (r & 7), which also keeps the writes free of bank conflicts) and leave as one TMA store; rows
@@ -748,6 +756,7 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                             bulk_commit_group();
                         }
                     }
+                    if (stamp && c2 == sub) ASCQ_CYCLES(p, 10, tAcc);
                 } else if (vecStore && n + 64 <= p.N) {
                     // Transpose through this warp's staging rows, sixteen rows at a time, so that every store instruction
                     // writes four complete 128-byte row segments (instead of thirty-two 16-byte pieces): the output leaves
@@ -787,7 +796,8 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     store_direct(packed + 16, n + 32);
                 }
             }
-            if (threadIdx.x == 64 && local < 5) ASCQ_STAMP(p, 2 + 2 * static_cast<int>(local));
+            if (threadIdx.x == 64 && local < 4) ASCQ_STAMP(p, 2 + 2 * static_cast<int>(local));
+            if (stamp) ASCQ_CYCLES(p, 11, tAcc);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {

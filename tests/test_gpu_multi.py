@@ -59,3 +59,24 @@ def test_two_python_processes_over_cuda_ipc():
 def test_two_cpp_processes_over_cuda_ipc(sharded_exe):
     with tempfile.TemporaryDirectory() as d:
         run_ranks(lambda r: [sharded_exe, str(r), "2", d], 2)
+
+
+@pytest.mark.gpu
+@two_gpus
+def test_peer_store_rate_probe(tmp_path, capsys):
+    """The link-rate probe behind the multi-GPU bound: stores of config 4's two-rank block (16.8 MB) into the peer's memory
+    under a dozen access patterns.  The table is printed (run with -s to see it); the check is only that peer stores work
+    and reach a rate of the right order."""
+    import shutil
+    nvcc = shutil.which("nvcc") or os.path.join(CUDA_HOME, "bin", "nvcc")
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc is needed to build the probe")
+    exe = tmp_path / "p2p_store_probe"
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", str(exe),
+                    os.path.join(ROOT, "tests", "cpp", "p2p_store_probe.cu")], check=True, capture_output=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "done" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+    with capsys.disabled():
+        print("\n" + r.stdout)
+    rates = [float(line.split("us/launch")[1].split("GB/s")[0]) for line in r.stdout.splitlines() if "contiguous" in line and "LOCAL" not in line]
+    assert rates and max(rates) > 200.0, rates
