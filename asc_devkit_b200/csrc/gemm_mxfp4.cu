@@ -457,11 +457,24 @@ mxfp4_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                     }
                     continue;
                 }
+                // fp32 -> bfloat16 pairs without a branch per pair (a branch keeps the conversions from overlapping); the
+                // saturation of finite overflow is applied afterwards, only if an infinity came out at all
                 uint32_t packed[32];
+                uint32_t inf = 0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    packed[j] = pack_bf16x2_sat(__uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15)]),
-                                                __uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15) + 1]));
+                for (int j = 0; j < 32; ++j) {
+                    uint32_t w;
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(__uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15) + 1])),
+                        "f"(__uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15)])));
+                    inf |= (w & 0x7FFF7FFFu) + 0x00800080u;   // bit 15 / 31 set: exponent all ones
+                    packed[j] = w;
+                }
+                if (__builtin_expect((inf & 0x80008000u) != 0, 0)) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        packed[j] = pack_bf16x2_sat(__uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15)]),
+                                                    __uint_as_float(r[2 * cp + (j >> 4)][2 * (j & 15) + 1]));
+                }
                 if (p.tmaStore && ti.rowsValid == kBM) {
                     // A whole tile of one aligned matrix: sixteen rows at a time go into the warp's swizzled staging rows
                     // (16-byte piece v of row r at v ^ (r & 7)) and leave as one TMA store; columns past N are clipped

@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
+#include <type_traits>
 #include <cstdlib>
 #include <cstring>
 
@@ -265,6 +266,7 @@ struct OutMaps {
     CUtensorMap m[kMaxPeers];
     CUtensorMap bHalf;  // B with a box of half the rows: what a CTA loads for a half-tile work item (pair shape)
 };
+
 
 template <int BN, bool PAIR, int EPI, bool CONV = false>
 __global__ void __launch_bounds__(Cfg<BN, PAIR, CONV>::kThreadsCta, 1)
@@ -585,29 +587,75 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     }
                     return;
                 }
+                // The dequantisation proper, as straight-line code: which optional steps run (bias, FasterGelu, half or
+                // bfloat16 result) is fixed per launch, so each combination is its own instantiation and the loop body has
+                // no branch -- a branch per packed pair (the saturation test used to be one) keeps the compiler from
+                // overlapping the 32 independent chains and cost two thirds of the arithmetic's time.  Saturation: the
+                // packed words are checked for an infinity AFTER the loop (rare: finite overflow of the 16-bit type) and
+                // only then redone with the saturating conversion.
+                auto dequant = [&](auto biasTag, auto actTag, auto halfTag) {
+                    constexpr bool kBias = decltype(biasTag)::value, kAct = decltype(actTag)::value, kHalf = decltype(halfTag)::value;
+                    uint32_t inf = 0;
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    const float4 s4 = sb4[v];
-                    const float4 b4 = bi4[v];
-                    float f0 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 0])), s4.x), sa);
-                    float f1 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 1])), s4.y), sa);
-                    float f2 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 2])), s4.z), sa);
-                    float f3 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 3])), s4.w), sa);
-                    if (hasBias) {
-                        f0 = __fadd_rn(f0, b4.x); f1 = __fadd_rn(f1, b4.y); f2 = __fadd_rn(f2, b4.z); f3 = __fadd_rn(f3, b4.w);
-                    }
-                    if constexpr (EPI == kEpiDequantAct) {
-                        if (p.act) {
+                    for (int v = 0; v < 8; ++v) {
+                        const float4 s4 = sb4[v];
+                        float f0 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 0])), s4.x), sa);
+                        float f1 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 1])), s4.y), sa);
+                        float f2 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 2])), s4.z), sa);
+                        float f3 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[4 * v + 3])), s4.w), sa);
+                        if constexpr (kBias) {
+                            const float4 b4 = bi4[v];
+                            f0 = __fadd_rn(f0, b4.x); f1 = __fadd_rn(f1, b4.y); f2 = __fadd_rn(f2, b4.z); f3 = __fadd_rn(f3, b4.w);
+                        }
+                        if constexpr (kAct) {
                             f0 = faster_gelu(f0); f1 = faster_gelu(f1); f2 = faster_gelu(f2); f3 = faster_gelu(f3);
                         }
-                        if (p.outKind == 1) {   // half: finite overflow saturates, as the reference's Cast does
-                            packed[2 * v] = pack_f16x2_sat(f0, f1);
-                            packed[2 * v + 1] = pack_f16x2_sat(f2, f3);
-                            continue;
+                        uint32_t w0, w1;
+                        if constexpr (kHalf) {
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w0) : "f"(f1), "f"(f0));
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w1) : "f"(f3), "f"(f2));
+                            inf |= ((w0 & 0x7FFF7FFFu) + 0x04000400u) | ((w1 & 0x7FFF7FFFu) + 0x04000400u);  // bit 15 / 31: exponent all ones
+                        } else {
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w0) : "f"(f1), "f"(f0));
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w1) : "f"(f3), "f"(f2));
+                            inf |= ((w0 & 0x7FFF7FFFu) + 0x00800080u) | ((w1 & 0x7FFF7FFFu) + 0x00800080u);
+                        }
+                        packed[2 * v] = w0;
+                        packed[2 * v + 1] = w1;
+                    }
+                    if (__builtin_expect((inf & 0x80008000u) != 0, 0)) {  // an infinity or NaN came out: redo with saturation
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {  // (unrolled: a run-time index would move the registers to local memory)
+                            float f[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int c = 2 * j + e;
+                                float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(r[c])), sBs[colInTile + c]), sa);
+                                if constexpr (kBias) x = __fadd_rn(x, biasS[colInTile + c]);
+                                if constexpr (kAct) x = faster_gelu(x);
+                                f[e] = x;
+                            }
+                            packed[j] = kHalf ? pack_f16x2_sat(f[0], f[1]) : pack_bf16x2_sat(f[0], f[1]);
                         }
                     }
-                    packed[2 * v] = pack_bf16x2_sat(f0, f1);
-                    packed[2 * v + 1] = pack_bf16x2_sat(f2, f3);
+                };
+                using T = std::true_type;
+                using F = std::false_type;
+                if constexpr (EPI == kEpiDequantAct) {
+                    const int sel = (hasBias ? 4 : 0) | (p.act ? 2 : 0) | (p.outKind == 1 ? 1 : 0);
+                    switch (sel) {
+                        case 0: dequant(F{}, F{}, F{}); break;
+                        case 1: dequant(F{}, F{}, T{}); break;
+                        case 2: dequant(F{}, T{}, F{}); break;
+                        case 3: dequant(F{}, T{}, T{}); break;
+                        case 4: dequant(T{}, F{}, F{}); break;
+                        case 5: dequant(T{}, F{}, T{}); break;
+                        case 6: dequant(T{}, T{}, F{}); break;
+                        default: dequant(T{}, T{}, T{}); break;
+                    }
+                } else {
+                    if (hasBias) dequant(T{}, F{}, F{});
+                    else dequant(F{}, F{}, F{});
                 }
             };
             // (V)REQ8, fixpipe_l0c2gm/scripts/gen_data_s322s8.py:75-97: optional arithmetic shift with saturation to int16,

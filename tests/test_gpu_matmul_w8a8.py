@@ -378,3 +378,24 @@ def test_group_matmul_argument_checks():
         ops.GroupMatmulW8A8(c, z, z.view(1, 256, 64), None, None, [1] * 129)
     with pytest.raises(ops.AscqError):
         ops.GroupMatmulW8A8(c.float(), z, z.view(1, 256, 64), None, None, [256])
+
+
+def test_results_beyond_the_16_bit_range_saturate_like_the_oracle():
+    """Scales large enough that some results overflow bfloat16 / half: the reference's casts saturate finite overflow to
+    the largest finite value; the epilogue detects the rare infinity after its branch-free conversion and redoes the
+    chunk with the saturating one."""
+    M, N, K = 256, 256, 512
+    A, B, sA, sB, bias = make_case(M, N, K, 77)
+    sA = sA.copy()
+    sA[::3] *= np.float32(3e37)          # rows whose results leave the bfloat16 range
+    want = O.matmul_w8a8(A, B, sA, sB, bias)
+    got, _ = run(A, B, sA, sB, bias, want_acc=False)
+    assert_bits_equal(got, want, "bf16 saturation")
+    assert (want == 0x7F7F).any() and (want == 0xFF7F).any(), "the case must saturate somewhere"
+    # half output (grouped entry point, one group)
+    sA2 = np.abs(sA) % np.float32(1.0) + np.float32(0.5)
+    sA2[::5] *= np.float32(1e6)
+    wanth = O.group_matmul_w8a8(A, B[None], sA2, sB[None], [M])
+    goth = run_group(A, B[None], sA2, sB[None], [M])
+    assert_bits_equal(goth, wanth.view(np.uint16), "half saturation")
+    assert (wanth.view(np.uint16) == 0x7BFF).any() or (wanth.view(np.uint16) == 0xFBFF).any()
