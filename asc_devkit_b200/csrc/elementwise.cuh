@@ -14,6 +14,8 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include <type_traits>
 
 #include "ascq_internal.h"
@@ -346,6 +348,12 @@ __global__ void __launch_bounds__(256, EwMinBlocks<OP, CT, SMODE, HAS_OFF>::valu
     constexpr int VEC = VecOf<Src, Dst>::value;
     constexpr bool kVecScale = (SMODE == kSColVec || SMODE == kSRowVec);
     constexpr int SV = kVecScale ? VEC : 1;
+    // Programmatic dependent launch: the next launch on the stream may bring its CTAs onto the SMs while this one's last
+    // rows drain, and this launch's CTAs were scheduled while its predecessor was still running -- nothing below touches
+    // global memory before that predecessor has completed.  For kernels of 9 to 60 us the ramp and the tail of a launch are
+    // a visible share; a stream of these operators (one per layer) then runs back to back.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (c0 >= a.cols) return;
 
@@ -440,6 +448,22 @@ __global__ void __launch_bounds__(256, EwMinBlocks<OP, CT, SMODE, HAS_OFF>::valu
             store_pack_wide<Dst, VEC>(static_cast<Dst*>(a.dst) + static_cast<size_t>(r) * a.dstStride + c0, out, a.wide32 != 0);
         }
     }
+}
+
+// Launch with programmatic stream serialisation allowed (see the kernel's first lines); ASCQ_EW_NOPDL=1 launches plainly.
+template <typename K> inline void launch_rows_kernel(K kernel, dim3 grid, dim3 block, cudaStream_t stream, const EwArgs& args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = getenv("ASCQ_EW_NOPDL") == nullptr ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, args);
 }
 
 // Grid shape: x covers the column vectors, y strides the rows; about ASCQ_EW_TARGET 256-thread CTAs per SM.
@@ -562,7 +586,7 @@ ascq_status launch_ew_rows(const EwArgs& a, int smode, bool hasOff, bool hasTok,
     b.wide32 = EwTune<OP>::kWide256 && ((reinterpret_cast<uintptr_t>(a.src) | reinterpret_cast<uintptr_t>(a.dst)) & 31u) == 0 &&
                (static_cast<size_t>(a.srcStride) * sizeof(Src)) % 32 == 0 && (static_cast<size_t>(a.dstStride) * sizeof(Dst)) % 32 == 0;
 #define ASCQ_EW_LAUNCH(SM, OFF, TOK) \
-    ew_rows_kernel<OP, Src, Dst, Sc, CT, SM, OFF, TOK><<<grid, block, 0, stream>>>(b)
+    launch_rows_kernel(ew_rows_kernel<OP, Src, Dst, Sc, CT, SM, OFF, TOK>, grid, block, stream, b)
 #define ASCQ_EW_SMODE(OFF, TOK)                            \
     switch (smode) {                                       \
         case kSScalar: ASCQ_EW_LAUNCH(kSScalar, OFF, TOK); break;     \
