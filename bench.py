@@ -1089,6 +1089,19 @@ def run_extras(args):
         yb = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
         add(f"AscendAntiQuant int8 -> bf16 {nm}", lambda i: L.check(L.lib().ascq_antiquant(ops._ptr(yb), L.DT_BF16, ops._ptr(d8), L.DT_I8, ops._ptr(of), ops._ptr(sc),
             L.DT_BF16, 0.0, 0.0, pol, C.byref(p2), ops._stream(None))), x.numel() * 3, "TB/s")
+    # ---- what plain fills and copies of the two small configurations' byte counts reach (torch kernels; a yardstick
+    # for the write direction of config 2 and for kernels of 10 to 30 us, not part of the library) ----
+    del x, d4, s4, d8, dst4, src4
+    torch.cuda.empty_cache()
+    for nm, nbytes in (("config 2's output, 90 MB", 4096 * 11008 * 2), ("1 GiB", 1 << 30)):
+        bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(max(2, int(2.5 * L2_BYTES / nbytes) + 1))]
+        add(f"torch fill_ of {nm} (write only)", lambda i: bufs[i % len(bufs)].fill_(1), nbytes, "TB/s")
+        del bufs
+    for nm, nbytes in (("config 2's total, 135 MB (67.6 MB read + 67.6 MB written)", 4096 * 11008 * 3 // 2), ("1 GiB read + 1 GiB written", 1 << 30)):
+        src_ = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(max(2, int(1.5 * L2_BYTES / nbytes) + 1))]
+        dst_ = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(len(src_))]
+        add(f"torch copy_ of {nm}", lambda i: dst_[i % len(dst_)].copy_(src_[i % len(src_)]), 2 * nbytes, "TB/s")
+        del src_, dst_
     ops.MatmulStatus()
     print(json.dumps({"metric": "operators of the path beside the five benchmark configurations", "n_gpus": 1, "steps": steps, "warmup": warm,
                       "data": "synthetic", "launch": "the K steps replayed from one CUDA graph", "extras": out}))
