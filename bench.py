@@ -1097,7 +1097,7 @@ def run_extras(args):
         bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(max(2, int(2.5 * L2_BYTES / nbytes) + 1))]
         add(f"torch fill_ of {nm} (write only)", lambda i: bufs[i % len(bufs)].fill_(1), nbytes, "TB/s")
         del bufs
-    for nm, nbytes in (("config 2's total, 135 MB (67.6 MB read + 67.6 MB written)", 4096 * 11008 * 3 // 2), ("1 GiB read + 1 GiB written", 1 << 30)):
+    for nm, nbytes in (("config 2's total, 135 MB (67.6 MB read + 67.6 MB written)", 4096 * 11008 * 3 // 2),):
         src_ = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(max(2, int(1.5 * L2_BYTES / nbytes) + 1))]
         dst_ = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(len(src_))]
         add(f"torch copy_ of {nm}", lambda i: dst_[i % len(dst_)].copy_(src_[i % len(src_)]), 2 * nbytes, "TB/s")
