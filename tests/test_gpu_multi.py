@@ -80,3 +80,45 @@ def test_peer_store_rate_probe(tmp_path, capsys):
         print("\n" + r.stdout)
     rates = [float(line.split("us/launch")[1].split("GB/s")[0]) for line in r.stdout.splitlines() if "contiguous" in line and "LOCAL" not in line]
     assert rates and max(rates) > 200.0, rates
+
+
+@pytest.mark.gpu
+@two_gpus
+def test_one_process_drives_two_devices():
+    """Kernel attributes (opt-in shared memory), the SM count and the built-in scratch address are per device: the same
+    process calls the matmuls on device 0, then on device 1, then on device 0 again, and every result is the oracle's."""
+    import ctypes as C
+
+    import numpy as np
+
+    from asc_devkit_b200 import ops
+    from oracle import oracle as O
+    from tests.test_gpu_matmul_mxfp4 import abs_product_sums, check_close, make_case as make_mx_case
+    from tests.test_gpu_matmul_w8a8 import make_case
+
+    M, N, K = 384, 512, 512
+    A, B, sA, sB, bias = make_case(M, N, K, 11)
+    want = O.matmul_w8a8(A, B, sA, sB, bias)
+    groups, N4, K4 = [130, 0, 77], 256, 512
+    A4, sA4, B4, sB4 = make_mx_case(groups, N4, K4, 12)
+    _, want4 = O.group_matmul_mxfp4(A4, sA4, B4, sB4, np.array(groups, np.int64), K4, N4, want_f32=True)
+    bound4 = abs_product_sums(A4, sA4, B4, sB4, groups, K4)
+    for dev in ("cuda:0", "cuda:1", "cuda:0"):
+        with torch.cuda.device(dev):
+            t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
+            out = torch.full((M, N), -1.0, dtype=torch.bfloat16, device=dev)
+            ops.MatmulW8A8(out, t(A), t(B), t(sA), t(sB), torch.from_numpy(bias.view(np.int16).copy()).to(dev).view(torch.bfloat16))
+            ops.MatmulStatus()
+            assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), want), dev
+            # grouped MX-FP4 through the workspace entry point and through the built-in scratch of THIS device
+            for no_alloc in (False, True):
+                c4 = torch.full((sum(groups), N4), -1.0, dtype=torch.bfloat16, device=dev)
+                if no_alloc:
+                    gl = (C.c_int64 * len(groups))(*groups)
+                    L.check(L.lib().ascq_group_matmul_mxfp4_noalloc(ops._ptr(c4), ops._ptr(dA4), ops._ptr(dsA4), ops._ptr(dB4), ops._ptr(dsB4),
+                                                                    gl, len(groups), K4, N4, ops._stream(None)))
+                else:
+                    dA4, dsA4, dB4, dsB4 = t(A4), t(sA4), t(B4), t(sB4)
+                    ops.GroupMatmulMxfp4(c4, dA4, dsA4, dB4, dsB4, groups, K4, N4)
+                ops.MatmulStatus()
+                check_close(c4.view(torch.int16).cpu().numpy().view(np.uint16), want4, f"{dev} no_alloc={no_alloc}", bound4, K4)
