@@ -83,6 +83,7 @@ struct Params {
     // a launch are late because its operands come from HBM cold, not because the tile is large.)
     int fullTiles, workItems;
     int tmaStore;  // 16-bit result, suitably aligned buffers: the epilogue hands its staged rows to TMA stores (one per buffer)
+    int narrowBox;  // one output matrix: 32 x 32 boxes (tmapC.cNarrow) instead of 64 columns x 16 rows
     CommArgs comm;      // sharded form: end-of-step exchange with the other ranks (nranks == 0: none)
 #ifdef ASCQ_TRACE
     unsigned long long* trace;  // diagnostic builds: 16 time stamps (ns) per CTA, see trace_stamp
@@ -265,6 +266,7 @@ __device__ __forceinline__ void convert_tiles(const Params& p, uint8_t* smem, fl
 struct OutMaps {
     CUtensorMap m[kMaxPeers];
     CUtensorMap bHalf;  // B with a box of half the rows: what a CTA loads for a half-tile work item (pair shape)
+    CUtensorMap cNarrow;  // output matrix 0 with a 32-column x 32-row box and the 64B swizzle (single-matrix launches)
 };
 
 
@@ -773,6 +775,34 @@ w8a8_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ C
                     continue;
                 }
                 uint32_t packed[32];
+                if (tileTma && p.narrowBox) {
+                    // One output matrix: 32 columns at a time.  Every lane stages its own row's 64 bytes (piece v of row
+                    // r at v ^ ((r >> 1) & 3): the 64B swizzle, free of bank conflicts) and the 32 x 32 box leaves as one
+                    // TMA store; the wait for the previous store's read of the staging rows comes after the next 32
+                    // columns' arithmetic, which hides it.  (Launches that write to peers keep the 128-byte rows below:
+                    // longer segments suit the link.)
+#pragma unroll
+                    for (int sc = 0; sc < 2; ++sc) {
+                        if (sc == 0) convert32(r0, c2 * 64, packed);
+                        else convert32(r1, c2 * 64 + 32, packed);
+                        if (stamp && c2 == sub && sc == 1) ASCQ_CYCLES(p, 9, tAcc);
+                        if (lane == 0) bulk_wait_group_read<0>();
+                        __syncwarp();
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            *reinterpret_cast<uint4*>(stageT + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) =
+                                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        fence_proxy_async();
+                        __syncwarp();
+                        const int row0 = m0 + q * 32;
+                        if (lane == 0 && row0 < rowEnd && n + sc * 32 < p.N) {
+                            tma_store_2d(&tmapC.cNarrow, stageT, p.colOffset + n + sc * 32, row0);
+                            bulk_commit_group();
+                        }
+                    }
+                    if (stamp && c2 == sub) ASCQ_CYCLES(p, 10, tAcc);
+                    continue;
+                }
                 convert32(r0, c2 * 64, packed);
                 convert32(r1, c2 * 64 + 32, packed + 16);
                 if (stamp && c2 == sub) ASCQ_CYCLES(p, 9, tAcc);
@@ -1092,6 +1122,14 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     if (rc != ASCQ_OK) return rc;
     for (int i = 0; i < kMaxPeers; ++i) tc.m[i] = ta;  // placeholders; the kernel reads maps [0, nPeers) and only for TMA stores
     tc.bHalf = tb;
+    tc.cNarrow = ta;
+    p.narrowBox = 0;
+    if (p.tmaStore && p.nPeers == 1 && getenv("ASCQ_W8A8_WIDEBOX") == nullptr) {
+        rc = make_tmap_out16(&tc.cNarrow, outBufs[0], static_cast<uint64_t>(M), static_cast<uint64_t>(colOffset) + N,
+                             static_cast<uint64_t>(ldc), 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != ASCQ_OK) return rc;
+        p.narrowBox = 1;
+    }
     if (mode == 2) {  // pair shape: half-tile work items load 64 rows of B per CTA instead of 128
         rc = make_tmap_u8(&tc.bHalf, B_nk, rowsB, static_cast<uint64_t>(K) * elemBytes, 64);
         if (rc != ASCQ_OK) return rc;

@@ -103,9 +103,11 @@ inline ascq_status make_tmap_kib_rows(CUtensorMap* out, const void* base, uint64
 
 // 16-bit [rows, cols] row-major output matrix with row pitch ldElems: a [boxRows, 64-element] box (128 bytes) with the
 // 128B swizzle, for TMA stores.  base 16-byte aligned, ldElems a multiple of 8.
-inline ascq_status make_tmap_out16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ldElems, uint32_t boxRows)
+inline ascq_status make_tmap_out16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ldElems, uint32_t boxRows,
+                                   uint32_t boxCols = 64, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B)
 {
-    return encode_2d(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, base, cols, rows, ldElems * 2, 64, boxRows, CU_TENSOR_MAP_SWIZZLE_128B,
+    // (boxCols = 32 with CU_TENSOR_MAP_SWIZZLE_64B: 64-byte rows)
+    return encode_2d(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, base, cols, rows, ldElems * 2, boxCols, boxRows, swizzle,
                      CU_TENSOR_MAP_L2_PROMOTION_NONE, "output");
 }
 
