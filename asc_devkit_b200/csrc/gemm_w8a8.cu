@@ -947,9 +947,14 @@ ascq_status launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& 
         // Tail split: when the last wave of whole tiles would keep at most half of the pairs busy, its tiles are cut
         // into two column halves, so that every pair gets at most one half tile and the wave lasts half as long.
         const int rest = p.fullTiles % maxClusters;
-        if (canSplit && p.fullTiles > maxClusters && rest > 0 && 2 * rest <= maxClusters && getenv("ASCQ_W8A8_NOSPLIT") == nullptr) {
+        const bool noSplit = getenv("ASCQ_W8A8_NOSPLIT") != nullptr;
+        if (canSplit && p.fullTiles > maxClusters && rest > 0 && 2 * rest <= maxClusters && !noSplit) {
             p.fullTiles -= rest;
             p.workItems += rest;
+        } else if (canSplit && 2 * tiles <= maxClusters && !noSplit) {
+            // a problem that would leave more than half of the pairs idle: every tile as two half items
+            p.fullTiles = 0;
+            p.workItems = 2 * tiles;
         }
         const int clusters = p.workItems < maxClusters ? p.workItems : maxClusters;
         cudaLaunchConfig_t cfg{};
