@@ -120,3 +120,41 @@ def test_oracle_rejects_the_same_malformed_calls():
         O.ascend_quant(x, O.F16, policy=O.PER_CHANNEL, n=48, calCount=64, scale=np.zeros(48, np.float16))
     with pytest.raises(O.OracleError):
         O.ascend_quant(x, O.F16, policy=O.PER_GROUP, m=2, n=32, scale=np.zeros(2, np.float16), groupSize=48)
+
+
+def test_partition_of_the_sharded_matmuls_matches_the_host_side_plan():
+    """Host-only entry points of the multi-GPU API: the column partition, and the longest-group-first deal, which must be
+    the one asc_devkit_b200.sharding uses (the data of a run is laid out by one and consumed by the other)."""
+    import numpy as np
+
+    from asc_devkit_b200 import ops, sharding
+    assert ops.ShardColumns(4096, 8, 3) == (1536, 512)
+    with pytest.raises(L.AscqError):
+        ops.ShardColumns(4096, 3, 0)
+    rng = np.random.default_rng(0)
+    for trial in range(50):
+        G = int(rng.integers(1, 40))
+        groups = [int(v) for v in rng.integers(0, 300, G)]
+        if trial % 5 == 0:
+            groups = [groups[0]] * G          # ties everywhere
+        for world in (1, 2, 3, 8):
+            assert ops.ShardGroupsLpt(groups, world) == sharding.assign_groups_lpt(groups, world).owner, (groups, world)
+    with pytest.raises(L.AscqError):
+        ops.ShardGroupsLpt([5, -1], 2)
+
+
+def test_communicator_argument_checks_need_no_gpu():
+    blocks = (C.c_void_p * 2)(C.c_void_p(0x1000), C.c_void_p(0x2000))     # never dereferenced on the host
+    h = C.c_void_p()
+    lib = L.lib()
+    assert lib.ascq_comm_flag_bytes() == 512
+    assert lib.ascq_comm_create(C.byref(h), 0, 2, blocks) == L.OK and h.value
+    r, n = C.c_int(), C.c_int()
+    assert lib.ascq_comm_rank(h, C.byref(r), C.byref(n)) == L.OK and (r.value, n.value) == (0, 2)
+    assert lib.ascq_comm_destroy(h) == L.OK
+    assert lib.ascq_comm_create(C.byref(h), 2, 2, blocks) == L.ERR_INVALID_ARG
+    assert lib.ascq_comm_create(C.byref(h), 0, 9, blocks) == L.ERR_INVALID_ARG
+    bad = (C.c_void_p * 2)(C.c_void_p(0x1010), C.c_void_p(0x2000))
+    assert lib.ascq_comm_create(C.byref(h), 0, 2, bad) == L.ERR_ALIGNMENT
+    assert lib.ascq_matmul_w8a8_sharded(None, blocks, None, None, None, None, None, None, 8, 8, 16, None) == L.ERR_INVALID_ARG
+    assert lib.ascq_group_matmul_w8a8(None, L.DT_F16, None, None, None, None, None, None, 1, 8, 16, 0, None) == L.ERR_INVALID_ARG
