@@ -33,6 +33,13 @@ ascq_status mxfp4_read_status(::CUstream_st* stream);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// gemm_w8a16_small.cu: the weight-only-quantised matmul for at most kW8A16SmallMaxM activation rows
+constexpr int kW8A16SmallMaxM = 32;
+bool w8a16_small_applies(int M, int N, int K, const void* A, const void* B, const void* workspace, size_t workspaceBytes);
+ascq_status w8a16_small(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk, const void* offset, const void* scale,
+                        float offsetScalar, float scaleScalar, bool hasOffset, int M, int N, int K, int ldc, void* workspace,
+                        size_t workspaceBytes, ::CUstream_st* st);
+
 // Sets the wait limit (SM cycles) of the bounded waits in each matmul translation unit on the current device.
 ascq_status w8a8_set_wait_cycles(long long cycles);
 ascq_status mxfp4_set_wait_cycles(long long cycles);

@@ -635,5 +635,22 @@ inline bool ew_fast_ok(const EwArgs& a, int vec, int smode, int scSize)
     return true;
 }
 
+// One int8 row segment of 16 weights -> 16 half / bfloat16 values with AscendAntiQuant's arithmetic (the elementwise
+// operator's own code: bfloat16 through fp32, half in half), as two 16-byte chunks.
+template <typename CT, typename Dst, bool HAS_OFF>
+__device__ __forceinline__ void antiquant16(const uint4& raw, CT s, CT o, uint4& lo, uint4& hi)
+{
+    Pack<int8_t, 16> in;
+    *reinterpret_cast<uint4*>(&in) = raw;
+    alignas(4) CT x[16];
+    unpack_src<int8_t, CT, 16>(in, x);
+    const CT sv[1] = {s}, ov[1] = {o};
+    apply_op<kOpAntiQuant, CT, 16, 1, HAS_OFF, false>(x, sv, ov, 1.0f);
+    Pack<Dst, 16> out;
+    pack_dst<Dst, CT, 16>(x, out, kRoundRint);
+    lo = reinterpret_cast<const uint4*>(&out)[0];
+    hi = reinterpret_cast<const uint4*>(&out)[1];
+}
+
 }  // namespace ascq
 #endif  // ASCQ_ELEMENTWISE_CUH_

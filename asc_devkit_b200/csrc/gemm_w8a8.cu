@@ -184,23 +184,6 @@ constexpr int kEpiFloat = 2;    // half / bfloat16 operands (kind::f16), fp32 ac
 constexpr int kEpiRequant = 3;  // SetQuantScalar / SetQuantVector with an int8 / uint8 result ((V)REQ8)
 constexpr int kBytePitch = 80;  // bytes per staged row of a byte-typed result: 64 B + 16 B pad
 
-// One int8 row segment of 16 weights -> 16 half / bfloat16 values with AscendAntiQuant's arithmetic (the elementwise
-// operator's own code: bfloat16 through fp32, half in half), as two 16-byte chunks.
-template <typename CT, typename Dst, bool HAS_OFF>
-__device__ __forceinline__ void antiquant16(const uint4& raw, CT s, CT o, uint4& lo, uint4& hi)
-{
-    Pack<int8_t, 16> in;
-    *reinterpret_cast<uint4*>(&in) = raw;
-    alignas(4) CT x[16];
-    unpack_src<int8_t, CT, 16>(in, x);
-    const CT sv[1] = {s}, ov[1] = {o};
-    apply_op<kOpAntiQuant, CT, 16, 1, HAS_OFF, false>(x, sv, ov, 1.0f);
-    Pack<Dst, 16> out;
-    pack_dst<Dst, CT, 16>(x, out, kRoundRint);
-    lo = reinterpret_cast<const uint4*>(&out)[0];
-    hi = reinterpret_cast<const uint4*>(&out)[1];
-}
-
 // Converter warps of the weight-only-quantised matmul.  Warp w takes the k-blocks that land in pipeline stage w (there
 // are as many stages as converter warps), so four k-blocks are being converted at any time and the fixed costs of a
 // hand-over (barrier wake-up, proxy fence, arrive) are paid once per 8192 weights.  Per pass of 8 rows, lane l owns row
@@ -1363,8 +1346,24 @@ static ascq_status matmul_wq_a16(ascq_dtype bT, void* C, ascq_dtype cT, const vo
     // MMA stage, so the dequantised weight never leaves shared memory -- same bits, but measured 2 to 4 times slower:
     // the tile then crosses shared memory three more times (int8 in, 16-bit out, 16-bit into the tensor cores) next to
     // the operand traffic of the MMAs, and a k-block waits for a whole warp's conversion before its MMAs can start.
+    // For at most 32 activation rows a third form converts the weight in registers on its way to the tensor cores
+    // (gemm_w8a16_small.cu); any value of ASCQ_W8A16 other than "small" switches it off.
     bool fused = false;
-    if (const char* e = getenv("ASCQ_W8A16")) fused = bT == ASCQ_DT_I8 && !strcmp(e, "fused") && (K % 32 == 0) && aligned16(B_nk);
+    const char* form = getenv("ASCQ_W8A16");
+    if (form) fused = bT == ASCQ_DT_I8 && !strcmp(form, "fused") && (K % 32 == 0) && aligned16(B_nk);
+    if (bT == ASCQ_DT_I8 && (!form || !strcmp(form, "small")) && w8a16_small_applies(M, N, K, A, B_nk, workspace, workspaceBytes)) {
+        if (!C || !A) return fail(ASCQ_ERR_INVALID_ARG, "C and A must not be NULL");
+        if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)
+            return fail(ASCQ_ERR_UNSUPPORTED, "output must be half, bfloat16_t or float");
+        if (ldc < N) return fail(ASCQ_ERR_INVALID_ARG, "ldc must be at least N");
+        float ss = scaleScalar, os = offsetScalar;
+        if (!scale) {  // the scalars arrive as aT values
+            if (aT == ASCQ_DT_F16) { ss = __half2float(__float2half_rn(ss)); os = __half2float(__float2half_rn(os)); }
+            else { ss = __bfloat162float(__float2bfloat16_rn(ss)); os = __bfloat162float(__float2bfloat16_rn(os)); }
+        }
+        return w8a16_small(C, cT, A, aT, B_nk, offset, scale, os, ss, scale ? offset != nullptr : true, M, N, K, ldc, workspace,
+                           workspaceBytes, static_cast<cudaStream_t>(stream));
+    }
     if (fused) {
         if (!C) return fail(ASCQ_ERR_INVALID_ARG, "C must not be NULL");
         if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)

@@ -41,6 +41,15 @@ def _ptr(t: Optional[torch.Tensor]):
     return C.c_void_p(t.data_ptr())
 
 
+def _ptr_pitched(t: torch.Tensor):
+    """Pointer of a 2-D output whose rows are contiguous but may be spaced by a pitch (``t.stride(0)`` goes in as ldc)."""
+    if not t.is_cuda:
+        raise ValueError("ascq operators take CUDA tensors (there is no CPU path)")
+    if t.dim() != 2 or t.stride(1) != 1 or t.stride(0) < t.shape[1]:
+        raise ValueError("a matmul output must be 2-D with contiguous rows")
+    return C.c_void_p(t.data_ptr())
+
+
 def _workspace(need: int, device, stream: Optional[torch.cuda.Stream]) -> torch.Tensor:
     """A temporary workspace for a call that returns while its kernels still run.  The caching allocator hands a freed
     block back to torch's current stream; when the kernels run on another stream the block is tied to that one too."""
@@ -314,7 +323,7 @@ def MatmulW8A16(C: torch.Tensor, A: torch.Tensor, B_nk: torch.Tensor, offset, sc
     if workspace is None:
         workspace = _workspace(N * K * 2, A.device, stream)
     st = isinstance(scale, torch.Tensor)
-    L.check(L.lib().ascq_matmul_w8a16(_ptr(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk),
+    L.check(L.lib().ascq_matmul_w8a16(_ptr_pitched(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk),
                                       _ptr(offset) if isinstance(offset, torch.Tensor) else None, _ptr(scale) if st else None,
                                       0.0 if st else float(offset), 0.0 if st else float(scale), M, N, K, C.stride(0),
                                       _ptr(workspace), workspace.numel(), _stream(stream)))
@@ -329,7 +338,7 @@ def MatmulW4A16(C: torch.Tensor, A: torch.Tensor, B_nk_int4: torch.Tensor, offse
     if workspace is None:
         workspace = _workspace(N * K * 2, A.device, stream)
     st = isinstance(scale, torch.Tensor)
-    L.check(L.lib().ascq_matmul_w4a16(_ptr(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk_int4),
+    L.check(L.lib().ascq_matmul_w4a16(_ptr_pitched(C), dtype_code(C), _ptr(A), dtype_code(A), _ptr(B_nk_int4),
                                       _ptr(offset) if isinstance(offset, torch.Tensor) else None, _ptr(scale) if st else None,
                                       0.0 if st else float(offset), 0.0 if st else float(scale), M, N, K, C.stride(0),
                                       _ptr(workspace), workspace.numel(), _stream(stream)))

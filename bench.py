@@ -1044,6 +1044,23 @@ def run_extras(args):
         add(f"weight-only-quantised matmul, int4 weights, {nm} activations", lambda i: ops.MatmulW4A16(Cc[i % ns], A[i % ns], B4[i % ns], of, sc, workspace=ws), flop, "TFLOPS")
         del A, B, Cc
     del B8, Cb
+    # ---- weight-only-quantised matmul with few activation rows: bound by reading the int8 weight once ----
+    Nw = Kw = 8192
+    nw = 6
+    Bw = [torch.randint(-128, 128, (Nw, Kw), dtype=torch.int8, device=dev) for _ in range(nw)]
+    wsw = torch.empty(Nw * Kw * 2, dtype=torch.uint8, device=dev)
+    for dt, nm in ((torch.float16, "half"), (torch.bfloat16, "bfloat16")):
+        scw = (torch.rand(Nw, device=dev) * 0.02).to(dt)
+        ofw = torch.randn(Nw, device=dev).to(dt)
+        for Mw in (1, 8, 16, 32):
+            Aw = torch.randn((Mw, Kw), device=dev).to(dt)
+            Cw = torch.empty((Mw, Nw), dtype=dt, device=dev)
+            for form, label in (("small", "weight converted in registers"), ("twostep", "AscendAntiQuant launch, then the matmul")):
+                os.environ["ASCQ_W8A16"] = form
+                add(f"weight-only-quantised matmul, {Mw} x 8192 {nm} activations, 8192 x 8192 int8 weight, {label}",
+                    lambda i: ops.MatmulW8A16(Cw, Aw, Bw[i % nw], ofw, scw, workspace=wsw), float(Nw * Kw), "TB/s of weight bytes")
+            os.environ.pop("ASCQ_W8A16", None)
+    del Bw, wsw
     # ---- MX matmul with fp8 operands at config 5's shape (uniform groups) ----
     G, K5, N5, sumM = 16, 7168, 2048, 16384
     groups = [sumM // G] * G

@@ -169,3 +169,119 @@ def test_matmul_f16_quant_matches_oracle(M, N, K, abT, vector, tile, monkeypatch
     ops.MatmulStatus()
     signed = ((qv >> np.uint64(46)) & np.uint64(1)).astype(bool) if vector else np.ones(N, bool)
     _one_step_apart(C.cpu().numpy(), want, signed)
+
+
+# ---- at most 32 activation rows: the weight is converted in registers on its way to the tensor cores -------------------
+
+def _w8a16_case(rng, M, N, K, abT, per_channel, with_offset):
+    A = rand_float(rng, (M, K), abT, -1, 1)
+    B = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    if per_channel:
+        sc_h = rand_float(rng, (N,), abT, 0.002, 0.02)
+        of_h = rand_float(rng, (N,), abT, -4, 4) if with_offset else None
+        return A, B, sc_h, of_h, to_dev(sc_h, abT), (to_dev(of_h, abT) if with_offset else None)
+    return A, B, 0.0078125, 1.5, 0.0078125, 1.5
+
+
+@pytest.mark.parametrize("abT,cT", [(O.F16, O.F16), (O.F16, O.F32), (O.BF16, O.BF16), (O.BF16, O.F32)])
+@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (7, 516, 384), (8, 4096, 4096), (16, 1000, 1024), (25, 640, 2176), (32, 2048, 1024)])
+@pytest.mark.parametrize("per_channel,with_offset", [(True, True), (True, False), (False, True)])
+def test_w8a16_few_rows(abT, cT, M, N, K, per_channel, with_offset, monkeypatch):
+    """Both forms against the oracle (AscendAntiQuant, then an fp64 matmul), into a pitched output whose guard row and guard
+    columns must stay untouched."""
+    rng = np.random.default_rng(M + N + K + abT + cT)
+    A, B, sc_h, of_h, scale, offset = _w8a16_case(rng, M, N, K, abT, per_channel, with_offset)
+    if per_channel:
+        W = O.ascend_antiquant(B, O.I8, abT, policy=O.PER_CHANNEL, m=N, n=K, scale=sc_h, offset=of_h, scaleT=abT, isTranspose=True)
+        _, want = O.matmul_f16(A, W, abT)
+    else:
+        (_, want), _ = O.matmul_w8a16(A, abT, B, of_h, sc_h)
+    dA, dB = to_dev(A, abT), torch.from_numpy(B).to(DEV)
+    outs = {}
+    for form in ("small", "twostep"):
+        monkeypatch.setenv("ASCQ_W8A16", form)
+        C = torch.full((M + 1, N + 8), -1.0, dtype=TDT[cT], device=DEV)   # a pitched output with a guard row and guard columns
+        ops.MatmulW8A16(C[:M, :N], dA, dB, offset, scale)
+        ops.MatmulStatus()
+        full = C.float().cpu().numpy()
+        assert (full[M:] == -1.0).all() and (full[:, N:] == -1.0).all(), form
+        outs[form] = full[:M, :N]
+        close(outs[form], want)
+
+
+@pytest.mark.parametrize("abT", [O.F16, O.BF16])
+@pytest.mark.parametrize("M", [1, 5, 24, 32])
+def test_w8a16_few_rows_exact_on_small_integers(abT, M, monkeypatch):
+    """Integer activations, scale a power of two, offset 1.5: every product and partial sum is exact in fp32, so the order of
+    summation cannot matter and the result must equal the oracle's, and the two-launch form's, bit for bit."""
+    rng = np.random.default_rng(70 + M + abT)
+    N, K = 768, 512
+    A = rng.integers(-4, 5, (M, K)).astype(np.float32)
+    A = A.astype(np.float16) if abT == O.F16 else (A.view(np.uint32) >> 16).astype(np.uint16)
+    B = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    (_, want), _ = O.matmul_w8a16(A, abT, B, 1.5, 0.0078125)
+    outs = {}
+    for form in ("small", "twostep"):
+        monkeypatch.setenv("ASCQ_W8A16", form)
+        C = torch.zeros((M, N), dtype=torch.float32, device=DEV)
+        ops.MatmulW8A16(C, to_dev(A, abT), torch.from_numpy(B).to(DEV), 1.5, 0.0078125)
+        ops.MatmulStatus()
+        outs[form] = C.cpu().numpy()
+    assert np.array_equal(outs["small"], want.astype(np.float32))
+    assert np.array_equal(outs["small"].view(np.uint32), outs["twostep"].view(np.uint32))
+
+
+def test_w8a16_few_rows_is_the_default_and_leaves_no_weight_behind(monkeypatch):
+    """With ASCQ_W8A16 unset, M <= 32 takes the in-register form: the workspace then holds at most fp32 partial sums, not the
+    dequantised weight; above 32 rows the two-launch form writes the weight there."""
+    monkeypatch.delenv("ASCQ_W8A16", raising=False)
+    rng = np.random.default_rng(3)
+    N, K = 512, 512
+    B = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    sc_h, of_h = rand_float(rng, (N,), O.F16, 0.002, 0.02), rand_float(rng, (N,), O.F16, -4, 4)
+    W = O.ascend_antiquant(B, O.I8, O.F16, policy=O.PER_CHANNEL, m=N, n=K, scale=sc_h, offset=of_h, scaleT=O.F16, isTranspose=True)
+    for M, weight_in_workspace in ((32, False), (33, True)):
+        A = rand_float(rng, (M, K), O.F16, -1, 1)
+        ws = torch.zeros(N * K * 2, dtype=torch.uint8, device=DEV)
+        C = torch.zeros((M, N), dtype=torch.float32, device=DEV)
+        ops.MatmulW8A16(C, to_dev(A, O.F16), torch.from_numpy(B).to(DEV), to_dev(of_h, O.F16), to_dev(sc_h, O.F16), workspace=ws)
+        ops.MatmulStatus()
+        _, want = O.matmul_f16(A, W, O.F16)
+        close(C.cpu().numpy(), want)
+        same = np.array_equal(ws.view(torch.float16).view(N, K).cpu().numpy().view(np.uint16), W.view(np.uint16))
+        assert same == weight_in_workspace, M
+
+
+@pytest.mark.parametrize("abT", [O.F16, O.BF16])
+@pytest.mark.parametrize("with_offset", [True, False])
+def test_w8a16_few_rows_reads_the_weight_antiquant_produces(abT, with_offset, monkeypatch):
+    """One-hot activation rows copy single weight columns into the fp32 result, so the weight the tensor cores were fed can
+    be compared with AscendAntiQuant's output bit for bit -- including, for bfloat16, a row whose scale is so large that
+    the product overflows and AscendAntiQuant saturates it."""
+    monkeypatch.setenv("ASCQ_W8A16", "small")
+    rng = np.random.default_rng(90 + abT + with_offset)
+    M, N, K = 32, 528, 384
+    B = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    sc_h = rand_float(rng, (N,), abT, 0.002, 0.02)
+    of_h = rand_float(rng, (N,), abT, -4, 4) if with_offset else None
+    if abT == O.BF16:
+        # row 17: scale 2^127; with offset 255/256 the weight 1 gives 1.99609375 * 2^127, which is finite in fp32 and rounds to
+        # infinity as a bfloat16 -- AscendAntiQuant stores the largest finite bfloat16 there.  The other weights of the row
+        # are kept where the fp32 product stays finite.
+        sc_h[17] = np.uint16(0x7F00)
+        B[17] = rng.integers(-1, 2, K)
+        if with_offset:
+            of_h[17] = np.uint16(0x3F7F)
+    W = O.ascend_antiquant(B, O.I8, abT, policy=O.PER_CHANNEL, m=N, n=K, scale=sc_h, offset=of_h, scaleT=abT, isTranspose=True)
+    Wf = W.astype(np.float32) if abT == O.F16 else (W.astype(np.uint32) << 16).view(np.float32)
+    assert np.isfinite(Wf).all()
+    if abT == O.BF16 and with_offset:
+        assert (W[17][B[17] == 1] == 0x7F7F).all() and (B[17] == 1).any()
+    cols = rng.choice(K, M, replace=False)
+    A = np.zeros((M, K), np.float32)
+    A[np.arange(M), cols] = 1.0
+    A = A.astype(np.float16) if abT == O.F16 else (A.view(np.uint32) >> 16).astype(np.uint16)
+    C = torch.zeros((M, N), dtype=torch.float32, device=DEV)
+    ops.MatmulW8A16(C, to_dev(A, abT), torch.from_numpy(B).to(DEV), to_dev(of_h, abT) if with_offset else None, to_dev(sc_h, abT))
+    ops.MatmulStatus()
+    assert np.array_equal(C.cpu().numpy().view(np.uint32), np.ascontiguousarray(Wf[:, cols].T).view(np.uint32))
