@@ -410,8 +410,12 @@ ascq_status ascq_matmul_f16_quant(void* C_b8, const void* A, const void* B_nk, a
  *   W[n, k] = AscendAntiQuant(B_nk[n, k]) = scale[n] * (B + offset[n]) in aT arithmetic (half: half add, half multiply;
  *   bfloat16: fp32 intermediates) -- offset / scale [N] tensors of aT, or (scale NULL) the two scalars;
  *   C = A . W^T with fp32 accumulation, cast to cT.
- * Two launches: the dequantised weight goes through `workspace` (N * K * 2 bytes, 16-byte aligned) and stays in L2 for
- * the matmul when it fits.  K % 32 == 0.  (With ASCQ_W8A16=fused in the environment the conversion runs inside the
+ * M <= 32 (with K % 128 == 0, N % 4 == 0, A and B_nk 32-byte aligned): the weight is converted in registers between its
+ * load from HBM and the tensor cores -- it is read once and written nowhere; `workspace` then receives at most fp32
+ * partial sums of a K split.  Otherwise two launches: the dequantised weight goes through `workspace` (N * K * 2 bytes,
+ * 16-byte aligned) and stays in L2 for the matmul when it fits; K % 32 == 0.  Either way the weight the tensor cores
+ * multiply is AscendAntiQuant's output bit for bit; the contents of `workspace` after the call are unspecified.
+ * (Environment: ASCQ_W8A16=twostep always takes two launches; ASCQ_W8A16=fused runs the conversion inside the tcgen05
  * matmul instead -- converter warps between the copy stage and the MMA stage, same bits, no workspace traffic; it is
  * slower on B200 and kept as a tested alternative.)
  */
