@@ -40,6 +40,12 @@ ascq_status w8a16_small(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, co
                         float offsetScalar, float scaleScalar, bool hasOffset, int M, int N, int K, int ldc, void* workspace,
                         size_t workspaceBytes, ::CUstream_st* st);
 
+// gemm_w8a8_small.cu: the W8A8 matmul with dequant epilogue for at most kW8A8SmallMaxM activation rows
+constexpr int kW8A8SmallMaxM = 32;
+bool w8a8_small_applies(int M, int N, int K, const void* A, const void* B);
+ascq_status w8a8_small(void* C, const int8_t* A, const int8_t* B_nk, const float* sA_m, const float* sB_n, const void* bias_bf16,
+                       int M, int N, int K, int ldc, int colOffset, ::CUstream_st* st);
+
 // Sets the wait limit (SM cycles) of the bounded waits in each matmul translation unit on the current device.
 ascq_status w8a8_set_wait_cycles(long long cycles);
 ascq_status mxfp4_set_wait_cycles(long long cycles);

@@ -1024,6 +1024,13 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     if ((K * elemBytes) % 16 != 0) return fail(ASCQ_ERR_ALIGNMENT, "K %d must be a multiple of %d (TMA row pitch of 16 bytes)", K, 16 / elemBytes);
     if (!aligned16(A) || !aligned16(B_nk)) return fail(ASCQ_ERR_ALIGNMENT, "A and B must be 16-byte aligned");
 
+    // Few activation rows: a kernel built for reading the weight once (gemm_w8a8_small.cu; same bits).  A tile shape forced
+    // through the environment, or ASCQ_W8A8_SMALL=0, keeps the call on the tcgen05 kernel.
+    if (!fix && !groups && !comm && !accDump && haveC && nBufs == 1 && !multicast && outKind == 0 && act == 0 && !getenv("ASCQ_W8A8_TILE") &&
+        g_stopAfterNext.load() < 0 && w8a8_small_applies(M, N, K, A, B_nk)) {
+        const char* e = getenv("ASCQ_W8A8_SMALL");
+        if (!e || strcmp(e, "0") != 0) return w8a8_small(outBufs[0], A, B_nk, sA_m, sB_n, bias_bf16, M, N, K, ldc, colOffset, st);
+    }
     Params p{};
     p.nPeers = haveC ? nBufs : 1;
     for (int i = 0; i < p.nPeers; ++i) {

@@ -1060,6 +1060,16 @@ def run_extras(args):
                 add(f"weight-only-quantised matmul, {Mw} x 8192 {nm} activations, 8192 x 8192 int8 weight, {label}",
                     lambda i: ops.MatmulW8A16(Cw, Aw, Bw[i % nw], ofw, scw, workspace=wsw), float(Nw * Kw), "TB/s of weight bytes")
             os.environ.pop("ASCQ_W8A16", None)
+    sBw = torch.rand(Nw, device=dev) * 0.01
+    for Mw in (1, 16, 32):
+        A8w = torch.randint(-127, 128, (Mw, Kw), dtype=torch.int8, device=dev)
+        sAw = torch.rand(Mw, device=dev) * 0.02
+        C8w = torch.empty((Mw, Nw), dtype=torch.bfloat16, device=dev)
+        for small, label in (("1", "few-row kernel"), ("0", "tcgen05 kernel")):
+            os.environ["ASCQ_W8A8_SMALL"] = small
+            add(f"W8A8 matmul + dequant, {Mw} x 8192 int8 activations, 8192 x 8192 int8 weight, {label}",
+                lambda i: ops.MatmulW8A8(C8w, A8w, Bw[i % nw], sAw, sBw, None), float(Nw * Kw), "TB/s of weight bytes")
+        os.environ.pop("ASCQ_W8A8_SMALL", None)
     del Bw, wsw
     # ---- MX matmul with fp8 operands at config 5's shape (uniform groups) ----
     G, K5, N5, sumM = 16, 7168, 2048, 16384

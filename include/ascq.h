@@ -246,6 +246,9 @@ ascq_status ascq_antiquantize(void* dst, ascq_dtype dstT, const void* src, ascq_
  * before it).  ldc = row stride of C in elements (>= N).  accDump (optional) receives the raw
  * int32 accumulators, [M,N] row-major; C may be NULL when only accDump is wanted.
  * K % 16 == 0; A, B 16-byte aligned (TMA).
+ * Two kernels produce the same bits: the tcgen05 kernel, and -- for M <= 32 with K % 128 == 0, A and B 32-byte aligned,
+ * no accDump -- a kernel shaped for reading the weight once (the product is then bound by the N x K weight bytes;
+ * ASCQ_W8A8_SMALL=0 in the environment keeps such calls on the tcgen05 kernel).
  */
 ascq_status ascq_matmul_w8a8(void* C_bf16, const int8_t* A, const int8_t* B_nk, const float* sA_m,
                              const float* sB_n, const void* bias_bf16, int M, int N, int K, int ldc,

@@ -399,3 +399,45 @@ def test_results_beyond_the_16_bit_range_saturate_like_the_oracle():
     goth = run_group(A, B[None], sA2, sB[None], [M])
     assert_bits_equal(goth, wanth.view(np.uint16), "half saturation")
     assert (wanth.view(np.uint16) == 0x7BFF).any() or (wanth.view(np.uint16) == 0xFBFF).any()
+
+
+# ---- at most 32 activation rows: the kernel that reads the weight once (mma.sync, K shared by a CTA's warps) ---------------
+
+@pytest.mark.parametrize("M", [1, 7, 8, 16, 25, 32, 33])
+@pytest.mark.parametrize("N,K", [(16, 512), (520, 640), (4096, 4096), (2300, 8192), (12288, 1024)])
+def test_few_rows_kernel_is_bit_exact(M, N, K, monkeypatch):
+    """Against the oracle, and against the tcgen05 kernel on the same inputs (ASCQ_W8A8_SMALL=0), into a pitched output
+    whose guard columns must stay untouched."""
+    A, B, sA, sB, bias = make_case(M, N, K, M * 13 + N + K)
+    want = O.matmul_w8a8(A, B, sA, sB, bias)
+    outs = {}
+    for small in ("1", "0"):
+        monkeypatch.setenv("ASCQ_W8A8_SMALL", small)
+        got, _ = run(A, B, sA, sB, bias, ldc=N + 8, want_acc=False)
+        assert (got[:, N:] == 0xBF80).all(), small
+        outs[small] = got[:, :N]
+        assert_bits_equal(outs[small], want, f"ASCQ_W8A8_SMALL={small}")
+
+
+def test_few_rows_kernel_optional_operands_and_extremes(monkeypatch):
+    monkeypatch.delenv("ASCQ_W8A8_SMALL", raising=False)
+    A, B, sA, sB, bias = make_case(24, 528, 1024, 77)
+    for kw in (dict(), dict(sA=sA), dict(sB=sB), dict(bias=bias), dict(sA=sA, sB=sB)):
+        want = O.matmul_w8a8(A, B, kw.get("sA"), kw.get("sB"), kw.get("bias"))
+        got, _ = run(A, B, kw.get("sA"), kw.get("sB"), kw.get("bias"), want_acc=False)
+        assert_bits_equal(got, want, f"operands {sorted(kw)}")
+    # +-127 everywhere: the largest accumulator magnitude for this K; unit scales make the bf16 result saturate-free but huge
+    M, N, K = 5, 256, 8192
+    A = np.full((M, K), 127, np.int8)
+    B = np.full((N, K), -127, np.int8)
+    B[::2] = 127
+    got, _ = run(A, B, want_acc=False)
+    assert_bits_equal(got, O.matmul_w8a8(A, B, None, None, None), "extreme values")
+    # rows whose results leave the bfloat16 range: finite overflow saturates, infinities stay, as in the oracle
+    A, B, sA, sB, bias = make_case(32, 1024, 512, 78)
+    sA = sA.copy()
+    sA[::3] *= np.float32(3e37)
+    want = O.matmul_w8a8(A, B, sA, sB, bias)
+    got, _ = run(A, B, sA, sB, bias, want_acc=False)
+    assert_bits_equal(got, want, "saturation")
+    assert (want == 0x7F7F).any() or (want == 0xFF7F).any(), "the case must saturate somewhere"
