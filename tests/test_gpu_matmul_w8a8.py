@@ -441,3 +441,26 @@ def test_few_rows_kernel_optional_operands_and_extremes(monkeypatch):
     got, _ = run(A, B, sA, sB, bias, want_acc=False)
     assert_bits_equal(got, want, "saturation")
     assert (want == 0x7F7F).any() or (want == 0xFF7F).any(), "the case must saturate somewhere"
+
+
+def test_read_rate_yardstick_of_the_few_rows_kernels(tmp_path, capsys):
+    """Builds and runs tests/cpp/read_pattern_probe.cu: the weight matrix read once with the few-row kernels' work split
+    and three request shapes.  The table is printed (run with -s to see it); the check is only that every variant ran
+    and reached a rate of the right order."""
+    import os
+    import shutil
+    import subprocess
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    nvcc = shutil.which("nvcc") or os.path.join(cuda_home, "bin", "nvcc")
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc is needed to build the probe")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = tmp_path / "read_pattern_probe"
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", str(exe),
+                    os.path.join(root, "tests", "cpp", "read_pattern_probe.cu")], check=True, capture_output=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "done" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+    with capsys.disabled():
+        print("\n" + r.stdout)
+    rates = [float(line.split("us")[1].split("GB/s")[0]) for line in r.stdout.splitlines() if "GB/s" in line]
+    assert len(rates) == 18 and min(rates) > 500.0 and all("no error" in line for line in r.stdout.splitlines() if "GB/s" in line), rates
