@@ -992,8 +992,40 @@ def run_published_shapes(torch, ops, dev, steps, warmup):
     return out
 
 
+def few_rows_section(torch, ops, dev, add):
+    """The matmuls with at most 32 activation rows (a decode step): bound by reading the 8192 x 8192 int8 weight once.  Six
+    weight matrices (400 MB) rotate, so every launch reads its weight from HBM; each line is timed beside the form it
+    replaces (two launches / the tcgen05 kernel), selected through the environment."""
+    Nw = Kw = 8192
+    nw = 6
+    Bw = [torch.randint(-128, 128, (Nw, Kw), dtype=torch.int8, device=dev) for _ in range(nw)]
+    wsw = torch.empty(Nw * Kw * 2, dtype=torch.uint8, device=dev)
+    for dt, nm in ((torch.float16, "half"), (torch.bfloat16, "bfloat16")):
+        scw = (torch.rand(Nw, device=dev) * 0.02).to(dt)
+        ofw = torch.randn(Nw, device=dev).to(dt)
+        for Mw in (1, 8, 16, 32):
+            Aw = torch.randn((Mw, Kw), device=dev).to(dt)
+            Cw = torch.empty((Mw, Nw), dtype=dt, device=dev)
+            for form, label in (("small", "weight converted in registers"), ("twostep", "AscendAntiQuant launch, then the matmul")):
+                os.environ["ASCQ_W8A16"] = form
+                add(f"weight-only-quantised matmul, {Mw} x 8192 {nm} activations, 8192 x 8192 int8 weight, {label}",
+                    lambda i: ops.MatmulW8A16(Cw, Aw, Bw[i % nw], ofw, scw, workspace=wsw), float(Nw * Kw), "TB/s of weight bytes")
+            os.environ.pop("ASCQ_W8A16", None)
+    sBw = torch.rand(Nw, device=dev) * 0.01
+    for Mw in (1, 16, 32):
+        A8w = torch.randint(-127, 128, (Mw, Kw), dtype=torch.int8, device=dev)
+        sAw = torch.rand(Mw, device=dev) * 0.02
+        C8w = torch.empty((Mw, Nw), dtype=torch.bfloat16, device=dev)
+        for small, label in (("1", "few-row kernel"), ("0", "tcgen05 kernel")):
+            os.environ["ASCQ_W8A8_SMALL"] = small
+            add(f"W8A8 matmul + dequant, {Mw} x 8192 int8 activations, 8192 x 8192 int8 weight, {label}",
+                lambda i: ops.MatmulW8A8(C8w, A8w, Bw[i % nw], sAw, sBw, None), float(Nw * Kw), "TB/s of weight bytes")
+        os.environ.pop("ASCQ_W8A8_SMALL", None)
+    del Bw, wsw
+
+
 def run_extras(args):
-    """`--workload extras`: the operators of the path that are not among the five benchmark configurations, each timed
+    """`--workload extras` (`--workload few_rows`: its few-row matmul section alone): the operators of the path that are not among the five benchmark configurations, each timed
     the same way (K steps replayed from one CUDA graph, CUDA events, inputs rotated over more than the L2 size where
     one set is smaller) and reported in one JSON line.  Single GPU."""
     import ctypes as C
@@ -1005,6 +1037,7 @@ def run_extras(args):
     dev = torch.device("cuda:0")
     steps, warm = min(args.steps, 40), max(args.warmup, 3)
     out = {}
+    few_rows_only = args.workload == "few_rows"
 
     def add(name, fn, work, unit):
         secs = time_graph(torch, fn, steps, warm)
@@ -1014,6 +1047,12 @@ def run_extras(args):
         out[name] = {"us": round(us, 1), "rate": round(work / us / 1e6, 2), "unit": unit}  # work per us -> T(unit)/s
         print(f"extras: {name}: {us:.1f} us, {work / us / 1e6:.2f} {unit}", file=sys.stderr)
 
+    if few_rows_only:
+        few_rows_section(torch, ops, dev, add)
+        ops.MatmulStatus()
+        print(json.dumps({"metric": "matmuls with at most 32 activation rows, 8192 x 8192 int8 weight", "n_gpus": 1, "steps": steps, "warmup": warm,
+                          "data": "synthetic", "launch": "the K steps replayed from one CUDA graph", "few_rows": out}))
+        return
     # ---- matmuls at 4096^3 (six operand sets: 200 MB of operands) ----
     M = N = K = 4096
     ns = 6
@@ -1044,33 +1083,7 @@ def run_extras(args):
         add(f"weight-only-quantised matmul, int4 weights, {nm} activations", lambda i: ops.MatmulW4A16(Cc[i % ns], A[i % ns], B4[i % ns], of, sc, workspace=ws), flop, "TFLOPS")
         del A, B, Cc
     del B8, Cb
-    # ---- weight-only-quantised matmul with few activation rows: bound by reading the int8 weight once ----
-    Nw = Kw = 8192
-    nw = 6
-    Bw = [torch.randint(-128, 128, (Nw, Kw), dtype=torch.int8, device=dev) for _ in range(nw)]
-    wsw = torch.empty(Nw * Kw * 2, dtype=torch.uint8, device=dev)
-    for dt, nm in ((torch.float16, "half"), (torch.bfloat16, "bfloat16")):
-        scw = (torch.rand(Nw, device=dev) * 0.02).to(dt)
-        ofw = torch.randn(Nw, device=dev).to(dt)
-        for Mw in (1, 8, 16, 32):
-            Aw = torch.randn((Mw, Kw), device=dev).to(dt)
-            Cw = torch.empty((Mw, Nw), dtype=dt, device=dev)
-            for form, label in (("small", "weight converted in registers"), ("twostep", "AscendAntiQuant launch, then the matmul")):
-                os.environ["ASCQ_W8A16"] = form
-                add(f"weight-only-quantised matmul, {Mw} x 8192 {nm} activations, 8192 x 8192 int8 weight, {label}",
-                    lambda i: ops.MatmulW8A16(Cw, Aw, Bw[i % nw], ofw, scw, workspace=wsw), float(Nw * Kw), "TB/s of weight bytes")
-            os.environ.pop("ASCQ_W8A16", None)
-    sBw = torch.rand(Nw, device=dev) * 0.01
-    for Mw in (1, 16, 32):
-        A8w = torch.randint(-127, 128, (Mw, Kw), dtype=torch.int8, device=dev)
-        sAw = torch.rand(Mw, device=dev) * 0.02
-        C8w = torch.empty((Mw, Nw), dtype=torch.bfloat16, device=dev)
-        for small, label in (("1", "few-row kernel"), ("0", "tcgen05 kernel")):
-            os.environ["ASCQ_W8A8_SMALL"] = small
-            add(f"W8A8 matmul + dequant, {Mw} x 8192 int8 activations, 8192 x 8192 int8 weight, {label}",
-                lambda i: ops.MatmulW8A8(C8w, A8w, Bw[i % nw], sAw, sBw, None), float(Nw * Kw), "TB/s of weight bytes")
-        os.environ.pop("ASCQ_W8A8_SMALL", None)
-    del Bw, wsw
+    few_rows_section(torch, ops, dev, add)
     # ---- MX matmul with fp8 operands at config 5's shape (uniform groups) ----
     G, K5, N5, sumM = 16, 7168, 2048, 16384
     groups = [sumM // G] * G
@@ -1202,7 +1215,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "extras"] + list(WORKLOADS))
+    ap.add_argument("--workload", default="all", choices=["all", "extras", "few_rows"] + list(WORKLOADS))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     # Libraries (NCCL's version banner, for one) write to file descriptor 1; the JSON line must be the only thing on
@@ -1212,10 +1225,10 @@ def main():
     os.dup2(2, 1)
     sys.stdout = os.fdopen(real_stdout, "w")
     if args.impl == "reference":
-        if args.workload == "extras":
+        if args.workload in ("extras", "few_rows"):
             args.workload = "all"
         run_reference(args)
-    elif args.workload == "extras":
+    elif args.workload in ("extras", "few_rows"):
         run_extras(args)
     else:
         run_ours(args)
