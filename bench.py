@@ -130,11 +130,11 @@ class AntiQuantCfg2(Workload):
         s = i % self.nsets
         self.ops.AscendAntiQuant(self.out[s], self.w[s], self.offset, self.scale, self.para)
 
-    def e2e_step(self, i):
-        s = i % self.nsets
-        self.w[s].copy_(self.h_in, non_blocking=True)
-        self.ops.AscendAntiQuant(self.out[s], self.w[s], self.offset, self.scale, self.para)
-        self.h_out.copy_(self.out[s], non_blocking=True)
+    def e2e_in(self, i):
+        self.w[i % self.nsets].copy_(self.h_in, non_blocking=True)
+
+    def e2e_out(self, i):
+        self.h_out.copy_(self.out[i % self.nsets], non_blocking=True)
 
     def e2e_bytes(self):
         return self.K * self.N, self.K * self.N * 2
@@ -188,11 +188,11 @@ class DequantCfg3(Workload):
         s = i % self.nsets
         self.ops.AscendDequant(self.out[s], self.acc[s], self.sch, self.params, tokScale=self.stok)
 
-    def e2e_step(self, i):
-        s = i % self.nsets
-        self.acc[s].copy_(self.h_in, non_blocking=True)
-        self.ops.AscendDequant(self.out[s], self.acc[s], self.sch, self.params, tokScale=self.stok)
-        self.h_out.copy_(self.out[s], non_blocking=True)
+    def e2e_in(self, i):
+        self.acc[i % self.nsets].copy_(self.h_in, non_blocking=True)
+
+    def e2e_out(self, i):
+        self.h_out.copy_(self.out[i % self.nsets], non_blocking=True)
 
     def e2e_bytes(self):
         return self.M * self.N * 4, self.M * self.N * 2
@@ -245,11 +245,11 @@ class QuantScaled(Workload):
         s = i % self.nsets
         self.ops.AscendQuant(self.out[s], self.x[s], 64.0, 0.0, self.rows * self.cols)
 
-    def e2e_step(self, i):
-        s = i % self.nsets
-        self.x[s].copy_(self.h_in, non_blocking=True)
-        self.ops.AscendQuant(self.out[s], self.x[s], 64.0, 0.0, self.rows * self.cols)
-        self.h_out.copy_(self.out[s], non_blocking=True)
+    def e2e_in(self, i):
+        self.x[i % self.nsets].copy_(self.h_in, non_blocking=True)
+
+    def e2e_out(self, i):
+        self.h_out.copy_(self.out[i % self.nsets], non_blocking=True)
 
     def e2e_bytes(self):
         return self.rows * self.cols * 2, self.rows * self.cols
@@ -316,6 +316,7 @@ class W8A8Cfg4(Workload):
         self.B = [torch.from_numpy(np.ascontiguousarray(h["B"][n0:n0 + self.nl])).to(dev) for _ in range(self.nsets)]
         self.C = [torch.empty((self.M, self.nl), dtype=torch.bfloat16, device=dev) for _ in range(self.nsets)]
         self.sA = torch.from_numpy(h["sA"]).to(dev)
+        self.sA_sets = [self.sA.clone() for _ in range(self.nsets)]   # one copy per operand set: the end-to-end pipeline refills them
         self.sB = torch.from_numpy(h["sB"][n0:n0 + self.nl].copy()).to(dev)
         self.bias = bf(h["bias"][n0:n0 + self.nl])
         self.gathered = torch.empty((world * self.M, self.nl), dtype=torch.bfloat16, device=dev) if world > 1 else None
@@ -340,10 +341,10 @@ class W8A8Cfg4(Workload):
     def step(self, i):
         s = i % self.nsets
         if self.world == 1:
-            self.ops.MatmulW8A8(self.C[s], self.A[s], self.B[s], self.sA, self.sB, self.bias)
+            self.ops.MatmulW8A8(self.C[s], self.A[s], self.B[s], self.sA_of(s), self.sB, self.bias)
         else:
             f = i % 2
-            self.ops.MatmulW8A8Sharded(self.sh.comm, self.sh.ptrs[f], self.A[s], self.B[s], self.sA, self.sB, self.bias, N=self.N,
+            self.ops.MatmulW8A8Sharded(self.sh.comm, self.sh.ptrs[f], self.A[s], self.B[s], self.sA_of(s), self.sB, self.bias, N=self.N,
                                        multicast_ptr=self.sh.mc[f] if self.variant == "multicast" else 0)
 
     def nccl_step(self, i):
@@ -358,13 +359,17 @@ class W8A8Cfg4(Workload):
     def single_gpu_step(self, i):
         self.ops.MatmulW8A8(self.C_all, self.A[i % self.nsets], self.B_all, self.sA, self.sB_all, self.bias_all)
 
-    def e2e_step(self, i):
+    def sA_of(self, s):
+        return self.sA_sets[s]
+
+    def e2e_in(self, i):
         s = i % self.nsets
         self.A[s].copy_(self.h_A, non_blocking=True)     # this step's activations and their scales
-        self.sA.copy_(self.h_sA, non_blocking=True)
-        self.step(i)
+        self.sA_of(s).copy_(self.h_sA, non_blocking=True)
+
+    def e2e_out(self, i):
         if self.world == 1:
-            self.h_C.copy_(self.C[s], non_blocking=True)
+            self.h_C.copy_(self.C[i % self.nsets], non_blocking=True)
         else:   # every rank reads back its own column block of the assembled matrix
             n0 = self.rank * self.nl
             self.h_C.copy_(self.sh.full[i % 2][:, n0:n0 + self.nl], non_blocking=True)
@@ -505,13 +510,14 @@ class Mxfp4Cfg5(Workload):
         self.padded[:self.local_rows].copy_(self.C[s][:self.local_rows])
         self.dist.all_gather_into_tensor(self.gathered, self.padded)
 
-    def e2e_step(self, i):
+    def e2e_in(self, i):
         s = i % self.nsets
         self.A[s].copy_(self.h_A, non_blocking=True)      # this step's tokens and their scales; expert weights stay resident
         self.sA[s].copy_(self.h_sA, non_blocking=True)
-        self.step(i)
+
+    def e2e_out(self, i):
         if self.world == 1:
-            self.h_C.copy_(self.C[s], non_blocking=True)
+            self.h_C.copy_(self.C[i % self.nsets], non_blocking=True)
         else:   # every rank reads back the rows of its own groups from the assembled matrix
             at = 0
             for r0, n in zip(self.out_row_start, self.groups):
@@ -666,17 +672,68 @@ def _regions(torch, dist, run_region, first_sec):
     return [float(v) for v in secs.cpu()]
 
 
-def time_steps(torch, fn, steps, warmup, dist=None, repeats=True):
+class E2EPipeline:
+    """The end-to-end step of a workload as a three-stage pipeline over three streams: while the kernel of step i runs on
+    the launching stream, the copy engines bring step i + 1's input from pinned host memory and take step i - 1's result
+    back (PCIe carries both directions at once).  Every step still copies its own input in and its own result out inside
+    the timed region; `drain` makes the launching stream wait for the last result, so a region's end event covers all of
+    its copies.  Order kept by events: the input copy into a buffer set waits for the kernel that last read that set;
+    a kernel waits for its input and for the previous step's result copy (which also keeps a peer's next-but-one step
+    from overwriting an assembled matrix that is still being read out)."""
+
+    def __init__(self, torch, wl):
+        self.torch, self.wl = torch, wl
+        self.h2d, self.d2h = torch.cuda.Stream(), torch.cuda.Stream()
+        self.ev_in = torch.cuda.Event()
+        self.ev_done = [torch.cuda.Event() for _ in range(wl.nsets)]
+        self.ev_out = torch.cuda.Event()
+        self.ev_begin = torch.cuda.Event()
+
+    def begin(self):    # no copy of a region starts before the region does
+        cur = self.torch.cuda.current_stream()
+        self.ev_begin.record(cur)
+        self.h2d.wait_event(self.ev_begin)
+        self.d2h.wait_event(self.ev_begin)
+
+    def step(self, i):
+        t, wl = self.torch, self.wl
+        cur = t.cuda.current_stream()
+        s = i % wl.nsets
+        self.h2d.wait_event(self.ev_done[s])      # (an event never recorded counts as complete)
+        with t.cuda.stream(self.h2d):
+            wl.e2e_in(i)
+            self.ev_in.record()
+        cur.wait_event(self.ev_in)
+        cur.wait_event(self.ev_out)
+        wl.step(i)
+        self.ev_done[s].record(cur)
+        self.d2h.wait_event(self.ev_done[s])
+        with t.cuda.stream(self.d2h):
+            wl.e2e_out(i)
+            self.ev_out.record()
+
+    def drain(self):
+        self.torch.cuda.current_stream().wait_event(self.ev_out)
+
+
+def time_steps(torch, fn, steps, warmup, dist=None, repeats=True, before=None, after=None):
     """W untimed calls of fn(i), then regions of K host-launched calls each (see _regions).  Returns the list of region
-    durations in seconds (one region when repeats is False)."""
+    durations in seconds (one region when repeats is False).  `before` / `after` run inside every timed region, at its
+    start and its end."""
     _sync_ranks(torch, dist)
     for i in range(warmup):
         fn(i)
+    if after:
+        after()
     _sync_ranks(torch, dist)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    if before:
+        before()
     for i in range(steps):
         fn(warmup + i)
+    if after:
+        after()
     e1.record()
     _sync_ranks(torch, dist)
     first = e0.elapsed_time(e1) / 1e3
@@ -687,8 +744,12 @@ def time_steps(torch, fn, steps, warmup, dist=None, repeats=True):
         return [float(t.item())]
 
     def region():
+        if before:
+            before()
         for i in range(steps):
             fn(warmup + i)
+        if after:
+            after()
     return _regions(torch, dist, region, first)
 
 
@@ -842,15 +903,19 @@ def run_ours(args):
         if world == 1:
             roof["traffic"] = profile_traffic(nm)
             roof["traffic_source"] = f"profiles/{nm}_ncu_counters.md" if roof["traffic"] is not None else None
-        e2e_steps = max(2, steps // 4)
-        e2e_sec = float(np.median(time_steps(torch, wl.e2e_step, e2e_steps, 2, dist)))
+        e2e_steps = max(4, steps // 4)
+        pipe = E2EPipeline(torch, wl)
+        e2e_sec = float(np.median(time_steps(torch, pipe.step, e2e_steps, 2, dist, before=pipe.begin, after=pipe.drain)))
         e2e_per = e2e_sec / e2e_steps
         h2d, d2h = wl.e2e_bytes()
         e2e_value = (work / e2e_per / 1e12 if sharded else
                      work / e2e_per / 1e12 * world if wl.bound == "tensor" else work / e2e_per / 1e9 * world)
         rec = {"name": wl.name, "value": total_value, "unit": wl.unit, "ms_per_step": per * 1e3,
                "roofline": roof, "timing": stats,
-               "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+               "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "steps_per_region": e2e_steps,
+                       "pipeline": "three streams: the input copy of step i+1 and the result copy of step i-1 overlap the kernel of step i; "
+                                   "every region ends with the last result on the host"},
                "scaling": "strong" if sharded else "weak",
                "nsets": wl.nsets, "launches_per_step": wl.launches_per_step, "launch": launch,
                "ms_per_step_host_launched": stats["host_launched_median_ms_per_step"]}
