@@ -128,7 +128,10 @@ __device__ __forceinline__ void antiquant32(const Word8& raw, CT s, CT o, bool p
 template <typename CT, typename Dst, bool HAS_OFF, int MB, int DEPTH, bool XAHEAD, int MINB>
 __global__ void __launch_bounds__(32 * kWarps, MINB) w8a16_small_kernel(const SmallParams p)
 {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the reduction may be scheduled; it waits for this grid's end
+    // launched programmatically, and so is what follows (the reduction, or the next call's kernel): each may be scheduled
+    // early and waits for its predecessor's end before it touches memory
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int n0 = blockIdx.x * kRowsPerCta + warp * 16;
     if (n0 >= p.N) return;
@@ -288,10 +291,18 @@ cudaError_t launch_small(const SmallParams& p, dim3 grid, cudaStream_t st)
     // Measured on B200 at N = K = 4096 and 8192: resident warps count for more than loads in flight per warp, so the
     // variants trade registers (ring depth 1, activations ahead only where they fit) for CTAs per SM.
     constexpr bool kHalf = std::is_same<Dst, __half>::value;
-    if (mb <= 1) w8a16_small_kernel<CT, Dst, HAS_OFF, 1, 1, kHalf, 5><<<grid, 32 * kWarps, 0, st>>>(p);
-    else if (mb <= 2) w8a16_small_kernel<CT, Dst, HAS_OFF, 2, 1, true, kHalf ? 4 : 3><<<grid, 32 * kWarps, 0, st>>>(p);
-    else w8a16_small_kernel<CT, Dst, HAS_OFF, 4, 1, false, 3><<<grid, 32 * kWarps, 0, st>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(32 * kWarps, 1, 1);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (mb <= 1) return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 1, 1, kHalf, 5>, p);
+    if (mb <= 2) return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 2, 1, true, kHalf ? 4 : 3>, p);
+    return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 4, 1, false, 3>, p);
 }
 
 template <int OUT> cudaError_t launch_reduce(void* C, const float* partial, int M, int N, int ldc, int splits, cudaStream_t st)

@@ -66,9 +66,14 @@ __device__ __forceinline__ void mma16832(int32_t (&d)[4], uint32_t a0, uint32_t 
 template <int MB, int WARPS, int DEPTH, int MINB>
 __global__ void __launch_bounds__(32 * WARPS, MINB) w8a8_small_kernel(const SmallI8Params p)
 {
+    // launched programmatically: the next launch in the stream may be scheduled now and waits here for this one's
+    // predecessor, so launch latency overlaps the neighbour's tail
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ int32_t red[WARPS][MB * 4 * 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     constexpr int kStep = WARPS * kChunkK;  // distance between two chunks of the same warp
+    constexpr int kEpi = (MB * 4 * 32 + 32 * WARPS - 1) / (32 * WARPS);  // results one thread finishes
     for (int n0 = blockIdx.x * kRows; n0 < p.N; n0 += gridDim.x * kRows) {
         // weight rows of this lane; a row past N is read as row N - 1 and its sums are dropped
         const int rLo = min(n0 + g, p.N - 1), rHi = min(n0 + g + 8, p.N - 1);
@@ -82,6 +87,21 @@ __global__ void __launch_bounds__(32 * WARPS, MINB) w8a8_small_kernel(const Smal
         for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[mb][i] = 0;
+        // the epilogue's operands are requested now, so that their latency is not added at the end: value v of the CTA's
+        // 16 x (8 MB) results is accumulator element i of block mb in lane l, i.e. weight row n0 + l / 4 (+ 8 for
+        // i >= 2) and activation row mb * 8 + 2 * (l % 4) + (i & 1); thread t finishes values t, t + 32 WARPS, ...
+        float eSB[kEpi], eSA[kEpi], eBias[kEpi];
+#pragma unroll
+        for (int e = 0; e < kEpi; ++e) {
+            const int v = threadIdx.x + e * 32 * WARPS;
+            const int l = v & 31, i = (v >> 5) & 3, mb = v >> 7;
+            const int m = mb * 8 + 2 * (l & 3) + (i & 1), n = n0 + (l >> 2) + ((i >> 1) << 3);
+            const bool ok = v < MB * 4 * 32 && m < p.M && n < p.N;
+            // a missing scale counts as 1.0, as in the tcgen05 kernel
+            eSB[e] = (ok && p.sB) ? __ldg(p.sB + n) : 1.0f;
+            eSA[e] = (ok && p.sA) ? __ldg(p.sA + m) : 1.0f;
+            eBias[e] = (ok && p.bias) ? __bfloat162float(p.bias[n]) : 0.0f;
+        }
 
         Word8 ringLo[DEPTH], ringHi[DEPTH];
 #pragma unroll
@@ -124,18 +144,18 @@ __global__ void __launch_bounds__(32 * WARPS, MINB) w8a8_small_kernel(const Smal
 #pragma unroll
             for (int i = 0; i < 4; ++i) red[warp][(mb * 4 + i) * 32 + lane] = acc[mb][i];
         __syncthreads();
-        for (int v = threadIdx.x; v < MB * 4 * 32; v += 32 * WARPS) {
+#pragma unroll
+        for (int e = 0; e < kEpi; ++e) {
+            const int v = threadIdx.x + e * 32 * WARPS;
+            if (v >= MB * 4 * 32) break;
             int32_t sum = red[0][v];
 #pragma unroll
             for (int w = 1; w < WARPS; ++w) sum += red[w][v];
-            // value v: accumulator element i of block mb in lane l: weight row n0 + l / 4 (+ 8 for i >= 2), activation row
-            // mb * 8 + 2 * (l % 4) + (i & 1)
             const int l = v & 31, i = (v >> 5) & 3, mb = v >> 7;
             const int m = mb * 8 + 2 * (l & 3) + (i & 1), n = n0 + (l >> 2) + ((i >> 1) << 3);
             if (m >= p.M || n >= p.N) continue;
-            // a missing scale counts as 1.0, as in the tcgen05 kernel
-            float f = __fmul_rn(__fmul_rn(__int2float_rn(sum), p.sB ? p.sB[n] : 1.0f), p.sA ? p.sA[m] : 1.0f);
-            if (p.bias != nullptr) f = __fadd_rn(f, __bfloat162float(p.bias[n]));
+            float f = __fmul_rn(__fmul_rn(__int2float_rn(sum), eSB[e]), eSA[e]);
+            if (p.bias != nullptr) f = __fadd_rn(f, eBias[e]);
             p.C[static_cast<size_t>(m) * p.ldc + p.colOffset + n] = f32_to_bf16_sat(f);
         }
         __syncthreads();  // `red` is reused by the next block of rows
@@ -144,9 +164,16 @@ __global__ void __launch_bounds__(32 * WARPS, MINB) w8a8_small_kernel(const Smal
 
 template <int MB, int WARPS, int DEPTH, int MINB> cudaError_t launch_i8(const SmallI8Params& p, int rowBlocks, cudaStream_t st)
 {
-    const int grid = std::min(rowBlocks, MINB * static_cast<int>(sm_count()));
-    w8a8_small_kernel<MB, WARPS, DEPTH, MINB><<<grid, 32 * WARPS, 0, st>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(std::min(rowBlocks, MINB * static_cast<int>(sm_count()))), 1, 1);
+    cfg.blockDim = dim3(32 * WARPS, 1, 1);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, w8a8_small_kernel<MB, WARPS, DEPTH, MINB>, p);
 }
 
 // CTAs per SM the variants are compiled for (the MINB of the launches below)
@@ -155,8 +182,9 @@ int ctas_per_sm(int warps) { return warps == 8 ? 2 : 4; }
 }  // namespace
 
 // Whether the few-row kernel should take a plain W8A8 call.  Beside the shape limits: every CTA owns 16 weight rows over
-// the whole of K, so the launch is one wave of CTAs when N / 16 fits the resident CTAs, and the last wave must not be
-// nearly empty otherwise.
+// the whole of K, so the launch is one wave of CTAs when N / 16 fits the resident CTAs.  With two waves it still wins
+// (measured at N = 11008 to 16384, K = 4096) for at most 16 rows when the second wave is reasonably full; beyond that the
+// tcgen05 kernel is as fast or faster.
 bool w8a8_small_applies(int M, int N, int K, const void* A, const void* B)
 {
     if (M < 1 || M > kW8A8SmallMaxM || K % kChunkK || K < 4 * kChunkK) return false;
@@ -165,7 +193,7 @@ bool w8a8_small_applies(int M, int N, int K, const void* A, const void* B)
     const int warps = rowBlocks <= 2 * static_cast<int>(sm_count()) ? 8 : 4;
     const int slots = ctas_per_sm(warps) * static_cast<int>(sm_count());
     const int waves = (rowBlocks + slots - 1) / slots;
-    return static_cast<double>(rowBlocks) >= 0.7 * waves * slots || waves == 1;
+    return waves == 1 || (M <= 16 && waves == 2 && static_cast<double>(rowBlocks) >= 0.6 * waves * slots);
 }
 
 ascq_status w8a8_small(void* C, const int8_t* A, const int8_t* B_nk, const float* sA_m, const float* sB_n, const void* bias_bf16,
