@@ -903,7 +903,7 @@ def run_ours(args):
         if world == 1:
             roof["traffic"] = profile_traffic(nm)
             roof["traffic_source"] = f"profiles/{nm}_ncu_counters.md" if roof["traffic"] is not None else None
-        e2e_steps = max(4, steps // 4)
+        e2e_steps = max(4, min(steps, 64))
         pipe = E2EPipeline(torch, wl)
         e2e_sec = float(np.median(time_steps(torch, pipe.step, e2e_steps, 2, dist, before=pipe.begin, after=pipe.drain)))
         e2e_per = e2e_sec / e2e_steps
