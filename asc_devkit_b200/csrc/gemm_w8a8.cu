@@ -1096,10 +1096,17 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     // idle until the first tiles are done: 128 x 128 tiles bring the first results out after half the time and in more,
     // smaller waves (measured: 49.2 against 50.0 us per step on two GPUs, 63.6 against 66.0 on four).
     if ((nBufs > 1 || multicast) && costNarrow <= 1.3 * (costWide < costPair ? costWide : costPair)) mode = 0;
+    // A skinny product whose 64-column tiles still fit the SMs in one wave is bound by streaming B: those tiles put twice
+    // as many CTAs on that as 128-column ones (mode 3, built for the dequant and the half / bfloat16 epilogues of one plain
+    // matrix; measured 8192 x 8192, M = 128: 17.7 against 20.9 us; with a second wave it loses).
+    const bool slimBuilt = (epi == kEpiDequant || (epi == kEpiFloat && !fix->convert && fix->outKind <= 2)) && gt.G == 0 && nBufs <= 1 && !multicast;
+    const long long tiles64 = static_cast<long long>(tilesM) * ((N + 63) / 64);
+    if (slimBuilt && tiles64 <= units && tiles64 > tiles128) mode = 3;
     if (const char* e = getenv("ASCQ_W8A8_TILE")) {
         if (!strcmp(e, "pair")) mode = 2;
         else if (!strcmp(e, "wide")) mode = 1;
         else if (!strcmp(e, "narrow")) mode = 0;
+        else if (!strcmp(e, "slim") && slimBuilt) mode = 3;
     }
     // 16-bit result in one suitably aligned buffer: TMA stores (ASCQ_W8A8_STORE=plain keeps the per-thread stores)
     const bool out16 = epi == kEpiDequant || epi == kEpiDequantAct || epi == kEpiFixpipe || (epi == kEpiFloat && fix->outKind <= 1);
@@ -1113,7 +1120,7 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     ascq_status rc = make_tmap_u8(&ta, A, static_cast<uint64_t>(M), static_cast<uint64_t>(K) * elemBytes, kBM);
     if (rc != ASCQ_OK) return rc;
     const uint64_t rowsB = static_cast<uint64_t>(N) * (gt.G > 0 ? gt.G : 1);
-    rc = make_tmap_u8(&tb, B_nk, rowsB, static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : 128);
+    rc = make_tmap_u8(&tb, B_nk, rowsB, static_cast<uint64_t>(K) * elemBytes, mode == 1 ? 256 : (mode == 3 ? 64 : 128));
     if (rc != ASCQ_OK) return rc;
     for (int i = 0; i < kMaxPeers; ++i) tc.m[i] = ta;  // placeholders; the kernel reads maps [0, nPeers) and only for TMA stores
     tc.bHalf = tb;
@@ -1144,6 +1151,7 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         return launch<256, true, kEpiFloat, true>(ta, tb, tc, p, st, gt);
     }
     if (epi == kEpiFloat) {
+        if (mode == 3) return launch<64, false, kEpiFloat>(ta, tb, tc, p, st, gt);
         if (mode == 2) return launch<256, true, kEpiFloat>(ta, tb, tc, p, st, gt);
         return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiFloat>(ta, tb, tc, p, st, gt);
     }
@@ -1159,6 +1167,7 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         if (mode == 2) return launch<256, true, kEpiDequantAct>(ta, tb, tc, p, st, gt);
         return mode == 1 ? launch<256, false, kEpiDequantAct>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiDequantAct>(ta, tb, tc, p, st, gt);
     }
+    if (mode == 3) return launch<64, false>(ta, tb, tc, p, st, gt);
     if (mode == 2) return launch<256, true>(ta, tb, tc, p, st, gt);
     return mode == 1 ? launch<256, false>(ta, tb, tc, p, st, gt) : launch<128, false>(ta, tb, tc, p, st, gt);
 }

@@ -20,7 +20,7 @@ def close(got, want):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 520, 264), (257, 384, 1024), (2048, 1024, 512)])
 @pytest.mark.parametrize("abT,cT", [(O.F16, O.F16), (O.F16, O.F32), (O.BF16, O.BF16), (O.BF16, O.F32)])
-@pytest.mark.parametrize("tile", ["pair", "wide", "narrow"])
+@pytest.mark.parametrize("tile", ["pair", "wide", "narrow", "slim"])
 def test_matmul_f16(M, N, K, abT, cT, tile, monkeypatch):
     monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
     rng = np.random.default_rng(M + N + K + abT)

@@ -464,3 +464,23 @@ def test_read_rate_yardstick_of_the_few_rows_kernels(tmp_path, capsys):
         print("\n" + r.stdout)
     rates = [float(line.split("us")[1].split("GB/s")[0]) for line in r.stdout.splitlines() if "GB/s" in line]
     assert len(rates) == 18 and min(rates) > 500.0 and all("no error" in line for line in r.stdout.splitlines() if "GB/s" in line), rates
+
+
+# ---- skinny products on 64-column tiles ----------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(33, 128, 128), (100, 520, 1024), (128, 4096, 4096), (200, 1000, 272), (256, 8192, 512),
+                                   (700, 300, 640)])
+@pytest.mark.parametrize("forced", [True, False])
+def test_skinny_products_on_64_column_tiles(M, N, K, forced, monkeypatch):
+    """One or two row tiles and fewer 128-column tiles than SMs: the launch takes 64-column tiles (forced here for every
+    shape, and chosen by the library itself for the skinny ones).  Accumulators and results are the oracle's bits."""
+    if forced:
+        monkeypatch.setenv("ASCQ_W8A8_TILE", "slim")
+    else:
+        monkeypatch.delenv("ASCQ_W8A8_TILE", raising=False)
+    A, B, sA, sB, bias = make_case(M, N, K, M + 3 * N + K)
+    want_C, want_acc = O.matmul_w8a8(A, B, sA, sB, bias, want_acc=True)
+    got_C, got_acc = run(A, B, sA, sB, bias, ldc=N + 8)
+    assert_bits_equal(got_acc, want_acc, "int32 accumulators")
+    assert_bits_equal(got_C[:, :N], want_C, "bf16 epilogue")
+    assert (got_C[:, N:] == 0xBF80).all()
