@@ -36,9 +36,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // gemm_w8a16_small.cu: the weight-only-quantised matmul for at most kW8A16SmallMaxM activation rows
 constexpr int kW8A16SmallMaxM = 32;
 bool w8a16_small_applies(int M, int N, int K, const void* A, const void* B, const void* workspace, size_t workspaceBytes);
-ascq_status w8a16_small(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk, const void* offset, const void* scale,
-                        float offsetScalar, float scaleScalar, bool hasOffset, int M, int N, int K, int ldc, void* workspace,
-                        size_t workspaceBytes, ::CUstream_st* st);
+ascq_status w8a16_small(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk, bool int4, const void* offset,
+                        const void* scale, float offsetScalar, float scaleScalar, bool hasOffset, int M, int N, int K, int ldc,
+                        void* workspace, size_t workspaceBytes, ::CUstream_st* st);
 
 // gemm_w8a8_small.cu: the W8A8 matmul with dequant epilogue for at most kW8A8SmallMaxM activation rows
 constexpr int kW8A8SmallMaxM = 32;

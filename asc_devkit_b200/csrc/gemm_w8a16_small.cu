@@ -28,7 +28,7 @@ constexpr int kRowsPerCta = 16 * kWarps;  // weight rows (output columns) per CT
 constexpr int kChunkK = 128;              // k values one warp consumes per step (4 lanes x 32)
 
 struct SmallParams {
-    const int8_t* B;      // [N, K] int8
+    const int8_t* B;      // [N, K] int8, or [N, K / 2] bytes of int4b_t pairs (even k in the low nibble)
     const void* A;        // [M, K] half / bfloat16
     const void* scale;    // [N] of the activation type, or null: scaleScalar / offsetScalar
     const void* offset;   // [N] or null
@@ -70,6 +70,23 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The 32 weights of one lane and row as they lie in memory: 32 bytes of int8 or 16 bytes of int4b_t pairs.
+template <bool I4> struct RawRow {
+    uint32_t w[I4 ? 4 : 8];
+};
+template <bool I4> __device__ __forceinline__ RawRow<I4> ld_weights(const void* p)
+{
+    RawRow<I4> v;
+    if constexpr (I4) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(p));
+    } else {
+        const Word8 t = ld_stream32(p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v.w[i] = t.w[i];
+    }
+    return v;
+}
+
 // 32 int8 weights of one row -> 16 words of two half / bfloat16 values, bit for bit what AscendAntiQuant computes
 // ((w + offset) * scale; half: both steps in half; bfloat16: both steps in fp32, then one rounding to bfloat16), without
 // the conversion pipe: int8 -> half by placing the biased byte in the mantissa of 1024.0 and subtracting 1152.0 (exact),
@@ -77,7 +94,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 // AscendAntiQuant saturates; `plain` is false for a row whose (|offset| + 128) * |scale| could get there, and such a row
 // goes through the elementwise operator's own code.
 template <typename CT, typename Dst, bool HAS_OFF>
-__device__ __forceinline__ void antiquant32(const Word8& raw, CT s, CT o, bool plain, uint32_t (&out)[16])
+__device__ __forceinline__ void antiquant32(const RawRow<false>& raw, CT s, CT o, bool plain, uint32_t (&out)[16])
 {
     if constexpr (std::is_same<Dst, __half>::value) {
         const __half2 s2 = __half2half2(s), o2 = __half2half2(o), bias = __half2half2(__ushort_as_half(0x6480));  // 1152.0
@@ -123,9 +140,74 @@ __device__ __forceinline__ void antiquant32(const Word8& raw, CT s, CT o, bool p
     }
 }
 
+// The int4b_t form of antiquant32: byte j of a word holds the weights k = 2j (low nibble) and 2j + 1.  Half: the byte goes
+// into both halves of a word whose upper bytes are 0x64 (PRMT), a mask keeps the low nibble in one half and the high
+// nibble, in place, in the other (1024 + n and 1024 + 16 n, n biased by 8), and one HFMA2 with the constants
+// {1, 1/16} and {-1032, -72} turns both into the signed weight exactly; then the same two roundings as for int8.
+// bfloat16: the nibbles go through fp32 as for int8.  Rows whose scale could overflow take the elementwise
+// operator's code on nibbles widened to int8, as AscendAntiQuant itself does.
+template <typename CT, typename Dst, bool HAS_OFF>
+__device__ __forceinline__ void antiquant32_i4(const RawRow<true>& raw, CT s, CT o, bool plain, uint32_t (&out)[16])
+{
+    if constexpr (std::is_same<Dst, __half>::value) {
+        const __half2 s2 = __half2half2(s), o2 = __half2half2(o);
+        const __half2 mul = __halves2half2(__ushort_as_half(0x3C00), __ushort_as_half(0x2C00));   // {1, 1/16}
+        const __half2 add = __halves2half2(__ushort_as_half(0xE408), __ushort_as_half(0xD480));   // {-1032, -72}
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t b = raw.w[q] ^ 0x88888888u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t pr = __byte_perm(b, 0x64646464u, 0x4040 + 0x0101 * j) & 0x64F0640Fu;
+                __half2 h = __hfma2(*reinterpret_cast<__half2*>(&pr), mul, add);
+                if constexpr (HAS_OFF) h = __hadd2_rn(h, o2);
+                h = __hmul2_rn(h, s2);
+                out[4 * q + j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+        }
+    } else {
+        if (plain) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t b = raw.w[q] ^ 0x88888888u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    // 2^23 + (n + 8) in the mantissa, minus 2^23 + 8: exact
+                    float f0 = __uint_as_float(0x4B000000u | ((b >> (8 * j)) & 0xFu));
+                    float f1 = __uint_as_float(0x4B000000u | ((b >> (8 * j + 4)) & 0xFu));
+                    add2_rn(f0, f1, -8388616.0f, -8388616.0f);
+                    if constexpr (HAS_OFF) add2_rn(f0, f1, o, o);
+                    mul2_rn(f0, f1, s, s);
+                    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out[4 * q + j]) : "f"(f1), "f"(f0));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                uint32_t w8[4];   // 16 weights widened to int8
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t src = raw.w[2 * hlf + (i >> 1)] >> (16 * (i & 1));   // two bytes = four nibbles
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int n = static_cast<int>((src >> (4 * e)) & 0xFu);
+                        word |= static_cast<uint32_t>(((n ^ 8) - 8) & 0xFF) << (8 * e);
+                    }
+                    w8[i] = word;
+                }
+                uint4 lo, hi;
+                antiquant16<CT, Dst, HAS_OFF>(make_uint4(w8[0], w8[1], w8[2], w8[3]), s, o, lo, hi);
+                out[8 * hlf + 0] = lo.x; out[8 * hlf + 1] = lo.y; out[8 * hlf + 2] = lo.z; out[8 * hlf + 3] = lo.w;
+                out[8 * hlf + 4] = hi.x; out[8 * hlf + 5] = hi.y; out[8 * hlf + 6] = hi.z; out[8 * hlf + 7] = hi.w;
+            }
+        }
+    }
+}
+
 // MB: blocks of 8 activation rows (M <= 8 * MB); DEPTH: weight chunks in flight per lane; XAHEAD: the activations of the
 // next step are requested before this step's arithmetic (costs 16 * MB registers), else at the start of their own step
-template <typename CT, typename Dst, bool HAS_OFF, int MB, int DEPTH, bool XAHEAD, int MINB>
+template <typename CT, typename Dst, bool HAS_OFF, int MB, int DEPTH, bool XAHEAD, int MINB, bool I4>
 __global__ void __launch_bounds__(32 * kWarps, MINB) w8a16_small_kernel(const SmallParams p)
 {
     // launched programmatically, and so is what follows (the reduction, or the next call's kernel): each may be scheduled
@@ -151,8 +233,9 @@ __global__ void __launch_bounds__(32 * kWarps, MINB) w8a16_small_kernel(const Sm
     const CT sLo = Ct<CT>::from_f32(fsLo), sHi = Ct<CT>::from_f32(fsHi), oLo = Ct<CT>::from_f32(foLo), oHi = Ct<CT>::from_f32(foHi);
     // warp-uniform, so the conversion does not diverge
     const bool plain = __all_sync(0xFFFFFFFFu, !((fabsf(foLo) + 128.f) * fabsf(fsLo) >= 3.0e38f) && !((fabsf(foHi) + 128.f) * fabsf(fsHi) >= 3.0e38f));
-    const int8_t* wLo = p.B + static_cast<size_t>(rLo) * p.K + 32 * c;
-    const int8_t* wHi = p.B + static_cast<size_t>(rHi) * p.K + 32 * c;
+    constexpr int kPack = I4 ? 2 : 1;   // weights per byte
+    const int8_t* wLo = p.B + (static_cast<size_t>(rLo) * p.K + 32 * c) / kPack;
+    const int8_t* wHi = p.B + (static_cast<size_t>(rHi) * p.K + 32 * c) / kPack;
     const Dst* x = static_cast<const Dst*>(p.A) + 32 * c;
 
     float acc[MB][4];
@@ -176,13 +259,13 @@ __global__ void __launch_bounds__(32 * kWarps, MINB) w8a16_small_kernel(const Sm
         }
     };
     // a ring of DEPTH weight chunks in flight per lane: the loads of step s + DEPTH are issued before step s is consumed
-    Word8 ringLo[DEPTH], ringHi[DEPTH];
+    RawRow<I4> ringLo[DEPTH], ringHi[DEPTH];
 #pragma unroll
     for (int d = 0; d < DEPTH; ++d) {
         const int k = kBeg + d * kChunkK;
         if (k < kEnd) {
-            ringLo[d] = ld_stream32(wLo + k);
-            ringHi[d] = ld_stream32(wHi + k);
+            ringLo[d] = ld_weights<I4>(wLo + k / kPack);
+            ringHi[d] = ld_weights<I4>(wHi + k / kPack);
         }
     }
     Word8 xCur[MB][2];
@@ -192,18 +275,23 @@ __global__ void __launch_bounds__(32 * kWarps, MINB) w8a16_small_kernel(const Sm
         for (int d = 0; d < DEPTH; ++d) {
             const int k0 = kBase + d * kChunkK;
             if (k0 >= kEnd) break;
-            const Word8 rawLo = ringLo[d], rawHi = ringHi[d];
+            const RawRow<I4> rawLo = ringLo[d], rawHi = ringHi[d];
             const int kNext = k0 + DEPTH * kChunkK;
             if (kNext < kEnd) {
-                ringLo[d] = ld_stream32(wLo + kNext);
-                ringHi[d] = ld_stream32(wHi + kNext);
+                ringLo[d] = ld_weights<I4>(wLo + kNext / kPack);
+                ringHi[d] = ld_weights<I4>(wHi + kNext / kPack);
             }
             Word8 xNext[XAHEAD ? MB : 1][2];
             if constexpr (XAHEAD) load_x(k0 + kChunkK, xNext);
             else load_x(k0, xCur);
             uint32_t al[16], ah[16];  // word i: elements 2i, 2i + 1 of the lane's 32
-            antiquant32<CT, Dst, HAS_OFF>(rawLo, sLo, oLo, plain, al);
-            antiquant32<CT, Dst, HAS_OFF>(rawHi, sHi, oHi, plain, ah);
+            if constexpr (I4) {
+                antiquant32_i4<CT, Dst, HAS_OFF>(rawLo, sLo, oLo, plain, al);
+                antiquant32_i4<CT, Dst, HAS_OFF>(rawHi, sHi, oHi, plain, ah);
+            } else {
+                antiquant32<CT, Dst, HAS_OFF>(rawLo, sLo, oLo, plain, al);
+                antiquant32<CT, Dst, HAS_OFF>(rawHi, sHi, oHi, plain, ah);
+            }
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
 #pragma unroll
@@ -284,7 +372,7 @@ __global__ void __launch_bounds__(256) w8a16_small_reduce_kernel(void* __restric
 // CTAs per SM the variant chosen below is compiled for (its __launch_bounds__)
 int small_ctas_per_sm(int M, bool half) { return M <= 8 ? 5 : (M <= 16 ? (half ? 4 : 3) : 3); }
 
-template <typename CT, typename Dst, bool HAS_OFF>
+template <typename CT, typename Dst, bool HAS_OFF, bool I4>
 cudaError_t launch_small(const SmallParams& p, dim3 grid, cudaStream_t st)
 {
     const int mb = (p.M + 7) / 8;
@@ -300,9 +388,9 @@ cudaError_t launch_small(const SmallParams& p, dim3 grid, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (mb <= 1) return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 1, 1, kHalf, 5>, p);
-    if (mb <= 2) return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 2, 1, true, kHalf ? 4 : 3>, p);
-    return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 4, 1, false, 3>, p);
+    if (mb <= 1) return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 1, 1, kHalf, 5, I4>, p);
+    if (mb <= 2) return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 2, 1, true, kHalf ? 4 : 3, I4>, p);
+    return cudaLaunchKernelEx(&cfg, w8a16_small_kernel<CT, Dst, HAS_OFF, 4, 1, false, 3, I4>, p);
 }
 
 template <int OUT> cudaError_t launch_reduce(void* C, const float* partial, int M, int N, int ldc, int splits, cudaStream_t st)
@@ -332,9 +420,9 @@ bool w8a16_small_applies(int M, int N, int K, const void* A, const void* B, cons
 // lasts about (number of CTA waves) x (steps per CTA + a fixed start-up cost of about two steps).  The split with the
 // smallest such estimate wins, among those whose partial sums stay below a quarter of the weight bytes and fit the
 // workspace the caller sized for the two-launch form.
-ascq_status w8a16_small(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk, const void* offset, const void* scale,
-                        float offsetScalar, float scaleScalar, bool hasOffset, int M, int N, int K, int ldc, void* workspace,
-                        size_t workspaceBytes, cudaStream_t st)
+ascq_status w8a16_small(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const int8_t* B_nk, bool int4, const void* offset,
+                        const void* scale, float offsetScalar, float scaleScalar, bool hasOffset, int M, int N, int K, int ldc,
+                        void* workspace, size_t workspaceBytes, cudaStream_t st)
 {
     const int rowBlocks = (N + kRowsPerCta - 1) / kRowsPerCta, chunks = K / kChunkK;
     const int slots = small_ctas_per_sm(M, aT == ASCQ_DT_F16) * static_cast<int>(sm_count());
@@ -357,10 +445,12 @@ ascq_status w8a16_small(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, co
     SmallParams p{B_nk, A, scale, offset, scaleScalar, offsetScalar, static_cast<float*>(workspace), C, M, N, K, kPerSplit, ldc, outKind};
     const dim3 grid(static_cast<unsigned>(rowBlocks), static_cast<unsigned>(splits), 1);
     cudaError_t e;
-    if (aT == ASCQ_DT_F16)
-        e = hasOffset ? launch_small<__half, __half, true>(p, grid, st) : launch_small<__half, __half, false>(p, grid, st);
-    else
-        e = hasOffset ? launch_small<float, __nv_bfloat16, true>(p, grid, st) : launch_small<float, __nv_bfloat16, false>(p, grid, st);
+    auto go = [&](auto off, auto i4) {
+        constexpr bool kOff = decltype(off)::value, kI4 = decltype(i4)::value;
+        return aT == ASCQ_DT_F16 ? launch_small<__half, __half, kOff, kI4>(p, grid, st) : launch_small<float, __nv_bfloat16, kOff, kI4>(p, grid, st);
+    };
+    if (int4) e = hasOffset ? go(std::true_type{}, std::true_type{}) : go(std::false_type{}, std::true_type{});
+    else e = hasOffset ? go(std::true_type{}, std::false_type{}) : go(std::false_type{}, std::false_type{});
     ASCQ_CUDA_CHECK(e);
     if (splits == 1) return ASCQ_OK;
     if (cT == ASCQ_DT_F16) e = launch_reduce<0>(C, p.partial, M, N, ldc, splits, st);

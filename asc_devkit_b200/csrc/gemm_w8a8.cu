@@ -1373,7 +1373,7 @@ static ascq_status matmul_wq_a16(ascq_dtype bT, void* C, ascq_dtype cT, const vo
     bool fused = false;
     const char* form = getenv("ASCQ_W8A16");
     if (form) fused = bT == ASCQ_DT_I8 && !strcmp(form, "fused") && (K % 32 == 0) && aligned16(B_nk);
-    if (bT == ASCQ_DT_I8 && (!form || !strcmp(form, "small")) && w8a16_small_applies(M, N, K, A, B_nk, workspace, workspaceBytes)) {
+    if ((!form || !strcmp(form, "small")) && w8a16_small_applies(M, N, K, A, B_nk, workspace, workspaceBytes)) {
         if (!C || !A) return fail(ASCQ_ERR_INVALID_ARG, "C and A must not be NULL");
         if (cT != ASCQ_DT_F16 && cT != ASCQ_DT_BF16 && cT != ASCQ_DT_F32)
             return fail(ASCQ_ERR_UNSUPPORTED, "output must be half, bfloat16_t or float");
@@ -1383,7 +1383,7 @@ static ascq_status matmul_wq_a16(ascq_dtype bT, void* C, ascq_dtype cT, const vo
             if (aT == ASCQ_DT_F16) { ss = __half2float(__float2half_rn(ss)); os = __half2float(__float2half_rn(os)); }
             else { ss = __bfloat162float(__float2bfloat16_rn(ss)); os = __bfloat162float(__float2bfloat16_rn(os)); }
         }
-        return w8a16_small(C, cT, A, aT, B_nk, offset, scale, os, ss, scale ? offset != nullptr : true, M, N, K, ldc, workspace,
+        return w8a16_small(C, cT, A, aT, B_nk, bT == ASCQ_DT_I4X2, offset, scale, os, ss, scale ? offset != nullptr : true, M, N, K, ldc, workspace,
                            workspaceBytes, static_cast<cudaStream_t>(stream));
     }
     if (fused) {

@@ -1076,6 +1076,19 @@ def few_rows_section(torch, ops, dev, add):
                 add(f"weight-only-quantised matmul, {Mw} x 8192 {nm} activations, 8192 x 8192 int8 weight, {label}",
                     lambda i: ops.MatmulW8A16(Cw, Aw, Bw[i % nw], ofw, scw, workspace=wsw), float(Nw * Kw), "TB/s of weight bytes")
             os.environ.pop("ASCQ_W8A16", None)
+    B4w = [b[:, : Kw // 2].contiguous().view(torch.uint8) for b in Bw]   # the same bytes read as int4b_t pairs
+    for dt, nm in ((torch.float16, "half"), (torch.bfloat16, "bfloat16")):
+        scw = (torch.rand(Nw, device=dev) * 0.2).to(dt)
+        ofw = torch.randn(Nw, device=dev).to(dt)
+        for Mw in (1, 16):
+            Aw = torch.randn((Mw, Kw), device=dev).to(dt)
+            Cw = torch.empty((Mw, Nw), dtype=dt, device=dev)
+            for form, label in (("small", "weight converted in registers"), ("twostep", "AscendAntiQuant launch, then the matmul")):
+                os.environ["ASCQ_W8A16"] = form
+                add(f"weight-only-quantised matmul, {Mw} x 8192 {nm} activations, 8192 x 8192 int4 weight, {label}",
+                    lambda i: ops.MatmulW4A16(Cw, Aw, B4w[i % nw], ofw, scw, workspace=wsw), float(Nw * Kw // 2), "TB/s of weight bytes")
+            os.environ.pop("ASCQ_W8A16", None)
+    del B4w
     sBw = torch.rand(Nw, device=dev) * 0.01
     for Mw in (1, 16, 32):
         A8w = torch.randint(-127, 128, (Mw, Kw), dtype=torch.int8, device=dev)

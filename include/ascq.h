@@ -427,7 +427,8 @@ ascq_status ascq_matmul_w8a16(void* C, ascq_dtype cT, const void* A, ascq_dtype 
                               void* workspace, size_t workspaceBytes, void* stream);
 size_t ascq_matmul_w8a16_workspace_size(int N, int K);
 /* The same with int4b_t weights (B_nk_int4: [N, K/2] bytes, two signed nibbles per byte, even k in the low nibble;
- * AscendAntiQuant's int4b_t source, ascend_antiquant_impl.h:246-247).  Same workspace size; always two launches. */
+ * AscendAntiQuant's int4b_t source, ascend_antiquant_impl.h:246-247).  Same workspace size and the same forms: M <= 32
+ * converts the weight in registers, larger M takes two launches (there is no converter-warp form for int4). */
 ascq_status ascq_matmul_w4a16(void* C, ascq_dtype cT, const void* A, ascq_dtype aT, const uint8_t* B_nk_int4, const void* offset,
                               const void* scale, float offsetScalar, float scaleScalar, int M, int N, int K, int ldc,
                               void* workspace, size_t workspaceBytes, void* stream);

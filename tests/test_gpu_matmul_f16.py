@@ -285,3 +285,66 @@ def test_w8a16_few_rows_reads_the_weight_antiquant_produces(abT, with_offset, mo
     ops.MatmulW8A16(C, to_dev(A, abT), torch.from_numpy(B).to(DEV), to_dev(of_h, abT) if with_offset else None, to_dev(sc_h, abT))
     ops.MatmulStatus()
     assert np.array_equal(C.cpu().numpy().view(np.uint32), np.ascontiguousarray(Wf[:, cols].T).view(np.uint32))
+
+
+# ---- int4b_t weights, at most 32 activation rows --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("abT,cT", [(O.F16, O.F16), (O.BF16, O.BF16), (O.BF16, O.F32)])
+@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (7, 516, 384), (8, 4096, 4096), (16, 1000, 1024), (32, 2048, 1024)])
+@pytest.mark.parametrize("per_channel,with_offset", [(True, True), (True, False), (False, True)])
+def test_w4a16_few_rows(abT, cT, M, N, K, per_channel, with_offset, monkeypatch):
+    rng = np.random.default_rng(M + N + K + abT + cT + 5)
+    A = rand_float(rng, (M, K), abT, -1, 1)
+    B4 = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    if per_channel:
+        sc_h = rand_float(rng, (N,), abT, 0.02, 0.2)
+        of_h = rand_float(rng, (N,), abT, -2, 2) if with_offset else None
+        W = O.ascend_antiquant(B4, O.I4X2, abT, policy=O.PER_CHANNEL, m=N, n=K, scale=sc_h, offset=of_h, scaleT=abT, isTranspose=True)
+        scale, offset = to_dev(sc_h, abT), (to_dev(of_h, abT) if with_offset else None)
+    else:
+        scale, offset = 0.125, 1.5
+        W = O.ascend_antiquant(B4, O.I4X2, abT, policy=O.PER_TENSOR, m=N, n=K, scaleScalar=scale, offsetScalar=offset, scaleT=abT,
+                               isTranspose=True, hasOffset=True)
+    _, want = O.matmul_f16(A, W, abT)
+    for form in ("small", "twostep"):
+        monkeypatch.setenv("ASCQ_W8A16", form)
+        C = torch.full((M + 1, N + 8), -1.0, dtype=TDT[cT], device=DEV)
+        ops.MatmulW4A16(C[:M, :N], to_dev(A, abT), torch.from_numpy(B4).to(DEV), offset, scale)
+        ops.MatmulStatus()
+        full = C.float().cpu().numpy()
+        assert (full[M:] == -1.0).all() and (full[:, N:] == -1.0).all(), form
+        close(full[:M, :N], want)
+
+
+@pytest.mark.parametrize("abT", [O.F16, O.BF16])
+@pytest.mark.parametrize("with_offset", [True, False])
+def test_w4a16_few_rows_reads_the_weight_antiquant_produces(abT, with_offset, monkeypatch):
+    """One-hot activation rows copy weight columns into the fp32 result: the int4 weight the tensor cores were fed is
+    AscendAntiQuant's output bit for bit, including (bfloat16) a row that takes the saturating path."""
+    monkeypatch.setenv("ASCQ_W8A16", "small")
+    rng = np.random.default_rng(190 + abT + with_offset)
+    M, N, K = 32, 528, 384
+    B4 = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    sc_h = rand_float(rng, (N,), abT, 0.02, 0.2)
+    of_h = rand_float(rng, (N,), abT, -2, 2) if with_offset else None
+    if abT == O.BF16:
+        # row 17: scale 2^127 and weights in {-1, 0, 1}; with offset 255/256 the weight 1 gives 1.99609375 * 2^127, finite
+        # in fp32 but past the largest bfloat16: AscendAntiQuant stores the largest finite value
+        sc_h[17] = np.uint16(0x7F00)
+        nib = rng.integers(-1, 2, K) & 0xF
+        B4[17] = (nib[0::2] | (nib[1::2] << 4)).astype(np.uint8)
+        if with_offset:
+            of_h[17] = np.uint16(0x3F7F)
+    W = O.ascend_antiquant(B4, O.I4X2, abT, policy=O.PER_CHANNEL, m=N, n=K, scale=sc_h, offset=of_h, scaleT=abT, isTranspose=True)
+    Wf = W.astype(np.float32) if abT == O.F16 else (W.astype(np.uint32) << 16).view(np.float32)
+    assert np.isfinite(Wf).all()
+    if abT == O.BF16 and with_offset:
+        assert (W[17] == 0x7F7F).any()
+    cols = rng.choice(K, M, replace=False)
+    A = np.zeros((M, K), np.float32)
+    A[np.arange(M), cols] = 1.0
+    A = A.astype(np.float16) if abT == O.F16 else (A.view(np.uint32) >> 16).astype(np.uint16)
+    C = torch.zeros((M, N), dtype=torch.float32, device=DEV)
+    ops.MatmulW4A16(C, to_dev(A, abT), torch.from_numpy(B4).to(DEV), to_dev(of_h, abT) if with_offset else None, to_dev(sc_h, abT))
+    ops.MatmulStatus()
+    assert np.array_equal(C.cpu().numpy().view(np.uint32), np.ascontiguousarray(Wf[:, cols].T).view(np.uint32))
