@@ -184,7 +184,7 @@ def _w8a16_case(rng, M, N, K, abT, per_channel, with_offset):
 
 
 @pytest.mark.parametrize("abT,cT", [(O.F16, O.F16), (O.F16, O.F32), (O.BF16, O.BF16), (O.BF16, O.F32)])
-@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (7, 516, 384), (8, 4096, 4096), (16, 1000, 1024), (25, 640, 2176), (32, 2048, 1024)])
+@pytest.mark.parametrize("M,N,K", [(1, 512, 256), (4, 64, 128), (7, 516, 384), (8, 4096, 4096), (16, 1000, 1024), (25, 640, 2176), (32, 2048, 1024)])
 @pytest.mark.parametrize("per_channel,with_offset", [(True, True), (True, False), (False, True)])
 def test_w8a16_few_rows(abT, cT, M, N, K, per_channel, with_offset, monkeypatch):
     """Both forms against the oracle (AscendAntiQuant, then an fp64 matmul), into a pitched output whose guard row and guard
