@@ -1090,7 +1090,7 @@ def few_rows_section(torch, ops, dev, add):
             os.environ.pop("ASCQ_W8A16", None)
     del B4w
     sBw = torch.rand(Nw, device=dev) * 0.01
-    for Mw in (1, 16, 32):
+    for Mw in (1, 16):   # (17 to 32 rows against a weight of this size stay on the tcgen05 kernel)
         A8w = torch.randint(-127, 128, (Mw, Kw), dtype=torch.int8, device=dev)
         sAw = torch.rand(Mw, device=dev) * 0.02
         C8w = torch.empty((Mw, Nw), dtype=torch.bfloat16, device=dev)
