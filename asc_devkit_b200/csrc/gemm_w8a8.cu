@@ -1098,9 +1098,10 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
     // smaller waves (measured: 49.2 against 50.0 us per step on two GPUs, 63.6 against 66.0 on four).
     if ((nBufs > 1 || multicast) && costNarrow <= 1.3 * (costWide < costPair ? costWide : costPair)) mode = 0;
     // A skinny product whose 64-column tiles still fit the SMs in one wave is bound by streaming B: those tiles put twice
-    // as many CTAs on that as 128-column ones (mode 3, built for the dequant and the half / bfloat16 epilogues of one plain
-    // matrix; measured 8192 x 8192, M = 128: 17.7 against 20.9 us; with a second wave it loses).
-    const bool slimBuilt = (epi == kEpiDequant || (epi == kEpiFloat && !fix->convert && fix->outKind <= 2)) && gt.G == 0 && nBufs <= 1 && !multicast;
+    // as many CTAs on that as 128-column ones (mode 3, built for every epilogue of one plain matrix but the grouped one;
+    // measured 8192 x 8192, M = 128: 17.7 against 20.9 us; with a second wave it loses).
+    const bool slimBuilt = (epi == kEpiDequant || epi == kEpiFixpipe || epi == kEpiRequant || (epi == kEpiFloat && !fix->convert)) && gt.G == 0 &&
+                           nBufs <= 1 && !multicast;
     const long long tiles64 = static_cast<long long>(tilesM) * ((N + 63) / 64);
     if (slimBuilt && tiles64 <= units && tiles64 > tiles128) mode = 3;
     if (const char* e = getenv("ASCQ_W8A8_TILE")) {
@@ -1162,10 +1163,12 @@ ascq_status run_w8a8(void* const* outBufs, int nBufs, int firstBuf, int colOffse
         return mode == 1 ? launch<256, false, kEpiFloat>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiFloat>(ta, tb, tc, p, st, gt);
     }
     if (epi == kEpiRequant) {
+        if (mode == 3) return launch<64, false, kEpiRequant>(ta, tb, tc, p, st, gt);
         if (mode == 2) return launch<256, true, kEpiRequant>(ta, tb, tc, p, st, gt);
         return mode == 1 ? launch<256, false, kEpiRequant>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiRequant>(ta, tb, tc, p, st, gt);
     }
     if (epi == kEpiFixpipe) {
+        if (mode == 3) return launch<64, false, kEpiFixpipe>(ta, tb, tc, p, st, gt);
         if (mode == 2) return launch<256, true, kEpiFixpipe>(ta, tb, tc, p, st, gt);
         return mode == 1 ? launch<256, false, kEpiFixpipe>(ta, tb, tc, p, st, gt) : launch<128, false, kEpiFixpipe>(ta, tb, tc, p, st, gt);
     }

@@ -153,7 +153,7 @@ def test_fixpipe_qf322b8_sample_golden_through_the_gpu():
 
 @pytest.mark.parametrize("M,N,K,abT,vector", [(128, 128, 64, O.F16, True), (300, 520, 264, O.BF16, True), (257, 384, 1024, O.F16, False),
                                              (2048, 1024, 512, O.BF16, True)])
-@pytest.mark.parametrize("tile", ["pair", "wide", "narrow"])
+@pytest.mark.parametrize("tile", ["pair", "wide", "narrow", "slim"])
 def test_matmul_f16_quant_matches_oracle(M, N, K, abT, vector, tile, monkeypatch):
     monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
     rng = np.random.default_rng(3 * M + N + K + abT)

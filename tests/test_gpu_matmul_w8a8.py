@@ -177,7 +177,7 @@ def test_matmul_quant_sample_golden_through_the_gpu(name):
 
 
 @pytest.mark.parametrize("M,N,K,vector", [(128, 128, 128, True), (300, 520, 272, True), (257, 384, 1024, False), (4096, 512, 512, True)])
-@pytest.mark.parametrize("tile", ["pair", "wide", "narrow"])
+@pytest.mark.parametrize("tile", ["pair", "wide", "narrow", "slim"])
 def test_matmul_quant_matches_oracle(M, N, K, vector, tile, monkeypatch):
     monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
     rng = np.random.default_rng(M + N + K)
@@ -221,7 +221,7 @@ def test_fixpipe_req8_sample_golden_through_the_gpu():
 
 
 @pytest.mark.parametrize("M,N,K,vector", [(128, 128, 128, True), (300, 520, 272, True), (257, 384, 1024, False), (4096, 512, 512, True)])
-@pytest.mark.parametrize("tile", ["pair", "wide", "narrow"])
+@pytest.mark.parametrize("tile", ["pair", "wide", "narrow", "slim"])
 def test_matmul_requant_matches_oracle(M, N, K, vector, tile, monkeypatch):
     monkeypatch.setenv("ASCQ_W8A8_TILE", tile)
     rng = np.random.default_rng(7 * M + N + K)
